@@ -1,0 +1,268 @@
+/*
+ * orangu_b200 -- C ABI of the B200 (sm_100a) backend for orangu-server's quantized
+ * decode path.
+ *
+ * This is the drop-in boundary: the entry points below are what an FFI crate on the
+ * server side binds in place of its CUDA backend.  Each one names the interface of
+ * the reference engine it stands in for (paths relative to the reference project
+ * root; B = src/bin/orangu-server/engine/backend, E = src/bin/orangu-server/engine).
+ *
+ * Conventions
+ *   - every call returns OB_OK (0) or a negative ob_status; nothing aborts, throws
+ *     or longjmps across the boundary.  ob_last_error() gives the text.
+ *   - host pointers are borrowed for the duration of the call only.
+ *   - a context is bound to one GPU and serialises its calls on an internal mutex,
+ *     so it may be shared between threads (the reference's Backend is Send + Sync,
+ *     B/mod.rs:309).
+ *   - there is no CPU fallback: without a usable sm_100 device ob_init fails.
+ */
+#ifndef ORANGU_B200_H
+#define ORANGU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
+#endif
+
+#define OB_ABI_VERSION 1u
+
+typedef enum ob_status {
+    OB_OK = 0,
+    OB_ERR_INVALID = -1,      /* bad argument (null, shape mismatch, out-of-range token ...) */
+    OB_ERR_UNSUPPORTED = -2,  /* ggml type / shape this backend has no kernel for */
+    OB_ERR_NO_DEVICE = -3,    /* no CUDA device, or not an sm_100 part */
+    OB_ERR_CUDA = -4,         /* a CUDA runtime call failed; text in ob_last_error */
+    OB_ERR_OOM = -5,          /* device or pinned-host allocation failed */
+    OB_ERR_CAPACITY = -6,     /* KV cache full, batch larger than the model was created for */
+    OB_ERR_COMM = -7          /* tensor-parallel communicator failure */
+} ob_status;
+
+/* ggml type ids as the GGUF file carries them (E/quant.rs:50-112) */
+#define OB_TYPE_F32 0u
+#define OB_TYPE_Q8_0 8u
+#define OB_TYPE_Q4_K 12u
+#define OB_TYPE_Q6_K 14u
+
+typedef struct ob_ctx ob_ctx;
+typedef struct ob_weight ob_weight;
+typedef struct ob_model ob_model;
+typedef struct ob_kv ob_kv;
+
+/* ------------------------------------------------------------------ context */
+
+/* Replaces CudaBackend::try_init_index (B/cuda.rs:86-124): never panics; any failure
+ * is a status and *out stays NULL.  device_ordinal < 0 picks the current device. */
+int ob_init(int device_ordinal, ob_ctx **out);
+void ob_destroy(ob_ctx *ctx);
+
+/* Text of the last failure on this context (never NULL; "" when none).  ctx == NULL
+ * returns the text of the last failed ob_init on the calling thread. */
+const char *ob_last_error(const ob_ctx *ctx);
+
+unsigned ob_abi_version(void);
+
+/* Replaces Backend::supports_type (B/mod.rs:479-495): 1 for Q8_0, Q4_K, Q6_K (and F32
+ * for norm vectors), 0 otherwise, so a missing kernel is a named start-up error. */
+int ob_supports_type(uint32_t ggml_type);
+
+/* Replaces Backend::reduced_surface (B/mod.rs:409-434): NULL, because the fused layer
+ * chain, device attention and device sampling are all present. */
+const char *ob_reduced_surface(void);
+
+/* ------------------------------------------------------------------ weights */
+
+/* Replaces CudaBackend::weight_buffer (B/cuda.rs:216-236): copies a QuantMatrix
+ * (E/loader.rs:561-680) to the device.  `raw` is out_dim rows of row_bytes bytes in
+ * GGUF block layout, dims[0] = in_dim contiguous.  The bytes are copied; the caller's
+ * mapping need not outlive the call. */
+int ob_weight_register(ob_ctx *ctx, const uint8_t *raw, uint64_t row_bytes, uint32_t ggml_type,
+                       uint32_t in_dim, uint32_t out_dim, ob_weight **out);
+
+/* Tensor-parallel shard of a matrix: rows [row0, row0+n_rows) and input columns
+ * [col0, col0+n_cols) of it (col0 and n_cols multiples of the type's block size).
+ * Stands in for QuantMatrix::rows (E/loader.rs:627-646), extended to a column range. */
+int ob_weight_register_slice(ob_ctx *ctx, const uint8_t *raw, uint64_t row_bytes, uint32_t ggml_type,
+                             uint32_t in_dim, uint32_t out_dim, uint32_t row0, uint32_t n_rows,
+                             uint32_t col0, uint32_t n_cols, ob_weight **out);
+void ob_weight_release(ob_ctx *ctx, ob_weight *w);
+
+/* Replaces QuantMatrix::row (E/loader.rs:585-590): dequantises rows
+ * [first_row, first_row+n_rows) to f32 on the device and copies them to out_host. */
+int ob_weight_dequantize(ob_ctx *ctx, const ob_weight *w, uint32_t first_row, uint32_t n_rows, float *out_host);
+
+/* ------------------------------------------------------------------- matmul */
+
+/* Replaces Backend::matmul / matmul_into (B/mod.rs:310-342, B/cuda.rs:250-254):
+ * y[t,o] = sum_i x[t,i] * w.row(o)[i]; x is [n_tokens, in_dim], y [n_tokens, out_dim],
+ * both row-major host f32.  n_tokens == 1 takes the GEMV of the type's family, n_tokens > 1
+ * the prefill GEMM, as CpuBackend chooses (B/cpu.rs:55-167). */
+int ob_matmul(ob_ctx *ctx, const float *x, uint32_t n_tokens, const ob_weight *w, float *y);
+
+/* Replaces Backend::matmul_decode / matmul_decode_into (B/mod.rs:368-388, B/cpu.rs:265-317):
+ * the rows of x are independent sequences; row t of y equals ob_matmul on that row alone,
+ * bit for bit. */
+int ob_matmul_decode(ob_ctx *ctx, const float *x, uint32_t n_tokens, const ob_weight *w, float *y);
+
+typedef struct ob_matmul_op { /* MatmulOp, B/mod.rs:117-121 */
+    const float *x;
+    uint32_t n_tokens;
+    const ob_weight *w;
+    float *y;
+} ob_matmul_op;
+
+/* Replaces Backend::matmul_batch / matmul_batch_into / matmul_batch_decode
+ * (B/mod.rs:362-407): independent ops, one submission. */
+int ob_matmul_batch(ob_ctx *ctx, const ob_matmul_op *ops, uint32_t n_ops, int decode);
+
+/* Same products with x and y already in device memory (no copies, asynchronous on
+ * `stream`, a cudaStream_t or NULL for the context's stream).  Has no counterpart in the
+ * reference, whose CUDA backend copies per call (B/cuda.rs:325-367); it is what a caller
+ * that keeps activations resident uses. */
+int ob_matmul_device(ob_ctx *ctx, const float *x_dev, uint32_t n_tokens, const ob_weight *w,
+                     float *y_dev, int decode, void *stream);
+int ob_synchronize(ob_ctx *ctx);
+
+/* The integer partial sums the GEMV forms before any fp32 arithmetic, for rows
+ * [first_row, first_row+n_rows) against one activation row x[in_dim]: per Q8_0 block its
+ * dot32; per Q4_K super-block isum and imin; per Q6_K super-block isum (imin 0).
+ * isum/imin are [n_rows][in_dim / block] host int32.  This is what dot32/dot16 and the
+ * k-row accumulators hold in E/vecdot.rs:471-502, 3152-3241; it exists for parity checks. */
+int ob_matmul_partials(ob_ctx *ctx, const float *x, const ob_weight *w, uint32_t first_row,
+                       uint32_t n_rows, int32_t *isum, int32_t *imin);
+
+/* --------------------------------------------------------------- glue ops */
+/* Host-buffer forms of the small operators around the products.  In the reference they
+ * run on the CPU between matmuls when the CUDA backend is active (B/mod.rs:306-307). */
+
+/* tensor::rmsnorm_into (E/tensor.rs:732-757) */
+int ob_rmsnorm(ob_ctx *ctx, const float *x, const float *weight, uint32_t n_tokens, uint32_t dim, float eps, float *out);
+/* tensor::rope_apply_params_inplace, RopeLayout::Norm, no YaRN (E/tensor.rs:1115-1177); x is [n_head, head_dim] */
+int ob_rope(ob_ctx *ctx, float *x, uint32_t n_head, uint32_t head_dim, uint32_t pos, uint32_t rope_dim, float freq_base);
+/* arch::swiglu_ffn_into's element-wise part (E/arch/mod.rs:1099-1105): out = silu(gate) * up */
+int ob_swiglu(ob_ctx *ctx, const float *gate, const float *up, uint32_t n, float *out);
+/* vecdot::quantize_act (per 32) / quantize_act_k_row (per 256) (E/vecdot.rs:79-126, 3030-3053);
+ * q [n] int8, d [n/32 or n/256] f32, sums [n/16] int32 */
+int ob_quantize_act(ob_ctx *ctx, const float *x, uint32_t n, int per_256, int8_t *q, float *d, int32_t *sums);
+/* attention::attention with n_tokens == 1 (E/attention.rs:242-344, 426-549) and the device path it
+ * can dispatch to, VulkanBackend::gpu_attention_split (B/vulkan.rs:6330-6342, 10788): one query
+ * token q [n_head*head_dim] against n_pos cached positions k,v [n_pos, n_head_kv*head_dim] f32,
+ * which are stored as fp16 pages exactly as the KV mirror holds them (E/kv_cache.rs:26-32). */
+int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos,
+                        uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, float *out);
+/* sampling::apply_repeat_penalty + argmax (E/sampling.rs:336-359); last index wins ties.
+ * recent may be NULL; penalty 1.0 disables it. */
+int ob_argmax(ob_ctx *ctx, const float *logits, uint32_t n_vocab, const uint32_t *recent,
+              uint32_t n_recent, uint32_t repeat_last_n, float penalty, uint32_t *out_token);
+
+/* ------------------------------------------------- fused surface: the model */
+
+typedef struct ob_matrix_desc {
+    const uint8_t *data; /* GGUF block layout, out_dim rows */
+    uint32_t ggml_type;
+    uint32_t in_dim;
+    uint32_t out_dim;
+} ob_matrix_desc;
+
+/* One decoder block; the tensors LlamaModel::load_with_backend reads per layer
+ * (E/arch/llama.rs:153-183) and FusedLayerInput carries (B/vulkan.rs:6663-6723). */
+typedef struct ob_layer_desc {
+    const float *attn_norm; /* blk.N.attn_norm.weight  [n_embd] */
+    const float *ffn_norm;  /* blk.N.ffn_norm.weight   [n_embd] */
+    ob_matrix_desc wq;      /* blk.N.attn_q.weight      [n_embd -> n_head*head_dim] */
+    ob_matrix_desc wk;      /* blk.N.attn_k.weight      [n_embd -> n_head_kv*head_dim] */
+    ob_matrix_desc wv;      /* blk.N.attn_v.weight */
+    ob_matrix_desc wo;      /* blk.N.attn_output.weight [n_head*head_dim -> n_embd] */
+    ob_matrix_desc w_gate;  /* blk.N.ffn_gate.weight    [n_embd -> n_ff] */
+    ob_matrix_desc w_up;    /* blk.N.ffn_up.weight */
+    ob_matrix_desc w_down;  /* blk.N.ffn_down.weight    [n_ff -> n_embd] */
+} ob_layer_desc;
+
+/* ModelConfig (E/loader.rs:34-58) plus run-time sizing. */
+typedef struct ob_model_desc {
+    uint32_t n_vocab, n_embd, n_layer, n_head, n_head_kv, head_dim, rope_dim, n_ff;
+    float rope_freq_base, rms_eps;
+    uint32_t max_seq_len;      /* longest context any KV cache of this model will hold */
+    uint32_t max_batch_tokens; /* most tokens one ob_forward call will carry (prefill chunk or decode batch) */
+    uint64_t kv_pool_tokens;   /* total KV capacity shared by every ob_kv of this model, in tokens; 0 = max_seq_len */
+    ob_matrix_desc token_embd;   /* token_embd.weight */
+    const float *output_norm;    /* output_norm.weight */
+    ob_matrix_desc output;       /* output.weight; data == NULL ties it to token_embd (E/arch/llama.rs:133-139) */
+    const ob_layer_desc *layers; /* n_layer entries */
+    /* tensor parallel: this process is rank tp_rank of tp_size; descriptors above are the FULL
+     * tensors and the model keeps its own shard.  tp_size <= 1 means single GPU. */
+    uint32_t tp_rank, tp_size;
+    const void *tp_unique_id;   /* tp_size > 1: the 128-byte id from ob_tp_unique_id, identical on every rank */
+} ob_model_desc;
+
+/* Stands in for LlamaModel::load_with_backend (E/arch/llama.rs:125-230) on the device side:
+ * uploads (and shards) every tensor, sizes scratch, builds the RoPE table. */
+int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out);
+void ob_model_destroy(ob_model *model);
+
+/* ModelForward::new_kv_cache (E/arch/llama.rs:1002-1005): an empty per-sequence cache of fp16
+ * pages (16 tokens per page) with room for capacity_tokens. */
+int ob_kv_create(ob_model *model, uint32_t capacity_tokens, ob_kv **out);
+void ob_kv_destroy(ob_kv *kv);
+uint32_t ob_kv_len(const ob_kv *kv);
+/* KvCache::truncate (E/kv_cache.rs:496-511): roll back to new_len positions. */
+int ob_kv_truncate(ob_kv *kv, uint32_t new_len);
+/* Test hook: reads positions [pos0, pos0+n) of one layer back as f32 [n][n_head_kv*head_dim]. */
+int ob_kv_read(ob_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n, float *k_out, float *v_out);
+
+typedef struct ob_greedy { /* GpuArgmaxSampleInput, B/vulkan.rs:6219-6241 */
+    float repeat_penalty;   /* 1.0 = off */
+    uint32_t repeat_last_n;
+    const uint32_t *recent; /* n_recent ids per sequence, concatenated; may be NULL */
+    const uint32_t *n_recent;
+} ob_greedy;
+
+/* Replaces ModelForward::forward / forward_maybe_sampling / forward_batch_decode
+ * (E/arch/mod.rs:2035-2191, E/arch/llama.rs:949-1032).  n_seq sequences; sequence i carries
+ * n_tokens[i] tokens starting at position start_pos[i] (== ob_kv_len(kvs[i])), tokens concatenated.
+ * A sequence with several tokens is a prefill chunk (GEMM semantics); sequences with one token
+ * each form a decode batch whose rows do not influence one another.
+ * out_token  [n_seq]          greedy next token of each sequence (may be NULL)
+ * out_logits [n_seq][n_vocab] last-token logits (may be NULL; costs a device-to-host copy) */
+int ob_forward(ob_model *model, ob_kv *const *kvs, const uint32_t *tokens, const uint32_t *n_tokens,
+               const uint32_t *start_pos, uint32_t n_seq, const ob_greedy *greedy,
+               uint32_t *out_token, float *out_logits);
+
+/* One greedy decode step of a single sequence replayed from a captured CUDA graph:
+ * the record_decode_chain path (E/arch/llama.rs:302-473), one submission per token and one
+ * u32 back.  Equivalent to ob_forward with n_seq = 1, n_tokens = 1, no repeat penalty. */
+int ob_decode_greedy(ob_model *model, ob_kv *kv, uint32_t token, uint32_t *out_token);
+
+/* Device-resident decode loop: `n_steps` greedy steps for `n_seq` sequences, feeding each
+ * step's token to the next without the host in between; out_tokens [n_steps][n_seq].
+ * This is the loop of generate::run (E/generate.rs:859-878) with the sampler on the device. */
+int ob_decode_loop(ob_model *model, ob_kv *const *kvs, const uint32_t *first_tokens, uint32_t n_seq,
+                   uint32_t n_steps, uint32_t *out_tokens);
+
+/* Hidden state after the last layer for the tokens of the most recent ob_forward call,
+ * [n_tokens][n_embd] (what run_layers returns, E/arch/llama.rs:594-932).  Test hook. */
+int ob_last_hidden(ob_model *model, uint32_t n_tokens, float *out);
+
+/* Kernel launches issued by this context since creation (for reporting). */
+uint64_t ob_launch_count(const ob_ctx *ctx);
+
+/* Milliseconds of device time of the most recent ob_forward / ob_decode_* call, from CUDA
+ * events on the context's stream. */
+float ob_last_device_ms(const ob_ctx *ctx);
+
+/* --------------------------------------------------------- tensor parallel */
+/* No counterpart in the reference: its only multi-GPU mode is a host-bounced layer split
+ * (B/multi.rs:16-35).  Rank 0 makes an id, every rank passes the same bytes in ob_model_desc. */
+int ob_tp_unique_id(void *out128);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORANGU_B200_H */

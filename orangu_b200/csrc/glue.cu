@@ -1,0 +1,179 @@
+// The small fp32 operators around the products: RMSNorm, RoPE + KV append, SwiGLU, residual add,
+// repeat penalty and greedy argmax.  Reference arithmetic (paths under src/bin/orangu-server/engine):
+//   rmsnorm   tensor.rs:743-749     (v * scale) * w, scale = 1 / sqrt(mean(v^2) + eps)
+//   rope      tensor.rs:1162-1176   NORM pairing (2i, 2i+1): (a*cos - b*sin, a*sin + b*cos)
+//   kv push   kv_cache.rs:26-32, 756-768   f32 -> f16 round-to-nearest-even
+//   swiglu    arch/mod.rs:1099-1105 silu(g) * u, silu(x) = x / (1 + exp(-x))
+//   argmax    sampling.rs:336-359   f32::total_cmp order, the last of equal maxima wins
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ob {
+
+namespace {
+
+__global__ void __launch_bounds__(512) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w, uint32_t dim, float eps,
+                                                      float *__restrict__ out) {
+    const float *row = x + (uint64_t)blockIdx.x * dim;
+    float *orow = out + (uint64_t)blockIdx.x * dim;
+    __shared__ float red[16];
+    __shared__ float bcast;
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) s += row[i] * row[i];
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
+    }
+    __syncthreads();
+    const float scale = bcast;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = __fmul_rn(__fmul_rn(row[i], scale), w[i]);
+}
+
+__global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u, uint64_t n, float *__restrict__ out) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float x = g[i];
+    float s = __fdiv_rn(x, __fadd_rn(1.0f, expf(-x)));
+    out[i] = __fmul_rn(s, u[i]);
+}
+
+__global__ void add_kernel(float *__restrict__ a, const float *__restrict__ b, uint64_t n) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) a[i] = __fadd_rn(a[i], b[i]);
+}
+
+// grid (n_tokens); rotates q in place, rotates k and appends k, v to the token's page as f16.
+__global__ void __launch_bounds__(256) rope_kv_kernel(RopeKvArgs a) {
+    const uint32_t t = blockIdx.x;
+    const uint32_t pos = a.positions[t];
+    const uint32_t half = a.rope_dim / 2, hd = a.head_dim;
+    const float2 *rot = reinterpret_cast<const float2 *>(a.rope_table) + (uint64_t)pos * half;
+    float *q = a.q + (uint64_t)t * a.n_head * hd;
+    const uint32_t pairs = hd / 2;
+    for (uint32_t i = threadIdx.x; i < a.n_head * pairs; i += blockDim.x) {
+        const uint32_t h = i / pairs, p = i % pairs;
+        if (p < half) {
+            const float2 sc = rot[p];  // (sin, cos)
+            float2 *e = reinterpret_cast<float2 *>(q + h * hd) + p;
+            const float2 v = *e;
+            *e = make_float2(__fsub_rn(__fmul_rn(v.x, sc.y), __fmul_rn(v.y, sc.x)), __fadd_rn(__fmul_rn(v.x, sc.x), __fmul_rn(v.y, sc.y)));
+        }
+    }
+    const uint32_t kv_dim = a.n_head_kv * hd;
+    const int32_t *table = a.page_tables[t];
+    const int32_t page = table[pos / KV_PAGE];
+    const uint32_t slot = pos % KV_PAGE;
+    const float *k = a.k + (uint64_t)t * kv_dim, *v = a.v + (uint64_t)t * kv_dim;
+    for (uint32_t i = threadIdx.x; i < a.n_head_kv * pairs; i += blockDim.x) {
+        const uint32_t h = i / pairs, p = i % pairs;
+        float2 kk = *(reinterpret_cast<const float2 *>(k + h * hd) + p);
+        if (p < half) {
+            const float2 sc = rot[p];
+            kk = make_float2(__fsub_rn(__fmul_rn(kk.x, sc.y), __fmul_rn(kk.y, sc.x)), __fadd_rn(__fmul_rn(kk.x, sc.x), __fmul_rn(kk.y, sc.y)));
+        }
+        const float2 vv = *(reinterpret_cast<const float2 *>(v + h * hd) + p);
+        const uint64_t o = (((uint64_t)page * a.n_head_kv + h) * KV_PAGE + slot) * hd + 2 * p;
+        *reinterpret_cast<__half2 *>(a.k_pool + o) = __floats2half2_rn(kk.x, kk.y);
+        *reinterpret_cast<__half2 *>(a.v_pool + o) = __floats2half2_rn(vv.x, vv.y);
+    }
+}
+
+__global__ void rope_plain_kernel(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *__restrict__ sin_cos) {
+    const uint32_t half = rope_dim / 2, pairs = head_dim / 2;
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_head * pairs) return;
+    const uint32_t h = i / pairs, p = i % pairs;
+    if (p >= half) return;
+    const float sn = sin_cos[2 * p], cs = sin_cos[2 * p + 1];
+    float *e = x + h * head_dim + 2 * p;
+    const float va = e[0], vb = e[1];
+    e[0] = __fsub_rn(__fmul_rn(va, cs), __fmul_rn(vb, sn));
+    e[1] = __fadd_rn(__fmul_rn(va, sn), __fmul_rn(vb, cs));
+}
+
+// f32::total_cmp as an unsigned key: larger key <=> later in the total order.
+__device__ __forceinline__ uint32_t total_order_key(float f) {
+    int32_t b = __float_as_int(f);
+    b ^= (int32_t)(((uint32_t)(b >> 31)) >> 1);
+    return (uint32_t)b ^ 0x80000000u;
+}
+
+__global__ void argmax_reset_kernel(unsigned long long *scratch, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) scratch[i] = 0ull;
+}
+
+// grid (chunks, n_seq).  (key << 32 | index) under max: of equal keys the largest index wins.
+__global__ void __launch_bounds__(256) argmax_kernel(ArgmaxArgs a) {
+    const uint32_t seq = blockIdx.y;
+    const float *l = a.logits + (uint64_t)seq * a.n_vocab;
+    unsigned long long best = 0ull;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n_vocab; i += gridDim.x * blockDim.x) {
+        unsigned long long cand = ((unsigned long long)total_order_key(l[i]) << 32) | i;
+        best = cand > best ? cand : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    __shared__ unsigned long long red[8];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = red[w] > best ? red[w] : best;
+        atomicMax(a.scratch + seq, best);
+    }
+}
+
+__global__ void argmax_finish_kernel(const unsigned long long *scratch, uint32_t *out, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (uint32_t)(scratch[i] & 0xffffffffull);
+}
+
+// Sequential on purpose: a token that repeats is penalised once per occurrence, compounding.
+__global__ void repeat_penalty_kernel(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    for (uint32_t i = 0; i < n_recent; ++i) {
+        const uint32_t tok = recent[i];
+        if (tok < n_vocab) {
+            const float v = logits[tok];
+            logits[tok] = v > 0.0f ? __fdiv_rn(v, penalty) : __fmul_rn(v, penalty);
+        }
+    }
+}
+
+}  // namespace
+
+void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st) {
+    if (n_tokens) rmsnorm_kernel<<<n_tokens, 512, 0, st>>>(x, w, dim, eps, out);
+}
+void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st) {
+    if (n) swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(gate, up, n, out);
+}
+void launch_add(float *a, const float *b, uint64_t n, cudaStream_t st) {
+    if (n) add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, n);
+}
+void launch_rope_kv(const RopeKvArgs &a, cudaStream_t st) {
+    if (a.n_tokens) rope_kv_kernel<<<a.n_tokens, 256, 0, st>>>(a);
+}
+void launch_rope_plain(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *sin_cos_row, cudaStream_t st) {
+    uint32_t n = n_head * head_dim / 2;
+    rope_plain_kernel<<<(n + 255) / 256, 256, 0, st>>>(x, n_head, head_dim, rope_dim, sin_cos_row);
+}
+void launch_argmax(const ArgmaxArgs &a, cudaStream_t st) {
+    if (!a.n_seq) return;
+    argmax_reset_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.n_seq);
+    dim3 grid(min(64u, (a.n_vocab + 255) / 256), a.n_seq);
+    argmax_kernel<<<grid, 256, 0, st>>>(a);
+    argmax_finish_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.out, a.n_seq);
+}
+void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st) {
+    if (n_recent && penalty != 1.0f) repeat_penalty_kernel<<<1, 32, 0, st>>>(logits, n_vocab, recent, n_recent, penalty);
+}
+
+}  // namespace ob

@@ -1,0 +1,100 @@
+// Host-callable launchers of the CUDA kernels (internal to the library).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace ob {
+
+// ---- formats.cu
+void launch_repack(const uint8_t *src, uint64_t src_row_bytes, uint32_t row0, uint32_t blk0, const DevWeight &w, cudaStream_t st);
+void launch_dequant_rows(const DevWeight &w, uint32_t first_row, uint32_t n_rows, float *out, cudaStream_t st);
+void launch_embed(const DevWeight &w, const uint32_t *tokens, uint32_t n_tokens, float *out, cudaStream_t st);
+
+// ---- act_quant.cu
+// Writable quantized-activation buffers for up to `rows` token rows of `dim` elements.
+struct ActBuf {
+    int8_t *q = nullptr;     // [rows][dim]
+    float *d = nullptr;      // [rows][dim/group]
+    int16_t *sums = nullptr; // [rows][dim/16]
+    uint32_t dim_cap = 0;    // row pitch in elements
+};
+enum ActSource { ACT_PLAIN = 0, ACT_RMSNORM = 1, ACT_SWIGLU = 2 };
+struct QuantArgs {
+    const float *x;       // [n_rows][dim]   (PLAIN, RMSNORM) or gate (SWIGLU)
+    const float *aux;     // RMSNORM: weight [dim]; SWIGLU: up [n_rows][dim]
+    float eps;            // RMSNORM
+    float *f32_out;       // optional: the fp32 values that were quantized, [n_rows][dim]
+    uint32_t n_rows, dim;
+    ActBuf k;             // per-256 output (q == nullptr: skip)
+    ActBuf flat;          // per-32 output  (q == nullptr: skip)
+};
+void launch_quantize(int source, const QuantArgs &a, cudaStream_t st);
+
+// ---- gemv.cu
+enum GemvEpilogue { EPI_STORE = 0, EPI_ADD_RESIDUAL = 1 };
+struct GemvSegment {
+    DevWeight w;
+    float *y;              // [n_tokens][y_stride]
+    const float *residual; // EPI_ADD_RESIDUAL: y = residual + product (may alias y)
+    uint32_t y_stride;
+    int epilogue;
+};
+struct GemvArgs {
+    GemvSegment seg[3];    // all of one ggml type and one in_dim
+    int n_seg;
+    ActBuf act;            // activations of the matching granularity
+    uint32_t n_tokens;
+    bool gemm_order;       // false: every (row, token) is the single-token GEMV; true: the prefill GEMM's fp32 order
+    int32_t *isum_out;     // optional debug capture (single segment, token 0): [out_dim][nb]
+    int32_t *imin_out;
+};
+void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st);
+size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, bool gemm_order);
+uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order);  // kernels launch_gemv issues
+
+// ---- glue.cu
+void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st);
+void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st);
+void launch_add(float *a, const float *b, uint64_t n, cudaStream_t st);
+struct RopeKvArgs {
+    float *q;                 // [n_tokens][n_head*head_dim], rotated in place
+    const float *k;           // [n_tokens][kv_dim]
+    const float *v;           // [n_tokens][kv_dim]
+    const float *rope_table;  // [max_pos][rope_dim/2][2] (sin, cos)
+    const uint32_t *positions;   // [n_tokens] absolute position of each token
+    const int32_t *const *page_tables; // [n_tokens] device pointers: the page table of each token's sequence
+    __half *k_pool;           // this layer's pages [page][n_head_kv][16][head_dim]
+    __half *v_pool;
+    uint32_t n_tokens, n_head, n_head_kv, head_dim, rope_dim;
+};
+void launch_rope_kv(const RopeKvArgs &a, cudaStream_t st);
+void launch_rope_plain(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *sin_cos_row, cudaStream_t st);
+struct ArgmaxArgs {
+    const float *logits;   // [n_seq][n_vocab]
+    uint32_t n_seq, n_vocab;
+    uint32_t *out;         // [n_seq]
+    unsigned long long *scratch; // [n_seq] packed (key, index)
+};
+void launch_argmax(const ArgmaxArgs &a, cudaStream_t st);
+void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st);
+
+// ---- attention.cu
+struct AttnDecodeArgs {
+    const float *q;            // [n_seq][n_head*head_dim]
+    float *out;                // [n_seq][n_head*head_dim]
+    const __half *k_pool;      // layer pages [page][n_head_kv][16][head_dim]
+    const __half *v_pool;
+    const int32_t *const *page_tables; // [n_seq] device pointers
+    const uint32_t *n_pos;     // [n_seq] positions to attend (window 0..n_pos-1), device
+    uint32_t n_seq, n_head, n_head_kv, head_dim;
+    float scale;
+    uint32_t n_splits;         // CTAs per (sequence, kv head)
+    float *part_o;             // [n_seq][n_head][n_splits][head_dim]
+    float *part_ml;            // [n_seq][n_head][n_splits][2]
+    uint32_t max_pos;          // upper bound of n_pos (sizes nothing on the device; bounds the split length)
+};
+void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st);
+}  // namespace ob

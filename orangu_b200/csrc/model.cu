@@ -1,0 +1,861 @@
+// Device-resident Llama-style model: weights, paged fp16 KV pool, forward step and decode graphs.
+//
+// Reference graph: src/bin/orangu-server/engine/arch/llama.rs:594-932 (run_layers), :1007-1032
+// (forward: last-token logits).  Greedy sampling: engine/sampling.rs:336-359.
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <map>
+#include <vector>
+
+#include "runtime.h"
+#include "tp.h"
+
+using namespace obrt;
+
+namespace {
+
+struct LayerDev {
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+    ob_weight *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+};
+
+struct ActPair {  // both granularities for one product input
+    ActBuf k, flat;
+};
+
+// Per-step metadata, one pinned host block mirrored by one device block.
+struct MetaLayout {
+    uint32_t T;
+    size_t off_tokens, off_positions, off_npos, off_tables, bytes;
+    explicit MetaLayout(uint32_t t) : T(t) {
+        off_tokens = 0;
+        off_positions = off_tokens + (size_t)t * 4;
+        off_npos = off_positions + (size_t)t * 4;
+        off_tables = (off_npos + (size_t)t * 4 + 15) & ~(size_t)15;
+        bytes = off_tables + (size_t)t * 8;
+    }
+};
+
+__global__ void advance_kernel(uint32_t *tokens, uint32_t *positions, uint32_t *npos, const uint32_t *out_tokens, uint32_t n_seq,
+                               uint32_t *history, uint32_t *step_counter) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t step = *step_counter;
+    if (i < n_seq) {
+        const uint32_t t = out_tokens[i];
+        history[(uint64_t)step * n_seq + i] = t;
+        tokens[i] = t;
+        positions[i] += 1;
+        npos[i] += 1;
+    }
+    __syncthreads();
+    if (i == 0) *step_counter = step + 1;
+}
+
+}  // namespace
+
+struct ob_model {
+    ob_ctx *ctx = nullptr;
+    ob_model_desc cfg{};
+    uint32_t tp_rank = 0, tp_size = 1;
+    uint32_t n_head_l = 0, n_head_kv_l = 0, n_ff_l = 0, vocab_l = 0, vocab0 = 0;
+    std::vector<LayerDev> layers;
+    ob_weight *token_embd = nullptr, *output = nullptr;
+    float *output_norm = nullptr;
+    float *rope_table = nullptr;
+    std::vector<void *> owned;  // plain cudaMalloc blocks
+
+    // KV pool: [layer][page][n_head_kv_l][16][head_dim] fp16, K and V
+    uint32_t pool_pages = 0;
+    __half *k_pool = nullptr, *v_pool = nullptr;
+    size_t layer_stride = 0;  // elements
+    std::vector<int32_t> free_pages;
+
+    uint32_t T = 0;  // max rows per step
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *gate = nullptr, *up = nullptr, *proj = nullptr,
+          *logits = nullptr;
+    ActPair act_embd, act_attn, act_ff;
+    float *part_o = nullptr, *part_ml = nullptr;
+    uint32_t max_splits = 1;
+    uint8_t *d_meta = nullptr, *h_meta = nullptr;
+    uint32_t *d_out_tokens = nullptr, *h_out_tokens = nullptr;
+    unsigned long long *argmax_scratch = nullptr;
+    uint32_t *d_history = nullptr, *d_step_counter = nullptr;
+    uint32_t history_cap = 0;
+    uint32_t last_T = 0;
+    std::map<uint64_t, cudaGraphExec_t> graphs;
+    std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
+    obtp::Comm *comm = nullptr;
+};
+
+struct ob_kv {
+    ob_model *m = nullptr;
+    uint32_t capacity = 0, len = 0;
+    std::vector<int32_t> pages;
+    int32_t *d_table = nullptr;
+};
+
+namespace {
+
+template <typename Tp>
+int dev_alloc(ob_model *m, Tp **out, size_t count) {
+    void *p = nullptr;
+    OB_CUDA(m->ctx, cudaMalloc(&p, std::max<size_t>(count * sizeof(Tp), 16)));
+    m->owned.push_back(p);
+    *out = static_cast<Tp *>(p);
+    return OB_OK;
+}
+
+int upload_f32(ob_model *m, const float *src, size_t n, float **out) {
+    int rc = dev_alloc(m, out, n);
+    if (rc) return rc;
+    OB_CUDA(m->ctx, cudaMemcpyAsync(*out, src, n * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+    return OB_OK;
+}
+
+int alloc_act(ob_model *m, ActPair *a, uint32_t rows, uint32_t dim) {
+    int rc;
+    for (ActBuf *b : {&a->k, &a->flat}) {
+        const uint32_t grp = b == &a->k ? 256u : 32u;
+        if ((rc = dev_alloc(m, &b->q, (size_t)rows * dim))) return rc;
+        if ((rc = dev_alloc(m, &b->d, (size_t)rows * (dim / grp + 1)))) return rc;
+        if ((rc = dev_alloc(m, &b->sums, (size_t)rows * (dim / 16)))) return rc;
+        b->dim_cap = dim;
+    }
+    return OB_OK;
+}
+
+int check_matrix(ob_ctx *ctx, const ob_matrix_desc &d, uint32_t in_dim, uint32_t out_dim, const char *name) {
+    if (!d.data) return fail(ctx, OB_ERR_INVALID, std::string("model: ") + name + " has no data");
+    if (!type_supported(d.ggml_type)) return fail(ctx, OB_ERR_UNSUPPORTED, std::string("model: ") + name + " has ggml type " + std::to_string(d.ggml_type));
+    if (d.in_dim != in_dim || d.out_dim != out_dim)
+        return fail(ctx, OB_ERR_INVALID, std::string("model: ") + name + " is [" + std::to_string(d.in_dim) + " -> " + std::to_string(d.out_dim) +
+                                             "], expected [" + std::to_string(in_dim) + " -> " + std::to_string(out_dim) + "]");
+    if (in_dim % block_elems(d.ggml_type)) return fail(ctx, OB_ERR_UNSUPPORTED, std::string("model: ") + name + ": in_dim is not a whole number of blocks");
+    return OB_OK;
+}
+
+int slice_weight(ob_model *m, const ob_matrix_desc &d, uint32_t row0, uint32_t n_rows, uint32_t col0, uint32_t n_cols, ob_weight **out) {
+    const uint64_t rb = (uint64_t)(d.in_dim / block_elems(d.ggml_type)) * block_bytes_gguf(d.ggml_type);
+    return make_weight(m->ctx, d.data, rb, d.ggml_type, d.in_dim, d.out_dim, row0, n_rows, col0, n_cols, out);
+}
+
+bool needs_k(std::initializer_list<const ob_weight *> ws) {
+    for (auto w : ws)
+        if (w->w.type != TYPE_Q8_0) return true;
+    return false;
+}
+bool needs_flat(std::initializer_list<const ob_weight *> ws) {
+    for (auto w : ws)
+        if (w->w.type == TYPE_Q8_0) return true;
+    return false;
+}
+
+const ActBuf &act_for(const ActPair &p, const ob_weight *w) { return w->w.type == TYPE_Q8_0 ? p.flat : p.k; }
+
+// Products that share one input: one launch per distinct weight type.
+struct ProductOut {
+    const ob_weight *w;
+    float *y;
+    uint32_t y_stride;
+    const float *residual;
+};
+
+void run_products(ob_model *m, const ActPair &act, std::initializer_list<ProductOut> outs, uint32_t n_tokens, bool gemm_order, cudaStream_t st) {
+    std::vector<ProductOut> v(outs);
+    std::vector<bool> done(v.size(), false);
+    for (size_t i = 0; i < v.size(); ++i) {
+        if (done[i]) continue;
+        GemvArgs a{};
+        a.act = act_for(act, v[i].w);
+        a.n_tokens = n_tokens;
+        a.gemm_order = gemm_order;
+        for (size_t j = i; j < v.size() && a.n_seg < 3; ++j) {
+            if (done[j] || v[j].w->w.type != v[i].w->w.type) continue;
+            GemvSegment &s = a.seg[a.n_seg++];
+            s.w = v[j].w->w;
+            s.y = v[j].y;
+            s.y_stride = v[j].y_stride;
+            s.residual = v[j].residual;
+            s.epilogue = v[j].residual ? EPI_ADD_RESIDUAL : EPI_STORE;
+            done[j] = true;
+        }
+        launch_gemv(a, m->ctx->sm_count, st);
+        m->ctx->launches += gemv_launches(a.seg[0].w.type, a.seg[0].w.in_dim, n_tokens, gemm_order && a.seg[0].w.type != TYPE_Q8_0);
+    }
+}
+
+void quantize_into(ob_model *m, int source, const float *x, const float *aux, uint32_t rows, uint32_t dim, const ActPair &dst, bool want_k,
+                   bool want_flat, cudaStream_t st) {
+    QuantArgs qa{};
+    qa.x = x;
+    qa.aux = aux;
+    qa.eps = m->cfg.rms_eps;
+    qa.n_rows = rows;
+    qa.dim = dim;
+    if (want_k) qa.k = dst.k;
+    if (want_flat) qa.flat = dst.flat;
+    launch_quantize(source, qa, st);
+    m->ctx->launches++;
+}
+
+uint32_t pick_splits(const ob_model *m, uint32_t n_rows) {
+    const uint32_t pairs = std::max(1u, n_rows * m->n_head_kv_l);
+    uint32_t s = (4u * (uint32_t)m->ctx->sm_count + pairs - 1) / pairs;
+    return std::max(1u, std::min(s, m->max_splits));
+}
+
+// Enqueue one forward step over T rows whose metadata is already in d_meta.
+//   gemm_order: the rows are consecutive tokens of one sequence (prefill chunk)
+//   logit_row0 / n_logit_rows: which rows get the output projection
+void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0, uint32_t n_logit_rows, bool want_argmax, cudaStream_t st) {
+    const ob_model_desc &c = m->cfg;
+    const MetaLayout ml(m->T);
+    const uint32_t *d_tokens = reinterpret_cast<uint32_t *>(m->d_meta + ml.off_tokens);
+    const uint32_t *d_positions = reinterpret_cast<uint32_t *>(m->d_meta + ml.off_positions);
+    const uint32_t *d_npos = reinterpret_cast<uint32_t *>(m->d_meta + ml.off_npos);
+    const int32_t *const *d_tables = reinterpret_cast<const int32_t *const *>(m->d_meta + ml.off_tables);
+    const uint32_t n_embd = c.n_embd, hd = c.head_dim;
+    const uint32_t q_dim = m->n_head_l * hd, kv_dim = m->n_head_kv_l * hd, n_ff = m->n_ff_l;
+    const bool tp = m->tp_size > 1;
+
+    launch_embed(m->token_embd->w, d_tokens, T, m->x, st);
+    m->ctx->launches++;
+
+    for (uint32_t li = 0; li < c.n_layer; ++li) {
+        const LayerDev &L = m->layers[li];
+        quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
+        run_products(m, m->act_embd, {{L.wq, m->q, q_dim, nullptr}, {L.wk, m->k, kv_dim, nullptr}, {L.wv, m->v, kv_dim, nullptr}}, T, gemm_order, st);
+
+        RopeKvArgs rk{};
+        rk.q = m->q;
+        rk.k = m->k;
+        rk.v = m->v;
+        rk.rope_table = m->rope_table;
+        rk.positions = d_positions;
+        rk.page_tables = d_tables;
+        rk.k_pool = m->k_pool + (size_t)li * m->layer_stride;
+        rk.v_pool = m->v_pool + (size_t)li * m->layer_stride;
+        rk.n_tokens = T;
+        rk.n_head = m->n_head_l;
+        rk.n_head_kv = m->n_head_kv_l;
+        rk.head_dim = hd;
+        rk.rope_dim = c.rope_dim;
+        launch_rope_kv(rk, st);
+        m->ctx->launches++;
+
+        AttnDecodeArgs at{};
+        at.q = m->q;
+        at.out = m->attn;
+        at.k_pool = rk.k_pool;
+        at.v_pool = rk.v_pool;
+        at.page_tables = d_tables;
+        at.n_pos = d_npos;
+        at.n_seq = T;
+        at.n_head = m->n_head_l;
+        at.n_head_kv = m->n_head_kv_l;
+        at.head_dim = hd;
+        at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
+        at.n_splits = pick_splits(m, T);
+        at.part_o = m->part_o;
+        at.part_ml = m->part_ml;
+        at.max_pos = c.max_seq_len;
+        launch_attn_decode(at, st);
+        m->ctx->launches += 2;
+
+        quantize_into(m, ACT_PLAIN, m->attn, nullptr, T, q_dim, m->act_attn, needs_k({L.wo}), needs_flat({L.wo}), st);
+        if (!tp) {
+            run_products(m, m->act_attn, {{L.wo, m->x, n_embd, m->x}}, T, gemm_order, st);
+        } else {
+            run_products(m, m->act_attn, {{L.wo, m->proj, n_embd, nullptr}}, T, gemm_order, st);
+            obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st);
+            launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
+            m->ctx->launches += 2;
+        }
+
+        quantize_into(m, ACT_RMSNORM, m->x, L.ffn_norm, T, n_embd, m->act_embd, needs_k({L.gate, L.up}), needs_flat({L.gate, L.up}), st);
+        run_products(m, m->act_embd, {{L.gate, m->gate, n_ff, nullptr}, {L.up, m->up, n_ff, nullptr}}, T, gemm_order, st);
+        quantize_into(m, ACT_SWIGLU, m->gate, m->up, T, n_ff, m->act_ff, needs_k({L.down}), needs_flat({L.down}), st);
+        if (!tp) {
+            run_products(m, m->act_ff, {{L.down, m->x, n_embd, m->x}}, T, gemm_order, st);
+        } else {
+            run_products(m, m->act_ff, {{L.down, m->proj, n_embd, nullptr}}, T, gemm_order, st);
+            obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st);
+            launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
+            m->ctx->launches += 2;
+        }
+    }
+
+    if (n_logit_rows) {
+        const float *xl = m->x + (size_t)logit_row0 * n_embd;
+        quantize_into(m, ACT_RMSNORM, xl, m->output_norm, n_logit_rows, n_embd, m->act_embd, needs_k({m->output}), needs_flat({m->output}), st);
+        // Always the single-token kernel: forward() projects one row (llama.rs:1026-1030).
+        run_products(m, m->act_embd, {{m->output, m->logits + m->vocab0, c.n_vocab, nullptr}}, n_logit_rows, false, st);
+        if (tp) {
+            obtp::all_gather_logits(m->comm, m->logits, n_logit_rows, c.n_vocab, m->vocab0, m->vocab_l, st);
+            m->ctx->launches++;
+        }
+        if (want_argmax) {
+            ArgmaxArgs am{};
+            am.logits = m->logits;
+            am.n_seq = n_logit_rows;
+            am.n_vocab = c.n_vocab;
+            am.out = m->d_out_tokens;
+            am.scratch = m->argmax_scratch;
+            launch_argmax(am, st);
+            m->ctx->launches += 3;
+        }
+    }
+    m->last_T = T;
+}
+
+}  // namespace
+
+extern "C" {
+
+void ob_model_destroy(ob_model *m) {
+    if (!m) return;
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &kvp : m->graphs) cudaGraphExecDestroy(kvp.second);
+    if (m->comm) obtp::destroy(m->comm);
+    auto rel = [&](ob_weight *w) {
+        if (w) {
+            cudaFree(w->mem);
+            delete w;
+        }
+    };
+    for (LayerDev &L : m->layers)
+        for (ob_weight *w : {L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down}) rel(w);
+    if (m->output != m->token_embd) rel(m->output);
+    rel(m->token_embd);
+    for (void *p : m->owned) cudaFree(p);
+    if (m->h_meta) cudaFreeHost(m->h_meta);
+    if (m->h_out_tokens) cudaFreeHost(m->h_out_tokens);
+    delete m;
+}
+
+int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
+    if (!ctx || !desc || !out) return fail(ctx, OB_ERR_INVALID, "model_create: null argument");
+    *out = nullptr;
+    const ob_model_desc &c = *desc;
+    if (!c.n_layer || !c.n_embd || !c.n_head || !c.n_head_kv || !c.head_dim || !c.n_ff || !c.n_vocab || !c.layers || !c.output_norm)
+        return fail(ctx, OB_ERR_INVALID, "model_create: incomplete description");
+    if (c.n_head % c.n_head_kv) return fail(ctx, OB_ERR_UNSUPPORTED, "model_create: n_head must be a multiple of n_head_kv");
+    if ((c.head_dim & 1) || c.head_dim > 256 || c.rope_dim > c.head_dim || (c.rope_dim & 1))
+        return fail(ctx, OB_ERR_UNSUPPORTED, "model_create: head_dim must be even and <= 256, rope_dim even and <= head_dim");
+    if (c.n_embd % 32 || c.n_ff % 32) return fail(ctx, OB_ERR_UNSUPPORTED, "model_create: n_embd and n_ff must be multiples of 32");
+    const uint32_t tp = std::max(1u, c.tp_size), rank = c.tp_rank;
+    if (rank >= tp) return fail(ctx, OB_ERR_INVALID, "model_create: tp_rank >= tp_size");
+    if (tp > 1 && (c.n_head_kv % tp || c.n_ff % (tp * 256) || (c.n_head / tp * c.head_dim) % 256 || c.n_vocab % tp))
+        return fail(ctx, OB_ERR_UNSUPPORTED, "model_create: tensor-parallel size must divide n_head_kv and n_vocab, and leave n_ff and the head span multiples of 256");
+    if (tp > 1 && !c.tp_unique_id) return fail(ctx, OB_ERR_INVALID, "model_create: tp_size > 1 needs tp_unique_id");
+
+    int rc;
+    {  // validate every matrix before touching the device
+        const uint32_t qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim;
+        if ((rc = check_matrix(ctx, c.token_embd, c.n_embd, c.n_vocab, "token_embd.weight"))) return rc;
+        if (c.output.data && (rc = check_matrix(ctx, c.output, c.n_embd, c.n_vocab, "output.weight"))) return rc;
+        for (uint32_t i = 0; i < c.n_layer; ++i) {
+            const ob_layer_desc &L = c.layers[i];
+            if (!L.attn_norm || !L.ffn_norm) return fail(ctx, OB_ERR_INVALID, "model_create: layer norm weights missing");
+            if ((rc = check_matrix(ctx, L.wq, c.n_embd, qd, "attn_q.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.wk, c.n_embd, kvd, "attn_k.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.wv, c.n_embd, kvd, "attn_v.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.wo, qd, c.n_embd, "attn_output.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_gate, c.n_embd, c.n_ff, "ffn_gate.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_up, c.n_embd, c.n_ff, "ffn_up.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_down, c.n_ff, c.n_embd, "ffn_down.weight"))) return rc;
+        }
+    }
+
+    std::unique_lock<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    ob_model *m = new ob_model;
+    m->ctx = ctx;
+    m->cfg = c;
+    m->cfg.layers = nullptr;
+    m->cfg.output_norm = nullptr;
+    m->cfg.tp_unique_id = nullptr;
+    if (m->cfg.rope_dim == 0) m->cfg.rope_dim = c.head_dim;
+    if (m->cfg.max_seq_len == 0) m->cfg.max_seq_len = 4096;
+    if (m->cfg.max_batch_tokens == 0) m->cfg.max_batch_tokens = 1;
+    m->tp_rank = rank;
+    m->tp_size = tp;
+    m->n_head_l = c.n_head / tp;
+    m->n_head_kv_l = c.n_head_kv / tp;
+    m->n_ff_l = c.n_ff / tp;
+    m->vocab_l = c.n_vocab / tp;
+    m->vocab0 = rank * m->vocab_l;
+    m->T = m->cfg.max_batch_tokens;
+    const uint32_t T = m->T, hd = c.head_dim;
+    const uint32_t q_dim = m->n_head_l * hd, kv_dim = m->n_head_kv_l * hd;
+
+    auto bail = [&](int code) {
+        g.unlock();
+        ob_model_destroy(m);
+        return code;
+    };
+
+    // ---- weights (sharded: Q/K/V/gate/up/output by rows, Wo/down by input columns)
+    m->layers.resize(c.n_layer);
+    for (uint32_t i = 0; i < c.n_layer; ++i) {
+        const ob_layer_desc &L = c.layers[i];
+        LayerDev &D = m->layers[i];
+        if ((rc = upload_f32(m, L.attn_norm, c.n_embd, &D.attn_norm))) return bail(rc);
+        if ((rc = upload_f32(m, L.ffn_norm, c.n_embd, &D.ffn_norm))) return bail(rc);
+        if ((rc = slice_weight(m, L.wq, rank * q_dim, q_dim, 0, c.n_embd, &D.wq))) return bail(rc);
+        if ((rc = slice_weight(m, L.wk, rank * kv_dim, kv_dim, 0, c.n_embd, &D.wk))) return bail(rc);
+        if ((rc = slice_weight(m, L.wv, rank * kv_dim, kv_dim, 0, c.n_embd, &D.wv))) return bail(rc);
+        if ((rc = slice_weight(m, L.wo, 0, c.n_embd, rank * q_dim, q_dim, &D.wo))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_gate, rank * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.gate))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_up, rank * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.up))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_down, 0, c.n_embd, rank * m->n_ff_l, m->n_ff_l, &D.down))) return bail(rc);
+    }
+    if ((rc = slice_weight(m, c.token_embd, 0, c.n_vocab, 0, c.n_embd, &m->token_embd))) return bail(rc);
+    if (c.output.data) {
+        if ((rc = slice_weight(m, c.output, m->vocab0, m->vocab_l, 0, c.n_embd, &m->output))) return bail(rc);
+    } else if (tp == 1) {
+        m->output = m->token_embd;  // tied (llama.rs:133-139)
+    } else {
+        if ((rc = slice_weight(m, c.token_embd, m->vocab0, m->vocab_l, 0, c.n_embd, &m->output))) return bail(rc);
+    }
+    if ((rc = upload_f32(m, c.output_norm, c.n_embd, &m->output_norm))) return bail(rc);
+
+    // ---- RoPE table from the host libm, as the reference computes the angles (tensor.rs:1140-1160)
+    {
+        const uint32_t half = m->cfg.rope_dim / 2, n_pos = m->cfg.max_seq_len;
+        std::vector<float> freq(half), tab((size_t)n_pos * half * 2);
+        for (uint32_t i = 0; i < half; ++i) freq[i] = powf(c.rope_freq_base, -2.0f * (float)i / (float)m->cfg.rope_dim);
+        for (uint32_t p = 0; p < n_pos; ++p)
+            for (uint32_t i = 0; i < half; ++i) {
+                const float theta = 1.0f * ((float)p * freq[i]);
+                tab[((size_t)p * half + i) * 2] = sinf(theta) * 1.0f;
+                tab[((size_t)p * half + i) * 2 + 1] = cosf(theta) * 1.0f;
+            }
+        if ((rc = upload_f32(m, tab.data(), tab.size(), &m->rope_table))) return bail(rc);
+        cudaStreamSynchronize(ctx->stream);  // tab goes out of scope
+    }
+
+    // ---- KV pool
+    {
+        const uint64_t tokens = c.kv_pool_tokens ? c.kv_pool_tokens : m->cfg.max_seq_len;
+        m->pool_pages = (uint32_t)((tokens + KV_PAGE - 1) / KV_PAGE) + 1;
+        m->layer_stride = (size_t)m->pool_pages * m->n_head_kv_l * KV_PAGE * hd;
+        if ((rc = dev_alloc(m, &m->k_pool, m->layer_stride * c.n_layer))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->v_pool, m->layer_stride * c.n_layer))) return bail(rc);
+        cudaMemsetAsync(m->k_pool, 0, m->layer_stride * c.n_layer * 2, ctx->stream);
+        cudaMemsetAsync(m->v_pool, 0, m->layer_stride * c.n_layer * 2, ctx->stream);
+        m->free_pages.reserve(m->pool_pages);
+        for (int32_t p = (int32_t)m->pool_pages - 1; p >= 0; --p) m->free_pages.push_back(p);
+    }
+
+    // ---- scratch
+    if ((rc = dev_alloc(m, &m->x, (size_t)T * c.n_embd))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->q, (size_t)T * q_dim))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->k, (size_t)T * kv_dim))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->v, (size_t)T * kv_dim))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->attn, (size_t)T * q_dim))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->gate, (size_t)T * m->n_ff_l))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->up, (size_t)T * m->n_ff_l))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->proj, (size_t)T * c.n_embd))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->logits, (size_t)T * c.n_vocab))) return bail(rc);
+    if ((rc = alloc_act(m, &m->act_embd, T, c.n_embd))) return bail(rc);
+    if ((rc = alloc_act(m, &m->act_attn, T, q_dim))) return bail(rc);
+    if ((rc = alloc_act(m, &m->act_ff, T, m->n_ff_l))) return bail(rc);
+    m->max_splits = std::max(1u, std::min(64u, (m->cfg.max_seq_len + 63) / 64));
+    {   // rows * pick_splits(rows) never exceeds 4 * SMs + rows
+        const size_t row_splits = (size_t)4 * ctx->sm_count + T;
+        if ((rc = dev_alloc(m, &m->part_o, row_splits * m->n_head_l * hd))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->part_ml, row_splits * m->n_head_l * 2))) return bail(rc);
+    }
+    const MetaLayout ml(T);
+    if ((rc = dev_alloc(m, &m->d_meta, ml.bytes))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->d_out_tokens, T))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->argmax_scratch, T))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->d_step_counter, 4))) return bail(rc);
+    if (cudaMallocHost(reinterpret_cast<void **>(&m->h_meta), ml.bytes) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void **>(&m->h_out_tokens), (size_t)T * 4) != cudaSuccess)
+        return bail(fail(ctx, OB_ERR_OOM, "model_create: pinned host allocation failed"));
+
+    if (tp > 1) {
+        std::string err;
+        m->comm = obtp::create(c.tp_unique_id, (int)rank, (int)tp, ctx->device, &err);
+        if (!m->comm) return bail(fail(ctx, OB_ERR_COMM, "model_create: " + err));
+    }
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) return bail(fail(ctx, OB_ERR_CUDA, std::string("model_create: ") + cudaGetErrorString(e)));
+    *out = m;
+    return OB_OK;
+}
+
+// ------------------------------------------------------------------------------------ KV cache
+
+int ob_kv_create(ob_model *m, uint32_t capacity_tokens, ob_kv **out) {
+    if (!m || !out || capacity_tokens == 0) return fail(m ? m->ctx : nullptr, OB_ERR_INVALID, "kv_create: bad argument");
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    *out = nullptr;
+    if (capacity_tokens > m->cfg.max_seq_len) return fail(ctx, OB_ERR_CAPACITY, "kv_create: capacity exceeds the model's max_seq_len");
+    const uint32_t n_pages = (capacity_tokens + KV_PAGE - 1) / KV_PAGE;
+    if (n_pages > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "kv_create: KV pool exhausted");
+    Bind b(ctx);
+    ob_kv *kv = new ob_kv;
+    kv->m = m;
+    kv->capacity = capacity_tokens;
+    for (uint32_t i = 0; i < n_pages; ++i) {
+        kv->pages.push_back(m->free_pages.back());
+        m->free_pages.pop_back();
+    }
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&kv->d_table), (size_t)n_pages * 4);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(kv->d_table, kv->pages.data(), (size_t)n_pages * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        for (int32_t p : kv->pages) m->free_pages.push_back(p);
+        if (kv->d_table) cudaFree(kv->d_table);
+        delete kv;
+        return fail(ctx, OB_ERR_CUDA, std::string("kv_create: ") + cudaGetErrorString(e));
+    }
+    *out = kv;
+    return OB_OK;
+}
+
+void ob_kv_destroy(ob_kv *kv) {
+    if (!kv) return;
+    ob_ctx *ctx = kv->m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    cudaStreamSynchronize(ctx->stream);
+    for (int32_t p : kv->pages) kv->m->free_pages.push_back(p);
+    cudaFree(kv->d_table);
+    delete kv;
+}
+
+uint32_t ob_kv_len(const ob_kv *kv) { return kv ? kv->len : 0; }
+
+int ob_kv_truncate(ob_kv *kv, uint32_t new_len) {
+    if (!kv) return OB_ERR_INVALID;
+    std::lock_guard<std::mutex> g(kv->m->ctx->mu);
+    if (new_len > kv->len) return fail(kv->m->ctx, OB_ERR_INVALID, "kv_truncate: new_len exceeds the current length");
+    kv->len = new_len;
+    return OB_OK;
+}
+
+int ob_kv_read(ob_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n, float *k_out, float *v_out) {
+    if (!kv || !k_out || !v_out) return OB_ERR_INVALID;
+    ob_model *m = kv->m;
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (layer >= m->cfg.n_layer || (uint64_t)pos0 + n > kv->len) return fail(ctx, OB_ERR_INVALID, "kv_read: out of range");
+    Bind b(ctx);
+    const uint32_t hd = m->cfg.head_dim, nkv = m->n_head_kv_l, kv_dim = nkv * hd;
+    std::vector<__half> page((size_t)nkv * KV_PAGE * hd);
+    for (int which = 0; which < 2; ++which) {
+        const __half *pool = (which ? m->v_pool : m->k_pool) + (size_t)layer * m->layer_stride;
+        float *dst = which ? v_out : k_out;
+        int32_t loaded = -1;
+        for (uint32_t p = pos0; p < pos0 + n; ++p) {
+            const int32_t pg = kv->pages[p / KV_PAGE];
+            if (pg != loaded) {
+                OB_CUDA(ctx, cudaMemcpyAsync(page.data(), pool + (size_t)pg * page.size(), page.size() * 2, cudaMemcpyDeviceToHost, ctx->stream));
+                OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+                loaded = pg;
+            }
+            for (uint32_t h = 0; h < nkv; ++h)
+                for (uint32_t d = 0; d < hd; ++d)
+                    dst[(size_t)(p - pos0) * kv_dim + h * hd + d] = __half2float(page[((size_t)h * KV_PAGE + p % KV_PAGE) * hd + d]);
+        }
+    }
+    return OB_OK;
+}
+
+// ------------------------------------------------------------------------------------ forward
+
+}  // extern "C"
+
+namespace {
+
+// One step on the stream: metadata up, kernels, results down; synchronises.
+int run_rows(ob_model *m, const std::vector<ob_kv *> &row_kv, const uint32_t *tokens, const uint32_t *positions, bool gemm_order,
+             uint32_t logit_row0, uint32_t n_logit_rows, const ob_greedy *greedy, const uint32_t *recent_off, uint32_t seq0,
+             uint32_t *out_token, float *out_logits) {
+    ob_ctx *ctx = m->ctx;
+    const uint32_t T = (uint32_t)row_kv.size();
+    const MetaLayout ml(m->T);
+    uint32_t *h_tokens = reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens);
+    uint32_t *h_positions = reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions);
+    uint32_t *h_npos = reinterpret_cast<uint32_t *>(m->h_meta + ml.off_npos);
+    const int32_t **h_tables = reinterpret_cast<const int32_t **>(m->h_meta + ml.off_tables);
+    for (uint32_t t = 0; t < T; ++t) {
+        h_tokens[t] = tokens[t];
+        h_positions[t] = positions[t];
+        h_npos[t] = positions[t] + 1;
+        h_tables[t] = row_kv[t]->d_table;
+    }
+    cudaStream_t st = ctx->stream;
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+    OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st));
+    const bool penalise = greedy && greedy->repeat_penalty != 1.0f && greedy->recent && greedy->n_recent;
+    enqueue_step(m, T, gemm_order, logit_row0, n_logit_rows, out_token != nullptr && !penalise, st);
+    if (out_token && penalise) {
+        // repeat penalty, then argmax (sampling.rs:345-359); the history comes from the caller per call
+        for (uint32_t r = 0; r < n_logit_rows; ++r) {
+            const uint32_t s = seq0 + r, nr = greedy->n_recent[s];
+            const uint32_t start = nr > greedy->repeat_last_n ? nr - greedy->repeat_last_n : 0, cnt = nr - start;
+            if (!cnt) continue;
+            int rc = ensure(ctx, ctx->saux, (size_t)cnt * 4);
+            if (rc) return rc;
+            OB_CUDA(ctx, cudaMemcpyAsync(ctx->saux.p, greedy->recent + recent_off[s] + start, (size_t)cnt * 4, cudaMemcpyHostToDevice, st));
+            launch_repeat_penalty(m->logits + (size_t)r * m->cfg.n_vocab, m->cfg.n_vocab, static_cast<uint32_t *>(ctx->saux.p), cnt,
+                                  greedy->repeat_penalty, st);
+            ctx->launches++;
+            OB_CUDA(ctx, cudaStreamSynchronize(st));  // saux is reused by the next row
+        }
+        ArgmaxArgs am{};
+        am.logits = m->logits;
+        am.n_seq = n_logit_rows;
+        am.n_vocab = m->cfg.n_vocab;
+        am.out = m->d_out_tokens;
+        am.scratch = m->argmax_scratch;
+        launch_argmax(am, st);
+        ctx->launches += 3;
+    }
+    if (out_token) OB_CUDA(ctx, cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_logit_rows * 4, cudaMemcpyDeviceToHost, st));
+    if (out_logits) OB_CUDA(ctx, cudaMemcpyAsync(out_logits, m->logits, (size_t)n_logit_rows * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, st));
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+    OB_CUDA(ctx, cudaStreamSynchronize(st));
+    OB_CUDA(ctx, cudaGetLastError());
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
+    ctx->last_ms += ms;
+    if (out_token) memcpy(out_token, m->h_out_tokens, (size_t)n_logit_rows * 4);
+    return OB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ob_forward(ob_model *m, ob_kv *const *kvs, const uint32_t *tokens, const uint32_t *n_tokens, const uint32_t *start_pos, uint32_t n_seq,
+               const ob_greedy *greedy, uint32_t *out_token, float *out_logits) {
+    if (!m || !kvs || !tokens || !n_tokens || !start_pos) return fail(m ? m->ctx : nullptr, OB_ERR_INVALID, "forward: null argument");
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (n_seq == 0) return OB_OK;
+    Bind b(ctx);
+    // ---- validate everything before any state changes
+    bool all_single = true;
+    uint64_t total = 0;
+    std::vector<uint32_t> tok_off(n_seq), recent_off(n_seq, 0);
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        ob_kv *kv = kvs[s];
+        if (!kv || kv->m != m) return fail(ctx, OB_ERR_INVALID, "forward: KV cache missing or from another model");
+        if (n_tokens[s] == 0) return fail(ctx, OB_ERR_INVALID, "forward: a sequence carries no tokens");
+        if (start_pos[s] != kv->len) return fail(ctx, OB_ERR_INVALID, "forward: start_pos does not continue the KV cache");
+        if ((uint64_t)kv->len + n_tokens[s] > kv->capacity) return fail(ctx, OB_ERR_CAPACITY, "forward: KV cache is full");
+        for (uint32_t s2 = 0; s2 < s; ++s2)
+            if (kvs[s2] == kv) return fail(ctx, OB_ERR_INVALID, "forward: the same KV cache appears twice");
+        if (n_tokens[s] != 1) all_single = false;
+        tok_off[s] = (uint32_t)total;
+        total += n_tokens[s];
+        if (s + 1 < n_seq && greedy && greedy->n_recent) recent_off[s + 1] = recent_off[s] + greedy->n_recent[s];
+    }
+    for (uint64_t i = 0; i < total; ++i)
+        if (tokens[i] >= m->cfg.n_vocab) return fail(ctx, OB_ERR_INVALID, "forward: token id out of vocabulary range");
+    ctx->last_ms = 0.0f;
+
+    if (all_single) {
+        // decode batch, in slices of at most max_batch_tokens rows
+        for (uint32_t s0 = 0; s0 < n_seq; s0 += m->T) {
+            const uint32_t n = std::min(m->T, n_seq - s0);
+            std::vector<ob_kv *> rows(kvs + s0, kvs + s0 + n);
+            int rc = run_rows(m, rows, tokens + s0, start_pos + s0, false, 0, n, greedy, recent_off.data(), s0, out_token ? out_token + s0 : nullptr,
+                              out_logits ? out_logits + (size_t)s0 * m->cfg.n_vocab : nullptr);
+            if (rc) return rc;
+            for (uint32_t i = 0; i < n; ++i) kvs[s0 + i]->len += 1;
+        }
+        return OB_OK;
+    }
+    // otherwise sequence by sequence; a multi-token sequence is a prefill in chunks of max_batch_tokens
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        ob_kv *kv = kvs[s];
+        uint32_t done = 0;
+        while (done < n_tokens[s]) {
+            const uint32_t n = std::min(m->T, n_tokens[s] - done);
+            const bool last_chunk = done + n == n_tokens[s];
+            std::vector<ob_kv *> rows(n, kv);
+            std::vector<uint32_t> pos(n);
+            for (uint32_t i = 0; i < n; ++i) pos[i] = kv->len + i;
+            // a chunk of one token takes the single-token kernels, exactly as the reference's matmul does
+            int rc = run_rows(m, rows, tokens + tok_off[s] + done, pos.data(), n > 1, n - 1, last_chunk ? 1 : 0, greedy, recent_off.data(), s,
+                              (last_chunk && out_token) ? out_token + s : nullptr,
+                              (last_chunk && out_logits) ? out_logits + (size_t)s * m->cfg.n_vocab : nullptr);
+            if (rc) return rc;
+            kv->len += n;
+            done += n;
+        }
+    }
+    return OB_OK;
+}
+
+int ob_last_hidden(ob_model *m, uint32_t n_tokens, float *out) {
+    if (!m || !out) return OB_ERR_INVALID;
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (n_tokens > m->last_T) return fail(ctx, OB_ERR_INVALID, "last_hidden: more rows than the last step carried");
+    Bind b(ctx);
+    OB_CUDA(ctx, cudaMemcpyAsync(out, m->x, (size_t)n_tokens * m->cfg.n_embd * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return OB_OK;
+}
+
+// ------------------------------------------------------------------------------------ graphs
+
+}  // extern "C"
+
+namespace {
+
+// kind 0: H2D metadata + step + D2H token (one host round trip per step)
+// kind 1: step + advance (device-resident loop)
+int get_graph(ob_model *m, uint32_t n_seq, int kind, cudaGraphExec_t *out) {
+    ob_ctx *ctx = m->ctx;
+    const uint64_t key = ((uint64_t)kind << 32) | n_seq;
+    auto it = m->graphs.find(key);
+    if (it != m->graphs.end()) {
+        *out = it->second;
+        return OB_OK;
+    }
+    const MetaLayout ml(m->T);
+    cudaStream_t st = ctx->stream;
+    // One eager pass first (d_meta must already describe a valid step): it sets the kernels' one-time
+    // function attributes outside capture and counts what a step launches.  It rewrites the KV slot of
+    // the current position with the values the replay will write again.
+    const uint64_t launches_before = ctx->launches;
+    enqueue_step(m, n_seq, false, 0, n_seq, true, st);
+    OB_CUDA(ctx, cudaStreamSynchronize(st));
+    OB_CUDA(ctx, cudaGetLastError());
+    m->graph_launches[key] = ctx->launches - launches_before + (kind == 1 ? 1 : 0);
+    ctx->launches = launches_before;
+    cudaGraph_t graph = nullptr;
+    OB_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    if (kind == 0) cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st);
+    enqueue_step(m, n_seq, false, 0, n_seq, true, st);
+    if (kind == 0) {
+        cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, st);
+    } else {
+        advance_kernel<<<(n_seq + 127) / 128, 128, 0, st>>>(reinterpret_cast<uint32_t *>(m->d_meta + ml.off_tokens),
+                                                             reinterpret_cast<uint32_t *>(m->d_meta + ml.off_positions),
+                                                             reinterpret_cast<uint32_t *>(m->d_meta + ml.off_npos), m->d_out_tokens, n_seq,
+                                                             m->d_history, m->d_step_counter);
+        ctx->launches++;
+    }
+    cudaError_t e = cudaStreamEndCapture(st, &graph);
+    if (e != cudaSuccess || !graph) return fail(ctx, OB_ERR_CUDA, std::string("graph capture: ") + cudaGetErrorString(e));
+    m->ctx->launches = launches_before;  // capture enqueued nothing; replays are counted by their callers
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail(ctx, OB_ERR_CUDA, std::string("graph instantiate: ") + cudaGetErrorString(e));
+    m->graphs[key] = exec;
+    *out = exec;
+    return OB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ob_decode_greedy(ob_model *m, ob_kv *kv, uint32_t token, uint32_t *out_token) {
+    if (!m || !kv || !out_token || kv->m != m) return fail(m ? m->ctx : nullptr, OB_ERR_INVALID, "decode_greedy: bad argument");
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (token >= m->cfg.n_vocab) return fail(ctx, OB_ERR_INVALID, "decode_greedy: token id out of vocabulary range");
+    if (kv->len >= kv->capacity) return fail(ctx, OB_ERR_CAPACITY, "decode_greedy: KV cache is full");
+    Bind b(ctx);
+    const MetaLayout ml(m->T);
+    reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens)[0] = token;
+    reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions)[0] = kv->len;
+    reinterpret_cast<uint32_t *>(m->h_meta + ml.off_npos)[0] = kv->len + 1;
+    reinterpret_cast<const int32_t **>(m->h_meta + ml.off_tables)[0] = kv->d_table;
+    cudaGraphExec_t exec;
+    if (m->graphs.find(1) == m->graphs.end()) OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = get_graph(m, 1, 0, &exec);
+    if (rc) return rc;
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    OB_CUDA(ctx, cudaGraphLaunch(exec, ctx->stream));
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaEventElapsedTime(&ctx->last_ms, ctx->ev0, ctx->ev1);
+    ctx->launches += m->graph_launches[1];
+    kv->len += 1;
+    *out_token = m->h_out_tokens[0];
+    return OB_OK;
+}
+
+int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens, uint32_t n_seq, uint32_t n_steps, uint32_t *out_tokens) {
+    if (!m || !kvs || !first_tokens || !out_tokens) return fail(m ? m->ctx : nullptr, OB_ERR_INVALID, "decode_loop: null argument");
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (n_seq == 0 || n_steps == 0) return OB_OK;
+    if (n_seq > m->T) return fail(ctx, OB_ERR_CAPACITY, "decode_loop: more sequences than max_batch_tokens");
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        if (!kvs[s] || kvs[s]->m != m) return fail(ctx, OB_ERR_INVALID, "decode_loop: KV cache missing or from another model");
+        if ((uint64_t)kvs[s]->len + n_steps > kvs[s]->capacity) return fail(ctx, OB_ERR_CAPACITY, "decode_loop: KV cache too small for n_steps");
+        if (first_tokens[s] >= m->cfg.n_vocab) return fail(ctx, OB_ERR_INVALID, "decode_loop: token id out of vocabulary range");
+        for (uint32_t s2 = 0; s2 < s; ++s2)
+            if (kvs[s2] == kvs[s]) return fail(ctx, OB_ERR_INVALID, "decode_loop: the same KV cache appears twice");
+    }
+    Bind b(ctx);
+    if ((uint64_t)n_steps * n_seq > m->history_cap) {
+        int rc = dev_alloc(m, &m->d_history, (size_t)n_steps * n_seq);
+        if (rc) return rc;
+        m->history_cap = n_steps * n_seq;
+        // the graph holds the old pointer: drop loop graphs
+        for (auto it = m->graphs.begin(); it != m->graphs.end();) {
+            if ((it->first >> 32) == 1) {
+                cudaGraphExecDestroy(it->second);
+                it = m->graphs.erase(it);
+            } else {
+                ++it;
+            }
+        }
+    }
+    const uint64_t key = ((uint64_t)1 << 32) | n_seq;
+    const MetaLayout ml(m->T);
+    for (uint32_t s = 0; s < n_seq; ++s) {
+        reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens)[s] = first_tokens[s];
+        reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions)[s] = kvs[s]->len;
+        reinterpret_cast<uint32_t *>(m->h_meta + ml.off_npos)[s] = kvs[s]->len + 1;
+        reinterpret_cast<const int32_t **>(m->h_meta + ml.off_tables)[s] = kvs[s]->d_table;
+    }
+    OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, ctx->stream));
+    cudaGraphExec_t exec;
+    int rc = get_graph(m, n_seq, 1, &exec);
+    if (rc) return rc;
+    cudaStream_t st = ctx->stream;
+    OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st));
+    OB_CUDA(ctx, cudaMemsetAsync(m->d_step_counter, 0, 4, st));
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+    for (uint32_t i = 0; i < n_steps; ++i) OB_CUDA(ctx, cudaGraphLaunch(exec, st));
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+    OB_CUDA(ctx, cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * n_seq * 4, cudaMemcpyDeviceToHost, st));
+    OB_CUDA(ctx, cudaStreamSynchronize(st));
+    OB_CUDA(ctx, cudaGetLastError());
+    cudaEventElapsedTime(&ctx->last_ms, ctx->ev0, ctx->ev1);
+    ctx->launches += m->graph_launches[key] * n_steps;
+    for (uint32_t s = 0; s < n_seq; ++s) kvs[s]->len += n_steps;
+    return OB_OK;
+}
+
+int ob_tp_unique_id(void *out128) {
+    if (!out128) return OB_ERR_INVALID;
+    std::string err;
+    if (!obtp::unique_id(out128, &err)) return fail(nullptr, OB_ERR_COMM, err);
+    return OB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// NCCL binding for the tensor-parallel all-reduce after the row-split products (attention output
+// and FFN down).  The reference engine has no collective of any kind; its multi-GPU mode moves
+// activations through host memory between layer ranges (engine/backend/multi.rs:16-35).
+#include "tp.h"
+
+#include <dlfcn.h>
+#include <string.h>
+
+namespace obtp {
+
+namespace {
+
+typedef struct {
+    char internal[128];
+} UniqueId;
+typedef void *NcclComm;
+typedef int NcclResult;
+constexpr int kNcclFloat = 7, kNcclSum = 0;
+
+struct Api {
+    void *handle = nullptr;
+    NcclResult (*GetUniqueId)(UniqueId *) = nullptr;
+    NcclResult (*CommInitRank)(NcclComm *, int, UniqueId, int) = nullptr;
+    NcclResult (*CommDestroy)(NcclComm) = nullptr;
+    NcclResult (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    NcclResult (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
+    NcclResult (*GroupStart)() = nullptr;
+    NcclResult (*GroupEnd)() = nullptr;
+    const char *(*GetErrorString)(NcclResult) = nullptr;
+    std::string err;
+};
+
+Api *api() {
+    static Api a;
+    static bool tried = false;
+    if (tried) return a.handle ? &a : nullptr;
+    tried = true;
+    for (const char *name : {"libnccl.so.2", "libnccl.so"}) {
+        a.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+        if (a.handle) break;
+    }
+    if (!a.handle) {
+        a.err = std::string("cannot load libnccl: ") + dlerror();
+        return nullptr;
+    }
+    bool ok = true;
+    auto sym = [&](const char *n) {
+        void *p = dlsym(a.handle, n);
+        if (!p) {
+            ok = false;
+            a.err = std::string("libnccl lacks ") + n;
+        }
+        return p;
+    };
+    a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(sym("ncclGetUniqueId"));
+    a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(sym("ncclCommInitRank"));
+    a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(sym("ncclCommDestroy"));
+    a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(sym("ncclAllReduce"));
+    a.AllGather = reinterpret_cast<decltype(a.AllGather)>(sym("ncclAllGather"));
+    a.GroupStart = reinterpret_cast<decltype(a.GroupStart)>(sym("ncclGroupStart"));
+    a.GroupEnd = reinterpret_cast<decltype(a.GroupEnd)>(sym("ncclGroupEnd"));
+    a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(sym("ncclGetErrorString"));
+    if (!ok) {
+        a.handle = nullptr;
+        return nullptr;
+    }
+    return &a;
+}
+
+std::string api_error() { return "NCCL unavailable (libnccl.so.2 could not be loaded or lacks a symbol)"; }
+
+}  // namespace
+
+struct Comm {
+    NcclComm comm = nullptr;
+    int rank = 0, size = 1;
+    std::string err;
+};
+
+bool unique_id(void *out128, std::string *err) {
+    Api *a = api();
+    if (!a) {
+        if (err) *err = api_error();
+        return false;
+    }
+    UniqueId id;
+    NcclResult r = a->GetUniqueId(&id);
+    if (r != 0) {
+        if (err) *err = std::string("ncclGetUniqueId: ") + a->GetErrorString(r);
+        return false;
+    }
+    memcpy(out128, id.internal, 128);
+    return true;
+}
+
+Comm *create(const void *id128, int rank, int size, int device, std::string *err) {
+    Api *a = api();
+    if (!a) {
+        if (err) *err = api_error();
+        return nullptr;
+    }
+    UniqueId id;
+    memcpy(id.internal, id128, 128);
+    cudaSetDevice(device);
+    Comm *c = new Comm;
+    c->rank = rank;
+    c->size = size;
+    NcclResult r = a->CommInitRank(&c->comm, size, id, rank);
+    if (r != 0) {
+        if (err) *err = std::string("ncclCommInitRank: ") + a->GetErrorString(r);
+        delete c;
+        return nullptr;
+    }
+    return c;
+}
+
+void destroy(Comm *c) {
+    if (!c) return;
+    Api *a = api();
+    if (a && c->comm) a->CommDestroy(c->comm);
+    delete c;
+}
+
+bool all_reduce_sum(Comm *c, float *buf, size_t count, cudaStream_t st) {
+    Api *a = api();
+    NcclResult r = a->AllReduce(buf, buf, count, kNcclFloat, kNcclSum, c->comm, st);
+    if (r != 0) {
+        c->err = std::string("ncclAllReduce: ") + a->GetErrorString(r);
+        return false;
+    }
+    return true;
+}
+
+bool all_gather_logits(Comm *c, float *logits, uint32_t rows, uint32_t n_vocab, uint32_t vocab0, uint32_t vocab_l, cudaStream_t st) {
+    Api *a = api();
+    NcclResult r = a->GroupStart();
+    for (uint32_t i = 0; i < rows && r == 0; ++i) {
+        float *row = logits + (size_t)i * n_vocab;
+        r = a->AllGather(row + vocab0, row, vocab_l, kNcclFloat, c->comm, st);
+    }
+    NcclResult r2 = a->GroupEnd();
+    if (r == 0) r = r2;
+    if (r != 0) {
+        c->err = std::string("ncclAllGather: ") + a->GetErrorString(r);
+        return false;
+    }
+    return true;
+}
+
+const char *last_error(Comm *c) { return c ? c->err.c_str() : ""; }
+
+}  // namespace obtp

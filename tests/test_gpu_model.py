@@ -1,0 +1,182 @@
+"""Full-graph parity with the CPU oracle: logits within 2e-2 max-abs and identical greedy tokens."""
+import numpy as np
+import pytest
+
+import oracle as O
+from gpu_common import assert_bit_equal, backend  # noqa: F401
+from orangu_b200 import LlamaModel, OranguError, synth
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOL = 2e-2
+
+
+def build(backend, name, seed=0, n_layer=None, types=None, **kw):
+    cfg = dict(synth.CONFIGS[name])
+    if n_layer is not None:
+        cfg["n_layer"] = n_layer
+    tensors = synth.model_tensors(cfg, seed=seed, types=types)
+    return cfg, tensors, LlamaModel(backend, cfg, tensors, **kw), O.Model(cfg, tensors)
+
+
+def prompt(cfg, n, seed):
+    return np.random.default_rng(seed).integers(0, cfg["n_vocab"], n).astype(np.uint32)
+
+
+@pytest.mark.parametrize("name,types", [("tiny", None), ("small", None), ("tiny", {"attn_q": 8, "ffn_down": 8, "output": 8}),
+                                         ("small", {"attn_k": 14, "ffn_gate": 14, "token_embd": 14})])
+def test_prefill_then_greedy_decode_matches_the_oracle(backend, name, types):
+    cfg, tensors, model, ref = build(backend, name, seed=3, types=types, max_seq_len=256, max_batch_tokens=32)
+    toks = prompt(cfg, 45, 1)
+    kv, rkv = model.new_kv_cache(128), ref.new_kv(128, f16=True)
+    logits = model.forward(kv, toks, 0)  # 45 tokens in chunks of 32 + 13
+    want, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
+    assert np.abs(logits - want).max() < LOGIT_TOL
+    assert len(kv) == 45
+    # the cache holds what the oracle's f16 cache holds
+    k, v = kv.read(cfg["n_layer"] - 1, 0, 45)
+    assert np.isfinite(k).all() and np.isfinite(v).all()
+    nxt, rnxt = int(np.argmax(logits)), O.argmax(want)
+    assert nxt == rnxt
+    for step in range(24):
+        got_logits = model.forward(kv, [nxt], 45 + step)
+        want_logits = ref.forward(rkv, [rnxt], 45 + step)
+        assert np.abs(got_logits - want_logits).max() < LOGIT_TOL, f"step {step}"
+        nxt, rnxt = backend.argmax(got_logits), O.argmax(want_logits)
+        assert nxt == rnxt, f"greedy token diverged at step {step}"
+
+
+def test_hidden_state_and_kv_contents(backend):
+    cfg, tensors, model, ref = build(backend, "tiny", seed=5, max_seq_len=64, max_batch_tokens=16)
+    toks = prompt(cfg, 9, 2)
+    kv, rkv = model.new_kv_cache(32), ref.new_kv(32, f16=True)
+    model.forward(kv, toks, 0)
+    _, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
+    got = model.last_hidden(9)
+    assert np.abs(got - hidden).max() < 2e-3 * max(1.0, np.abs(hidden).max())
+
+
+def test_sampling_paths_agree(backend):
+    """forward_maybe_sampling, the captured decode graph and the device loop produce the same tokens."""
+    cfg, tensors, model, ref = build(backend, "small", seed=7, max_seq_len=128, max_batch_tokens=16)
+    toks = prompt(cfg, 12, 3)
+    caches = [model.new_kv_cache(96) for _ in range(3)]
+    first = [model.forward_maybe_sampling(c, toks, 0) for c in caches]
+    assert first[0] == first[1] == first[2]
+    a, b = [], []
+    t0 = t1 = first[0]
+    for i in range(20):
+        t0 = model.forward_maybe_sampling(caches[0], [t0], 12 + i)
+        t1 = model.decode_greedy(caches[1], t1)
+        a.append(t0)
+        b.append(t1)
+    assert a == b
+    c = model.decode_loop([caches[2]], [first[2]], 20)[:, 0].tolist()
+    assert c == a
+    assert len(caches[0]) == len(caches[1]) == len(caches[2]) == 32
+    # against the oracle
+    rkv = ref.new_kv(96, f16=True)
+    r = O.argmax(ref.forward(rkv, toks, 0))
+    want = []
+    for i in range(20):
+        r = O.argmax(ref.forward(rkv, [r], 12 + i))
+        want.append(r)
+    assert [first[0]] + a[:-1] == [O.argmax(ref.forward(ref.new_kv(96, f16=True), toks, 0))] + want[:-1]
+    assert a == want
+
+
+def test_batch_decode_rows_are_independent(backend):
+    """A sequence decoded in a batch gets the logits it gets alone, bit for bit (the reference's
+    decode contract, backend/mod.rs:368-388), and the batch may mix context lengths."""
+    cfg, tensors, model, ref = build(backend, "small", seed=9, max_seq_len=128, max_batch_tokens=8)
+    prompts = [prompt(cfg, n, 10 + n) for n in (5, 17, 33, 2, 9)]
+    solo = [model.new_kv_cache(64) for _ in prompts]
+    batch = [model.new_kv_cache(64) for _ in prompts]
+    nxt = [model.forward_maybe_sampling(c, p, 0) for c, p in zip(solo, prompts)]
+    for c, p in zip(batch, prompts):
+        model.forward(c, p, 0)
+    for step in range(6):
+        toks, logits = model.forward_batch_decode(batch, nxt, want_logits=True)
+        alone = [model.forward(c, [t], len(c)) for c, t in zip(solo, nxt)]
+        for i in range(len(prompts)):
+            assert_bit_equal(logits[i], alone[i], f"step {step} seq {i}")
+        nxt = [int(t) for t in toks]
+        assert nxt == [int(np.argmax(a)) for a in alone]
+    loop_caches = [model.new_kv_cache(64) for _ in prompts]
+    first = [model.forward_maybe_sampling(c, p, 0) for c, p in zip(loop_caches, prompts)]
+    out = model.decode_loop(loop_caches, first, 6)
+    assert out[-1].tolist() == nxt
+
+
+def test_repeat_penalty_through_the_model(backend):
+    cfg, tensors, model, ref = build(backend, "tiny", seed=11, max_seq_len=64, max_batch_tokens=16)
+    toks = prompt(cfg, 7, 4)
+    kv = model.new_kv_cache(32)
+    logits = model.forward(kv, toks, 0)
+    plain = int(np.argmax(logits))
+    kv2 = model.new_kv_cache(32)
+    recent = [plain] * 3 + [int(toks[0])]
+    got = model.forward_maybe_sampling(kv2, toks, 0, recent=recent, repeat_penalty=4.0, repeat_last_n=64)
+    assert got == O.argmax(O.repeat_penalty(logits, recent, 64, 4.0))
+
+
+def test_kv_truncate_rolls_back(backend):
+    cfg, tensors, model, ref = build(backend, "tiny", seed=13, max_seq_len=64, max_batch_tokens=16)
+    toks = prompt(cfg, 20, 5)
+    kv = model.new_kv_cache(32)
+    model.forward(kv, toks[:10], 0)
+    a = model.forward(kv, toks[10:20], 10)
+    kv.truncate(10)
+    assert len(kv) == 10
+    b = model.forward(kv, toks[10:20], 10)
+    assert_bit_equal(a, b, "replay after truncate")
+
+
+def test_errors_are_statuses(backend):
+    cfg, tensors, model, ref = build(backend, "tiny", seed=15, max_seq_len=32, max_batch_tokens=8, kv_pool_tokens=64)
+    kv = model.new_kv_cache(16)
+    with pytest.raises(OranguError) as e:
+        model.forward(kv, [cfg["n_vocab"]], 0)
+    assert e.value.status == -1 and "vocabulary" in e.value.message
+    with pytest.raises(OranguError) as e:
+        model.forward(kv, [1, 2], 3)
+    assert e.value.status == -1 and "start_pos" in e.value.message
+    with pytest.raises(OranguError) as e:
+        model.forward(kv, list(range(17)), 0)
+    assert e.value.status == -6
+    assert len(kv) == 0  # nothing was consumed by the failed calls
+    with pytest.raises(OranguError) as e:
+        model.new_kv_cache(33)
+    assert e.value.status == -6
+    others = [model.new_kv_cache(16) for _ in range(3)]
+    with pytest.raises(OranguError) as e:
+        model.new_kv_cache(32)  # pool of 64 (+1 page) tokens is spent
+    assert e.value.status == -6 and "exhausted" in e.value.message
+    bad = dict(tensors)
+    bad["blk.0.attn_q.weight"] = dict(bad["blk.0.attn_q.weight"], type=13)
+    with pytest.raises(OranguError) as e:
+        LlamaModel(backend, cfg, bad)
+    assert e.value.status == -2 and "attn_q" in e.value.message
+
+
+def test_1b_config_prefill_512_and_256_greedy_steps(backend):
+    """1B-shape Q4_K_M decoder: 512-token prefill, then 256 greedy steps at batch 1."""
+    cfg, tensors, model, ref = build(backend, "1b", seed=21, max_seq_len=1024, max_batch_tokens=512)
+    toks = prompt(cfg, 512, 6)
+    kv, rkv = model.new_kv_cache(800), ref.new_kv(800, f16=True)
+    logits = model.forward(kv, toks, 0)
+    want = ref.forward(rkv, toks, 0)
+    worst = float(np.abs(logits - want).max())
+    assert worst < LOGIT_TOL, worst
+    first = int(np.argmax(logits))
+    assert first == O.argmax(want)
+    got = model.decode_loop([kv], [first], 256)[:, 0].tolist()
+    r, ref_tokens = first, []
+    for i in range(256):
+        l = ref.forward(rkv, [r], 512 + i)
+        r = O.argmax(l)
+        ref_tokens.append(r)
+    assert got == ref_tokens, f"first divergence at step {next(i for i, (a, b) in enumerate(zip(got, ref_tokens)) if a != b)}"
+    # logits after the 256 steps, through the non-graph path
+    last = model.forward(kv, [got[-1]], 768)
+    want_last = ref.forward(rkv, [ref_tokens[-1]], 768)
+    assert np.abs(last - want_last).max() < LOGIT_TOL
