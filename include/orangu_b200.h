@@ -151,9 +151,11 @@ int ob_quantize_act(ob_ctx *ctx, const float *x, uint32_t n, int per_256, int8_t
 /* attention::attention with n_tokens == 1 (E/attention.rs:242-344, 426-549) and the device path it
  * can dispatch to, VulkanBackend::gpu_attention_split (B/vulkan.rs:6330-6342, 10788): one query
  * token q [n_head*head_dim] against n_pos cached positions k,v [n_pos, n_head_kv*head_dim] f32,
- * which are stored as fp16 pages exactly as the KV mirror holds them (E/kv_cache.rs:26-32). */
+ * which are stored as fp16 pages exactly as the KV mirror holds them (E/kv_cache.rs:26-32).
+ * exact_order != 0 evaluates in the CPU loop's operation order (bit-identical to it); 0 takes the
+ * split flash-decode kernel, whose result differs from the CPU's in the last bits. */
 int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos,
-                        uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, float *out);
+                        uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, int exact_order, float *out);
 /* sampling::apply_repeat_penalty + argmax (E/sampling.rs:336-359); last index wins ties.
  * recent may be NULL; penalty 1.0 disables it. */
 int ob_argmax(ob_ctx *ctx, const float *logits, uint32_t n_vocab, const uint32_t *recent,
@@ -189,6 +191,11 @@ typedef struct ob_model_desc {
     uint32_t max_seq_len;      /* longest context any KV cache of this model will hold */
     uint32_t max_batch_tokens; /* most tokens one ob_forward call will carry (prefill chunk or decode batch) */
     uint64_t kv_pool_tokens;   /* total KV capacity shared by every ob_kv of this model, in tokens; 0 = max_seq_len */
+    /* Attention windows up to this many positions are evaluated in the CPU loop's own operation order
+     * (bit-identical to CpuBackend given the same f16 cache); longer windows take the split flash-decode
+     * kernel, as the reference moves long windows to its split-k device kernel (E/attention.rs:117,
+     * 264-300).  0 = 1024. */
+    uint32_t exact_attention_max_pos;
     ob_matrix_desc token_embd;   /* token_embd.weight */
     const float *output_norm;    /* output_norm.weight */
     ob_matrix_desc output;       /* output.weight; data == NULL ties it to token_embd (E/arch/llama.rs:133-139) */

@@ -25,6 +25,12 @@ constexpr size_t SUPER_BLOCK = 256; /* E/vecdot.rs:1800 */
 constexpr size_t SUBS = 8;
 constexpr size_t TOKEN_TILE = 4;    /* E/vecdot.rs:1682 */
 
+/* exp for f32: the reference calls f32::exp, i.e. the platform libm's expf, whose last bit is not
+ * specified (glibc documents 0.502 ULP).  The oracle pins it to the correctly rounded value, taken
+ * in double and rounded once, which a device can reproduce; glibc's expf returns that same value
+ * for all but about one argument in several hundred. */
+inline float exp_f32(float x) { return (float)exp((double)x); }
+
 inline float bits_f32(uint32_t b) {
     float f;
     memcpy(&f, &b, 4);
@@ -761,14 +767,14 @@ void oref_softmax(float *x, size_t n) {
     for (size_t i = 0; i < n; ++i) mx = fmaxf(mx, x[i]);
     float sum = 0.0f;
     for (size_t i = 0; i < n; ++i) {
-        x[i] = expf(x[i] - mx);
+        x[i] = exp_f32(x[i] - mx);
         sum += x[i];
     }
     if (sum > 0.0f)
         for (size_t i = 0; i < n; ++i) x[i] /= sum;
 }
 
-float oref_silu(float x) { return x / (1.0f + expf(-x)); }
+float oref_silu(float x) { return x / (1.0f + exp_f32(-x)); }
 
 void oref_swiglu(float *gate, const float *up, size_t n) {
     for (size_t i = 0; i < n; ++i) gate[i] = oref_silu(gate[i]);

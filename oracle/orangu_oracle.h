@@ -12,8 +12,10 @@
  * its own sources (dequantisation bit checksums, activation-quantiser tie and
  * NaN cases, GEMV/GEMM-versus-dequantise bounds, batch-size independence,
  * attention head-outer form); see tests/test_oracle_golden.py.  Parity for the
- * libm transcendentals (expf, powf, sinf, cosf) is unpinned at the ulp level:
- * the reference calls the platform libm through Rust std, as this file does.
+ * libm transcendentals is unpinned at the ulp level: the reference calls the
+ * platform libm through Rust std.  powf, sinf and cosf (RoPE angles) are the
+ * platform's here too; exp (SiLU, softmax) is pinned to the correctly rounded
+ * value, (float)exp((double)x), so that a device can reproduce it bit for bit.
  *
  * Every function cites the reference file:line it follows.  Paths are relative
  * to the reference project root; E = src/bin/orangu-server/engine.

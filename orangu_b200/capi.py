@@ -30,7 +30,7 @@ class LayerDesc(C.Structure):
 class ModelDesc(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_vocab", "n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "rope_dim", "n_ff")] + [
         ("rope_freq_base", C.c_float), ("rms_eps", C.c_float),
-        ("max_seq_len", C.c_uint32), ("max_batch_tokens", C.c_uint32), ("kv_pool_tokens", C.c_uint64),
+        ("max_seq_len", C.c_uint32), ("max_batch_tokens", C.c_uint32), ("kv_pool_tokens", C.c_uint64), ("exact_attention_max_pos", C.c_uint32),
         ("token_embd", MatrixDesc), ("output_norm", C.c_void_p), ("output", MatrixDesc),
         ("layers", C.POINTER(LayerDesc)), ("tp_rank", C.c_uint32), ("tp_size", C.c_uint32), ("tp_unique_id", C.c_void_p)]
 
@@ -67,7 +67,7 @@ SIGNATURES = {
     "ob_rope": (_i32, [_vp, _vp, _u32, _u32, _u32, _u32, _f32]),
     "ob_swiglu": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "ob_quantize_act": (_i32, [_vp, _vp, _u32, _i32, _vp, _vp, _vp]),
-    "ob_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _f32, _vp]),
+    "ob_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _f32, _i32, _vp]),
     "ob_argmax": (_i32, [_vp, _vp, _u32, _vp, _u32, _u32, _f32, _vp]),
     "ob_model_create": (_i32, [_vp, C.POINTER(ModelDesc), _PP]),
     "ob_model_destroy": (None, [_vp]),

@@ -9,6 +9,7 @@
 // One CTA per token row.  A thread owns 8 consecutive elements; a warp owns one 256-block.
 #include "common.cuh"
 #include "kernels.h"
+#include "seqsum.cuh"
 
 namespace ob {
 
@@ -17,10 +18,15 @@ namespace {
 constexpr int QT = 512;  // threads per CTA
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
-    // silu(x) = x / (1 + exp(-x)), then * up   (engine/tensor.rs:825-827, engine/arch/mod.rs:1099-1105)
-    float s = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+    // silu(x) = x / (1 + exp(-x)), then * up   (engine/tensor.rs:825-827, engine/arch/mod.rs:1099-1105).
+    // exp is taken in double and rounded once, the value the CPU oracle uses as well.
+    float s = __fdiv_rn(g, __fadd_rn(1.0f, (float)exp((double)(-g))));
     return __fmul_rn(s, u);
 }
+
+// Shared-memory index with one pad word per 16, so that lanes reading runs of 16 consecutive
+// elements (the sequential-sum scan) fall on different banks.
+__device__ __forceinline__ uint32_t padded(uint32_t i) { return i + (i >> 4); }
 
 template <int SOURCE>
 __global__ void __launch_bounds__(QT) quantize_kernel(QuantArgs a) {
@@ -30,26 +36,22 @@ __global__ void __launch_bounds__(QT) quantize_kernel(QuantArgs a) {
     const int lane = threadIdx.x & 31;
 
     float norm_scale = 1.0f;
+    extern __shared__ float srow[];  // RMSNORM only: the row, padded()
     if (SOURCE == ACT_RMSNORM) {
-        // sum of squares; the CPU sums left to right, this sums in a tree: covered by tolerance.
-        __shared__ float red[QT / 32];
+        // mean of squares with the squares added left to right, as the CPU adds them (tensor.rs:743)
         __shared__ float bcast;
-        float s = 0.0f;
         for (uint32_t i = threadIdx.x * 4; i < dim; i += QT * 4) {
-            float4 v = *reinterpret_cast<const float4 *>(x + i);
-            s += v.x * v.x;
-            s += v.y * v.y;
-            s += v.z * v.z;
-            s += v.w * v.w;
+            const float4 v = *reinterpret_cast<const float4 *>(x + i);
+            srow[padded(i)] = v.x;
+            srow[padded(i + 1)] = v.y;
+            srow[padded(i + 2)] = v.z;
+            srow[padded(i + 3)] = v.w;
         }
-        s = warp_sum(s);
-        if (lane == 0) red[threadIdx.x >> 5] = s;
         __syncthreads();
         if (threadIdx.x < 32) {
-            float t = threadIdx.x < QT / 32 ? red[threadIdx.x] : 0.0f;
-            t = warp_sum(t);
+            const float t = warp_sequential_sum<16>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim);
             if (threadIdx.x == 0) {
-                float mean_sq = __fdiv_rn(t, (float)dim);
+                const float mean_sq = __fdiv_rn(t, (float)dim);
                 bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean_sq, a.eps)));
             }
         }
@@ -135,7 +137,16 @@ void launch_quantize(int source, const QuantArgs &a, cudaStream_t st) {
     if (a.n_rows == 0) return;
     switch (source) {
     case ACT_PLAIN: quantize_kernel<ACT_PLAIN><<<a.n_rows, QT, 0, st>>>(a); break;
-    case ACT_RMSNORM: quantize_kernel<ACT_RMSNORM><<<a.n_rows, QT, 0, st>>>(a); break;
+    case ACT_RMSNORM: {
+        const size_t smem = ((size_t)a.dim + a.dim / 16 + 16) * 4;
+        static bool configured = false;
+        if (!configured) {
+            cudaFuncSetAttribute(quantize_kernel<ACT_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            configured = true;
+        }
+        quantize_kernel<ACT_RMSNORM><<<a.n_rows, QT, smem, st>>>(a);
+        break;
+    }
     default: quantize_kernel<ACT_SWIGLU><<<a.n_rows, QT, 0, st>>>(a); break;
     }
 }

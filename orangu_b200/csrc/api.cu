@@ -504,7 +504,7 @@ int ob_argmax(ob_ctx *ctx, const float *logits, uint32_t n_vocab, const uint32_t
 }
 
 int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos, uint32_t n_head, uint32_t n_head_kv,
-                        uint32_t head_dim, float scale, float *out) {
+                        uint32_t head_dim, float scale, int exact_order, float *out) {
     if (!ctx || !q || !k || !v || !out || n_head == 0 || n_head_kv == 0 || head_dim == 0 || (head_dim & 1) || head_dim > 256)
         return fail(ctx, OB_ERR_INVALID, "attention_decode: bad argument");
     std::lock_guard<std::mutex> g(ctx->mu);
@@ -525,6 +525,8 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
     const uint32_t n_splits = std::max(1u, std::min(16u, n_pages / 4));
     const size_t pool_b = kp.size() * 2, part_o_b = (size_t)n_head * n_splits * head_dim * 4, part_ml_b = (size_t)n_head * n_splits * 8;
     const size_t meta_b = 256 + (size_t)n_pages * 4;
+    if (exact_order && !attn_exact_supported(n_head, n_head_kv, head_dim))
+        return fail(ctx, OB_ERR_UNSUPPORTED, "attention_decode: exact order needs head_dim % 16 == 0 and a group of 1, 2, 3, 4 or 8 heads");
     int rc;
     if ((rc = ensure(ctx, ctx->sx, (size_t)q_dim * 4))) return rc;
     if ((rc = ensure(ctx, ctx->sy, (size_t)q_dim * 4))) return rc;
@@ -559,8 +561,30 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
     a.part_o = static_cast<float *>(ctx->saux2.p);
     a.part_ml = reinterpret_cast<float *>(static_cast<uint8_t *>(ctx->saux2.p) + part_o_b);
     a.max_pos = n_pos;
-    launch_attn_decode(a, ctx->stream);
-    ctx->launches += 2;
+    if (exact_order) {
+        const uint32_t stride = (n_pos + 63) / 64 * 64;
+        if ((rc = ensure(ctx, ctx->sq, (size_t)n_head * stride * 4))) return rc;
+        AttnExactArgs e{};
+        e.q = a.q;
+        e.out = a.out;
+        e.k_pool = a.k_pool;
+        e.v_pool = a.v_pool;
+        e.page_tables = a.page_tables;
+        e.n_pos = a.n_pos;
+        e.scores = static_cast<float *>(ctx->sq.p);
+        e.score_stride = stride;
+        e.n_rows = 1;
+        e.n_head = n_head;
+        e.n_head_kv = n_head_kv;
+        e.head_dim = head_dim;
+        e.scale = scale;
+        e.max_pos = n_pos;
+        launch_attn_exact(e, ctx->stream);
+        ctx->launches += 3;
+    } else {
+        launch_attn_decode(a, ctx->stream);
+        ctx->launches += 2;
+    }
     OB_CUDA(ctx, cudaMemcpyAsync(out, ctx->sy.p, (size_t)q_dim * 4, cudaMemcpyDeviceToHost, ctx->stream));
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     OB_CUDA(ctx, cudaGetLastError());

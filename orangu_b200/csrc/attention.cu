@@ -323,3 +323,152 @@ void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st) {
 }
 
 }  // namespace ob
+
+// ====================================================================================================
+// Exact-order attention: the reference's CPU loop reproduced operation for operation, so that the
+// output equals the CPU's bit for bit (given the same f16 K/V and the same exp).  Three kernels:
+//
+//   scores   score[h][p] = fold8(q_h . k_p) * scale.  The dot keeps eight running sums, element i going
+//            to sum i % 8, folded ((a0+a4)+(a1+a5))+((a2+a6)+(a3+a7)); multiply and add are separate
+//            roundings (engine/tensor.rs:393-430).  Positions are independent: any number of CTAs.
+//   softmax  max; e_p = exp(score_p - max); sum left to right; e_p / sum (engine/tensor.rs:809-821).
+//            The sum is the warp_sequential_sum of seqsum.cuh.  exp is evaluated in double and rounded
+//            once to float, which is what the oracle does too; the reference calls its platform's expf.
+//   output   out_h[d] = (..((0 + w_0*v_0[d]) + w_1*v_1[d]) + ..), ascending p, multiply and add rounded
+//            separately (engine/attention.rs:515-546, engine/tensor.rs:679-681).  One thread per (h, d)
+//            carries the chain; the cost is 4 cycles x positions of latency, which is why windows longer
+//            than a configurable bound take the flash-decode kernels above instead.
+// ====================================================================================================
+
+#include "seqsum.cuh"
+
+namespace ob {
+
+namespace {
+
+constexpr int SC_THREADS = 128;
+constexpr int SC_TILE = 64;  // positions per CTA
+
+template <int G>
+__global__ void __launch_bounds__(SC_THREADS) attn_scores_kernel(AttnExactArgs a) {
+    extern __shared__ float sq[];  // [G][hd]
+    const uint32_t tile = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const uint32_t n_pos = a.n_pos[row];
+    const uint32_t p0 = tile * SC_TILE;
+    if (p0 >= n_pos) return;
+    const uint32_t hd = a.head_dim, head0 = kvh * G;
+    for (uint32_t i = threadIdx.x; i < G * hd; i += SC_THREADS) sq[i] = a.q[(uint64_t)row * a.n_head * hd + (uint64_t)head0 * hd + i];
+    __syncthreads();
+    const int32_t *table = a.page_tables[row];
+    const uint32_t j = threadIdx.x & 7, grp = threadIdx.x >> 3;  // 16 groups of 8 lanes
+    const uint32_t chunks = hd / 8;
+#pragma unroll
+    for (int it = 0; it < SC_TILE / 16; ++it) {
+        const uint32_t p = p0 + grp + 16 * it;
+        const bool live = p < n_pos;  // uniform within a group of 8
+        float acc[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[g] = 0.0f;
+        if (live) {
+            const __half *kp = a.k_pool + (((uint64_t)table[p / KV_PAGE] * a.n_head_kv + kvh) * KV_PAGE + p % KV_PAGE) * hd;
+            for (uint32_t c = 0; c < chunks; ++c) {
+                const float kf = __half2float(kp[8 * c + j]);
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(sq[g * hd + 8 * c + j], kf));
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            acc[g] = __fadd_rn(acc[g], __shfl_xor_sync(0xffffffffu, acc[g], 4));
+            acc[g] = __fadd_rn(acc[g], __shfl_xor_sync(0xffffffffu, acc[g], 1));
+            acc[g] = __fadd_rn(acc[g], __shfl_xor_sync(0xffffffffu, acc[g], 2));
+        }
+        if (live && j == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) a.scores[((uint64_t)row * a.n_head + head0 + g) * a.score_stride + p] = __fmul_rn(acc[g], a.scale);
+        }
+    }
+}
+
+// exp(x) correctly rounded to float through double precision
+__device__ __forceinline__ float exp_via_double(float x) { return (float)exp((double)x); }
+
+// grid (n_head, n_rows)
+__global__ void __launch_bounds__(128) attn_softmax_kernel(AttnExactArgs a) {
+    const uint32_t head = blockIdx.x, row = blockIdx.y;
+    const uint32_t n_pos = a.n_pos[row];
+    float *s = a.scores + ((uint64_t)row * a.n_head + head) * a.score_stride;
+    __shared__ float red[4];
+    __shared__ float bcast;
+    float mx = -INFINITY;
+    for (uint32_t p = threadIdx.x; p < n_pos; p += blockDim.x) mx = fmaxf(mx, s[p]);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    for (uint32_t p = threadIdx.x; p < n_pos; p += blockDim.x) s[p] = exp_via_double(__fsub_rn(s[p], mx));
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const float sum = warp_sequential_sum<16>([&](uint32_t i) { return s[i]; }, n_pos);
+        if (threadIdx.x == 0) bcast = sum;
+    }
+    __syncthreads();
+    const float sum = bcast;
+    if (sum > 0.0f)
+        for (uint32_t p = threadIdx.x; p < n_pos; p += blockDim.x) s[p] = __fdiv_rn(s[p], sum);
+}
+
+// grid (hd / 16, n_head_kv, n_rows), G * 16 threads: thread (g, d) carries out[h][d]
+template <int G>
+__global__ void __launch_bounds__(G * 16) attn_output_kernel(AttnExactArgs a) {
+    const uint32_t slice = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const uint32_t n_pos = a.n_pos[row], hd = a.head_dim;
+    const uint32_t g = threadIdx.x >> 4, d = slice * 16 + (threadIdx.x & 15);
+    const uint32_t head = kvh * G + g;
+    const float *w = a.scores + ((uint64_t)row * a.n_head + head) * a.score_stride;
+    const int32_t *table = a.page_tables[row];
+    float o = 0.0f;
+    for (uint32_t pg = 0; pg * KV_PAGE < n_pos; ++pg) {
+        const __half *vp = a.v_pool + ((uint64_t)table[pg] * a.n_head_kv + kvh) * KV_PAGE * hd + d;
+        const uint32_t cnt = min((uint32_t)KV_PAGE, n_pos - pg * KV_PAGE);
+        float wv[KV_PAGE], vv[KV_PAGE];
+#pragma unroll
+        for (int t = 0; t < KV_PAGE; ++t) {  // the loads do not depend on the chain: issue them all first
+            wv[t] = t < (int)cnt ? w[pg * KV_PAGE + t] : 0.0f;
+            vv[t] = t < (int)cnt ? __half2float(vp[(uint32_t)t * hd]) : 0.0f;
+        }
+#pragma unroll
+        for (int t = 0; t < KV_PAGE; ++t)
+            if (t < (int)cnt) o = __fadd_rn(o, __fmul_rn(wv[t], vv[t]));
+    }
+    a.out[(uint64_t)row * a.n_head * hd + (uint64_t)head * hd + d] = o;
+}
+
+template <int G>
+void launch_exact_g(const AttnExactArgs &a, cudaStream_t st) {
+    const uint32_t tiles = (a.max_pos + SC_TILE - 1) / SC_TILE;
+    attn_scores_kernel<G><<<dim3(tiles, a.n_head_kv, a.n_rows), SC_THREADS, (size_t)G * a.head_dim * 4, st>>>(a);
+    attn_softmax_kernel<<<dim3(a.n_head, a.n_rows), 128, 0, st>>>(a);
+    attn_output_kernel<G><<<dim3(a.head_dim / 16, a.n_head_kv, a.n_rows), G * 16, 0, st>>>(a);
+}
+
+}  // namespace
+
+bool attn_exact_supported(uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim) {
+    if (n_head % n_head_kv || head_dim % 16) return false;
+    const uint32_t g = n_head / n_head_kv;
+    return g == 1 || g == 2 || g == 3 || g == 4 || g == 8;
+}
+
+void launch_attn_exact(const AttnExactArgs &a, cudaStream_t st) {
+    if (a.n_rows == 0) return;
+    switch (a.n_head / a.n_head_kv) {
+    case 1: launch_exact_g<1>(a, st); break;
+    case 2: launch_exact_g<2>(a, st); break;
+    case 3: launch_exact_g<3>(a, st); break;
+    case 4: launch_exact_g<4>(a, st); break;
+    default: launch_exact_g<8>(a, st); break;
+    }
+}
+
+}  // namespace ob

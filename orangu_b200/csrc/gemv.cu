@@ -209,7 +209,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(GemvArgs a, uint3
                         }
                     }
                 }
-                const uint32_t pbase = (b >> 1) * 512 + chunk_off;
+                // lanes past the end of the row read block 0's slot (any valid address): their results are never used
+                const uint32_t pbase = (live ? (b >> 1) * 512 : 0u) + chunk_off;
 
                 if (type == TYPE_Q4_K) {
                     // 6-bit scale / min of sub-blocks 2*j4 and 2*j4+1 as byte pairs

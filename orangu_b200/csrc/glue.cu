@@ -7,37 +7,37 @@
 //   argmax    sampling.rs:336-359   f32::total_cmp order, the last of equal maxima wins
 #include "common.cuh"
 #include "kernels.h"
+#include "seqsum.cuh"
 
 namespace ob {
 
 namespace {
 
+__device__ __forceinline__ uint32_t padded(uint32_t i) { return i + (i >> 4); }
+
+// The squares are added left to right, as the CPU adds them; see seqsum.cuh.
 __global__ void __launch_bounds__(512) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w, uint32_t dim, float eps,
                                                       float *__restrict__ out) {
+    extern __shared__ float srow[];
     const float *row = x + (uint64_t)blockIdx.x * dim;
     float *orow = out + (uint64_t)blockIdx.x * dim;
-    __shared__ float red[16];
     __shared__ float bcast;
-    float s = 0.0f;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) s += row[i] * row[i];
-    s = warp_sum(s);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) srow[padded(i)] = row[i];
     __syncthreads();
     if (threadIdx.x < 32) {
-        float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
-        t = warp_sum(t);
+        const float t = warp_sequential_sum<16>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim);
         if (threadIdx.x == 0) bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
     }
     __syncthreads();
     const float scale = bcast;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = __fmul_rn(__fmul_rn(row[i], scale), w[i]);
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = __fmul_rn(__fmul_rn(srow[padded(i)], scale), w[i]);
 }
 
 __global__ void swiglu_kernel(const float *__restrict__ g, const float *__restrict__ u, uint64_t n, float *__restrict__ out) {
     uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float x = g[i];
-    float s = __fdiv_rn(x, __fadd_rn(1.0f, expf(-x)));
+    float s = __fdiv_rn(x, __fadd_rn(1.0f, (float)exp((double)(-x))));  // exp in double, rounded once (as the oracle)
     out[i] = __fmul_rn(s, u[i]);
 }
 
@@ -150,7 +150,13 @@ __global__ void repeat_penalty_kernel(float *logits, uint32_t n_vocab, const uin
 }  // namespace
 
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st) {
-    if (n_tokens) rmsnorm_kernel<<<n_tokens, 512, 0, st>>>(x, w, dim, eps, out);
+    if (!n_tokens) return;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        configured = true;
+    }
+    rmsnorm_kernel<<<n_tokens, 512, ((size_t)dim + dim / 16 + 16) * 4, st>>>(x, w, dim, eps, out);
 }
 void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st) {
     if (n) swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(gate, up, n, out);

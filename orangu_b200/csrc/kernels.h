@@ -97,4 +97,21 @@ struct AttnDecodeArgs {
     uint32_t max_pos;          // upper bound of n_pos (sizes nothing on the device; bounds the split length)
 };
 void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st);
+
+// Exact-order attention (three kernels: scores, softmax, output); see attention.cu.
+struct AttnExactArgs {
+    const float *q;            // [n_rows][n_head*head_dim]
+    float *out;                // [n_rows][n_head*head_dim]
+    const __half *k_pool;
+    const __half *v_pool;
+    const int32_t *const *page_tables; // [n_rows]
+    const uint32_t *n_pos;     // [n_rows], device
+    float *scores;             // [n_rows][n_head][score_stride] scratch: scores, then probabilities
+    uint32_t score_stride;
+    uint32_t n_rows, n_head, n_head_kv, head_dim;
+    float scale;
+    uint32_t max_pos;          // upper bound of n_pos over the rows (sizes the score grid)
+};
+void launch_attn_exact(const AttnExactArgs &a, cudaStream_t st);
+bool attn_exact_supported(uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim);
 }  // namespace ob

@@ -77,6 +77,8 @@ struct ob_model {
           *logits = nullptr;
     ActPair act_embd, act_attn, act_ff;
     float *part_o = nullptr, *part_ml = nullptr;
+    float *scores = nullptr;          // exact-order attention scratch [T][n_head_l][score_stride]
+    uint32_t score_stride = 0, exact_attn_max_pos = 0;
     uint32_t max_splits = 1;
     uint8_t *d_meta = nullptr, *h_meta = nullptr;
     uint32_t *d_out_tokens = nullptr, *h_out_tokens = nullptr;
@@ -209,7 +211,9 @@ uint32_t pick_splits(const ob_model *m, uint32_t n_rows) {
 // Enqueue one forward step over T rows whose metadata is already in d_meta.
 //   gemm_order: the rows are consecutive tokens of one sequence (prefill chunk)
 //   logit_row0 / n_logit_rows: which rows get the output projection
-void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0, uint32_t n_logit_rows, bool want_argmax, cudaStream_t st) {
+//   exact_attn: take the exact-order attention kernels (every row's window <= pos_bound <= exact_attn_max_pos)
+void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0, uint32_t n_logit_rows, bool want_argmax, bool exact_attn,
+                  uint32_t pos_bound, cudaStream_t st) {
     const ob_model_desc &c = m->cfg;
     const MetaLayout ml(m->T);
     const uint32_t *d_tokens = reinterpret_cast<uint32_t *>(m->d_meta + ml.off_tokens);
@@ -245,24 +249,44 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         launch_rope_kv(rk, st);
         m->ctx->launches++;
 
-        AttnDecodeArgs at{};
-        at.q = m->q;
-        at.out = m->attn;
-        at.k_pool = rk.k_pool;
-        at.v_pool = rk.v_pool;
-        at.page_tables = d_tables;
-        at.n_pos = d_npos;
-        at.n_seq = T;
-        at.n_head = m->n_head_l;
-        at.n_head_kv = m->n_head_kv_l;
-        at.head_dim = hd;
-        at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
-        at.n_splits = pick_splits(m, T);
-        at.part_o = m->part_o;
-        at.part_ml = m->part_ml;
-        at.max_pos = c.max_seq_len;
-        launch_attn_decode(at, st);
-        m->ctx->launches += 2;
+        if (exact_attn) {
+            AttnExactArgs at{};
+            at.q = m->q;
+            at.out = m->attn;
+            at.k_pool = rk.k_pool;
+            at.v_pool = rk.v_pool;
+            at.page_tables = d_tables;
+            at.n_pos = d_npos;
+            at.scores = m->scores;
+            at.score_stride = m->score_stride;
+            at.n_rows = T;
+            at.n_head = m->n_head_l;
+            at.n_head_kv = m->n_head_kv_l;
+            at.head_dim = hd;
+            at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
+            at.max_pos = pos_bound;
+            launch_attn_exact(at, st);
+            m->ctx->launches += 3;
+        } else {
+            AttnDecodeArgs at{};
+            at.q = m->q;
+            at.out = m->attn;
+            at.k_pool = rk.k_pool;
+            at.v_pool = rk.v_pool;
+            at.page_tables = d_tables;
+            at.n_pos = d_npos;
+            at.n_seq = T;
+            at.n_head = m->n_head_l;
+            at.n_head_kv = m->n_head_kv_l;
+            at.head_dim = hd;
+            at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
+            at.n_splits = pick_splits(m, T);
+            at.part_o = m->part_o;
+            at.part_ml = m->part_ml;
+            at.max_pos = c.max_seq_len;
+            launch_attn_decode(at, st);
+            m->ctx->launches += 2;
+        }
 
         quantize_into(m, ACT_PLAIN, m->attn, nullptr, T, q_dim, m->act_attn, needs_k({L.wo}), needs_flat({L.wo}), st);
         if (!tp) {
@@ -472,6 +496,9 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         if ((rc = dev_alloc(m, &m->part_o, row_splits * m->n_head_l * hd))) return bail(rc);
         if ((rc = dev_alloc(m, &m->part_ml, row_splits * m->n_head_l * 2))) return bail(rc);
     }
+    m->exact_attn_max_pos = attn_exact_supported(m->n_head_l, m->n_head_kv_l, hd) ? std::min(m->cfg.max_seq_len, c.exact_attention_max_pos ? c.exact_attention_max_pos : 1024u) : 0u;
+    m->score_stride = (m->exact_attn_max_pos + 63) / 64 * 64;
+    if (m->score_stride && (rc = dev_alloc(m, &m->scores, (size_t)T * m->n_head_l * m->score_stride))) return bail(rc);
     const MetaLayout ml(T);
     if ((rc = dev_alloc(m, &m->d_meta, ml.bytes))) return bail(rc);
     if ((rc = dev_alloc(m, &m->d_out_tokens, T))) return bail(rc);
@@ -590,17 +617,20 @@ int run_rows(ob_model *m, const std::vector<ob_kv *> &row_kv, const uint32_t *to
     uint32_t *h_positions = reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions);
     uint32_t *h_npos = reinterpret_cast<uint32_t *>(m->h_meta + ml.off_npos);
     const int32_t **h_tables = reinterpret_cast<const int32_t **>(m->h_meta + ml.off_tables);
+    uint32_t pos_bound = 0;
     for (uint32_t t = 0; t < T; ++t) {
         h_tokens[t] = tokens[t];
         h_positions[t] = positions[t];
         h_npos[t] = positions[t] + 1;
         h_tables[t] = row_kv[t]->d_table;
+        pos_bound = std::max(pos_bound, positions[t] + 1);
     }
+    const bool exact_attn = pos_bound <= m->exact_attn_max_pos;
     cudaStream_t st = ctx->stream;
     OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
     OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st));
     const bool penalise = greedy && greedy->repeat_penalty != 1.0f && greedy->recent && greedy->n_recent;
-    enqueue_step(m, T, gemm_order, logit_row0, n_logit_rows, out_token != nullptr && !penalise, st);
+    enqueue_step(m, T, gemm_order, logit_row0, n_logit_rows, out_token != nullptr && !penalise, exact_attn, pos_bound, st);
     if (out_token && penalise) {
         // repeat penalty, then argmax (sampling.rs:345-359); the history comes from the caller per call
         for (uint32_t r = 0; r < n_logit_rows; ++r) {
@@ -721,9 +751,12 @@ namespace {
 
 // kind 0: H2D metadata + step + D2H token (one host round trip per step)
 // kind 1: step + advance (device-resident loop)
-int get_graph(ob_model *m, uint32_t n_seq, int kind, cudaGraphExec_t *out) {
+// exact: every window stays within exact_attn_max_pos for as long as the graph is replayed
+int get_graph(ob_model *m, uint32_t n_seq, int kind, bool exact, cudaGraphExec_t *out, uint64_t *key_out) {
     ob_ctx *ctx = m->ctx;
-    const uint64_t key = ((uint64_t)kind << 32) | n_seq;
+    const uint64_t key = ((uint64_t)kind << 32) | ((uint64_t)(exact ? 1 : 0) << 33) | n_seq;
+    if (key_out) *key_out = key;
+    const uint32_t pos_bound = exact ? m->exact_attn_max_pos : m->cfg.max_seq_len;
     auto it = m->graphs.find(key);
     if (it != m->graphs.end()) {
         *out = it->second;
@@ -735,7 +768,7 @@ int get_graph(ob_model *m, uint32_t n_seq, int kind, cudaGraphExec_t *out) {
     // function attributes outside capture and counts what a step launches.  It rewrites the KV slot of
     // the current position with the values the replay will write again.
     const uint64_t launches_before = ctx->launches;
-    enqueue_step(m, n_seq, false, 0, n_seq, true, st);
+    enqueue_step(m, n_seq, false, 0, n_seq, true, exact, pos_bound, st);
     OB_CUDA(ctx, cudaStreamSynchronize(st));
     OB_CUDA(ctx, cudaGetLastError());
     m->graph_launches[key] = ctx->launches - launches_before + (kind == 1 ? 1 : 0);
@@ -743,7 +776,7 @@ int get_graph(ob_model *m, uint32_t n_seq, int kind, cudaGraphExec_t *out) {
     cudaGraph_t graph = nullptr;
     OB_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     if (kind == 0) cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st);
-    enqueue_step(m, n_seq, false, 0, n_seq, true, st);
+    enqueue_step(m, n_seq, false, 0, n_seq, true, exact, pos_bound, st);
     if (kind == 0) {
         cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, st);
     } else {
@@ -782,15 +815,17 @@ int ob_decode_greedy(ob_model *m, ob_kv *kv, uint32_t token, uint32_t *out_token
     reinterpret_cast<uint32_t *>(m->h_meta + ml.off_npos)[0] = kv->len + 1;
     reinterpret_cast<const int32_t **>(m->h_meta + ml.off_tables)[0] = kv->d_table;
     cudaGraphExec_t exec;
-    if (m->graphs.find(1) == m->graphs.end()) OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, ctx->stream));
-    int rc = get_graph(m, 1, 0, &exec);
+    uint64_t key = 0;
+    const bool exact = kv->len + 1 <= m->exact_attn_max_pos;
+    OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, ctx->stream));  // the first build runs a step eagerly
+    int rc = get_graph(m, 1, 0, exact, &exec, &key);
     if (rc) return rc;
     OB_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     OB_CUDA(ctx, cudaGraphLaunch(exec, ctx->stream));
     OB_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     cudaEventElapsedTime(&ctx->last_ms, ctx->ev0, ctx->ev1);
-    ctx->launches += m->graph_launches[1];
+    ctx->launches += m->graph_launches[key];
     kv->len += 1;
     *out_token = m->h_out_tokens[0];
     return OB_OK;
@@ -816,7 +851,7 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
         m->history_cap = n_steps * n_seq;
         // the graph holds the old pointer: drop loop graphs
         for (auto it = m->graphs.begin(); it != m->graphs.end();) {
-            if ((it->first >> 32) == 1) {
+            if (((it->first >> 32) & 1) == 1) {
                 cudaGraphExecDestroy(it->second);
                 it = m->graphs.erase(it);
             } else {
@@ -824,7 +859,9 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
             }
         }
     }
-    const uint64_t key = ((uint64_t)1 << 32) | n_seq;
+    uint64_t key = 0;
+    bool exact = true;
+    for (uint32_t s = 0; s < n_seq; ++s) exact = exact && (uint64_t)kvs[s]->len + n_steps <= m->exact_attn_max_pos;
     const MetaLayout ml(m->T);
     for (uint32_t s = 0; s < n_seq; ++s) {
         reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens)[s] = first_tokens[s];
@@ -834,7 +871,7 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
     }
     OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, ctx->stream));
     cudaGraphExec_t exec;
-    int rc = get_graph(m, n_seq, 1, &exec);
+    int rc = get_graph(m, n_seq, 1, exact, &exec, &key);
     if (rc) return rc;
     cudaStream_t st = ctx->stream;
     OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st));

@@ -58,7 +58,7 @@ class LlamaModel:
     ``{"data": np.ndarray, "type": ggml_type, "in_dim": .., "out_dim": ..}``; norm vectors are f32."""
 
     def __init__(self, backend: CudaBackend, cfg: dict, tensors: dict, max_seq_len: int = 4096, max_batch_tokens: int = 512,
-                 kv_pool_tokens: int = 0, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: bytes | None = None):
+                 kv_pool_tokens: int = 0, exact_attention_max_pos: int = 0, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: bytes | None = None):
         self.backend = backend
         self._lib = backend._lib
         self.cfg = dict(cfg)
@@ -78,6 +78,7 @@ class LlamaModel:
         d.max_seq_len = max_seq_len
         d.max_batch_tokens = max_batch_tokens
         d.kv_pool_tokens = kv_pool_tokens
+        d.exact_attention_max_pos = exact_attention_max_pos
         d.token_embd = _matrix(tensors["token_embd.weight"])
         d.output_norm = tensors["output_norm.weight"]["data"].ctypes.data
         if "output.weight" in tensors:

@@ -10,14 +10,45 @@ from refdata import xorshift32_kv
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("n_tokens,dim", [(1, 256), (3, 2048), (5, 4096), (2, 8192)])
-def test_rmsnorm(backend, n_tokens, dim):
+@pytest.mark.parametrize("n_tokens,dim", [(1, 256), (3, 2048), (5, 4096), (2, 8192), (1, 32), (2, 2080)])
+def test_rmsnorm_is_bit_exact(backend, n_tokens, dim):
+    """The squares are summed left to right on the CPU; the device reproduces that sum exactly."""
     x = synth.normal(n_tokens * dim, 1, 2.0).reshape(n_tokens, dim)
     w = 1.0 + 0.1 * synth.normal(dim, 2)
+    assert_bit_equal(backend.rmsnorm(x, w, 1e-5), O.rmsnorm(x, w, 1e-5), f"rmsnorm [{n_tokens}x{dim}]")
+
+
+def adversarial_rows(dim):
+    rng = np.random.default_rng(dim)
+    rows = []
+    rows.append(np.zeros(dim, np.float32))
+    r = np.zeros(dim, np.float32); r[dim // 2] = 3.0; rows.append(r)                       # one term, late
+    rows.append(np.full(dim, 1.0, np.float32))                                              # exact integers, many binade crossings
+    rows.append(np.full(dim, np.float32(2.0 ** -12), np.float32))                           # squares of 2^-24: ties against a sum near 1
+    r = np.full(dim, np.float32(2.0 ** -12), np.float32); r[0] = 1.0; rows.append(r)        # every later term is exactly half an ulp... then less
+    r = np.full(dim, np.float32(2.0 ** -11.5), np.float32); r[0] = 1.0; rows.append(r)
+    rows.append((rng.standard_normal(dim) * np.exp(rng.standard_normal(dim) * 6)).astype(np.float32))  # 30 binades of range
+    r = rng.standard_normal(dim).astype(np.float32); r[::7] = 0; r[5] = 1e18; rows.append(r)  # a huge early term
+    r = rng.standard_normal(dim).astype(np.float32) * 1e-22; rows.append(r)                 # subnormal squares
+    r = rng.standard_normal(dim).astype(np.float32); r[dim - 3] = 1e19; rows.append(r)       # overflow of the square to inf
+    r = rng.standard_normal(dim).astype(np.float32); r[3] = np.nan; rows.append(r)
+    r = np.sqrt(np.arange(dim, dtype=np.float32)); rows.append(r)                            # 0,1,2,3,.. as squares (rounded)
+    for k in range(6):                                                                       # half-integers relative to the running ulp
+        base = np.float32(2.0 ** (k - 3))
+        r = np.full(dim, base, np.float32); r[1::2] *= np.float32(1.5); rows.append(r)
+    return np.stack(rows)
+
+
+@pytest.mark.parametrize("dim", [64, 512, 4096, 8192])
+def test_rmsnorm_sequential_sum_adversarial(backend, dim):
+    x = adversarial_rows(dim)
+    w = np.ones(dim, np.float32)
+    with np.errstate(all="ignore"):
+        want = O.rmsnorm(x, w, 1e-5)
     got = backend.rmsnorm(x, w, 1e-5)
-    want = O.rmsnorm(x, w, 1e-5)
-    # the sum of squares is a tree on the device and left-to-right on the CPU: a few ulp
-    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-6)) < 1e-5
+    nan = np.isnan(want)
+    assert (np.isnan(got) == nan).all()
+    assert (bits(got)[~nan] == bits(want)[~nan]).all()
 
 
 @pytest.mark.parametrize("pos", [0, 1, 17, 1000, 8191])
@@ -29,13 +60,12 @@ def test_rope_is_bit_exact(backend, pos, n_head, head_dim, rope_dim):
     assert_bit_equal(got, want, f"rope pos {pos}")
 
 
-def test_swiglu(backend):
+def test_swiglu_is_bit_exact(backend):
     g = synth.normal(14336, 3, 3.0)
     u = synth.normal(14336, 4, 3.0)
-    g[:4] = [0.0, -0.0, 80.0, -80.0]
+    g[:6] = [0.0, -0.0, 80.0, -80.0, 104.0, -104.0]
     got = backend.swiglu(g, u)
-    want = O.swiglu(g, u)
-    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 1e-6)) < 1e-5
+    assert_bit_equal(got, O.swiglu(g, u), "silu(g) * u")
     assert got[0] == 0.0 and np.isfinite(got).all()
 
 
@@ -43,27 +73,46 @@ def f16_round(a):
     return a.astype(np.float16).astype(np.float32)
 
 
+def attention_case(n_head, n_head_kv, head_dim, n_pos):
+    seed = 0x12345678 ^ (n_head * 31 + head_dim)
+    n = n_pos * n_head_kv * head_dim
+    if n <= 40000:
+        k, v = xorshift32_kv(n_pos, n_head_kv * head_dim, seed)
+    else:
+        k, v = synth.normal(n, seed).reshape(n_pos, -1), synth.normal(n, seed + 1).reshape(n_pos, -1)
+    q = (((np.arange(n_head * head_dim) % 17).astype(np.float32) - 8.0) / 8.0).astype(np.float32)
+    # the cache holds f16 (kv_cache.rs:26-32): the oracle attends over the rounded values
+    want = O.attention(q, f16_round(k), f16_round(v), n_head, n_head_kv, head_dim, 0.125, 1, n_pos - 1)[0]
+    return q, k, v, want
+
+
 @pytest.mark.parametrize("n_head,n_head_kv", [(8, 1), (8, 2), (4, 4), (6, 3), (1, 1), (32, 8)])
 @pytest.mark.parametrize("head_dim", [16, 64, 128])
 @pytest.mark.parametrize("n_pos", [1, 8, 40, 331])
-def test_decode_attention_reference_shapes(backend, n_head, n_head_kv, head_dim, n_pos):
-    seed = 0x12345678 ^ (n_head * 31 + head_dim)
-    k, v = xorshift32_kv(n_pos, n_head_kv * head_dim, seed) if n_pos * n_head_kv * head_dim <= 40000 else (
-        synth.normal(n_pos * n_head_kv * head_dim, 1).reshape(n_pos, -1), synth.normal(n_pos * n_head_kv * head_dim, 2).reshape(n_pos, -1))
-    q = (((np.arange(n_head * head_dim) % 17).astype(np.float32) - 8.0) / 8.0).astype(np.float32)
-    got = backend.attention_decode(q, k, v, n_head, n_head_kv, head_dim, 0.125)
-    # the cache holds f16 (kv_cache.rs:26-32): the oracle attends over the rounded values
-    want = O.attention(q, f16_round(k), f16_round(v), n_head, n_head_kv, head_dim, 0.125, 1, n_pos - 1)[0]
+def test_exact_order_attention_is_bit_exact(backend, n_head, n_head_kv, head_dim, n_pos):
+    q, k, v, want = attention_case(n_head, n_head_kv, head_dim, n_pos)
+    got = backend.attention_decode(q, k, v, n_head, n_head_kv, head_dim, 0.125, exact_order=True)
+    assert_bit_equal(got, want, "exact-order attention")
+
+
+@pytest.mark.parametrize("n_head,n_head_kv", [(8, 1), (8, 2), (4, 4), (6, 3), (1, 1), (32, 8)])
+@pytest.mark.parametrize("head_dim", [16, 64, 128])
+@pytest.mark.parametrize("n_pos", [1, 8, 40, 331])
+def test_flash_decode_attention_within_rounding(backend, n_head, n_head_kv, head_dim, n_pos):
+    q, k, v, want = attention_case(n_head, n_head_kv, head_dim, n_pos)
+    got = backend.attention_decode(q, k, v, n_head, n_head_kv, head_dim, 0.125, exact_order=False)
     assert np.abs(got - want).max() < 2e-5
 
 
-def test_decode_attention_long_context_8b_shape(backend):
+def test_attention_long_context_8b_shape(backend):
     n_pos, n_head, n_kv, hd = 4096 + 37, 32, 8, 128
     k = synth.normal(n_pos * n_kv * hd, 5).reshape(n_pos, -1)
     v = synth.normal(n_pos * n_kv * hd, 6).reshape(n_pos, -1)
     q = synth.normal(n_head * hd, 7)
-    got = backend.attention_decode(q, k, v, n_head, n_kv, hd, 1.0 / np.sqrt(hd))
-    want = O.attention(q, f16_round(k), f16_round(v), n_head, n_kv, hd, 1.0 / np.sqrt(hd), 1, n_pos - 1)[0]
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    want = O.attention(q, f16_round(k), f16_round(v), n_head, n_kv, hd, scale, 1, n_pos - 1)[0]
+    assert_bit_equal(backend.attention_decode(q, k, v, n_head, n_kv, hd, scale, exact_order=True), want, "exact order, 4133 positions")
+    got = backend.attention_decode(q, k, v, n_head, n_kv, hd, scale, exact_order=False)
     assert np.abs(got - want).max() < 2e-5
 
 

@@ -1,4 +1,11 @@
-"""Full-graph parity with the CPU oracle: logits within 2e-2 max-abs and identical greedy tokens."""
+"""Full-graph parity with the CPU oracle.
+
+The bar is logits within 2e-2 max-abs and identical greedy tokens.  On random-initialised weights that
+bar can only be met by matching bit for bit: every product quantizes its input to int8, so a last-bit
+difference in an activation now and then flips a code, and a few layers later the two computations
+differ by the whole int8 quantisation noise (several percent of a logit).  The graph is therefore
+built to be bit-identical to the oracle (exact-order sums and attention), and these tests assert that;
+the flash-decode attention used beyond `exact_attention_max_pos` is checked to its own tolerance."""
 import numpy as np
 import pytest
 
@@ -25,12 +32,13 @@ def prompt(cfg, n, seed):
 @pytest.mark.parametrize("name,types", [("tiny", None), ("small", None), ("tiny", {"attn_q": 8, "ffn_down": 8, "output": 8}),
                                          ("small", {"attn_k": 14, "ffn_gate": 14, "token_embd": 14})])
 def test_prefill_then_greedy_decode_matches_the_oracle(backend, name, types):
-    cfg, tensors, model, ref = build(backend, name, seed=3, types=types, max_seq_len=256, max_batch_tokens=32)
+    cfg, tensors, model, ref = build(backend, name, seed=3, types=types, max_seq_len=256, max_batch_tokens=32, kv_pool_tokens=512)
     toks = prompt(cfg, 45, 1)
     kv, rkv = model.new_kv_cache(128), ref.new_kv(128, f16=True)
     logits = model.forward(kv, toks, 0)  # 45 tokens in chunks of 32 + 13
     want, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
     assert np.abs(logits - want).max() < LOGIT_TOL
+    assert_bit_equal(logits, want, "prefill logits")
     assert len(kv) == 45
     # the cache holds what the oracle's f16 cache holds
     k, v = kv.read(cfg["n_layer"] - 1, 0, 45)
@@ -41,6 +49,7 @@ def test_prefill_then_greedy_decode_matches_the_oracle(backend, name, types):
         got_logits = model.forward(kv, [nxt], 45 + step)
         want_logits = ref.forward(rkv, [rnxt], 45 + step)
         assert np.abs(got_logits - want_logits).max() < LOGIT_TOL, f"step {step}"
+        assert_bit_equal(got_logits, want_logits, f"decode step {step}")
         nxt, rnxt = backend.argmax(got_logits), O.argmax(want_logits)
         assert nxt == rnxt, f"greedy token diverged at step {step}"
 
@@ -51,13 +60,14 @@ def test_hidden_state_and_kv_contents(backend):
     kv, rkv = model.new_kv_cache(32), ref.new_kv(32, f16=True)
     model.forward(kv, toks, 0)
     _, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
-    got = model.last_hidden(9)
-    assert np.abs(got - hidden).max() < 2e-3 * max(1.0, np.abs(hidden).max())
+    assert_bit_equal(model.last_hidden(9), hidden, "residual stream after the last layer")
+    k, v = kv.read(1, 0, 9)
+    assert np.isfinite(k).all() and (k.astype(np.float16).astype(np.float32) == k).all()
 
 
 def test_sampling_paths_agree(backend):
     """forward_maybe_sampling, the captured decode graph and the device loop produce the same tokens."""
-    cfg, tensors, model, ref = build(backend, "small", seed=7, max_seq_len=128, max_batch_tokens=16)
+    cfg, tensors, model, ref = build(backend, "small", seed=7, max_seq_len=128, max_batch_tokens=16, kv_pool_tokens=512)
     toks = prompt(cfg, 12, 3)
     caches = [model.new_kv_cache(96) for _ in range(3)]
     first = [model.forward_maybe_sampling(c, toks, 0) for c in caches]
@@ -87,7 +97,7 @@ def test_sampling_paths_agree(backend):
 def test_batch_decode_rows_are_independent(backend):
     """A sequence decoded in a batch gets the logits it gets alone, bit for bit (the reference's
     decode contract, backend/mod.rs:368-388), and the batch may mix context lengths."""
-    cfg, tensors, model, ref = build(backend, "small", seed=9, max_seq_len=128, max_batch_tokens=8)
+    cfg, tensors, model, ref = build(backend, "small", seed=9, max_seq_len=128, max_batch_tokens=8, kv_pool_tokens=2048)
     prompts = [prompt(cfg, n, 10 + n) for n in (5, 17, 33, 2, 9)]
     solo = [model.new_kv_cache(64) for _ in prompts]
     batch = [model.new_kv_cache(64) for _ in prompts]
@@ -160,13 +170,14 @@ def test_errors_are_statuses(backend):
 
 def test_1b_config_prefill_512_and_256_greedy_steps(backend):
     """1B-shape Q4_K_M decoder: 512-token prefill, then 256 greedy steps at batch 1."""
-    cfg, tensors, model, ref = build(backend, "1b", seed=21, max_seq_len=1024, max_batch_tokens=512)
+    cfg, tensors, model, ref = build(backend, "1b", seed=21, max_seq_len=1024, max_batch_tokens=512, kv_pool_tokens=2048)
     toks = prompt(cfg, 512, 6)
     kv, rkv = model.new_kv_cache(800), ref.new_kv(800, f16=True)
     logits = model.forward(kv, toks, 0)
     want = ref.forward(rkv, toks, 0)
     worst = float(np.abs(logits - want).max())
     assert worst < LOGIT_TOL, worst
+    assert_bit_equal(logits, want, "logits after the 512-token prefill")
     first = int(np.argmax(logits))
     assert first == O.argmax(want)
     got = model.decode_loop([kv], [first], 256)[:, 0].tolist()
@@ -180,3 +191,20 @@ def test_1b_config_prefill_512_and_256_greedy_steps(backend):
     last = model.forward(kv, [got[-1]], 768)
     want_last = ref.forward(rkv, [ref_tokens[-1]], 768)
     assert np.abs(last - want_last).max() < LOGIT_TOL
+    assert_bit_equal(last, want_last, "logits after 256 greedy steps")
+
+
+def test_flash_decode_path_through_the_model(backend):
+    """Windows longer than exact_attention_max_pos take the split flash-decode kernel.  Its output differs
+    from the CPU loop's in the last bits, so this is a tolerance check on one layer's worth of drift:
+    teacher-forced (same tokens on both sides), a single decode step past the bound."""
+    cfg, tensors, model, ref = build(backend, "small", seed=23, n_layer=1, max_seq_len=256, max_batch_tokens=64, kv_pool_tokens=512,
+                                     exact_attention_max_pos=64)
+    toks = prompt(cfg, 100, 8)
+    kv, rkv = model.new_kv_cache(128), ref.new_kv(128, f16=True)
+    logits = model.forward(kv, toks, 0)   # 64 + 36 tokens: the second chunk's windows exceed the bound
+    want = ref.forward(rkv, toks, 0)
+    assert np.abs(logits - want).max() < LOGIT_TOL
+    got = model.forward(kv, [5], 100)
+    want = ref.forward(rkv, [5], 100)
+    assert np.abs(got - want).max() < LOGIT_TOL
