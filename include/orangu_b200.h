@@ -220,6 +220,9 @@ uint32_t ob_kv_len(const ob_kv *kv);
 int ob_kv_truncate(ob_kv *kv, uint32_t new_len);
 /* Test hook: reads positions [pos0, pos0+n) of one layer back as f32 [n][n_head_kv*head_dim]. */
 int ob_kv_read(ob_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n, float *k_out, float *v_out);
+/* KvCache::copy_prefix_from (E/kv_cache.rs:1079-1100): makes dst (empty) hold src's first n positions, by a
+ * device-side copy of the pages.  Both caches belong to the same model. */
+int ob_kv_copy_prefix(ob_kv *dst, const ob_kv *src, uint32_t n);
 
 typedef struct ob_greedy { /* GpuArgmaxSampleInput, B/vulkan.rs:6219-6241 */
     float repeat_penalty;   /* 1.0 = off */
@@ -260,6 +263,13 @@ uint64_t ob_launch_count(const ob_ctx *ctx);
 /* Milliseconds of device time of the most recent ob_forward / ob_decode_* call, from CUDA
  * events on the context's stream. */
 float ob_last_device_ms(const ob_ctx *ctx);
+
+/* Measurement hook (no counterpart in the reference): runs the single-token GEMV of every layer's
+ * matrices of one ggml type back to back `iters` times, with nothing else in between, and reports the
+ * device time between CUDA events on the launching stream.  bytes_per_pass is the quantized weight bytes
+ * one pass over the layers reads (plus the fp32 in/out vectors); launches_per_pass the kernels it issues. */
+int ob_profile_gemv(ob_model *model, uint32_t ggml_type, uint32_t iters, float *ms_total,
+                    uint64_t *bytes_per_pass, uint32_t *launches_per_pass);
 
 /* --------------------------------------------------------- tensor parallel */
 /* No counterpart in the reference: its only multi-GPU mode is a host-bounced layer split

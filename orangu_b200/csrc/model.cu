@@ -600,6 +600,81 @@ int ob_kv_read(ob_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n, float *k_ou
     return OB_OK;
 }
 
+int ob_kv_copy_prefix(ob_kv *dst, const ob_kv *src, uint32_t n) {
+    if (!dst || !src || dst->m != src->m) return OB_ERR_INVALID;
+    ob_model *m = dst->m;
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    if (dst->len != 0) return fail(ctx, OB_ERR_INVALID, "kv_copy_prefix: the destination is not empty");
+    if (n > src->len || n > dst->capacity) return fail(ctx, OB_ERR_CAPACITY, "kv_copy_prefix: n exceeds the source length or the destination capacity");
+    Bind b(ctx);
+    const size_t page_elems = (size_t)m->n_head_kv_l * KV_PAGE * m->cfg.head_dim;
+    const uint32_t n_pages = (n + KV_PAGE - 1) / KV_PAGE;
+    for (uint32_t li = 0; li < m->cfg.n_layer; ++li)
+        for (uint32_t p = 0; p < n_pages; ++p)
+            for (__half *pool : {m->k_pool, m->v_pool}) {
+                __half *base = pool + (size_t)li * m->layer_stride;
+                OB_CUDA(ctx, cudaMemcpyAsync(base + (size_t)dst->pages[p] * page_elems, base + (size_t)src->pages[p] * page_elems, page_elems * 2,
+                                             cudaMemcpyDeviceToDevice, ctx->stream));
+            }
+    OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    dst->len = n;
+    return OB_OK;
+}
+
+int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t iters, float *ms_total, uint64_t *bytes_per_pass, uint32_t *launches_per_pass) {
+    if (!m || !ms_total) return OB_ERR_INVALID;
+    ob_ctx *ctx = m->ctx;
+    std::lock_guard<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    cudaStream_t st = ctx->stream;
+    // any finite activations will do: the kernel's work does not depend on the values
+    OB_CUDA(ctx, cudaMemsetAsync(m->x, 0, (size_t)m->cfg.n_embd * 4, st));
+    OB_CUDA(ctx, cudaMemsetAsync(m->attn, 0, (size_t)m->n_head_l * m->cfg.head_dim * 4, st));
+    OB_CUDA(ctx, cudaMemsetAsync(m->gate, 0, (size_t)m->n_ff_l * 4, st));
+    quantize_into(m, ACT_PLAIN, m->x, nullptr, 1, m->cfg.n_embd, m->act_embd, true, true, st);
+    quantize_into(m, ACT_PLAIN, m->attn, nullptr, 1, m->n_head_l * m->cfg.head_dim, m->act_attn, true, true, st);
+    quantize_into(m, ACT_PLAIN, m->gate, nullptr, 1, m->n_ff_l, m->act_ff, true, true, st);
+    uint64_t bytes = 0;
+    uint32_t launches = 0;
+    for (uint32_t it = 0; it <= iters; ++it) {  // pass 0 is a warm-up
+        if (it == 1) OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+        for (const LayerDev &L : m->layers) {
+            struct Item {
+                const ob_weight *w;
+                const ActPair *act;
+                float *y;
+            } items[] = {{L.wq, &m->act_embd, m->q}, {L.wk, &m->act_embd, m->k},  {L.wv, &m->act_embd, m->v},   {L.wo, &m->act_attn, m->proj},
+                         {L.gate, &m->act_embd, m->gate}, {L.up, &m->act_embd, m->up}, {L.down, &m->act_ff, m->proj}};
+            for (const Item &i : items) {
+                if (i.w->w.type != ggml_type) continue;
+                GemvArgs a{};
+                a.n_seg = 1;
+                a.seg[0].w = i.w->w;
+                a.seg[0].y = i.y;
+                a.seg[0].y_stride = i.w->w.out_dim;
+                a.seg[0].epilogue = EPI_STORE;
+                a.act = act_for(*i.act, i.w);
+                a.n_tokens = 1;
+                launch_gemv(a, ctx->sm_count, st);
+                if (it == 1) {
+                    bytes += (uint64_t)i.w->w.nb * block_bytes_gguf(ggml_type) * i.w->w.out_dim + 4ull * (i.w->w.in_dim + i.w->w.out_dim);
+                    launches++;
+                }
+            }
+        }
+    }
+    OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+    OB_CUDA(ctx, cudaStreamSynchronize(st));
+    OB_CUDA(ctx, cudaGetLastError());
+    if (!launches) return fail(ctx, OB_ERR_INVALID, "profile_gemv: the model has no matrix of that type");
+    cudaEventElapsedTime(ms_total, ctx->ev0, ctx->ev1);
+    ctx->launches += (uint64_t)launches * (iters + 1);
+    if (bytes_per_pass) *bytes_per_pass = bytes;
+    if (launches_per_pass) *launches_per_pass = launches;
+    return OB_OK;
+}
+
 // ------------------------------------------------------------------------------------ forward
 
 }  // extern "C"

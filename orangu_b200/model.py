@@ -40,6 +40,10 @@ class KvCache:
         capi.check(self.model.backend._h, self._lib.ob_kv_read(self._h, layer, pos0, n, k.ctypes.data, v.ctypes.data))
         return k, v
 
+    def copy_prefix_from(self, src: "KvCache", n: int):
+        """KvCache::copy_prefix_from (kv_cache.rs:1079-1100)."""
+        capi.check(self.model.backend._h, self._lib.ob_kv_copy_prefix(self._h, src._h, n))
+
     def close(self):
         if self._h:
             self._lib.ob_kv_destroy(self._h)
@@ -146,6 +150,12 @@ class LlamaModel:
         out = np.empty((n_steps, n_seq), np.uint32)
         capi.check(self.backend._h, self._lib.ob_decode_loop(self._h, kvs, ft.ctypes.data, n_seq, n_steps, out.ctypes.data))
         return out
+
+    def profile_gemv(self, ggml_type: int, iters: int):
+        """(ms_total, bytes_per_pass, launches_per_pass) of the single-token GEMVs of one weight type, run alone."""
+        ms, nbytes, nl = C.c_float(), C.c_uint64(), C.c_uint32()
+        capi.check(self.backend._h, self._lib.ob_profile_gemv(self._h, ggml_type, iters, C.byref(ms), C.byref(nbytes), C.byref(nl)))
+        return ms.value, nbytes.value, nl.value
 
     def last_hidden(self, n_tokens: int) -> np.ndarray:
         out = np.empty((n_tokens, self.cfg["n_embd"]), np.float32)
