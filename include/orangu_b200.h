@@ -156,6 +156,21 @@ int ob_quantize_act(ob_ctx *ctx, const float *x, uint32_t n, int per_256, int8_t
  * split flash-decode kernel, whose result differs from the CPU's in the last bits. */
 int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos,
                         uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, int exact_order, float *out);
+/* The split flash-decode attention of ob_attention_decode for callers that must not allocate: a slot's worker
+ * thread in the middle of a request, where cudaMalloc / cudaFree would synchronise the whole device and stall
+ * the other slots' streams, or a process whose KV pool already holds the rest of the memory.  It has no
+ * counterpart in the reference.  All pointers are device pointers supplied by the caller: q_dev
+ * [n_head*head_dim] f32; k_pages_dev / v_pages_dev fp16 pages laid out [page][n_head_kv][16][head_dim];
+ * page_table_dev int32 page ids of the sequence; out_dev [n_head*head_dim] f32.  The call is asynchronous on
+ * `stream` (a cudaStream_t, or NULL for the context's stream).  The partial results of the splits live in a
+ * 1 MiB array that is part of the library image on every GPU that loads it: shapes with
+ * n_head * min(16, pages/4) * (head_dim + 2) * 4 bytes above 1 MiB are refused with OB_ERR_CAPACITY; head_dim is
+ * 64 or 128 and n_head / n_head_kv is 1, 2, 4 or 8.  The first call on a device looks the array's address up
+ * (one-time set-up; make that call before starting a stream capture).  Every call on a device shares the
+ * array, so calls that may overlap on the GPU must be ordered by the caller. */
+int ob_attention_decode_static(ob_ctx *ctx, const float *q_dev, const void *k_pages_dev, const void *v_pages_dev,
+                               const int32_t *page_table_dev, uint32_t n_pos, uint32_t n_head, uint32_t n_head_kv,
+                               uint32_t head_dim, float scale, float *out_dev, void *stream);
 /* sampling::apply_repeat_penalty + argmax (E/sampling.rs:336-359); last index wins ties.
  * recent may be NULL; penalty 1.0 disables it. */
 int ob_argmax(ob_ctx *ctx, const float *logits, uint32_t n_vocab, const uint32_t *recent,

@@ -68,6 +68,7 @@ SIGNATURES = {
     "ob_swiglu": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "ob_quantize_act": (_i32, [_vp, _vp, _u32, _i32, _vp, _vp, _vp]),
     "ob_attention_decode": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _f32, _i32, _vp]),
+    "ob_attention_decode_static": (_i32, [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _f32, _vp, _vp]),
     "ob_argmax": (_i32, [_vp, _vp, _u32, _vp, _u32, _u32, _f32, _vp]),
     "ob_model_create": (_i32, [_vp, C.POINTER(ModelDesc), _PP]),
     "ob_model_destroy": (None, [_vp]),
