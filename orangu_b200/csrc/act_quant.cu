@@ -48,12 +48,11 @@ __global__ void __launch_bounds__(QT) quantize_kernel(QuantArgs a) {
             srow[padded(i + 3)] = v.w;
         }
         __syncthreads();
-        if (threadIdx.x < 32) {
-            const float t = warp_sequential_sum<16>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim);
-            if (threadIdx.x == 0) {
-                const float mean_sq = __fdiv_rn(t, (float)dim);
-                bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean_sq, a.eps)));
-            }
+        __shared__ SeqSumWorkspace<QT> ws;
+        const float t = cta_sequential_sum<QT>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim, ws);
+        if (threadIdx.x == 0) {
+            const float mean_sq = __fdiv_rn(t, (float)dim);
+            bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(mean_sq, a.eps)));
         }
         __syncthreads();
         norm_scale = bcast;

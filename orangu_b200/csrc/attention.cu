@@ -408,10 +408,9 @@ __global__ void __launch_bounds__(128) attn_softmax_kernel(AttnExactArgs a) {
     mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
     for (uint32_t p = threadIdx.x; p < n_pos; p += blockDim.x) s[p] = exp_via_double(__fsub_rn(s[p], mx));
     __syncthreads();
-    if (threadIdx.x < 32) {
-        const float sum = warp_sequential_sum<16>([&](uint32_t i) { return s[i]; }, n_pos);
-        if (threadIdx.x == 0) bcast = sum;
-    }
+    __shared__ SeqSumWorkspace<128> ws;
+    const float total = cta_sequential_sum<128>([&](uint32_t i) { return s[i]; }, n_pos, ws);
+    if (threadIdx.x == 0) bcast = total;
     __syncthreads();
     const float sum = bcast;
     if (sum > 0.0f)

@@ -24,10 +24,9 @@ __global__ void __launch_bounds__(512) rmsnorm_kernel(const float *__restrict__ 
     __shared__ float bcast;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) srow[padded(i)] = row[i];
     __syncthreads();
-    if (threadIdx.x < 32) {
-        const float t = warp_sequential_sum<16>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim);
-        if (threadIdx.x == 0) bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
-    }
+    __shared__ SeqSumWorkspace<512> ws;
+    const float t = cta_sequential_sum<512>([&](uint32_t i) { const float v = srow[padded(i)]; return __fmul_rn(v, v); }, dim, ws);
+    if (threadIdx.x == 0) bcast = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
     __syncthreads();
     const float scale = bcast;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = __fmul_rn(__fmul_rn(srow[padded(i)], scale), w[i]);

@@ -123,4 +123,140 @@ __device__ float warp_sequential_sum(F term, uint32_t n) {
     return s;
 }
 
+
+// ----------------------------------------------------------------------------------------------------
+// The same sum by a whole CTA, with the sequential part reduced to a few dozen steps.
+//
+// The binade of every partial sum is known in advance, up to a rigorous margin: with E_i the exact prefix
+// sum (taken in double), the sequentially rounded s_i satisfies |s_i - E_i| <= i * 2^-24 * s_i.  A term whose
+// two neighbouring partial sums are, with that margin, inside one binade is "safe": its increment function
+// can be formed without knowing S.  All safe functions are formed in parallel; a thread whose terms are all
+// safe composes them; runs of such threads are composed by a segmented warp scan; and only the threads that
+// hold an unsafe term (the start of the sum and the ~log2(n) binade crossings) are added with real float
+// additions, one after the other.  Every application checks that s really is in the assumed binade; if that
+// ever failed the warp-level routine above recomputes the sum from scratch.
+// ----------------------------------------------------------------------------------------------------
+struct SeqSumRecord {
+    uint32_t c0, c1;   // composed function of the thread's terms (valid when clean)
+    uint32_t es;       // biased exponent of the binade the function assumes (0: the thread has no terms)
+    uint32_t dirty;    // the thread holds a term that must be added for real
+};
+
+template <int THREADS>
+struct SeqSumWorkspace {
+    SeqSumRecord rec[THREADS];
+    double warp_tot[THREADS / 32];
+    float result;
+};
+
+// Every thread of the CTA must call this (it contains __syncthreads); every thread returns the sum.
+template <int THREADS, class F>
+__device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS> &ws) {
+    using namespace seqsum_detail;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t ept = (n + THREADS - 1) / THREADS;
+    const uint32_t first = min(n, (uint32_t)tid * ept), last = min(n, first + ept);
+
+    // ---- exact prefix sums in double ------------------------------------------------------------
+    double local = 0.0;
+    for (uint32_t i = first; i < last; ++i) local += (double)term(i);
+    double incl = local;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) ws.warp_tot[warp] = incl;
+    __syncthreads();
+    double base = incl - local;
+    for (int w = 0; w < warp; ++w) base += ws.warp_tot[w];
+
+    // ---- classify and compose this thread's terms -------------------------------------------------
+    uint32_t c0 = 0, c1 = 0, es_run = 0, dirty = 0;
+    double prev = base;
+    for (uint32_t i = first; i < last; ++i) {
+        const float t = term(i);
+        const double cur = prev + (double)t;
+        const double margin = (double)(i + 2) * 6.1e-8;  // > (i + 1) * 2^-24, with room for the double sum's own error
+        const double lo = prev * (1.0 - margin), hi = cur * (1.0 + margin);
+        // both bounds as floats' binades: safe iff identical, normal and finite
+        const float flo = __double2float_rd(lo), fhi = __double2float_ru(hi);
+        const uint32_t elo = (__float_as_uint(flo) >> 23) & 0xff, ehi = (__float_as_uint(fhi) >> 23) & 0xff;
+        const bool safe = elo == ehi && elo != 0 && elo != 255 && !(margin >= 0.25) && t >= 0.0f;
+        if (!safe || (es_run != 0 && es_run != elo)) {
+            dirty = 1;
+        } else {
+            es_run = elo;
+            uint32_t a0, a1;
+            term_function(__float_as_uint(t), (int)elo, a0, a1);
+            const uint32_t n0 = sat_add(c0, (c0 & 1u) ? a1 : a0);
+            const uint32_t n1 = sat_add(c1, ((1u + c1) & 1u) ? a1 : a0);
+            c0 = n0;
+            c1 = n1;
+        }
+        prev = cur;
+    }
+    ws.rec[tid] = SeqSumRecord{c0, c1, es_run, dirty};
+    __syncthreads();
+
+    // ---- warp 0 walks the threads in order ----------------------------------------------------------
+    if (warp == 0) {
+        float s = 0.0f;
+        bool ok = true;
+        for (int chunk = 0; chunk < THREADS / 32 && ok; ++chunk) {
+            const int owner = chunk * 32 + lane;
+            SeqSumRecord r = ws.rec[owner];
+            const bool is_dirty = r.dirty != 0;
+            // segmented inclusive scan of function composition: a dirty lane, an empty lane or a change of
+            // binade starts a new segment
+            uint32_t f0 = r.c0, f1 = r.c1;
+            const uint32_t prev_es = __shfl_up_sync(0xffffffffu, r.es, 1);
+            const uint32_t prev_dirty = __shfl_up_sync(0xffffffffu, r.dirty, 1);
+            bool head = lane == 0 || is_dirty || prev_dirty != 0 || r.es == 0 || prev_es != r.es;
+            uint32_t seg_start = __ballot_sync(0xffffffffu, head);
+            // distance to the head of this lane's segment
+            const uint32_t below = seg_start & (0xffffffffu >> (31 - lane));
+            const int my_head = 31 - __clz(below);
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t l0 = __shfl_up_sync(0xffffffffu, f0, d), l1 = __shfl_up_sync(0xffffffffu, f1, d);
+                if (lane - d >= my_head) {
+                    const uint32_t n0 = sat_add(l0, (l0 & 1u) ? f1 : f0);
+                    const uint32_t n1 = sat_add(l1, ((1u + l1) & 1u) ? f1 : f0);
+                    f0 = n0;
+                    f1 = n1;
+                }
+            }
+            // the last lane of every segment now holds the segment's function; walk the segments
+            const uint32_t seg_end = (seg_start >> 1) | 0x80000000u;  // lane l ends a segment iff lane l+1 starts one
+            uint32_t todo = seg_end;
+            while (todo && ok) {
+                const int e = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const uint32_t e_dirty = __shfl_sync(0xffffffffu, r.dirty, e);
+                const uint32_t e_es = __shfl_sync(0xffffffffu, r.es, e);
+                const uint32_t g0 = __shfl_sync(0xffffffffu, f0, e), g1 = __shfl_sync(0xffffffffu, f1, e);
+                if (e_dirty) {
+                    const uint32_t o = (uint32_t)(chunk * 32 + e);
+                    const uint32_t b = min(n, o * ept), en = min(n, b + ept);
+                    for (uint32_t i = b; i < en; ++i) s = __fadd_rn(s, term(i));
+                } else if (e_es != 0) {
+                    const uint32_t sb = __float_as_uint(s);
+                    const uint32_t S = (sb & 0x7fffffu) | 0x800000u;
+                    const uint32_t S2 = S + ((S & 1u) ? g1 : g0);
+                    if (((sb >> 23) & 0x1ff) != e_es || S2 >= (1u << 24)) {
+                        ok = false;  // the assumed binade did not hold: recompute below
+                    } else {
+                        s = __uint_as_float((sb & 0xff800000u) | (S2 & 0x7fffffu));
+                    }
+                }
+            }
+        }
+        if (!ok) s = warp_sequential_sum<16>(term, n);
+        if (lane == 0) ws.result = s;
+    }
+    __syncthreads();
+    return ws.result;
+}
+
 }  // namespace ob
