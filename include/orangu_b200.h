@@ -279,11 +279,13 @@ uint64_t ob_launch_count(const ob_ctx *ctx);
  * events on the context's stream. */
 float ob_last_device_ms(const ob_ctx *ctx);
 
-/* Measurement hook (no counterpart in the reference): runs the single-token GEMV of every layer's
- * matrices of one ggml type back to back `iters` times, with nothing else in between, and reports the
- * device time between CUDA events on the launching stream.  bytes_per_pass is the quantized weight bytes
- * one pass over the layers reads (plus the fp32 in/out vectors); launches_per_pass the kernels it issues. */
-int ob_profile_gemv(ob_model *model, uint32_t ggml_type, uint32_t iters, float *ms_total,
+/* Measurement hook (no counterpart in the reference): runs one kind of product kernel for every layer back to
+ * back `iters` times, with nothing else in between, and reports the device time between CUDA events on the
+ * launching stream.  variant 0: the unfused single-token GEMV of every matrix of `ggml_type`; variants 1-5:
+ * the fused batch-1 decode kernels -- 1 norm+q/k/v+RoPE+KV append, 2 attention-output+residual,
+ * 3 norm+gate/up+SwiGLU, 4 down+residual, 5 norm+output projection (ggml_type ignored).  bytes_per_pass is the
+ * quantized weight bytes one pass reads plus the fp32 in/out vectors; launches_per_pass the kernels it issues. */
+int ob_profile_gemv(ob_model *model, uint32_t ggml_type, uint32_t variant, uint32_t iters, float *ms_total,
                     uint64_t *bytes_per_pass, uint32_t *launches_per_pass);
 
 /* --------------------------------------------------------- tensor parallel */

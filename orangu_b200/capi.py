@@ -78,7 +78,7 @@ SIGNATURES = {
     "ob_kv_truncate": (_i32, [_vp, _u32]),
     "ob_kv_read": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "ob_kv_copy_prefix": (_i32, [_vp, _vp, _u32]),
-    "ob_profile_gemv": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp]),
+    "ob_profile_gemv": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp, _vp]),
     "ob_forward": (_i32, [_vp, _vp, _vp, _vp, _vp, _u32, _vp, _vp, _vp]),
     "ob_decode_greedy": (_i32, [_vp, _vp, _u32, _vp]),
     "ob_decode_loop": (_i32, [_vp, _vp, _vp, _u32, _u32, _vp]),

@@ -55,6 +55,36 @@ void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st);
 size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, bool gemm_order);
 uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order);  // kernels launch_gemv issues
 
+// ---- stream_gemv.cu: fused single-token products for decode (Q4_K / Q6_K weights)
+enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1 };
+enum StreamEpilogue { SG_EP_STORE = 0, SG_EP_RESIDUAL = 1, SG_EP_SWIGLU = 2, SG_EP_ROPE_Q = 3, SG_EP_ROPE_K = 4, SG_EP_V = 5 };
+struct StreamSeg {
+    DevWeight w;       // rows 2p, 2p+1 form pair p ...
+    DevWeight w2;      // ... unless w2.data != nullptr: then pair p is (w row p, w2 row p)  (gate / up)
+    float *y;          // STORE/RESIDUAL/ROPE_Q: [rows]; SWIGLU: [pairs]
+    int epilogue;
+};
+struct StreamArgs {
+    StreamSeg seg[3];
+    int n_seg;
+    uint32_t in_dim;
+    int prologue;
+    const float *x;          // [in_dim] fp32 input of the token
+    const float *norm_w;     // RMSNORM: weight [in_dim]
+    float eps;
+    const float *residual;   // RESIDUAL: y = residual + product (may alias y)
+    // RoPE + KV append (ROPE_Q / ROPE_K / V)
+    const float *rope_table; // [pos][rope_dim/2](sin, cos)
+    const uint32_t *position;        // device: position of the token
+    const int32_t *const *page_table; // device: pointer to the sequence's page table
+    __half *k_pool, *v_pool;
+    uint32_t n_head_kv, head_dim, rope_dim;
+    bool stage_x;            // set by the launcher: the fp32 row is staged in shared memory for the exact norm
+    bool wait_dependency;    // launched with programmatic stream serialisation: wait for the predecessor before reading x
+};
+bool stream_gemv_supported(const StreamArgs &a);
+void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st);
+
 // ---- glue.cu
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st);
 void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st);

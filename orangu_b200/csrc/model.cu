@@ -3,6 +3,7 @@
 // Reference graph: src/bin/orangu-server/engine/arch/llama.rs:594-932 (run_layers), :1007-1032
 // (forward: last-token logits).  Greedy sampling: engine/sampling.rs:336-359.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -89,6 +90,7 @@ struct ob_model {
     std::map<uint64_t, cudaGraphExec_t> graphs;
     std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
     obtp::Comm *comm = nullptr;
+    bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
 };
 
 struct ob_kv {
@@ -208,6 +210,114 @@ uint32_t pick_splits(const ob_model *m, uint32_t n_rows) {
     return std::max(1u, std::min(s, m->max_splits));
 }
 
+// The fused batch-1 decode kernels of layer li: 1 norm + q/k/v + RoPE + KV append, 2 attention output + residual,
+// 3 norm + gate/up + SwiGLU, 4 down + residual, 5 final norm + output projection (li ignored).
+StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
+    const ob_model_desc &c = m->cfg;
+    const LayerDev &L = m->layers[li];
+    const MetaLayout ml(m->T);
+    const uint32_t hd = c.head_dim, q_dim = m->n_head_l * hd;
+    StreamArgs a{};
+    a.eps = c.rms_eps;
+    switch (which) {
+    case 1:
+        a.n_seg = 3;
+        a.in_dim = c.n_embd;
+        a.prologue = SG_PRO_RMSNORM;
+        a.x = m->x;
+        a.norm_w = L.attn_norm;
+        a.seg[0] = StreamSeg{L.wq->w, DevWeight{}, m->q, SG_EP_ROPE_Q};
+        a.seg[1] = StreamSeg{L.wk->w, DevWeight{}, nullptr, SG_EP_ROPE_K};
+        a.seg[2] = StreamSeg{L.wv->w, DevWeight{}, nullptr, SG_EP_V};
+        a.rope_table = m->rope_table;
+        a.position = reinterpret_cast<const uint32_t *>(m->d_meta + ml.off_positions);
+        a.page_table = reinterpret_cast<const int32_t *const *>(m->d_meta + ml.off_tables);
+        a.k_pool = m->k_pool + (size_t)li * m->layer_stride;
+        a.v_pool = m->v_pool + (size_t)li * m->layer_stride;
+        a.n_head_kv = m->n_head_kv_l;
+        a.head_dim = hd;
+        a.rope_dim = c.rope_dim;
+        break;
+    case 2:
+        a.n_seg = 1;
+        a.in_dim = q_dim;
+        a.prologue = SG_PRO_PLAIN;
+        a.x = m->attn;
+        a.residual = m->x;
+        a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
+        break;
+    case 3:
+        a.n_seg = 1;
+        a.in_dim = c.n_embd;
+        a.prologue = SG_PRO_RMSNORM;
+        a.x = m->x;
+        a.norm_w = L.ffn_norm;
+        a.seg[0] = StreamSeg{L.gate->w, L.up->w, m->gate, SG_EP_SWIGLU};
+        break;
+    case 4:
+        a.n_seg = 1;
+        a.in_dim = m->n_ff_l;
+        a.prologue = SG_PRO_PLAIN;
+        a.x = m->gate;
+        a.residual = m->x;
+        a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
+        break;
+    default:
+        a.n_seg = 1;
+        a.in_dim = c.n_embd;
+        a.prologue = SG_PRO_RMSNORM;
+        a.x = m->x;
+        a.norm_w = m->output_norm;
+        a.seg[0] = StreamSeg{m->output->w, DevWeight{}, m->logits, SG_EP_STORE};
+        break;
+    }
+    return a;
+}
+
+void run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32_t pos_bound, const int32_t *const *d_tables,
+                   const uint32_t *d_npos, cudaStream_t st) {
+    const uint32_t hd = m->cfg.head_dim;
+    const __half *k_pool = m->k_pool + (size_t)li * m->layer_stride, *v_pool = m->v_pool + (size_t)li * m->layer_stride;
+    if (exact_attn) {
+        AttnExactArgs at{};
+        at.q = m->q;
+        at.out = m->attn;
+        at.k_pool = k_pool;
+        at.v_pool = v_pool;
+        at.page_tables = d_tables;
+        at.n_pos = d_npos;
+        at.scores = m->scores;
+        at.score_stride = m->score_stride;
+        at.n_rows = T;
+        at.n_head = m->n_head_l;
+        at.n_head_kv = m->n_head_kv_l;
+        at.head_dim = hd;
+        at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
+        at.max_pos = pos_bound;
+        launch_attn_exact(at, st);
+        m->ctx->launches += 3;
+    } else {
+        AttnDecodeArgs at{};
+        at.q = m->q;
+        at.out = m->attn;
+        at.k_pool = k_pool;
+        at.v_pool = v_pool;
+        at.page_tables = d_tables;
+        at.n_pos = d_npos;
+        at.n_seq = T;
+        at.n_head = m->n_head_l;
+        at.n_head_kv = m->n_head_kv_l;
+        at.head_dim = hd;
+        at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
+        at.n_splits = pick_splits(m, T);
+        at.part_o = m->part_o;
+        at.part_ml = m->part_ml;
+        at.max_pos = m->cfg.max_seq_len;
+        launch_attn_decode(at, st);
+        m->ctx->launches += 2;
+    }
+}
+
 // Enqueue one forward step over T rows whose metadata is already in d_meta.
 //   gemm_order: the rows are consecutive tokens of one sequence (prefill chunk)
 //   logit_row0 / n_logit_rows: which rows get the output projection
@@ -227,8 +337,23 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
     launch_embed(m->token_embd->w, d_tokens, T, m->x, st);
     m->ctx->launches++;
 
+    // Batch-1 decode on one GPU with K-type weights takes the fused streaming kernels (stream_gemv.cu):
+    // norm / quantize as prologue, RoPE + KV append, residual and SwiGLU as epilogues, 5 product kernels per layer.
+    const bool stream = T == 1 && !tp && m->use_stream;
+    auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
+
     for (uint32_t li = 0; li < c.n_layer; ++li) {
         const LayerDev &L = m->layers[li];
+        const bool stream_layer = stream && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
+                                  k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
+        if (stream_layer) {
+            launch_stream_gemv(stream_args(m, li, 1), m->ctx->sm_count, true, st);
+            m->ctx->launches++;
+            run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
+            for (int v = 2; v <= 4; ++v) launch_stream_gemv(stream_args(m, li, v), m->ctx->sm_count, true, st);
+            m->ctx->launches += 3;
+            continue;
+        }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
         run_products(m, m->act_embd, {{L.wq, m->q, q_dim, nullptr}, {L.wk, m->k, kv_dim, nullptr}, {L.wv, m->v, kv_dim, nullptr}}, T, gemm_order, st);
 
@@ -249,44 +374,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         launch_rope_kv(rk, st);
         m->ctx->launches++;
 
-        if (exact_attn) {
-            AttnExactArgs at{};
-            at.q = m->q;
-            at.out = m->attn;
-            at.k_pool = rk.k_pool;
-            at.v_pool = rk.v_pool;
-            at.page_tables = d_tables;
-            at.n_pos = d_npos;
-            at.scores = m->scores;
-            at.score_stride = m->score_stride;
-            at.n_rows = T;
-            at.n_head = m->n_head_l;
-            at.n_head_kv = m->n_head_kv_l;
-            at.head_dim = hd;
-            at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
-            at.max_pos = pos_bound;
-            launch_attn_exact(at, st);
-            m->ctx->launches += 3;
-        } else {
-            AttnDecodeArgs at{};
-            at.q = m->q;
-            at.out = m->attn;
-            at.k_pool = rk.k_pool;
-            at.v_pool = rk.v_pool;
-            at.page_tables = d_tables;
-            at.n_pos = d_npos;
-            at.n_seq = T;
-            at.n_head = m->n_head_l;
-            at.n_head_kv = m->n_head_kv_l;
-            at.head_dim = hd;
-            at.scale = 1.0f / sqrtf((float)hd);  // llama.rs:823
-            at.n_splits = pick_splits(m, T);
-            at.part_o = m->part_o;
-            at.part_ml = m->part_ml;
-            at.max_pos = c.max_seq_len;
-            launch_attn_decode(at, st);
-            m->ctx->launches += 2;
-        }
+        run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
 
         quantize_into(m, ACT_PLAIN, m->attn, nullptr, T, q_dim, m->act_attn, needs_k({L.wo}), needs_flat({L.wo}), st);
         if (!tp) {
@@ -311,7 +399,22 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         }
     }
 
-    if (n_logit_rows) {
+    if (n_logit_rows == 1 && stream && k_type(m->output)) {
+        StreamArgs la = stream_args(m, 0, 5);
+        la.x = m->x + (size_t)logit_row0 * n_embd;
+        launch_stream_gemv(la, m->ctx->sm_count, true, st);
+        m->ctx->launches++;
+        if (want_argmax) {
+            ArgmaxArgs am{};
+            am.logits = m->logits;
+            am.n_seq = 1;
+            am.n_vocab = c.n_vocab;
+            am.out = m->d_out_tokens;
+            am.scratch = m->argmax_scratch;
+            launch_argmax(am, st);
+            m->ctx->launches += 3;
+        }
+    } else if (n_logit_rows) {
         const float *xl = m->x + (size_t)logit_row0 * n_embd;
         quantize_into(m, ACT_RMSNORM, xl, m->output_norm, n_logit_rows, n_embd, m->act_embd, needs_k({m->output}), needs_flat({m->output}), st);
         // Always the single-token kernel: forward() projects one row (llama.rs:1026-1030).
@@ -407,6 +510,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     if (m->cfg.rope_dim == 0) m->cfg.rope_dim = c.head_dim;
     if (m->cfg.max_seq_len == 0) m->cfg.max_seq_len = 4096;
     if (m->cfg.max_batch_tokens == 0) m->cfg.max_batch_tokens = 1;
+    if (const char *e = getenv("OB_STREAM_GEMV")) m->use_stream = !(e[0] == '0' && e[1] == 0);
     m->tp_rank = rank;
     m->tp_size = tp;
     m->n_head_l = c.n_head / tp;
@@ -622,12 +726,46 @@ int ob_kv_copy_prefix(ob_kv *dst, const ob_kv *src, uint32_t n) {
     return OB_OK;
 }
 
-int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t iters, float *ms_total, uint64_t *bytes_per_pass, uint32_t *launches_per_pass) {
-    if (!m || !ms_total) return OB_ERR_INVALID;
+int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t variant, uint32_t iters, float *ms_total, uint64_t *bytes_per_pass,
+                    uint32_t *launches_per_pass) {
+    if (!m || !ms_total || variant > 5) return OB_ERR_INVALID;
     ob_ctx *ctx = m->ctx;
     std::lock_guard<std::mutex> g(ctx->mu);
     Bind b(ctx);
     cudaStream_t st = ctx->stream;
+    if (variant) {
+        if (m->last_T == 0) return fail(ctx, OB_ERR_INVALID, "profile_gemv: run a decode step first (the fused kernels read its position and page table)");
+        if (m->tp_size > 1) return fail(ctx, OB_ERR_UNSUPPORTED, "profile_gemv: the fused kernels are single-GPU");
+        uint64_t bytes = 0;
+        uint32_t launches = 0;
+        auto seg_bytes = [](const StreamSeg &sg) {
+            uint64_t n = (uint64_t)sg.w.nb * block_bytes_gguf(sg.w.type) * sg.w.out_dim + 4ull * sg.w.out_dim;
+            if (sg.w2.data) n += (uint64_t)sg.w2.nb * block_bytes_gguf(sg.w2.type) * sg.w2.out_dim;
+            return n;
+        };
+        for (uint32_t it = 0; it <= iters; ++it) {  // pass 0 is a warm-up
+            if (it == 1) OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
+            const uint32_t n = variant == 5 ? 1u : m->cfg.n_layer;
+            for (uint32_t li = 0; li < n; ++li) {
+                const StreamArgs a = stream_args(m, li, (int)variant);
+                if (!stream_gemv_supported(a)) return fail(ctx, OB_ERR_UNSUPPORTED, "profile_gemv: this model's tensors do not take the fused kernels");
+                launch_stream_gemv(a, ctx->sm_count, true, st);
+                if (it == 1) {
+                    for (int s = 0; s < a.n_seg; ++s) bytes += seg_bytes(a.seg[s]);
+                    bytes += 4ull * a.in_dim;
+                    launches++;
+                }
+            }
+        }
+        OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+        OB_CUDA(ctx, cudaStreamSynchronize(st));
+        OB_CUDA(ctx, cudaGetLastError());
+        cudaEventElapsedTime(ms_total, ctx->ev0, ctx->ev1);
+        ctx->launches += (uint64_t)launches * (iters + 1);
+        if (bytes_per_pass) *bytes_per_pass = bytes;
+        if (launches_per_pass) *launches_per_pass = launches;
+        return OB_OK;
+    }
     // any finite activations will do: the kernel's work does not depend on the values
     OB_CUDA(ctx, cudaMemsetAsync(m->x, 0, (size_t)m->cfg.n_embd * 4, st));
     OB_CUDA(ctx, cudaMemsetAsync(m->attn, 0, (size_t)m->n_head_l * m->cfg.head_dim * 4, st));

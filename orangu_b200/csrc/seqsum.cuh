@@ -137,7 +137,7 @@ __device__ float warp_sequential_sum(F term, uint32_t n) {
 // ever failed the warp-level routine above recomputes the sum from scratch.
 // ----------------------------------------------------------------------------------------------------
 struct SeqSumRecord {
-    uint32_t c0, c1;   // composed function of the thread's terms (valid when clean)
+    uint32_t c0, c1;   // composed function: of the thread's terms, then (after the warp's scan) of its segment so far
     uint32_t es;       // biased exponent of the binade the function assumes (0: the thread has no terms)
     uint32_t dirty;    // the thread holds a term that must be added for real
 };
@@ -146,6 +146,7 @@ template <int THREADS>
 struct SeqSumWorkspace {
     SeqSumRecord rec[THREADS];
     double warp_tot[THREADS / 32];
+    uint32_t seg_end[THREADS / 32];  // per warp: lanes that end a segment
     float result;
 };
 
@@ -196,55 +197,57 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
         }
         prev = cur;
     }
-    ws.rec[tid] = SeqSumRecord{c0, c1, es_run, dirty};
+
+    // ---- every warp composes the runs of its own 32 threads: segmented inclusive scan ------------------
+    {
+        const uint32_t prev_es = __shfl_up_sync(0xffffffffu, es_run, 1);
+        const uint32_t prev_dirty = __shfl_up_sync(0xffffffffu, dirty, 1);
+        // a dirty lane, an empty lane or a change of binade starts a new segment
+        const bool head = lane == 0 || dirty != 0 || prev_dirty != 0 || es_run == 0 || prev_es != es_run;
+        const uint32_t seg_start = __ballot_sync(0xffffffffu, head);
+        const uint32_t below = seg_start & (0xffffffffu >> (31 - lane));
+        const int my_head = 31 - __clz(below);
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t l0 = __shfl_up_sync(0xffffffffu, c0, d), l1 = __shfl_up_sync(0xffffffffu, c1, d);
+            if (lane - d >= my_head) {
+                const uint32_t n0 = sat_add(l0, (l0 & 1u) ? c1 : c0);
+                const uint32_t n1 = sat_add(l1, ((1u + l1) & 1u) ? c1 : c0);
+                c0 = n0;
+                c1 = n1;
+            }
+        }
+        ws.rec[tid] = SeqSumRecord{c0, c1, es_run, dirty};
+        if (lane == 0) ws.seg_end[warp] = (seg_start >> 1) | 0x80000000u;  // lane l ends a segment iff lane l+1 starts one
+    }
     __syncthreads();
 
-    // ---- warp 0 walks the threads in order ----------------------------------------------------------
+    // ---- warp 0 walks the segments in order ----------------------------------------------------------------
     if (warp == 0) {
         float s = 0.0f;
         bool ok = true;
         for (int chunk = 0; chunk < THREADS / 32 && ok; ++chunk) {
-            const int owner = chunk * 32 + lane;
-            SeqSumRecord r = ws.rec[owner];
-            const bool is_dirty = r.dirty != 0;
-            // segmented inclusive scan of function composition: a dirty lane, an empty lane or a change of
-            // binade starts a new segment
-            uint32_t f0 = r.c0, f1 = r.c1;
-            const uint32_t prev_es = __shfl_up_sync(0xffffffffu, r.es, 1);
-            const uint32_t prev_dirty = __shfl_up_sync(0xffffffffu, r.dirty, 1);
-            bool head = lane == 0 || is_dirty || prev_dirty != 0 || r.es == 0 || prev_es != r.es;
-            uint32_t seg_start = __ballot_sync(0xffffffffu, head);
-            // distance to the head of this lane's segment
-            const uint32_t below = seg_start & (0xffffffffu >> (31 - lane));
-            const int my_head = 31 - __clz(below);
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const uint32_t l0 = __shfl_up_sync(0xffffffffu, f0, d), l1 = __shfl_up_sync(0xffffffffu, f1, d);
-                if (lane - d >= my_head) {
-                    const uint32_t n0 = sat_add(l0, (l0 & 1u) ? f1 : f0);
-                    const uint32_t n1 = sat_add(l1, ((1u + l1) & 1u) ? f1 : f0);
-                    f0 = n0;
-                    f1 = n1;
-                }
-            }
-            // the last lane of every segment now holds the segment's function; walk the segments
-            const uint32_t seg_end = (seg_start >> 1) | 0x80000000u;  // lane l ends a segment iff lane l+1 starts one
-            uint32_t todo = seg_end;
+            uint32_t todo = ws.seg_end[chunk];
             while (todo && ok) {
                 const int e = __ffs(todo) - 1;
                 todo &= todo - 1;
-                const uint32_t e_dirty = __shfl_sync(0xffffffffu, r.dirty, e);
-                const uint32_t e_es = __shfl_sync(0xffffffffu, r.es, e);
-                const uint32_t g0 = __shfl_sync(0xffffffffu, f0, e), g1 = __shfl_sync(0xffffffffu, f1, e);
-                if (e_dirty) {
+                const SeqSumRecord r = ws.rec[chunk * 32 + e];
+                if (r.dirty) {
                     const uint32_t o = (uint32_t)(chunk * 32 + e);
                     const uint32_t b = min(n, o * ept), en = min(n, b + ept);
-                    for (uint32_t i = b; i < en; ++i) s = __fadd_rn(s, term(i));
-                } else if (e_es != 0) {
+                    for (uint32_t i = b; i < en; i += 4) {  // fetch four terms, then add them: the loads overlap
+                        const float t0 = term(i), t1 = i + 1 < en ? term(i + 1) : 0.0f, t2 = i + 2 < en ? term(i + 2) : 0.0f,
+                                    t3 = i + 3 < en ? term(i + 3) : 0.0f;
+                        s = __fadd_rn(s, t0);
+                        if (i + 1 < en) s = __fadd_rn(s, t1);
+                        if (i + 2 < en) s = __fadd_rn(s, t2);
+                        if (i + 3 < en) s = __fadd_rn(s, t3);
+                    }
+                } else if (r.es != 0) {
                     const uint32_t sb = __float_as_uint(s);
                     const uint32_t S = (sb & 0x7fffffu) | 0x800000u;
-                    const uint32_t S2 = S + ((S & 1u) ? g1 : g0);
-                    if (((sb >> 23) & 0x1ff) != e_es || S2 >= (1u << 24)) {
+                    const uint32_t S2 = S + ((S & 1u) ? r.c1 : r.c0);
+                    if (((sb >> 23) & 0x1ff) != r.es || S2 >= (1u << 24)) {
                         ok = false;  // the assumed binade did not hold: recompute below
                     } else {
                         s = __uint_as_float((sb & 0xff800000u) | (S2 & 0x7fffffu));

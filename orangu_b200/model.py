@@ -151,10 +151,10 @@ class LlamaModel:
         capi.check(self.backend._h, self._lib.ob_decode_loop(self._h, kvs, ft.ctypes.data, n_seq, n_steps, out.ctypes.data))
         return out
 
-    def profile_gemv(self, ggml_type: int, iters: int):
+    def profile_gemv(self, ggml_type: int, iters: int, variant: int = 0):
         """(ms_total, bytes_per_pass, launches_per_pass) of the single-token GEMVs of one weight type, run alone."""
         ms, nbytes, nl = C.c_float(), C.c_uint64(), C.c_uint32()
-        capi.check(self.backend._h, self._lib.ob_profile_gemv(self._h, ggml_type, iters, C.byref(ms), C.byref(nbytes), C.byref(nl)))
+        capi.check(self.backend._h, self._lib.ob_profile_gemv(self._h, ggml_type, variant, iters, C.byref(ms), C.byref(nbytes), C.byref(nl)))
         return ms.value, nbytes.value, nl.value
 
     def last_hidden(self, n_tokens: int) -> np.ndarray:
