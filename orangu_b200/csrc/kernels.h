@@ -71,6 +71,7 @@ struct StreamArgs {
     int prologue;
     const float *x;          // [in_dim] fp32 input of the token
     const float *norm_w;     // RMSNORM: weight [in_dim]
+    const float *norm_scale; // RMSNORM: device word holding 1 / sqrt(mean(x^2) + eps), from launch_norm_scale
     float eps;
     const float *residual;   // RESIDUAL: y = residual + product (may alias y)
     // RoPE + KV append (ROPE_Q / ROPE_K / V)
@@ -79,11 +80,11 @@ struct StreamArgs {
     const int32_t *const *page_table; // device: pointer to the sequence's page table
     __half *k_pool, *v_pool;
     uint32_t n_head_kv, head_dim, rope_dim;
-    bool stage_x;            // set by the launcher: the fp32 row is staged in shared memory for the exact norm
     bool wait_dependency;    // launched with programmatic stream serialisation: wait for the predecessor before reading x
 };
 bool stream_gemv_supported(const StreamArgs &a);
 void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st);
+void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool programmatic, cudaStream_t st);
 
 // ---- glue.cu
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st);

@@ -78,6 +78,7 @@ struct ob_model {
           *logits = nullptr;
     ActPair act_embd, act_attn, act_ff;
     float *part_o = nullptr, *part_ml = nullptr;
+    float *norm_scale = nullptr;      // [2] RMSNorm scales for the fused decode kernels (attention norm, FFN / output norm)
     float *scores = nullptr;          // exact-order attention scratch [T][n_head_l][score_stride]
     uint32_t score_stride = 0, exact_attn_max_pos = 0;
     uint32_t max_splits = 1;
@@ -226,6 +227,7 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.prologue = SG_PRO_RMSNORM;
         a.x = m->x;
         a.norm_w = L.attn_norm;
+        a.norm_scale = m->norm_scale;
         a.seg[0] = StreamSeg{L.wq->w, DevWeight{}, m->q, SG_EP_ROPE_Q};
         a.seg[1] = StreamSeg{L.wk->w, DevWeight{}, nullptr, SG_EP_ROPE_K};
         a.seg[2] = StreamSeg{L.wv->w, DevWeight{}, nullptr, SG_EP_V};
@@ -252,6 +254,7 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.prologue = SG_PRO_RMSNORM;
         a.x = m->x;
         a.norm_w = L.ffn_norm;
+        a.norm_scale = m->norm_scale + 1;
         a.seg[0] = StreamSeg{L.gate->w, L.up->w, m->gate, SG_EP_SWIGLU};
         break;
     case 4:
@@ -268,6 +271,7 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.prologue = SG_PRO_RMSNORM;
         a.x = m->x;
         a.norm_w = m->output_norm;
+        a.norm_scale = m->norm_scale;
         a.seg[0] = StreamSeg{m->output->w, DevWeight{}, m->logits, SG_EP_STORE};
         break;
     }
@@ -347,11 +351,14 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         const bool stream_layer = stream && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
                                   k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
         if (stream_layer) {
+            launch_norm_scale(m->x, n_embd, c.rms_eps, m->norm_scale, true, st);
             launch_stream_gemv(stream_args(m, li, 1), m->ctx->sm_count, true, st);
-            m->ctx->launches++;
             run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
-            for (int v = 2; v <= 4; ++v) launch_stream_gemv(stream_args(m, li, v), m->ctx->sm_count, true, st);
-            m->ctx->launches += 3;
+            launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
+            launch_norm_scale(m->x, n_embd, c.rms_eps, m->norm_scale + 1, true, st);
+            launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
+            launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
+            m->ctx->launches += 6;
             continue;
         }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
@@ -402,8 +409,9 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
     if (n_logit_rows == 1 && stream && k_type(m->output)) {
         StreamArgs la = stream_args(m, 0, 5);
         la.x = m->x + (size_t)logit_row0 * n_embd;
+        launch_norm_scale(la.x, n_embd, c.rms_eps, m->norm_scale, true, st);
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
-        m->ctx->launches++;
+        m->ctx->launches += 2;
         if (want_argmax) {
             ArgmaxArgs am{};
             am.logits = m->logits;
@@ -603,6 +611,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     m->exact_attn_max_pos = attn_exact_supported(m->n_head_l, m->n_head_kv_l, hd) ? std::min(m->cfg.max_seq_len, c.exact_attention_max_pos ? c.exact_attention_max_pos : 1024u) : 0u;
     m->score_stride = (m->exact_attn_max_pos + 63) / 64 * 64;
     if (m->score_stride && (rc = dev_alloc(m, &m->scores, (size_t)T * m->n_head_l * m->score_stride))) return bail(rc);
+    if ((rc = dev_alloc(m, &m->norm_scale, 4))) return bail(rc);
     const MetaLayout ml(T);
     if ((rc = dev_alloc(m, &m->d_meta, ml.bytes))) return bail(rc);
     if ((rc = dev_alloc(m, &m->d_out_tokens, T))) return bail(rc);
@@ -743,6 +752,8 @@ int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t variant, uint32_t 
             if (sg.w2.data) n += (uint64_t)sg.w2.nb * block_bytes_gguf(sg.w2.type) * sg.w2.out_dim;
             return n;
         };
+        launch_norm_scale(m->x, m->cfg.n_embd, m->cfg.rms_eps, m->norm_scale, false, st);
+        launch_norm_scale(m->x, m->cfg.n_embd, m->cfg.rms_eps, m->norm_scale + 1, false, st);
         for (uint32_t it = 0; it <= iters; ++it) {  // pass 0 is a warm-up
             if (it == 1) OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
             const uint32_t n = variant == 5 ? 1u : m->cfg.n_layer;
