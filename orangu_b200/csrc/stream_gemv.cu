@@ -66,6 +66,32 @@ __host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6) {
     return s;
 }
 
+// Explicit shared-space accesses with 32-bit addresses (a generic pointer would cost 64-bit address arithmetic per load).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory"); }
+__device__ __forceinline__ void cp_async16(uint32_t saddr, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(g) : "memory");
+}
+
 __device__ __forceinline__ float silu_mul_exact(float g, float u) {
     const float s = __fdiv_rn(g, __fadd_rn(1.0f, (float)exp((double)(-g))));
     return __fmul_rn(s, u);
@@ -79,37 +105,56 @@ __device__ void sg_quantize(const StreamArgs &a, uint8_t *smem, const SgSmem &L,
     float *sd = reinterpret_cast<float *>(smem + L.off_d);
     int16_t *bsum = reinterpret_cast<int16_t *>(smem + L.off_bsum);
     int16_t *sum16 = reinterpret_cast<int16_t *>(smem + L.off_sum16);
-    for (uint32_t b = warp; b < nb; b += n_warps) {
-        const uint32_t e0 = b * 256 + lane * 8;
-        float v[8];
-        const float4 x0 = *reinterpret_cast<const float4 *>(a.x + e0), x1 = *reinterpret_cast<const float4 *>(a.x + e0 + 4);
-        v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
+    // four blocks per pass, all their loads issued before any arithmetic: the pass costs one memory latency, not four
+    for (uint32_t bb = warp; bb < nb; bb += 4 * n_warps) {
+        float v[4][8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t b = bb + k * n_warps;
+            if (b < nb) {
+                const uint32_t e0 = b * 256 + lane * 8;
+                const float4 x0 = *reinterpret_cast<const float4 *>(a.x + e0), x1 = *reinterpret_cast<const float4 *>(a.x + e0 + 4);
+                v[k][0] = x0.x; v[k][1] = x0.y; v[k][2] = x0.z; v[k][3] = x0.w; v[k][4] = x1.x; v[k][5] = x1.y; v[k][6] = x1.z; v[k][7] = x1.w;
+            }
+        }
         if (a.prologue == SG_PRO_RMSNORM) {
-            const float4 w0 = *reinterpret_cast<const float4 *>(a.norm_w + e0), w1 = *reinterpret_cast<const float4 *>(a.norm_w + e0 + 4);
-            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(v[i], norm_scale), w[i]);  // (v * scale) * w, tensor.rs:747
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t b = bb + k * n_warps;
+                if (b < nb) {
+                    const uint32_t e0 = b * 256 + lane * 8;
+                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0)), w1 = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0 + 4));
+                    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[k][i] = __fmul_rn(__fmul_rn(v[k][i], norm_scale), w[i]);  // (v * scale) * w, tensor.rs:747
+                }
+            }
         }
-        float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-        amax = warp_max(amax);
-        const float scale = __fdiv_rn(amax, 127.0f);
-        const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
-        int q[8], s8 = 0;
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t b = bb + k * n_warps;
+            if (b >= nb) break;  // warp-uniform
+            float amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            q[i] = quantize_value(v[i], inv);
-            s8 += q[i];
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[k][i]));
+            amax = warp_max(amax);
+            const float scale = __fdiv_rn(amax, 127.0f);
+            const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+            int q[8], s8 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                q[i] = quantize_value(v[k][i], inv);
+                s8 += q[i];
+            }
+            const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+            const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+            const uint32_t lo = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+            const uint32_t hi = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+            *reinterpret_cast<uint2 *>(smem + L.off_act + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
+            if ((lane & 1) == 0) sum16[b * 16 + (lane >> 1)] = (int16_t)s16;
+            if ((lane & 3) == 0) bsum[b * 8 + (lane >> 2)] = (int16_t)s32;
+            if (lane == 0) sd[b] = scale;
         }
-        const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
-        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-        const uint32_t lo = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-        const uint32_t hi = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-        *reinterpret_cast<uint2 *>(smem + L.off_act + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
-        if ((lane & 1) == 0) sum16[b * 16 + (lane >> 1)] = (int16_t)s16;
-        if ((lane & 3) == 0) bsum[b * 8 + (lane >> 2)] = (int16_t)s32;
-        if (lane == 0) sd[b] = scale;
     }
 }
 
@@ -132,20 +177,22 @@ __device__ __forceinline__ void pair_rows(const StreamSeg &sg, uint32_t pair, co
     }
 }
 
-__device__ __forceinline__ void issue_part(uint8_t *dst, const uint8_t *row, uint32_t type, uint32_t d_off, uint32_t lp, uint32_t b0, uint32_t nblk,
+__device__ __forceinline__ void issue_part(uint32_t dst, const uint8_t *row, uint32_t type, uint32_t d_off, uint32_t lp, uint32_t b0, uint32_t nblk,
                                            int lane) {
     if (type == TYPE_Q4_K) {
-        const uint8_t *src = row + (uint64_t)b0 * 144;
-        for (uint32_t c = lane; c < nblk * 9; c += 32) __pipeline_memcpy_async(dst + c * 16, src + c * 16, 16);
+        const uint8_t *src = row + (uint64_t)b0 * 144 + lane * 16;
+        dst += lane * 16;
+        for (uint32_t c = lane; c < nblk * 9; c += 32, src += 512, dst += 512) cp_async16(dst, src);
     } else {
-        const uint8_t *src = row + (uint64_t)b0 * 208;
-        for (uint32_t c = lane; c < nblk * 13; c += 32) __pipeline_memcpy_async(dst + c * 16, src + c * 16, 16);
+        const uint8_t *src = row + (uint64_t)b0 * 208 + lane * 16;
+        uint32_t dm = dst + lane * 16;
+        for (uint32_t c = lane; c < nblk * 13; c += 32, src += 512, dm += 512) cp_async16(dm, src);
         const uint8_t *dsrc = row + d_off + 2 * b0;  // f16 d values of these blocks; b0 is a multiple of 32, so 16-byte aligned
-        if (lane < (int)((nblk * 2 + 15) / 16)) __pipeline_memcpy_async(dst + lp * 208 + lane * 16, dsrc + lane * 16, 16);
+        if (lane < (int)((nblk * 2 + 15) / 16)) cp_async16(dst + lp * 208 + lane * 16, dsrc + lane * 16);
     }
 }
 
-__device__ __forceinline__ void issue_unit(uint8_t *slot, const StreamArgs &a, const Unit &u, uint32_t lp, int lane) {
+__device__ __forceinline__ void issue_unit(uint32_t slot, const StreamArgs &a, const Unit &u, uint32_t lp, int lane) {
     const StreamSeg &sg = a.seg[u.seg];
     const uint32_t pb = part_bytes(sg.w.type, lp);
     for (uint32_t j = 0; j < u.n_pairs; ++j) {
@@ -169,13 +216,14 @@ __device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {  // c + 
 }
 
 // blk[r]: the 144-byte block of row r in the slot; xa: the block's 256 int8 activations; bs: its eight per-32 sums.
-__device__ __forceinline__ void dot_block_q4k(const uint8_t *const blk[2], int n_rows, const uint8_t *xa, const int16_t *bs, float ad, float term[2]) {
+__device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, int n_rows, uint32_t xa, uint32_t bs, float ad, float term[2]) {
+    const uint32_t blk[2] = {blk0, blk1};
     uint32_t scl[2], sch[2], ml[2], mh[2], dd[2];
     int isum[2] = {0, 0};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         uint4 hd = make_uint4(0, 0, 0, 0);
-        if (r < n_rows) hd = *reinterpret_cast<const uint4 *>(blk[r]);
+        if (r < n_rows) hd = lds128(blk[r]);
         dd[r] = hd.x;
         // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of four words
         scl[r] = hd.y & 0x3f3f3f3fu;
@@ -185,12 +233,11 @@ __device__ __forceinline__ void dot_block_q4k(const uint8_t *const blk[2], int n
     }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {  // 64 elements: sub-blocks 2g (low nibbles) and 2g+1 (high nibbles)
-        const uint4 x0 = *reinterpret_cast<const uint4 *>(xa + 64 * g), x1 = *reinterpret_cast<const uint4 *>(xa + 64 * g + 16);
-        const uint4 x2 = *reinterpret_cast<const uint4 *>(xa + 64 * g + 32), x3 = *reinterpret_cast<const uint4 *>(xa + 64 * g + 48);
+        const uint4 x0 = lds128(xa + 64 * g), x1 = lds128(xa + 64 * g + 16), x2 = lds128(xa + 64 * g + 32), x3 = lds128(xa + 64 * g + 48);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             if (r >= n_rows) continue;
-            const uint4 qa = *reinterpret_cast<const uint4 *>(blk[r] + 16 + 32 * g), qb = *reinterpret_cast<const uint4 *>(blk[r] + 32 + 32 * g);
+            const uint4 qa = lds128(blk[r] + 16 + 32 * g), qb = lds128(blk[r] + 32 + 32 * g);
             const uint32_t Lm = 0x0f0f0f0fu, Hm = 0xf0f0f0f0u;
             int lo0 = dp4a_us(qa.x & Lm, x0.x, 0), lo1 = dp4a_us(qa.y & Lm, x0.y, 0);
             lo0 = dp4a_us(qa.z & Lm, x0.z, lo0);
@@ -212,7 +259,7 @@ __device__ __forceinline__ void dot_block_q4k(const uint8_t *const blk[2], int n
             isum[r] += sca * lo + scb * hi;
         }
     }
-    const uint4 bsv = *reinterpret_cast<const uint4 *>(bs);  // eight int16 sums as four pairs
+    const uint4 bsv = lds128(bs);  // eight int16 sums as four pairs
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         int imin = dp2a_lo(bsv.x, ml[r], 0);
@@ -225,33 +272,34 @@ __device__ __forceinline__ void dot_block_q4k(const uint8_t *const blk[2], int n
 }
 
 // blk[r]: the 208-byte block [ql 128 | qh 64 | scales 16]; dsup[r]: its f16 d; s16: the block's sixteen per-16 sums.
-__device__ __forceinline__ void dot_block_q6k(const uint8_t *const blk[2], const float dsup[2], int n_rows, const uint8_t *xa, const int16_t *s16p,
-                                              float ad, float term[2]) {
+__device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, const float dsup[2], int n_rows, uint32_t xa, uint32_t s16p, float ad,
+                                              float term[2]) {
+    const uint32_t blk[2] = {blk0, blk1};
     int isum[2] = {0, 0};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // 128 elements: runs 0..3 of 32
         uint32_t xw[32];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(xa + 128 * h + 16 * k);
+            const uint4 v = lds128(xa + 128 * h + 16 * k);
             xw[4 * k] = v.x;
             xw[4 * k + 1] = v.y;
             xw[4 * k + 2] = v.z;
             xw[4 * k + 3] = v.w;
         }
-        const uint4 sv = *reinterpret_cast<const uint4 *>(s16p + 8 * h);  // eight int16 sums, groups 8h .. 8h+7
+        const uint4 sv = lds128(s16p + 16 * h);  // eight int16 sums, groups 8h .. 8h+7
         const int s16[8] = {(int16_t)(sv.x & 0xffff), (int16_t)(sv.x >> 16), (int16_t)(sv.y & 0xffff), (int16_t)(sv.y >> 16),
                             (int16_t)(sv.z & 0xffff), (int16_t)(sv.z >> 16), (int16_t)(sv.w & 0xffff), (int16_t)(sv.w >> 16)};
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             if (r >= n_rows) continue;
-            const uint2 scw = *reinterpret_cast<const uint2 *>(blk[r] + 192 + 8 * h);  // signed scales of groups 8h .. 8h+7
+            const uint2 scw = lds64(blk[r] + 192 + 8 * h);  // signed scales of groups 8h .. 8h+7
             int dots[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // group 2 * run + k
 #pragma unroll
             for (int k = 0; k < 2; ++k) {  // k: 16-byte chunk of l (elements l = 16k .. 16k+15 of each run)
-                const uint4 qla = *reinterpret_cast<const uint4 *>(blk[r] + 64 * h + 16 * k);       // runs 0 (low nibble) and 2 (high)
-                const uint4 qlb = *reinterpret_cast<const uint4 *>(blk[r] + 64 * h + 32 + 16 * k);  // runs 1 and 3
-                const uint4 qhv = *reinterpret_cast<const uint4 *>(blk[r] + 128 + 32 * h + 16 * k);
+                const uint4 qla = lds128(blk[r] + 64 * h + 16 * k);       // runs 0 (low nibble) and 2 (high)
+                const uint4 qlb = lds128(blk[r] + 64 * h + 32 + 16 * k);  // runs 1 and 3
+                const uint4 qhv = lds128(blk[r] + 128 + 32 * h + 16 * k);
                 const uint32_t A[4] = {qla.x, qla.y, qla.z, qla.w}, B[4] = {qlb.x, qlb.y, qlb.z, qlb.w}, Hh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
@@ -286,8 +334,9 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_gemv_kernel(StreamArgs a) {
     const SgSmem L = sg_smem(a.in_dim, has_q6);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int *next_group = reinterpret_cast<int *>(smem);
-    float *terms = reinterpret_cast<float *>(smem + L.off_terms) + warp * 64;
-    uint8_t *slots = smem + L.off_ring + (size_t)warp * 2 * L.slot_bytes;
+    const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t terms = sbase + L.off_terms + warp * 256;
+    const uint32_t slots = sbase + L.off_ring + warp * 2 * L.slot_bytes;
     const uint32_t nb = a.in_dim / 256, lp = lanes_per_pair(nb), ppu = 32 / lp;
 
     // groups of ppu pairs, segments concatenated (a group never straddles two segments); this CTA's contiguous share
@@ -358,7 +407,7 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_gemv_kernel(StreamArgs a) {
     for (int i = 0;; ++i) {
         const Unit u = (i & 1) ? u1 : u0;
         if (!u.valid) break;
-        uint8_t *slot = slots + (size_t)(i & 1) * L.slot_bytes;
+        const uint32_t slot = slots + (i & 1) * L.slot_bytes;
         __pipeline_wait_prior(1);
         __syncwarp();
         {
@@ -367,36 +416,33 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_gemv_kernel(StreamArgs a) {
             const uint32_t lb = live ? bl : 0, lpj = live ? pj : 0, gb = u.b0 + lb;
             const uint32_t pb = part_bytes(sg.w.type, lp);
             const bool two = sg.w2.data != nullptr || 2 * (u.pair0 + lpj) + 1 < sg.w.out_dim;
-            const uint8_t *xa = smem + L.off_act + gb * ACT_BLOCK_STRIDE;
-            const float ad = reinterpret_cast<const float *>(smem + L.off_d)[gb];
+            const uint32_t xa = sbase + L.off_act + gb * ACT_BLOCK_STRIDE;
+            const float ad = __uint_as_float(lds32(sbase + L.off_d + gb * 4));
             float term[2];
             if (sg.w.type == TYPE_Q4_K) {
-                const uint8_t *blk[2] = {slot + (2 * lpj) * pb + lb * 144, slot + (2 * lpj + 1) * pb + lb * 144};
-                dot_block_q4k(blk, two ? 2 : 1, xa, reinterpret_cast<const int16_t *>(smem + L.off_bsum) + gb * 8, ad, term);
+                dot_block_q4k(slot + (2 * lpj) * pb + lb * 144, slot + (2 * lpj + 1) * pb + lb * 144, two ? 2 : 1, xa, sbase + L.off_bsum + gb * 16, ad, term);
             } else {
-                const uint8_t *pA = slot + (2 * lpj) * pb, *pB = pA + pb;
-                const uint8_t *blk[2] = {pA + lb * 208, pB + lb * 208};
-                const float dsup[2] = {f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(pA + lp * 208 + 2 * lb)),
-                                       two ? f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(pB + lp * 208 + 2 * lb)) : 0.0f};
-                dot_block_q6k(blk, dsup, two ? 2 : 1, xa, reinterpret_cast<const int16_t *>(smem + L.off_sum16) + gb * 16, ad, term);
+                const uint32_t pA = slot + (2 * lpj) * pb, pB = pA + pb;
+                const float dsup[2] = {f16_bits_to_f32(lds16(pA + lp * 208 + 2 * lb)), two ? f16_bits_to_f32(lds16(pB + lp * 208 + 2 * lb)) : 0.0f};
+                dot_block_q6k(pA + lb * 208, pB + lb * 208, dsup, two ? 2 : 1, xa, sbase + L.off_sum16 + gb * 32, ad, term);
             }
             if (live) {
-                terms[(2 * pj) * lp + bl] = term[0];
-                terms[(2 * pj + 1) * lp + bl] = term[1];
+                sts32(terms + ((2 * pj) * lp + bl) * 4, term[0]);
+                sts32(terms + ((2 * pj + 1) * lp + bl) * 4, term[1]);
             }
         }
         __syncwarp();
         // ordered sum: lane s < 2 * ppu continues the running total of (pair s / 2, row s % 2) over this unit's blocks, in order
         if (u.b0 == 0) tot = 0.0f;
         if (lane < (int)(2 * ppu)) {
-            const float *tp = terms + lane * lp;
+            const uint32_t tp = terms + lane * lp * 4;
             for (uint32_t b = 0; b < u.nblk; b += 4) {
                 float t4[4];
                 if (lp >= 4) {
-                    const float4 v = *reinterpret_cast<const float4 *>(tp + b);
-                    t4[0] = v.x; t4[1] = v.y; t4[2] = v.z; t4[3] = v.w;
+                    const uint4 v = lds128(tp + b * 4);
+                    t4[0] = __uint_as_float(v.x); t4[1] = __uint_as_float(v.y); t4[2] = __uint_as_float(v.z); t4[3] = __uint_as_float(v.w);
                 } else {
-                    for (int k = 0; k < 4; ++k) t4[k] = b + k < lp ? tp[b + k] : 0.0f;
+                    for (int k = 0; k < 4; ++k) t4[k] = b + k < lp ? __uint_as_float(lds32(tp + (b + k) * 4)) : 0.0f;
                 }
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
