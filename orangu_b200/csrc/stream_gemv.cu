@@ -3,15 +3,18 @@
 // One decode step reads every weight byte once and does almost nothing else, so the step time is the
 // HBM time plus whatever stops the stream: kernel boundaries, the norm / quantize prologue, the ramp of
 // a fresh kernel -- and, on this part, instruction issue: at 6.5 TB/s an SM receives 23 bytes per clock
-// and can issue at most four warp instructions in that clock, so the dot loop has to spend well under one
-// instruction per 10 bytes.  Hence:
+// and can issue at most four warp instructions in that clock, so the whole loop (copy, dot, sums, bookkeeping)
+// has to stay near one instruction per 15-20 bytes.  Hence:
 //
 //   * one lane owns one whole super-block, for two rows at once: the six-bit scales of the block are unpacked
 //     once (10 instructions for all eight scales and mins), the activations are read once per pair of rows,
 //     and no cross-lane reduction is needed for the integer sums;
 //   * every warp owns two shared-memory slots and fills them with cp.async (16-byte, L1-bypassing) copies of
 //     its next "units" (32 lanes' worth of blocks, two rows each), so the bytes in flight do not occupy
-//     registers; the first units are requested before anything else happens in the kernel;
+//     registers; the first units are requested before anything else happens in the kernel.  A lane copies
+//     from one row only, at a fixed stride, so a unit costs it one pointer computation and 18 copies;
+//   * the lanes-per-row-pair count is a template parameter and the work is split statically over all warps of
+//     the grid, so the loop has no divisions, no atomics and no per-unit descriptors;
 //   * the operator that produces the activations is the kernel's prologue (RMSNorm scaling and the int8
 //     quantisation, written straight into shared memory in a conflict-free layout), and the operator that
 //     consumes the product is its epilogue (residual add, silu(gate) * up, or RoPE and the fp16 KV append);
@@ -48,6 +51,10 @@ __host__ __device__ inline uint32_t lanes_per_pair(uint32_t nb) {
 
 __host__ __device__ inline int sg_warps(bool has_q6) { return has_q6 ? 3 : 4; }
 
+// Per-segment words the loop needs, kept in shared memory so that a run-time segment index costs one load:
+// [0,1] w.data  [2,3] w2.data  [4] row stride  [5] type  [6] out_dim  [7] pairs  [8] d_off  [9] epilogue  [10,11] y  [12] first group
+constexpr uint32_t SEG_WORDS = 16, SEG_TABLE_BYTES = 3 * SEG_WORDS * 4 + 64;
+
 struct SgSmem {  // byte offsets inside dynamic shared memory
     uint32_t off_act, off_d, off_bsum, off_sum16, off_terms, off_ring, slot_bytes, total;
 };
@@ -55,7 +62,7 @@ struct SgSmem {  // byte offsets inside dynamic shared memory
 __host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6) {
     SgSmem s;
     const uint32_t nb = in_dim / 256, nw = (uint32_t)sg_warps(has_q6), lp = lanes_per_pair(nb);
-    s.off_act = 64;  // [0,64): work counter and broadcast words
+    s.off_act = SEG_TABLE_BYTES;  // [0, SEG_TABLE_BYTES): the segment table
     s.off_d = s.off_act + nb * ACT_BLOCK_STRIDE;
     s.off_bsum = (s.off_d + nb * 4 + 15) & ~15u;  // int16 [nb][8]  sums per 32
     s.off_sum16 = s.off_bsum + nb * 16;            // int16 [nb][16] sums per 16
@@ -159,51 +166,13 @@ __device__ void sg_quantize(const StreamArgs &a, uint8_t *smem, const SgSmem &L,
 }
 
 // ---- units ---------------------------------------------------------------------------------------------------
-// A unit is what one warp processes at a time: `ppu` pairs of rows (32 / lp of them, consecutive in one
-// segment) x up to lp blocks [b0, b0 + nblk).  Lane l works on pair l / lp, block b0 + l % lp.
-struct Unit {
-    uint32_t seg, pair0, n_pairs;  // pairs pair0 .. pair0 + n_pairs - 1 of segment seg
-    uint32_t b0, nblk;
-    bool valid;
-};
+// A unit is what one warp processes at a time: PPU = 32 / LP consecutive pairs of rows of one segment x up to LP
+// blocks [b0, b0 + nblk).  In the dot, lane l works on pair l / LP, block b0 + l % LP.  In the copy, the 2 * PPU
+// row parts of the unit get LP / 2 lanes each: lane l copies chunks l % (LP/2), + LP/2, ... of part l / (LP/2).
+// A "group" is the PPU pairs of a unit over all blocks of their rows; a warp processes whole groups, chunk by chunk,
+// so that the running totals of the rows stay in its registers.
 
-__device__ __forceinline__ void pair_rows(const StreamSeg &sg, uint32_t pair, const uint8_t *&rowA, const uint8_t *&rowB) {
-    if (sg.w2.data) {
-        rowA = sg.w.data + (uint64_t)pair * sg.w.row_stride;
-        rowB = sg.w2.data + (uint64_t)pair * sg.w2.row_stride;
-    } else {
-        rowA = sg.w.data + (uint64_t)(2 * pair) * sg.w.row_stride;
-        rowB = 2 * pair + 1 < sg.w.out_dim ? rowA + sg.w.row_stride : nullptr;
-    }
-}
-
-__device__ __forceinline__ void issue_part(uint32_t dst, const uint8_t *row, uint32_t type, uint32_t d_off, uint32_t lp, uint32_t b0, uint32_t nblk,
-                                           int lane) {
-    if (type == TYPE_Q4_K) {
-        const uint8_t *src = row + (uint64_t)b0 * 144 + lane * 16;
-        dst += lane * 16;
-        for (uint32_t c = lane; c < nblk * 9; c += 32, src += 512, dst += 512) cp_async16(dst, src);
-    } else {
-        const uint8_t *src = row + (uint64_t)b0 * 208 + lane * 16;
-        uint32_t dm = dst + lane * 16;
-        for (uint32_t c = lane; c < nblk * 13; c += 32, src += 512, dm += 512) cp_async16(dm, src);
-        const uint8_t *dsrc = row + d_off + 2 * b0;  // f16 d values of these blocks; b0 is a multiple of 32, so 16-byte aligned
-        if (lane < (int)((nblk * 2 + 15) / 16)) cp_async16(dst + lp * 208 + lane * 16, dsrc + lane * 16);
-    }
-}
-
-__device__ __forceinline__ void issue_unit(uint32_t slot, const StreamArgs &a, const Unit &u, uint32_t lp, int lane) {
-    const StreamSeg &sg = a.seg[u.seg];
-    const uint32_t pb = part_bytes(sg.w.type, lp);
-    for (uint32_t j = 0; j < u.n_pairs; ++j) {
-        const uint8_t *rowA, *rowB;
-        pair_rows(sg, u.pair0 + j, rowA, rowB);
-        issue_part(slot + (2 * j) * pb, rowA, sg.w.type, sg.w.d_off, lp, u.b0, u.nblk, lane);
-        if (rowB) issue_part(slot + (2 * j + 1) * pb, rowB, sg.w.type, sg.w.d_off, lp, u.b0, u.nblk, lane);
-    }
-}
-
-// ---- dot of one super-block for two rows, by one lane -------------------------------------------------------------
+// blk0/blk1: the 144-byte blocks of rows A and B in the slot; xa: the block's 256 int8 activations; bs: its eight per-32 sums.
 __device__ __forceinline__ int dp2a_lo(uint32_t a, uint32_t b, int c) {  // c + a.lo16 * b.byte0 + a.hi16 * b.byte1 (a signed, b unsigned)
     int d;
     asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -215,15 +184,13 @@ __device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {  // c + 
     return d;
 }
 
-// blk[r]: the 144-byte block of row r in the slot; xa: the block's 256 int8 activations; bs: its eight per-32 sums.
-__device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, int n_rows, uint32_t xa, uint32_t bs, float ad, float term[2]) {
+__device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, uint32_t xa, uint32_t bs, float ad, float term[2]) {
     const uint32_t blk[2] = {blk0, blk1};
     uint32_t scl[2], sch[2], ml[2], mh[2], dd[2];
     int isum[2] = {0, 0};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        uint4 hd = make_uint4(0, 0, 0, 0);
-        if (r < n_rows) hd = lds128(blk[r]);
+        const uint4 hd = lds128(blk[r]);
         dd[r] = hd.x;
         // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of four words
         scl[r] = hd.y & 0x3f3f3f3fu;
@@ -236,7 +203,6 @@ __device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, int 
         const uint4 x0 = lds128(xa + 64 * g), x1 = lds128(xa + 64 * g + 16), x2 = lds128(xa + 64 * g + 32), x3 = lds128(xa + 64 * g + 48);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            if (r >= n_rows) continue;
             const uint4 qa = lds128(blk[r] + 16 + 32 * g), qb = lds128(blk[r] + 32 + 32 * g);
             const uint32_t Lm = 0x0f0f0f0fu, Hm = 0xf0f0f0f0u;
             int lo0 = dp4a_us(qa.x & Lm, x0.x, 0), lo1 = dp4a_us(qa.y & Lm, x0.y, 0);
@@ -271,9 +237,8 @@ __device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, int 
     }
 }
 
-// blk[r]: the 208-byte block [ql 128 | qh 64 | scales 16]; dsup[r]: its f16 d; s16: the block's sixteen per-16 sums.
-__device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, const float dsup[2], int n_rows, uint32_t xa, uint32_t s16p, float ad,
-                                              float term[2]) {
+// blk0/blk1: the 208-byte blocks [ql 128 | qh 64 | scales 16]; dsup[r]: their f16 d; s16p: the block's sixteen per-16 sums.
+__device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, const float dsup[2], uint32_t xa, uint32_t s16p, float ad, float term[2]) {
     const uint32_t blk[2] = {blk0, blk1};
     int isum[2] = {0, 0};
 #pragma unroll
@@ -292,7 +257,6 @@ __device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, cons
                             (int16_t)(sv.z & 0xffff), (int16_t)(sv.z >> 16), (int16_t)(sv.w & 0xffff), (int16_t)(sv.w >> 16)};
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            if (r >= n_rows) continue;
             const uint2 scw = lds64(blk[r] + 192 + 8 * h);  // signed scales of groups 8h .. 8h+7
             int dots[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // group 2 * run + k
 #pragma unroll
@@ -327,70 +291,107 @@ __device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, cons
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
-template <int NW>
-__global__ void __launch_bounds__(NW * 32, 2) stream_gemv_kernel(StreamArgs a) {
+template <int LP, bool Q6>  // LP: lanes (= blocks per unit) of a row pair; Q6: the launch has Q6_K segments (three warps, larger slots)
+__global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr bool has_q6 = NW == 3;
-    const SgSmem L = sg_smem(a.in_dim, has_q6);
+    constexpr int NW = Q6 ? 3 : 4, PPU = 32 / LP, HL = LP / 2;
+    constexpr uint32_t PB4 = LP * 144u, PB6 = LP * 208u + ((LP * 2u + 15u) & ~15u);
+    constexpr uint32_t SLOT = 2u * PPU * (Q6 ? PB6 : PB4);
+    const SgSmem L = sg_smem(a.in_dim, Q6);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int *next_group = reinterpret_cast<int *>(smem);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t terms = sbase + L.off_terms + warp * 256;
-    const uint32_t slots = sbase + L.off_ring + warp * 2 * L.slot_bytes;
-    const uint32_t nb = a.in_dim / 256, lp = lanes_per_pair(nb), ppu = 32 / lp;
+    const uint32_t slots = sbase + L.off_ring + warp * 2 * SLOT;
+    const uint32_t nb = a.in_dim / 256, nchunk = (nb + LP - 1) / LP;
 
-    // groups of ppu pairs, segments concatenated (a group never straddles two segments); this CTA's contiguous share
-    uint32_t groups_of[3], pairs_of[3], total_groups = 0;
+    // groups of PPU pairs, segments concatenated (a group never straddles two segments)
+    uint32_t pairs_of[3], first_of[4];
+    first_of[0] = 0;
+#pragma unroll
     for (int s = 0; s < 3; ++s) {
         pairs_of[s] = s >= a.n_seg ? 0u : (a.seg[s].w2.data ? a.seg[s].w.out_dim : (a.seg[s].w.out_dim + 1) / 2);
-        groups_of[s] = (pairs_of[s] + ppu - 1) / ppu;
-        total_groups += groups_of[s];
+        first_of[s + 1] = first_of[s] + (pairs_of[s] + PPU - 1) / PPU;
     }
-    const uint32_t g_begin = (uint32_t)(((uint64_t)total_groups * blockIdx.x) / gridDim.x);
-    const uint32_t g_end = (uint32_t)(((uint64_t)total_groups * (blockIdx.x + 1)) / gridDim.x);
-    if (threadIdx.x == 0) *next_group = (int)g_begin;
+    const uint32_t gb1 = first_of[1], gb2 = first_of[2], G = first_of[3];
+    {
+        auto put = [&](int s, const StreamSeg &g, uint32_t pairs, uint32_t first) {
+            uint32_t *t = reinterpret_cast<uint32_t *>(smem) + s * SEG_WORDS;
+            *reinterpret_cast<const uint8_t **>(t) = g.w.data;
+            *reinterpret_cast<const uint8_t **>(t + 2) = g.w2.data;
+            t[4] = (uint32_t)g.w.row_stride;
+            t[5] = g.w.type;
+            t[6] = g.w.out_dim;
+            t[7] = pairs;
+            t[8] = g.w.d_off;
+            t[9] = (uint32_t)g.epilogue;
+            *reinterpret_cast<float **>(t + 10) = g.y;
+            t[12] = first;
+        };
+        if (threadIdx.x == 0) put(0, a.seg[0], pairs_of[0], 0);
+        else if (threadIdx.x == 1 && a.n_seg > 1) put(1, a.seg[1], pairs_of[1], gb1);
+        else if (threadIdx.x == 2 && a.n_seg > 2) put(2, a.seg[2], pairs_of[2], gb2);
+    }
     __syncthreads();
 
-    // the stream of units this warp will process: groups come off the shared counter, a group's units in block order
-    Unit cur;
-    cur.valid = false;
-    cur.b0 = 0;
-    cur.nblk = nb;
-    auto next_unit = [&]() -> Unit {
-        if (!cur.valid || cur.b0 + cur.nblk >= nb) {  // need a new group
-            int g = 0;
-            if (lane == 0) g = atomicAdd(next_group, 1);
-            g = __shfl_sync(0xffffffffu, g, 0);
-            if ((uint32_t)g >= g_end) {
-                cur.valid = false;
-                cur.nblk = nb;
-                return cur;
+    // this warp's contiguous share of the groups
+    const uint32_t n_warps = gridDim.x * NW, gw = blockIdx.x * NW + warp;
+    const uint32_t g_end = (uint32_t)(((uint64_t)G * (gw + 1)) / n_warps);
+    uint32_t ig = (uint32_t)(((uint64_t)G * gw) / n_warps), ic = 0;  // next unit to request: group, chunk
+    uint32_t cg = ig, cc = 0;                                        // next unit to compute
+
+    const uint32_t q = lane / HL, sub = lane % HL, cj = q >> 1, cr = q & 1;  // copy role: part q = (pair cj, row cr), chunks sub + HL * k
+    const uint32_t pj = lane / LP, bl = lane % LP;                          // dot role
+
+    auto issue = [&](uint32_t slot, uint32_t g, uint32_t ch) {
+        const uint32_t e = sbase + ((g >= gb1) + (g >= gb2)) * (SEG_WORDS * 4);
+        const uint2 wa = lds64(e), wb = lds64(e + 8);
+        const uint4 m = lds128(e + 16);  // row stride, type, out_dim, pairs
+        const bool dual = (wb.x | wb.y) != 0;
+        const uint32_t pair = min((g - lds32(e + 48)) * PPU + cj, m.w - 1);  // past the segment's last pair: fetch that pair again
+        const uint32_t row_index = dual ? pair : min(2 * pair + cr, m.z - 1);
+        const uint2 wp = dual && cr ? wb : wa;
+        const uint8_t *row = reinterpret_cast<const uint8_t *>(((uint64_t)wp.y << 32) | wp.x) + (uint64_t)row_index * m.x;
+        const uint32_t b0 = ch * LP, nblk = min((uint32_t)LP, nb - b0);
+        if (!Q6 || m.y == TYPE_Q4_K) {
+            const uint8_t *src = row + b0 * 144 + sub * 16;
+            const uint32_t dst = slot + q * PB4 + sub * 16;
+            if (nblk == LP) {
+#pragma unroll
+                for (int k = 0; k < 18; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 18; ++k)
+                    if (sub + HL * k < nblk * 9) cp_async16(dst + k * HL * 16, src + k * HL * 16);
             }
-            uint32_t gi = (uint32_t)g;
-            int s = 0;
-            while (gi >= groups_of[s]) {
-                gi -= groups_of[s];
-                ++s;
-            }
-            cur.seg = (uint32_t)s;
-            cur.pair0 = gi * ppu;
-            cur.n_pairs = min(ppu, pairs_of[s] - cur.pair0);
-            cur.b0 = 0;
-            cur.valid = true;
         } else {
-            cur.b0 += cur.nblk;
+            const uint8_t *src = row + b0 * 208 + sub * 16;
+            const uint32_t dst = slot + q * PB6 + sub * 16;
+            if (nblk == LP) {
+#pragma unroll
+                for (int k = 0; k < 26; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 26; ++k)
+                    if (sub + HL * k < nblk * 13) cp_async16(dst + k * HL * 16, src + k * HL * 16);
+            }
+            // the f16 d values of these blocks; b0 is 0 or a multiple of 8, so the source is 16-byte aligned
+            if (sub < (nblk * 2 + 15) / 16) cp_async16(slot + q * PB6 + LP * 208 + sub * 16, row + lds32(e + 32) + 2 * b0 + sub * 16);
         }
-        cur.nblk = min(lp, nb - cur.b0);
-        return cur;
+    };
+    auto advance = [&](uint32_t &g, uint32_t &c) {
+        if (++c == nchunk) {
+            c = 0;
+            ++g;
+        }
     };
 
     // request the first two units before anything else: weights do not depend on the predecessor kernel
-    Unit u0 = next_unit();
-    if (u0.valid) issue_unit(slots, a, u0, lp, lane);
+    if (ig < g_end) issue(slots, ig, ic);
     __pipeline_commit();
-    Unit u1 = next_unit();
-    if (u1.valid) issue_unit(slots + L.slot_bytes, a, u1, lp, lane);
+    advance(ig, ic);
+    if (ig < g_end) issue(slots + SLOT, ig, ic);
     __pipeline_commit();
+    advance(ig, ic);
 
     // ---- prologue ---------------------------------------------------------------------------------------------
     if (a.wait_dependency) {
@@ -401,98 +402,110 @@ __global__ void __launch_bounds__(NW * 32, 2) stream_gemv_kernel(StreamArgs a) {
     sg_quantize(a, smem, L, norm_scale, NW);
     __syncthreads();
 
-    // ---- main loop: slot 0 / slot 1 alternate ---------------------------------------------------------------------
-    const uint32_t pj = lane / lp, bl = lane % lp;
-    float tot = 0.0f;  // lanes 2j, 2j+1: rows A, B of the unit's pair j (running over the units of a long row)
-    for (int i = 0;; ++i) {
-        const Unit u = (i & 1) ? u1 : u0;
-        if (!u.valid) break;
-        const uint32_t slot = slots + (i & 1) * L.slot_bytes;
+    // ---- main loop ------------------------------------------------------------------------------------------------
+    float tot = 0.0f;  // lanes 2j, 2j+1: rows A, B of the group's pair j, running over the chunks of the row
+    uint32_t par = 0;
+    while (cg < g_end) {
+        const uint32_t slot = slots + par * SLOT;
+        const uint32_t e = sbase + ((cg >= gb1) + (cg >= gb2)) * (SEG_WORDS * 4);
+        const uint32_t b0 = cc * LP, nblk = min((uint32_t)LP, nb - b0);
         __pipeline_wait_prior(1);
         __syncwarp();
         {
-            const StreamSeg &sg = a.seg[u.seg];
-            const bool live = pj < u.n_pairs && bl < u.nblk;
-            const uint32_t lb = live ? bl : 0, lpj = live ? pj : 0, gb = u.b0 + lb;
-            const uint32_t pb = part_bytes(sg.w.type, lp);
-            const bool two = sg.w2.data != nullptr || 2 * (u.pair0 + lpj) + 1 < sg.w.out_dim;
+            const uint32_t gb = min(b0 + bl, nb - 1);  // lanes past the row's end recompute its last block; nobody reads their terms
             const uint32_t xa = sbase + L.off_act + gb * ACT_BLOCK_STRIDE;
             const float ad = __uint_as_float(lds32(sbase + L.off_d + gb * 4));
             float term[2];
-            if (sg.w.type == TYPE_Q4_K) {
-                dot_block_q4k(slot + (2 * lpj) * pb + lb * 144, slot + (2 * lpj + 1) * pb + lb * 144, two ? 2 : 1, xa, sbase + L.off_bsum + gb * 16, ad, term);
+            if (!Q6 || lds32(e + 20) == TYPE_Q4_K) {
+                const uint32_t pA = slot + (2 * pj) * PB4 + bl * 144;
+                dot_block_q4k(pA, pA + PB4, xa, sbase + L.off_bsum + gb * 16, ad, term);
             } else {
-                const uint32_t pA = slot + (2 * lpj) * pb, pB = pA + pb;
-                const float dsup[2] = {f16_bits_to_f32(lds16(pA + lp * 208 + 2 * lb)), two ? f16_bits_to_f32(lds16(pB + lp * 208 + 2 * lb)) : 0.0f};
-                dot_block_q6k(pA + lb * 208, pB + lb * 208, dsup, two ? 2 : 1, xa, sbase + L.off_sum16 + gb * 32, ad, term);
+                const uint32_t pA = slot + (2 * pj) * PB6, pB = pA + PB6;
+                const float dsup[2] = {f16_bits_to_f32(lds16(pA + LP * 208 + 2 * bl)), f16_bits_to_f32(lds16(pB + LP * 208 + 2 * bl))};
+                dot_block_q6k(pA + bl * 208, pB + bl * 208, dsup, xa, sbase + L.off_sum16 + gb * 32, ad, term);
             }
-            if (live) {
-                sts32(terms + ((2 * pj) * lp + bl) * 4, term[0]);
-                sts32(terms + ((2 * pj + 1) * lp + bl) * 4, term[1]);
-            }
+            sts32(terms + ((2 * pj) * LP + bl) * 4, term[0]);
+            sts32(terms + ((2 * pj + 1) * LP + bl) * 4, term[1]);
         }
         __syncwarp();
-        // ordered sum: lane s < 2 * ppu continues the running total of (pair s / 2, row s % 2) over this unit's blocks, in order
-        if (u.b0 == 0) tot = 0.0f;
-        if (lane < (int)(2 * ppu)) {
-            const uint32_t tp = terms + lane * lp * 4;
-            for (uint32_t b = 0; b < u.nblk; b += 4) {
-                float t4[4];
-                if (lp >= 4) {
-                    const uint4 v = lds128(tp + b * 4);
-                    t4[0] = __uint_as_float(v.x); t4[1] = __uint_as_float(v.y); t4[2] = __uint_as_float(v.z); t4[3] = __uint_as_float(v.w);
-                } else {
-                    for (int k = 0; k < 4; ++k) t4[k] = b + k < lp ? __uint_as_float(lds32(tp + (b + k) * 4)) : 0.0f;
-                }
+        // ordered sum: lane s < 2 * PPU continues the running total of (pair s / 2, row s % 2) over this chunk's blocks, in order
+        if (cc == 0) tot = 0.0f;
+        if (lane < 2 * PPU) {
+            const uint32_t tp = terms + lane * LP * 4;
+            if constexpr (LP >= 4) {
+                if (nblk == LP) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (b + k < u.nblk) tot = __fadd_rn(tot, t4[k]);
+                    for (int b = 0; b < LP; b += 4) {
+                        const uint4 v = lds128(tp + b * 4);
+                        tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, __uint_as_float(v.x)), __uint_as_float(v.y)), __uint_as_float(v.z)), __uint_as_float(v.w));
+                    }
+                } else {
+#pragma unroll
+                    for (int b = 0; b < LP; b += 4) {
+                        if (b < (int)nblk) {
+                            const uint4 v = lds128(tp + b * 4);
+                            tot = __fadd_rn(tot, __uint_as_float(v.x));
+                            if (b + 1 < (int)nblk) tot = __fadd_rn(tot, __uint_as_float(v.y));
+                            if (b + 2 < (int)nblk) tot = __fadd_rn(tot, __uint_as_float(v.z));
+                            if (b + 3 < (int)nblk) tot = __fadd_rn(tot, __uint_as_float(v.w));
+                        }
+                    }
+                }
+            } else {
+                const uint2 v = lds64(tp);
+                tot = __fadd_rn(tot, __uint_as_float(v.x));
+                if (nblk > 1) tot = __fadd_rn(tot, __uint_as_float(v.y));
             }
         }
         __syncwarp();
         // refill the slot just consumed
-        const Unit nu = next_unit();
-        if (nu.valid) issue_unit(slot, a, nu, lp, lane);
+        if (ig < g_end) issue(slot, ig, ic);
         __pipeline_commit();
-        if (i & 1) u1 = nu;
-        else u0 = nu;
+        advance(ig, ic);
+        const bool row_done = cc + 1 == nchunk;
+        const uint32_t g_done = cg;
+        advance(cg, cc);
+        par ^= 1;
+        if (!row_done) continue;
 
-        if (u.b0 + u.nblk < nb) continue;
         // ---- epilogue of the finished pairs: lane 2j holds row A's total, lane 2j+1 row B's --------------------------
         const float tB = __shfl_down_sync(0xffffffffu, tot, 1);
-        if ((lane & 1) || lane >= (int)(2 * u.n_pairs)) continue;
+        const uint4 m = lds128(e + 16);  // row stride, type, out_dim, pairs
+        const uint32_t pair = (g_done - lds32(e + 48)) * PPU + (lane >> 1);
+        if ((lane & 1) || lane >= 2 * PPU || pair >= m.w) continue;
         const float tA = tot;
-        const StreamSeg &sg = a.seg[u.seg];
-        const uint32_t pair = u.pair0 + (lane >> 1);
-        const bool hasB = sg.w2.data != nullptr || 2 * pair + 1 < sg.w.out_dim;
-        switch (sg.epilogue) {
+        const uint2 wb = lds64(e + 8), yp = lds64(e + 40);
+        float *y = reinterpret_cast<float *>(((uint64_t)yp.y << 32) | yp.x);
+        const int epilogue = (int)lds32(e + 36);
+        const bool hasB = (wb.x | wb.y) != 0 || 2 * pair + 1 < m.z;
+        switch (epilogue) {
         case SG_EP_STORE:
-            sg.y[2 * pair] = tA;
-            if (hasB) sg.y[2 * pair + 1] = tB;
+            y[2 * pair] = tA;
+            if (hasB) y[2 * pair + 1] = tB;
             break;
         case SG_EP_RESIDUAL:
-            sg.y[2 * pair] = __fadd_rn(a.residual[2 * pair], tA);
-            if (hasB) sg.y[2 * pair + 1] = __fadd_rn(a.residual[2 * pair + 1], tB);
+            y[2 * pair] = __fadd_rn(a.residual[2 * pair], tA);
+            if (hasB) y[2 * pair + 1] = __fadd_rn(a.residual[2 * pair + 1], tB);
             break;
         case SG_EP_SWIGLU:
-            sg.y[pair] = silu_mul_exact(tA, tB);
+            y[pair] = silu_mul_exact(tA, tB);
             break;
         default: {  // q, k, v rows of the token: rotate (q, k) and append (k, v) to the page as f16
             const uint32_t row = 2 * pair, hd = a.head_dim, head = row / hd, idx = (row % hd) / 2;
             const uint32_t pos = *a.position;
             float oa = tA, ob_ = tB;
-            if (sg.epilogue != SG_EP_V && 2 * idx < a.rope_dim) {
+            if (epilogue != SG_EP_V && 2 * idx < a.rope_dim) {
                 const float2 sc = reinterpret_cast<const float2 *>(a.rope_table)[(uint64_t)pos * (a.rope_dim / 2) + idx];  // (sin, cos)
                 oa = __fsub_rn(__fmul_rn(tA, sc.y), __fmul_rn(tB, sc.x));
                 ob_ = __fadd_rn(__fmul_rn(tA, sc.x), __fmul_rn(tB, sc.y));
             }
-            if (sg.epilogue == SG_EP_ROPE_Q) {
-                sg.y[row] = oa;
-                sg.y[row + 1] = ob_;
+            if (epilogue == SG_EP_ROPE_Q) {
+                y[row] = oa;
+                y[row + 1] = ob_;
             } else {
                 const int32_t page = (*a.page_table)[pos / KV_PAGE];
                 const uint64_t o = (((uint64_t)page * a.n_head_kv + head) * KV_PAGE + pos % KV_PAGE) * hd + (row % hd);
-                __half *pool = sg.epilogue == SG_EP_ROPE_K ? a.k_pool : a.v_pool;
+                __half *pool = epilogue == SG_EP_ROPE_K ? a.k_pool : a.v_pool;
                 *reinterpret_cast<__half2 *>(pool + o) = __floats2half2_rn(oa, ob_);
             }
             break;
@@ -526,7 +539,7 @@ bool stream_gemv_supported(const StreamArgs &a) {
     for (int s = 0; s < a.n_seg; ++s) {
         const StreamSeg &g = a.seg[s];
         if (g.w.type != TYPE_Q4_K && g.w.type != TYPE_Q6_K) return false;
-        if (g.w.in_dim != a.in_dim) return false;
+        if (g.w.in_dim != a.in_dim || g.w.row_stride >> 32 || g.w.out_dim == 0) return false;
         if (g.w2.data && (g.w2.type != g.w.type || g.w2.in_dim != a.in_dim || g.w2.out_dim != g.w.out_dim)) return false;
         if (g.epilogue >= SG_EP_ROPE_Q && (g.w.out_dim & 1)) return false;
         q6 = q6 || g.w.type == TYPE_Q6_K;
@@ -553,24 +566,40 @@ void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool
     cudaLaunchKernelEx(&cfg, norm_scale_kernel, x, dim, eps, out, programmatic);
 }
 
-void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st) {
-    bool q6 = false;
-    uint32_t pairs = 0;
-    for (int s = 0; s < a.n_seg; ++s) {
-        q6 = q6 || a.seg[s].w.type == TYPE_Q6_K;
-        pairs += a.seg[s].w2.data ? a.seg[s].w.out_dim : (a.seg[s].w.out_dim + 1) / 2;
-    }
-    const SgSmem L = sg_smem(a.in_dim, q6);
-    static bool configured = false;
+template <int LP, bool Q6>
+void launch_instance(const cudaLaunchConfig_t &cfg, const StreamArgs &args) {
+    static bool configured = false;  // one flag per instantiation
     if (!configured) {
-        cudaFuncSetAttribute(stream_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 108 * 1024);
-        cudaFuncSetAttribute(stream_gemv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 108 * 1024);
+        cudaFuncSetAttribute(stream_gemv_kernel<LP, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 108 * 1024);
         configured = true;
     }
+    cudaLaunchKernelEx(&cfg, stream_gemv_kernel<LP, Q6>, args);
+}
+
+template <bool Q6>
+void launch_lp(uint32_t lp, const cudaLaunchConfig_t &cfg, const StreamArgs &args) {
+    switch (lp) {
+    case 2: launch_instance<2, Q6>(cfg, args); break;
+    case 4: launch_instance<4, Q6>(cfg, args); break;
+    case 8: launch_instance<8, Q6>(cfg, args); break;
+    case 16: launch_instance<16, Q6>(cfg, args); break;
+    default: launch_instance<32, Q6>(cfg, args); break;
+    }
+}
+
+void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st) {
+    bool q6 = false;
+    uint32_t groups = 0;
+    const uint32_t lp = lanes_per_pair(a.in_dim / 256), ppu = 32 / lp;
+    for (int s = 0; s < a.n_seg; ++s) {
+        q6 = q6 || a.seg[s].w.type == TYPE_Q6_K;
+        const uint32_t pairs = a.seg[s].w2.data ? a.seg[s].w.out_dim : (a.seg[s].w.out_dim + 1) / 2;
+        groups += (pairs + ppu - 1) / ppu;
+    }
+    const SgSmem L = sg_smem(a.in_dim, q6);
     StreamArgs args = a;
     args.wait_dependency = programmatic;
-    const uint32_t nw = (uint32_t)sg_warps(q6), ppu = 32 / lanes_per_pair(a.in_dim / 256);
-    const uint32_t groups = (pairs + ppu - 1) / ppu;
+    const uint32_t nw = (uint32_t)sg_warps(q6);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(std::min<uint32_t>(2u * (uint32_t)sm_count, std::max(1u, (groups + nw - 1) / nw)));  // two CTAs per SM
     cfg.blockDim = dim3(nw * 32);
@@ -581,8 +610,8 @@ void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cu
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    if (q6) cudaLaunchKernelEx(&cfg, stream_gemv_kernel<3>, args);
-    else cudaLaunchKernelEx(&cfg, stream_gemv_kernel<4>, args);
+    if (q6) launch_lp<true>(lp, cfg, args);
+    else launch_lp<false>(lp, cfg, args);
 }
 
 }  // namespace ob
