@@ -56,7 +56,7 @@ size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, boo
 uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order);  // kernels launch_gemv issues
 
 // ---- stream_gemv.cu: fused single-token products for decode (Q4_K / Q6_K weights)
-enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1 };
+enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1, SG_PRO_READY = 2 };
 enum StreamEpilogue { SG_EP_STORE = 0, SG_EP_RESIDUAL = 1, SG_EP_SWIGLU = 2, SG_EP_ROPE_Q = 3, SG_EP_ROPE_K = 4, SG_EP_V = 5 };
 struct StreamSeg {
     DevWeight w;       // rows 2p, 2p+1 form pair p ...
@@ -73,6 +73,7 @@ struct StreamArgs {
     const float *norm_w;     // RMSNORM: weight [in_dim]
     const float *norm_scale; // RMSNORM: device word holding 1 / sqrt(mean(x^2) + eps), from launch_norm_scale
     float eps;
+    const uint8_t *ready;    // READY: the token's quantized activations as launch_norm_quant / launch_quant_image left them
     const float *residual;   // RESIDUAL: y = residual + product (may alias y)
     // RoPE + KV append (ROPE_Q / ROPE_K / V)
     const float *rope_table; // [pos][rope_dim/2](sin, cos)
@@ -85,6 +86,12 @@ struct StreamArgs {
 bool stream_gemv_supported(const StreamArgs &a);
 void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st);
 void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool programmatic, cudaStream_t st);
+// Bytes of the quantized-activation image of one token row of `dim` elements (dim a multiple of 256).
+size_t act_image_bytes(uint32_t dim);
+// RMSNorm scale as launch_norm_scale (also stored to *scale_out), then (x * scale) * norm_w quantized per 256 into `image`.
+void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, bool programmatic, cudaStream_t st);
+// x quantized per 256 into `image`.
+void launch_quant_image(const float *x, uint32_t dim, uint8_t *image, bool programmatic, cudaStream_t st);
 
 // ---- glue.cu
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st);

@@ -79,6 +79,7 @@ struct ob_model {
     ActPair act_embd, act_attn, act_ff;
     float *part_o = nullptr, *part_ml = nullptr;
     float *norm_scale = nullptr;      // [2] RMSNorm scales for the fused decode kernels (attention norm, FFN / output norm)
+    uint8_t *ready_embd = nullptr, *ready_attn = nullptr, *ready_ff = nullptr;  // quantized activations of the single decode token
     float *scores = nullptr;          // exact-order attention scratch [T][n_head_l][score_stride]
     uint32_t score_stride = 0, exact_attn_max_pos = 0;
     uint32_t max_splits = 1;
@@ -224,10 +225,8 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
     case 1:
         a.n_seg = 3;
         a.in_dim = c.n_embd;
-        a.prologue = SG_PRO_RMSNORM;
-        a.x = m->x;
-        a.norm_w = L.attn_norm;
-        a.norm_scale = m->norm_scale;
+        a.prologue = SG_PRO_READY;
+        a.ready = m->ready_embd;
         a.seg[0] = StreamSeg{L.wq->w, DevWeight{}, m->q, SG_EP_ROPE_Q};
         a.seg[1] = StreamSeg{L.wk->w, DevWeight{}, nullptr, SG_EP_ROPE_K};
         a.seg[2] = StreamSeg{L.wv->w, DevWeight{}, nullptr, SG_EP_V};
@@ -243,35 +242,31 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
     case 2:
         a.n_seg = 1;
         a.in_dim = q_dim;
-        a.prologue = SG_PRO_PLAIN;
-        a.x = m->attn;
+        a.prologue = SG_PRO_READY;
+        a.ready = m->ready_attn;
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
         break;
     case 3:
         a.n_seg = 1;
         a.in_dim = c.n_embd;
-        a.prologue = SG_PRO_RMSNORM;
-        a.x = m->x;
-        a.norm_w = L.ffn_norm;
-        a.norm_scale = m->norm_scale + 1;
+        a.prologue = SG_PRO_READY;
+        a.ready = m->ready_embd;
         a.seg[0] = StreamSeg{L.gate->w, L.up->w, m->gate, SG_EP_SWIGLU};
         break;
     case 4:
         a.n_seg = 1;
         a.in_dim = m->n_ff_l;
-        a.prologue = SG_PRO_PLAIN;
-        a.x = m->gate;
+        a.prologue = SG_PRO_READY;
+        a.ready = m->ready_ff;
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
         break;
     default:
         a.n_seg = 1;
         a.in_dim = c.n_embd;
-        a.prologue = SG_PRO_RMSNORM;
-        a.x = m->x;
-        a.norm_w = m->output_norm;
-        a.norm_scale = m->norm_scale;
+        a.prologue = SG_PRO_READY;
+        a.ready = m->ready_embd;
         a.seg[0] = StreamSeg{m->output->w, DevWeight{}, m->logits, SG_EP_STORE};
         break;
     }
@@ -343,7 +338,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
 
     // Batch-1 decode on one GPU with K-type weights takes the fused streaming kernels (stream_gemv.cu):
     // norm / quantize as prologue, RoPE + KV append, residual and SwiGLU as epilogues, 5 product kernels per layer.
-    const bool stream = T == 1 && !tp && m->use_stream;
+    const bool stream = T == 1 && !tp && m->use_stream && m->ready_embd;
     auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
 
     for (uint32_t li = 0; li < c.n_layer; ++li) {
@@ -351,14 +346,16 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         const bool stream_layer = stream && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
                                   k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
         if (stream_layer) {
-            launch_norm_scale(m->x, n_embd, c.rms_eps, m->norm_scale, true, st);
+            launch_norm_quant(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 1), m->ctx->sm_count, true, st);
             run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
+            launch_quant_image(m->attn, q_dim, m->ready_attn, true, st);
             launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
-            launch_norm_scale(m->x, n_embd, c.rms_eps, m->norm_scale + 1, true, st);
+            launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
+            launch_quant_image(m->gate, n_ff, m->ready_ff, true, st);
             launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
-            m->ctx->launches += 6;
+            m->ctx->launches += 8;
             continue;
         }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
@@ -408,8 +405,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
 
     if (n_logit_rows == 1 && stream && k_type(m->output)) {
         StreamArgs la = stream_args(m, 0, 5);
-        la.x = m->x + (size_t)logit_row0 * n_embd;
-        launch_norm_scale(la.x, n_embd, c.rms_eps, m->norm_scale, true, st);
+        launch_norm_quant(m->x + (size_t)logit_row0 * n_embd, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
         m->ctx->launches += 2;
         if (want_argmax) {
@@ -612,6 +608,11 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     m->score_stride = (m->exact_attn_max_pos + 63) / 64 * 64;
     if (m->score_stride && (rc = dev_alloc(m, &m->scores, (size_t)T * m->n_head_l * m->score_stride))) return bail(rc);
     if ((rc = dev_alloc(m, &m->norm_scale, 4))) return bail(rc);
+    if (c.n_embd % 256 == 0 && (m->n_head_l * c.head_dim) % 256 == 0 && m->n_ff_l % 256 == 0) {
+        if ((rc = dev_alloc(m, &m->ready_embd, act_image_bytes(c.n_embd)))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->ready_attn, act_image_bytes(m->n_head_l * c.head_dim)))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->ready_ff, act_image_bytes(m->n_ff_l)))) return bail(rc);
+    }
     const MetaLayout ml(T);
     if ((rc = dev_alloc(m, &m->d_meta, ml.bytes))) return bail(rc);
     if ((rc = dev_alloc(m, &m->d_out_tokens, T))) return bail(rc);
@@ -752,8 +753,9 @@ int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t variant, uint32_t 
             if (sg.w2.data) n += (uint64_t)sg.w2.nb * block_bytes_gguf(sg.w2.type) * sg.w2.out_dim;
             return n;
         };
-        launch_norm_scale(m->x, m->cfg.n_embd, m->cfg.rms_eps, m->norm_scale, false, st);
-        launch_norm_scale(m->x, m->cfg.n_embd, m->cfg.rms_eps, m->norm_scale + 1, false, st);
+        launch_norm_quant(m->x, m->output_norm, m->cfg.n_embd, m->cfg.rms_eps, nullptr, m->ready_embd, false, st);
+        launch_quant_image(m->attn, m->n_head_l * m->cfg.head_dim, m->ready_attn, false, st);
+        launch_quant_image(m->gate, m->n_ff_l, m->ready_ff, false, st);
         for (uint32_t it = 0; it <= iters; ++it) {  // pass 0 is a warm-up
             if (it == 1) OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
             const uint32_t n = variant == 5 ? 1u : m->cfg.n_layer;

@@ -51,6 +51,21 @@ __host__ __device__ inline uint32_t lanes_per_pair(uint32_t nb) {
 
 __host__ __device__ inline int sg_warps(bool has_q6) { return has_q6 ? 3 : 4; }
 
+// The "image" is what the dot loop reads from shared memory: [nb][272] int8 (256 used), [nb] f32 scales, [nb][8] int16
+// sums per 32, [nb][16] int16 sums per 16.  A kernel either builds it in its own shared memory from the fp32 row, or a
+// producer builds it once in global memory and every CTA of the consumer copies it.
+struct ActImage {
+    uint32_t off_d, off_bsum, off_sum16, bytes;
+};
+__host__ __device__ inline ActImage act_image(uint32_t nb) {
+    ActImage im;
+    im.off_d = nb * ACT_BLOCK_STRIDE;
+    im.off_bsum = (im.off_d + nb * 4 + 15) & ~15u;
+    im.off_sum16 = im.off_bsum + nb * 16;
+    im.bytes = im.off_sum16 + nb * 32;
+    return im;
+}
+
 // Per-segment words the loop needs, kept in shared memory so that a run-time segment index costs one load:
 // [0,1] w.data  [2,3] w2.data  [4] row stride  [5] type  [6] out_dim  [7] pairs  [8] d_off  [9] epilogue  [10,11] y  [12] first group
 constexpr uint32_t SEG_WORDS = 16, SEG_TABLE_BYTES = 3 * SEG_WORDS * 4 + 64;
@@ -63,10 +78,11 @@ __host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6) {
     SgSmem s;
     const uint32_t nb = in_dim / 256, nw = (uint32_t)sg_warps(has_q6), lp = lanes_per_pair(nb);
     s.off_act = SEG_TABLE_BYTES;  // [0, SEG_TABLE_BYTES): the segment table
-    s.off_d = s.off_act + nb * ACT_BLOCK_STRIDE;
-    s.off_bsum = (s.off_d + nb * 4 + 15) & ~15u;  // int16 [nb][8]  sums per 32
-    s.off_sum16 = s.off_bsum + nb * 16;            // int16 [nb][16] sums per 16
-    s.off_terms = s.off_sum16 + nb * 32;           // float [warp][pair slot][row][lp]  = [warp][64]
+    const ActImage im = act_image(nb);
+    s.off_d = s.off_act + im.off_d;
+    s.off_bsum = s.off_act + im.off_bsum;    // int16 [nb][8]  sums per 32
+    s.off_sum16 = s.off_act + im.off_sum16;  // int16 [nb][16] sums per 16
+    s.off_terms = s.off_act + im.bytes;      // float [warp][pair slot][row][lp]  = [warp][64]
     s.off_ring = s.off_terms + nw * 64 * 4;
     s.slot_bytes = (32 / lp) * 2 * part_bytes(has_q6 ? TYPE_Q6_K : TYPE_Q4_K, lp);
     s.total = s.off_ring + nw * 2 * s.slot_bytes;
@@ -104,14 +120,15 @@ __device__ __forceinline__ float silu_mul_exact(float g, float u) {
     return __fmul_rn(s, u);
 }
 
-// ---- prologue: activations of the single token, quantized per 256 into shared memory ---------------------
-// Every warp takes blocks round-robin; a lane owns 8 consecutive elements of the block.
-__device__ void sg_quantize(const StreamArgs &a, uint8_t *smem, const SgSmem &L, float norm_scale, uint32_t n_warps) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t nb = a.in_dim / 256;
-    float *sd = reinterpret_cast<float *>(smem + L.off_d);
-    int16_t *bsum = reinterpret_cast<int16_t *>(smem + L.off_bsum);
-    int16_t *sum16 = reinterpret_cast<int16_t *>(smem + L.off_sum16);
+// ---- activations of the single token, quantized per 256 ------------------------------------------------------
+// Warps `warp`, `warp + n_warps`, ... of the callers take blocks round-robin; a lane owns 8 consecutive elements of the block.
+// x * norm_scale * norm_w is quantized when norm_w != nullptr (tensor.rs:747), x itself otherwise.
+__device__ void quantize_image(const float *x, const float *norm_w, float norm_scale, uint32_t nb, uint8_t *img, uint32_t warp, uint32_t n_warps) {
+    const int lane = threadIdx.x & 31;
+    const ActImage im = act_image(nb);
+    float *sd = reinterpret_cast<float *>(img + im.off_d);
+    int16_t *bsum = reinterpret_cast<int16_t *>(img + im.off_bsum);
+    int16_t *sum16 = reinterpret_cast<int16_t *>(img + im.off_sum16);
     // four blocks per pass, all their loads issued before any arithmetic: the pass costs one memory latency, not four
     for (uint32_t bb = warp; bb < nb; bb += 4 * n_warps) {
         float v[4][8];
@@ -120,17 +137,17 @@ __device__ void sg_quantize(const StreamArgs &a, uint8_t *smem, const SgSmem &L,
             const uint32_t b = bb + k * n_warps;
             if (b < nb) {
                 const uint32_t e0 = b * 256 + lane * 8;
-                const float4 x0 = *reinterpret_cast<const float4 *>(a.x + e0), x1 = *reinterpret_cast<const float4 *>(a.x + e0 + 4);
+                const float4 x0 = __ldcg(reinterpret_cast<const float4 *>(x + e0)), x1 = __ldcg(reinterpret_cast<const float4 *>(x + e0 + 4));
                 v[k][0] = x0.x; v[k][1] = x0.y; v[k][2] = x0.z; v[k][3] = x0.w; v[k][4] = x1.x; v[k][5] = x1.y; v[k][6] = x1.z; v[k][7] = x1.w;
             }
         }
-        if (a.prologue == SG_PRO_RMSNORM) {
+        if (norm_w) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const uint32_t b = bb + k * n_warps;
                 if (b < nb) {
                     const uint32_t e0 = b * 256 + lane * 8;
-                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0)), w1 = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0 + 4));
+                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + e0)), w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + e0 + 4));
                     const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                     for (int i = 0; i < 8; ++i) v[k][i] = __fmul_rn(__fmul_rn(v[k][i], norm_scale), w[i]);  // (v * scale) * w, tensor.rs:747
@@ -157,7 +174,7 @@ __device__ void sg_quantize(const StreamArgs &a, uint8_t *smem, const SgSmem &L,
             const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
             const uint32_t lo = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
             const uint32_t hi = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-            *reinterpret_cast<uint2 *>(smem + L.off_act + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
+            *reinterpret_cast<uint2 *>(img + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
             if ((lane & 1) == 0) sum16[b * 16 + (lane >> 1)] = (int16_t)s16;
             if ((lane & 3) == 0) bsum[b * 8 + (lane >> 2)] = (int16_t)s32;
             if (lane == 0) sd[b] = scale;
@@ -398,8 +415,16 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the successor may start requesting its weights
         asm volatile("griddepcontrol.wait;" ::: "memory");               // the predecessor's output is complete and visible
     }
-    const float norm_scale = a.prologue == SG_PRO_RMSNORM ? *a.norm_scale : 1.0f;
-    sg_quantize(a, smem, L, norm_scale, NW);
+    if (a.prologue == SG_PRO_READY) {  // the producer left the image in global memory
+        const uint32_t n16 = (L.off_terms - L.off_act) / 16;
+        for (uint32_t c = threadIdx.x; c < n16; c += NW * 32) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(a.ready) + c);
+            *reinterpret_cast<uint4 *>(smem + L.off_act + c * 16) = v;
+        }
+    } else {
+        const bool norm = a.prologue == SG_PRO_RMSNORM;
+        quantize_image(a.x, norm ? a.norm_w : nullptr, norm ? *a.norm_scale : 1.0f, nb, smem + L.off_act, warp, NW);
+    }
     __syncthreads();
 
     // ---- main loop ------------------------------------------------------------------------------------------------
@@ -515,20 +540,32 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
     __pipeline_wait_prior(0);
 }
 
-// 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.
+// 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.  With `image` set the
+// CTA goes on to quantize (x * scale) * norm_w per 256, so that the product kernels that follow only copy the result.
 constexpr int NS_THREADS = 1024;
-__global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__restrict__ x, uint32_t dim, float eps, float *__restrict__ out,
-                                                                bool wait_dependency) {
+__global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__restrict__ x, const float *__restrict__ norm_w, uint32_t dim, float eps,
+                                                                float *__restrict__ out, uint8_t *__restrict__ image, bool wait_dependency) {
     extern __shared__ float srow[];  // the row, one pad word per 16
     __shared__ SeqSumWorkspace<NS_THREADS> ws;
     if (wait_dependency) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) srow[i + (i >> 4)] = x[i];
+    for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) srow[i + (i >> 4)] = __ldcg(x + i);
     __syncthreads();
     const float t = cta_sequential_sum<NS_THREADS>([&](uint32_t i) { const float v = srow[i + (i >> 4)]; return __fmul_rn(v, v); }, dim, ws);
-    if (threadIdx.x == 0) *out = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
+    const float scale = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
+    if (threadIdx.x == 0 && out) *out = scale;
+    if (image) quantize_image(x, norm_w, scale, dim / 256, image, threadIdx.x >> 5, NS_THREADS / 32);
+}
+
+// x quantized per 256 into the image, one warp per block.
+__global__ void __launch_bounds__(128) quant_image_kernel(const float *__restrict__ x, uint32_t nb, uint8_t *__restrict__ image, bool wait_dependency) {
+    if (wait_dependency) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    quantize_image(x, nullptr, 1.0f, nb, image, blockIdx.x * 4 + (threadIdx.x >> 5), gridDim.x * 4);
 }
 
 }  // namespace
@@ -547,7 +584,9 @@ bool stream_gemv_supported(const StreamArgs &a) {
     return sg_smem(a.in_dim, q6).total <= 108 * 1024;
 }
 
-void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool programmatic, cudaStream_t st) {
+size_t act_image_bytes(uint32_t dim) { return act_image(dim / 256).bytes; }
+
+void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, bool programmatic, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(norm_scale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -563,7 +602,25 @@ void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, norm_scale_kernel, x, dim, eps, out, programmatic);
+    cudaLaunchKernelEx(&cfg, norm_scale_kernel, x, norm_w, dim, eps, scale_out, image, programmatic);
+}
+
+void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool programmatic, cudaStream_t st) {
+    launch_norm_quant(x, nullptr, dim, eps, out, nullptr, programmatic, st);
+}
+
+void launch_quant_image(const float *x, uint32_t dim, uint8_t *image, bool programmatic, cudaStream_t st) {
+    const uint32_t nb = dim / 256;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((nb + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, quant_image_kernel, x, nb, image, programmatic);
 }
 
 template <int LP, bool Q6>
