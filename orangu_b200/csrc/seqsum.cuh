@@ -20,6 +20,11 @@
 
 #include <stdint.h>
 
+#ifndef SEQSUM_MARK
+#define SEQSUM_MARK(i)      // a timing harness may define these to record the clock at phase boundaries
+#define SEQSUM_VALUE(i, v)  // ... and a value
+#endif
+
 namespace ob {
 
 namespace seqsum_detail {
@@ -136,17 +141,17 @@ __device__ float warp_sequential_sum(F term, uint32_t n) {
 // additions, one after the other.  Every application checks that s really is in the assumed binade; if that
 // ever failed the warp-level routine above recomputes the sum from scratch.
 // ----------------------------------------------------------------------------------------------------
-struct SeqSumRecord {
-    uint32_t c0, c1;   // composed function: of the thread's terms, then (after the warp's scan) of its segment so far
-    uint32_t es;       // biased exponent of the binade the function assumes (0: the thread has no terms)
-    uint32_t dirty;    // the thread holds a term that must be added for real
-};
+constexpr int SEQSUM_MAX_EVENTS = 256;
 
 template <int THREADS>
 struct SeqSumWorkspace {
-    SeqSumRecord rec[THREADS];
+    // The serial part of the sum as a list of events in term order.  An event is either a composed increment function of
+    // a run of safe terms (a0, a1 by parity; es = the binade it assumes) or up to four terms to be added for real.
+    uint4 ev_fn[SEQSUM_MAX_EVENTS];      // a0, a1, es, dirty
+    float4 ev_terms[SEQSUM_MAX_EVENTS];  // four terms, +0 where there is none (s + 0 == s)
+    float ev_s[SEQSUM_MAX_EVENTS];       // the sum after each event
     double warp_tot[THREADS / 32];
-    uint32_t seg_end[THREADS / 32];  // per warp: lanes that end a segment
+    uint32_t warp_events[THREADS / 32];
     float result;
 };
 
@@ -154,10 +159,12 @@ struct SeqSumWorkspace {
 template <int THREADS, class F>
 __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS> &ws) {
     using namespace seqsum_detail;
+    constexpr int NWARP = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t ept = (n + THREADS - 1) / THREADS;
     const uint32_t first = min(n, (uint32_t)tid * ept), last = min(n, first + ept);
 
+    SEQSUM_MARK(0);
     // ---- exact prefix sums in double ------------------------------------------------------------
     double local = 0.0;
     for (uint32_t i = first; i < last; ++i) local += (double)term(i);
@@ -170,41 +177,51 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
     if (lane == 31) ws.warp_tot[warp] = incl;
     __syncthreads();
     double base = incl - local;
-    for (int w = 0; w < warp; ++w) base += ws.warp_tot[w];
-
-    // ---- classify and compose this thread's terms -------------------------------------------------
-    uint32_t c0 = 0, c1 = 0, es_run = 0, dirty = 0;
-    double prev = base;
-    for (uint32_t i = first; i < last; ++i) {
-        const float t = term(i);
-        const double cur = prev + (double)t;
-        const double margin = (double)(i + 2) * 6.1e-8;  // > (i + 1) * 2^-24, with room for the double sum's own error
-        const double lo = prev * (1.0 - margin), hi = cur * (1.0 + margin);
-        // both bounds as floats' binades: safe iff identical, normal and finite
-        const float flo = __double2float_rd(lo), fhi = __double2float_ru(hi);
-        const uint32_t elo = (__float_as_uint(flo) >> 23) & 0xff, ehi = (__float_as_uint(fhi) >> 23) & 0xff;
-        const bool safe = elo == ehi && elo != 0 && elo != 255 && !(margin >= 0.25) && t >= 0.0f;
-        if (!safe || (es_run != 0 && es_run != elo)) {
-            dirty = 1;
-        } else {
-            es_run = elo;
-            uint32_t a0, a1;
-            term_function(__float_as_uint(t), (int)elo, a0, a1);
-            const uint32_t n0 = sat_add(c0, (c0 & 1u) ? a1 : a0);
-            const uint32_t n1 = sat_add(c1, ((1u + c1) & 1u) ? a1 : a0);
-            c0 = n0;
-            c1 = n1;
+    {   // plus the totals of the warps before this one: a shuffle scan over the (at most 32) warp totals
+        double wt = lane < NWARP ? ws.warp_tot[lane] : 0.0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, wt, d);
+            if (lane >= d) wt += up;
         }
-        prev = cur;
+        const double before = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
+        if (warp > 0) base += before;
     }
 
+    SEQSUM_MARK(1);
+    // ---- classify and compose this thread's terms -------------------------------------------------
+    // With the margin of the thread's last term, [base * (1 - m), (base + local) * (1 + m)] contains every partial sum the
+    // thread can see; if both ends are in one binade, every term of the thread is safe in that binade.
+    uint32_t c0 = 0, c1 = 0, es_run = 0, dirty = 0;
+    if (first < last) {
+        const double m_last = (double)(last + 1) * 6.1e-8;  // > last * 2^-24, with room for the double sum's own error
+        const float flo = __double2float_rd(base * (1.0 - m_last)), fhi = __double2float_ru((base + local) * (1.0 + m_last));
+        const uint32_t elo = (__float_as_uint(flo) >> 23) & 0xff, ehi = (__float_as_uint(fhi) >> 23) & 0xff;
+        if (elo == ehi && elo != 0 && elo != 255 && !(m_last >= 0.25)) {
+            es_run = elo;
+            for (uint32_t i = first; i < last; ++i) {
+                const float t = term(i);
+                if (!(t >= 0.0f)) dirty = 1;  // negative or NaN: not this routine's case, add for real
+                uint32_t a0, a1;
+                term_function(__float_as_uint(t), (int)elo, a0, a1);
+                const uint32_t n0 = sat_add(c0, (c0 & 1u) ? a1 : a0);
+                const uint32_t n1 = sat_add(c1, ((1u + c1) & 1u) ? a1 : a0);
+                c0 = n0;
+                c1 = n1;
+            }
+        } else {
+            dirty = 1;
+        }
+    }
+
+    SEQSUM_MARK(2);
     // ---- every warp composes the runs of its own 32 threads: segmented inclusive scan ------------------
+    const uint32_t prev_es = __shfl_up_sync(0xffffffffu, es_run, 1);
+    const uint32_t prev_dirty = __shfl_up_sync(0xffffffffu, dirty, 1);
+    // a dirty lane, an empty lane or a change of binade starts a new segment
+    const bool head = lane == 0 || dirty != 0 || prev_dirty != 0 || es_run == 0 || prev_es != es_run;
+    const uint32_t seg_start = __ballot_sync(0xffffffffu, head);
     {
-        const uint32_t prev_es = __shfl_up_sync(0xffffffffu, es_run, 1);
-        const uint32_t prev_dirty = __shfl_up_sync(0xffffffffu, dirty, 1);
-        // a dirty lane, an empty lane or a change of binade starts a new segment
-        const bool head = lane == 0 || dirty != 0 || prev_dirty != 0 || es_run == 0 || prev_es != es_run;
-        const uint32_t seg_start = __ballot_sync(0xffffffffu, head);
         const uint32_t below = seg_start & (0xffffffffu >> (31 - lane));
         const int my_head = 31 - __clz(below);
 #pragma unroll
@@ -217,44 +234,82 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
                 c1 = n1;
             }
         }
-        ws.rec[tid] = SeqSumRecord{c0, c1, es_run, dirty};
-        if (lane == 0) ws.seg_end[warp] = (seg_start >> 1) | 0x80000000u;  // lane l ends a segment iff lane l+1 starts one
+    }
+    // events of this lane: a dirty thread's terms four at a time; the end of a clean segment; nothing for a thread without terms
+    const bool seg_end = lane == 31 || ((seg_start >> (lane + 1)) & 1u);
+    const uint32_t my_events = first >= last ? 0u : (dirty ? (last - first + 3) / 4 : (seg_end ? 1u : 0u));
+    uint32_t ev_incl = my_events;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, ev_incl, d);
+        if (lane >= d) ev_incl += up;
+    }
+    if (lane == 31) ws.warp_events[warp] = ev_incl;
+    __syncthreads();
+    uint32_t total;
+    {
+        uint32_t we = lane < NWARP ? ws.warp_events[lane] : 0u;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, we, d);
+            if (lane >= d) we += up;
+        }
+        total = __shfl_sync(0xffffffffu, we, 31);
+        const uint32_t before = __shfl_sync(0xffffffffu, we, warp > 0 ? warp - 1 : 0);
+        uint32_t pos = (warp > 0 ? before : 0u) + ev_incl - my_events;
+        if (total <= (uint32_t)SEQSUM_MAX_EVENTS && my_events) {
+            if (dirty) {
+                for (uint32_t i = first; i < last; i += 4, ++pos) {
+                    ws.ev_fn[pos] = make_uint4(0u, 0u, 0u, 1u);
+                    ws.ev_terms[pos] = make_float4(term(i), i + 1 < last ? term(i + 1) : 0.0f, i + 2 < last ? term(i + 2) : 0.0f, i + 3 < last ? term(i + 3) : 0.0f);
+                }
+            } else {
+                ws.ev_fn[pos] = make_uint4(c0, c1, es_run, 0u);
+                ws.ev_terms[pos] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
     }
     __syncthreads();
 
-    // ---- warp 0 walks the segments in order ----------------------------------------------------------------
+    SEQSUM_MARK(3);
+    SEQSUM_VALUE(10, total);
+    // ---- warp 0 applies the events in order -----------------------------------------------------------------------
+    // The dependent chain per event is four additions (dirty) or the increment added to the bit pattern (clean: inside a
+    // binade, adding a * ulp is adding a to the bits).  The loads run ahead; the value after every event is stored, and
+    // whether every clean event really found and left s in its binade is checked afterwards, by all lanes at once.
     if (warp == 0) {
         float s = 0.0f;
-        bool ok = true;
-        for (int chunk = 0; chunk < THREADS / 32 && ok; ++chunk) {
-            uint32_t todo = ws.seg_end[chunk];
-            while (todo && ok) {
-                const int e = __ffs(todo) - 1;
-                todo &= todo - 1;
-                const SeqSumRecord r = ws.rec[chunk * 32 + e];
-                if (r.dirty) {
-                    const uint32_t o = (uint32_t)(chunk * 32 + e);
-                    const uint32_t b = min(n, o * ept), en = min(n, b + ept);
-                    for (uint32_t i = b; i < en; i += 4) {  // fetch four terms, then add them: the loads overlap
-                        const float t0 = term(i), t1 = i + 1 < en ? term(i + 1) : 0.0f, t2 = i + 2 < en ? term(i + 2) : 0.0f,
-                                    t3 = i + 3 < en ? term(i + 3) : 0.0f;
-                        s = __fadd_rn(s, t0);
-                        if (i + 1 < en) s = __fadd_rn(s, t1);
-                        if (i + 2 < en) s = __fadd_rn(s, t2);
-                        if (i + 3 < en) s = __fadd_rn(s, t3);
-                    }
-                } else if (r.es != 0) {
+        bool ok = total <= (uint32_t)SEQSUM_MAX_EVENTS;
+        if (ok) {
+            uint4 fn = ws.ev_fn[0];
+            float4 tm = ws.ev_terms[0];
+            for (uint32_t k = 0; k < total; ++k) {
+                const uint4 f = fn;
+                const float4 t = tm;
+                if (k + 1 < total) {
+                    fn = ws.ev_fn[k + 1];
+                    tm = ws.ev_terms[k + 1];
+                }
+                if (f.w) {
+                    s = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s, t.x), t.y), t.z), t.w);
+                } else {
                     const uint32_t sb = __float_as_uint(s);
-                    const uint32_t S = (sb & 0x7fffffu) | 0x800000u;
-                    const uint32_t S2 = S + ((S & 1u) ? r.c1 : r.c0);
-                    if (((sb >> 23) & 0x1ff) != r.es || S2 >= (1u << 24)) {
-                        ok = false;  // the assumed binade did not hold: recompute below
-                    } else {
-                        s = __uint_as_float((sb & 0xff800000u) | (S2 & 0x7fffffu));
-                    }
+                    s = __uint_as_float(sb + ((sb & 1u) ? f.y : f.x));
+                }
+                ws.ev_s[k] = s;
+            }
+            __syncwarp();
+            bool bad = false;
+            for (uint32_t k = lane; k < total; k += 32) {
+                const uint4 f = ws.ev_fn[k];
+                if (!f.w) {  // the assumed binade must hold before and after
+                    const uint32_t before = k ? __float_as_uint(ws.ev_s[k - 1]) : 0u, after = __float_as_uint(ws.ev_s[k]);
+                    bad = bad || (before >> 23) != f.z || (after >> 23) != f.z;
                 }
             }
+            ok = !__any_sync(0xffffffffu, bad);
         }
+        SEQSUM_MARK(4);
         if (!ok) s = warp_sequential_sum<16>(term, n);
         if (lane == 0) ws.result = s;
     }
