@@ -309,6 +309,442 @@ bool launch_hd(const AttnDecodeArgs &a, uint32_t group, cudaStream_t st) {
     }
 }
 
+
+// ====================================================================================================
+// Fused flash-decode: split, merge and (optionally) int8 quantisation of the output in one kernel.
+//
+// A CTA has four warps and no barrier inside its loop.  Each warp streams its own 16-token pages of K and V into a
+// private two-slot shared-memory ring with cp.async, scores the page for all `G` query heads of the kv head, keeps an
+// online softmax per head in registers and accumulates its part of the output.  Scores and outputs are products of
+// a [heads x dims] or [heads x tokens] matrix with the fp16 page, so they go through the tensor cores
+// (mma.sync m16n8k16, fp32 accumulation).  The fp32 operands (q, and the probabilities) enter as two fp16 rows each, a
+// rounded value and the remainder, which keeps their error near 2^-22 instead of 2^-11; with at most 8 heads the
+// sixteen rows of the tile have room for both.
+//
+// The four warps merge through shared memory, the CTA writes one partial per head, and the CTA that finds itself
+// last for its (sequence, kv head) -- a counter in global memory tells -- merges the partials of all splits,
+// normalises and stores the result.  When the caller passes `image`, that CTA also quantizes its G * HD outputs per
+// 256 exactly as the activation quantizer does (engine/vecdot.rs:3030-3053), so the attention-output product can
+// start from int8 without another launch.
+// ====================================================================================================
+constexpr int AF_WARPS = 8;
+
+#ifdef OB_ATTN_PROF
+__device__ unsigned long long g_attn_prof[4096 * 8];
+#define AF_STAMP(i)                                                                                      \
+    do {                                                                                                 \
+        if (threadIdx.x == 0) {                                                                          \
+            unsigned long long t;                                                                        \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));                                        \
+            g_attn_prof[((blockIdx.y * gridDim.x + blockIdx.x) % 4096) * 8 + (i)] = t;                    \
+        }                                                                                                \
+    } while (0)
+#else
+#define AF_STAMP(i)
+#endif
+
+template <int HD, int G>
+struct AttnFusedSmem {
+    static constexpr int ROW = HD * 2 + 16;             // bytes per token row: the pad spreads eight rows over all banks
+    uint8_t kv[AF_WARPS][2][2][KV_PAGE * ROW];          // [warp][slot][k|v]
+    float q[G][HD];
+    float wo[AF_WARPS][G][HD];                          // per-warp partial outputs
+    float4 acc_part[AF_WARPS * 32];                     // final merge: partial sums of the threads that share a piece
+    float wgt[G][64];                                   // final merge: weight of every split
+    float wm[AF_WARPS][G], wl[AF_WARPS][G];
+    float red[8];
+    int is_last;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (16x8, fp32) += A (16x16, fp16, row) * B (16x8, fp16, col)
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+// the fp16 remainders of (x, y) after their fp16 roundings
+__device__ __forceinline__ uint32_t pack_half2_rest(float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 f = __half22float2(h);
+    return pack_half2(x - f.x, y - f.y);
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDecodeArgs a, bool wait_dependency, bool early_pages) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    using Smem = AttnFusedSmem<HD, G>;
+    Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
+    constexpr int ROW = Smem::ROW;
+    constexpr int THREADS = AF_WARPS * 32;
+    constexpr bool LO8 = G == 8;          // remainders in rows 8..15 (else in rows 4..7)
+    constexpr int KS = HD / 16;           // k-steps of the score product
+    constexpr int NT = HD / 8;            // n-tiles of the output product
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;  // the fragment's row (group) and column pair
+    const uint32_t head0 = kvh * G;
+    AF_STAMP(0);
+
+    // ---- before the grid dependency: everything that the predecessor (which appends this token's K and V and writes q)
+    // does not produce -- the window, the page table and all pages but the one the new token lands in
+    const uint32_t n_pos = a.n_pos[seq];
+    const int32_t *table = a.page_tables[seq];
+    const uint32_t n_pages = (n_pos + KV_PAGE - 1) / KV_PAGE;
+    const uint32_t pages_per_split = (n_pages + a.n_splits - 1) / a.n_splits;
+    const uint32_t page_begin = min(n_pages, split * pages_per_split);
+    const uint32_t page_end = min(n_pages, page_begin + pages_per_split);
+    const uint32_t kv_base = (uint32_t)__cvta_generic_to_shared(&sm.kv[warp][0][0][0]);
+    constexpr uint32_t SLOT_BYTES = 2 * KV_PAGE * ROW, HALF_BYTES = KV_PAGE * ROW;
+
+    auto stage_page = [&](uint32_t pg, int slot) {
+        const uint64_t base = ((uint64_t)table[pg] * a.n_head_kv + kvh) * KV_PAGE * HD;
+        const uint8_t *ks = reinterpret_cast<const uint8_t *>(a.k_pool + base), *vs = reinterpret_cast<const uint8_t *>(a.v_pool + base);
+        constexpr int CPR = HD / 8;  // 16-byte chunks per token row
+        constexpr int CHUNKS = KV_PAGE * CPR;
+#pragma unroll
+        for (int c = 0; c < CHUNKS / 32; ++c) {
+            const int ch = lane + 32 * c, tok = ch / CPR, j = ch % CPR;
+            const uint32_t dst = kv_base + slot * SLOT_BYTES + tok * ROW + j * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(ks + ch * 16) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + HALF_BYTES), "l"(vs + ch * 16) : "memory");
+        }
+    };
+
+    // this warp's pages: page_begin + warp, + AF_WARPS, ...
+    uint32_t pg = page_begin + warp;
+    const uint32_t fresh_page = n_pos ? (n_pos - 1) / KV_PAGE : 0;  // only this page changes under the predecessor
+    // (with several rows the predecessor may be writing any page of a shared sequence: then nothing is fetched early)
+    const bool defer0 = wait_dependency && (!early_pages || pg == fresh_page), defer1 = wait_dependency && (!early_pages || pg + AF_WARPS == fresh_page);
+    if (pg < page_end && !defer0) stage_page(pg, 0);
+    if (pg + AF_WARPS < page_end && !defer1) stage_page(pg + AF_WARPS, 1);
+    if (wait_dependency) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    AF_STAMP(1);
+    if (pg < page_end && defer0) stage_page(pg, 0);
+    __pipeline_commit();
+    if (pg + AF_WARPS < page_end && defer1) stage_page(pg + AF_WARPS, 1);
+    __pipeline_commit();
+    AF_STAMP(2);
+
+    for (int i = tid; i < G * HD; i += THREADS) sm.q[i / HD][i % HD] = __ldcg(a.q + (uint64_t)seq * a.n_head * HD + (uint64_t)head0 * HD + i);
+    __syncthreads();
+    AF_STAMP(3);
+
+    // A fragments of q: row gid holds the rounded q of head gid, row gid + 4 (or + 8) its remainder
+    const int my_head = LO8 ? gid : (gid & 3);
+    const bool head_ok = my_head < G;
+    const bool lo_row = !LO8 && gid >= 4;
+    uint32_t qa[KS][LO8 ? 4 : 2];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        const float *qh = sm.q[head_ok ? my_head : 0];
+        const float x0 = qh[16 * ks + tig * 2], x1 = qh[16 * ks + tig * 2 + 1], x2 = qh[16 * ks + 8 + tig * 2], x3 = qh[16 * ks + 8 + tig * 2 + 1];
+        if constexpr (LO8) {
+            qa[ks][0] = pack_half2(x0, x1);
+            qa[ks][1] = pack_half2_rest(x0, x1);
+            qa[ks][2] = pack_half2(x2, x3);
+            qa[ks][3] = pack_half2_rest(x2, x3);
+        } else {
+            qa[ks][0] = !head_ok ? 0u : (lo_row ? pack_half2_rest(x0, x1) : pack_half2(x0, x1));
+            qa[ks][1] = !head_ok ? 0u : (lo_row ? pack_half2_rest(x2, x3) : pack_half2(x2, x3));
+        }
+    }
+
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;  // of head my_head, the same in the lanes that share it
+
+    int slot = 0;
+    for (; pg < page_end; pg += AF_WARPS, slot ^= 1) {
+        __pipeline_wait_prior(1);
+        __syncwarp();
+        const uint32_t kb = kv_base + slot * SLOT_BYTES, vb = kb + HALF_BYTES;
+        const uint32_t pos0 = pg * KV_PAGE;
+        // ---- scores of the 16 tokens: two n-tiles of 8 tokens
+        float sv[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int kk = 0; kk < KS / 2; ++kk) {
+                uint32_t b0, b1, b2, b3;  // token rows 8 nt .., dims 32 kk + 8 * (lane / 8) ..
+                ldmatrix_x4(kb + (8 * nt + (lane & 7)) * ROW + (32 * kk + 8 * (lane >> 3)) * 2, b0, b1, b2, b3);
+                if constexpr (LO8) {
+                    mma_16816(c, qa[2 * kk][0], qa[2 * kk][1], qa[2 * kk][2], qa[2 * kk][3], b0, b1);
+                    mma_16816(c, qa[2 * kk + 1][0], qa[2 * kk + 1][1], qa[2 * kk + 1][2], qa[2 * kk + 1][3], b2, b3);
+                } else {
+                    mma_16816(c, qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, b0, b1);
+                    mma_16816(c, qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, b2, b3);
+                }
+            }
+            float s0, s1;  // rounded part + remainder part
+            if constexpr (LO8) {
+                s0 = c[0] + c[2];
+                s1 = c[1] + c[3];
+            } else {
+                s0 = c[0] + __shfl_xor_sync(0xffffffffu, c[0], 16);
+                s1 = c[1] + __shfl_xor_sync(0xffffffffu, c[1], 16);
+            }
+            const uint32_t t0 = pos0 + 8 * nt + tig * 2;
+            sv[nt][0] = head_ok && t0 < n_pos ? __fmul_rn(s0, a.scale) : -INFINITY;
+            sv[nt][1] = head_ok && t0 + 1 < n_pos ? __fmul_rn(s1, a.scale) : -INFINITY;
+        }
+        // ---- online softmax: the four lanes of a group hold the head's 16 scores
+        float mx = fmaxf(fmaxf(sv[0][0], sv[0][1]), fmaxf(sv[1][0], sv[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        float pv[2][2], sum = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                pv[nt][e] = sv[nt][e] == -INFINITY ? 0.0f : expf(sv[nt][e] - m_new);
+                sum += pv[nt][e];
+            }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float al = m_run == -INFINITY ? 0.0f : expf(m_run - m_new);
+        l_run = __fmaf_rn(l_run, al, sum);
+        m_run = m_new;
+        // ---- output: A = probabilities (rounded and remainder rows), B = V through transposing loads
+        uint32_t pa[4];
+        if constexpr (LO8) {
+            pa[0] = pack_half2(pv[0][0], pv[0][1]);
+            pa[1] = pack_half2_rest(pv[0][0], pv[0][1]);
+            pa[2] = pack_half2(pv[1][0], pv[1][1]);
+            pa[3] = pack_half2_rest(pv[1][0], pv[1][1]);
+        } else {
+            pa[0] = lo_row ? pack_half2_rest(pv[0][0], pv[0][1]) : pack_half2(pv[0][0], pv[0][1]);
+            pa[1] = 0u;
+            pa[2] = lo_row ? pack_half2_rest(pv[1][0], pv[1][1]) : pack_half2(pv[1][0], pv[1][1]);
+            pa[3] = 0u;
+        }
+        if (__any_sync(0xffffffffu, al != 1.0f)) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                o[j][0] *= al;
+                o[j][1] *= al;
+                o[j][2] *= al;
+                o[j][3] *= al;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NT / 2; ++j) {
+            uint32_t b0, b1, b2, b3;  // tokens (lane & 7) + 8 * ((lane >> 3) & 1), dims 16 j + 8 * (lane >> 4) ..
+            ldmatrix_x4_trans(vb + ((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + (16 * j + 8 * (lane >> 4)) * 2, b0, b1, b2, b3);
+            mma_16816(o[2 * j], pa[0], pa[1], pa[2], pa[3], b0, b1);
+            mma_16816(o[2 * j + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+        }
+        __syncwarp();
+        if (pg + 2 * AF_WARPS < page_end) stage_page(pg + 2 * AF_WARPS, slot);
+        __pipeline_commit();
+    }
+    __pipeline_wait_prior(0);
+    AF_STAMP(4);
+
+    // ---- the warps' partials meet in shared memory (rounded-row part + remainder-row part)
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        float v0, v1;
+        if constexpr (LO8) {
+            v0 = o[j][0] + o[j][2];
+            v1 = o[j][1] + o[j][3];
+        } else {
+            v0 = o[j][0] + __shfl_xor_sync(0xffffffffu, o[j][0], 16);
+            v1 = o[j][1] + __shfl_xor_sync(0xffffffffu, o[j][1], 16);
+        }
+        if (head_ok && !lo_row) *reinterpret_cast<float2 *>(&sm.wo[warp][my_head][8 * j + tig * 2]) = make_float2(v0, v1);
+    }
+    if (head_ok && !lo_row && tig == 0) {
+        sm.wm[warp][my_head] = m_run;
+        sm.wl[warp][my_head] = l_run;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += THREADS) {
+        const int g = i / HD, d = i % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AF_WARPS; ++w) M = fmaxf(M, sm.wm[w][g]);
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < AF_WARPS; ++w) {
+            const float mw = sm.wm[w][g];
+            const float sc = mw == -INFINITY ? 0.0f : expf(mw - M);
+            acc = __fmaf_rn(sc, sm.wo[w][g][d], acc);
+            l = __fmaf_rn(sc, sm.wl[w][g], l);
+        }
+        const uint64_t slot_index = ((uint64_t)seq * a.n_head + head0 + g) * a.n_splits + split;
+        a.part_o[slot_index * HD + d] = acc;
+        if (d == 0) {
+            a.part_ml[slot_index * 2] = M;
+            a.part_ml[slot_index * 2 + 1] = l;
+        }
+    }
+    // ---- who is last for this (sequence, kv head)?
+    AF_STAMP(5);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t done = atomicAdd(&a.counters[seq * a.n_head_kv + kvh], 1u);
+        sm.is_last = done == a.n_splits - 1;
+        if (sm.is_last) a.counters[seq * a.n_head_kv + kvh] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    AF_STAMP(6);
+    if (!sm.is_last) return;
+    __threadfence();
+
+    // ---- merge of all splits.  First every split's weight exp(m_s - M) / (sum of weighted l) per head, in shared memory
+    // then the threads sum 16-byte pieces of the partials, each thread its share
+    // of the splits with all its loads in flight together.
+    float *wgt = &sm.wgt[0][0];   // [G][64], n_splits <= 64
+    float4 *acc_area = sm.acc_part;  // [PARTS][NCH]
+    for (int g = warp; g < G; g += AF_WARPS) {  // one warp per head
+        const float *pm = a.part_ml + ((uint64_t)seq * a.n_head + head0 + g) * a.n_splits * 2;
+        float ms[2], ls[2], M = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t s = lane + 32 * r;
+            ms[r] = s < a.n_splits ? __ldcg(pm + 2 * s) : -INFINITY;
+            ls[r] = s < a.n_splits ? __ldcg(pm + 2 * s + 1) : 0.0f;
+            M = fmaxf(M, ms[r]);
+        }
+        M = warp_max(M);
+        float w[2], l = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            w[r] = ms[r] == -INFINITY ? 0.0f : expf(ms[r] - M);
+            l = __fmaf_rn(w[r], ls[r], l);
+        }
+        l = warp_sum(l);
+        const float inv_l = l > 0.0f ? __fdiv_rn(1.0f, l) : 0.0f;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t s = lane + 32 * r;
+            if (s < a.n_splits) wgt[g * 64 + s] = w[r] * inv_l;
+        }
+    }
+    __syncthreads();
+    constexpr int NCH = G * HD / 4;                             // 16-byte pieces of the kv head's output
+    constexpr int PARTS = THREADS / NCH > 0 ? THREADS / NCH : 1;  // threads per piece, each taking every PARTS-th split
+    constexpr int ROUNDS = NCH > THREADS ? NCH / THREADS : 1;
+    static_assert(NCH % 32 == 0 && (THREADS % NCH == 0 || NCH % THREADS == 0), "unsupported head shape");
+    float4 res[ROUNDS];
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int c = tid % NCH + rd * THREADS, part = tid / NCH;  // part < PARTS
+        const int g = c / (HD / 4), d4 = c % (HD / 4);
+        const float4 *po = reinterpret_cast<const float4 *>(a.part_o + ((uint64_t)seq * a.n_head + head0 + g) * a.n_splits * HD) + d4;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t s0 = part; s0 < a.n_splits; s0 += 8 * PARTS) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t s = s0 + u * PARTS;
+                v[u] = s < a.n_splits ? __ldcg(po + (uint64_t)s * (HD / 4)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint32_t s = s0 + u * PARTS;
+                const float w = s < a.n_splits ? wgt[g * 64 + s] : 0.0f;
+                acc.x = __fmaf_rn(w, v[u].x, acc.x);
+                acc.y = __fmaf_rn(w, v[u].y, acc.y);
+                acc.z = __fmaf_rn(w, v[u].z, acc.z);
+                acc.w = __fmaf_rn(w, v[u].w, acc.w);
+            }
+        }
+        if (PARTS > 1) {
+            acc_area[part * NCH + c] = acc;
+            __syncthreads();
+            if (part == 0) {
+#pragma unroll
+                for (int pp = 1; pp < PARTS; ++pp) {
+                    const float4 o2 = acc_area[pp * NCH + c];
+                    acc.x += o2.x;
+                    acc.y += o2.y;
+                    acc.z += o2.z;
+                    acc.w += o2.w;
+                }
+            }
+        }
+        res[rd] = acc;
+        if (part == 0) *reinterpret_cast<float4 *>(a.out + (uint64_t)seq * a.n_head * HD + (uint64_t)(head0 + g) * HD + 4 * d4) = acc;
+    }
+    if (a.image == nullptr) return;
+    if constexpr (G * HD % 256 == 0) {
+        // quantize per 256 (engine/vecdot.rs:3030-3053): piece c of this kv head holds elements head0 * HD + 4 c .. + 3 of
+        // the row, so a 256-block is 64 consecutive pieces = two warps of the threads with part == 0.
+        const uint32_t nb_row = a.n_head * HD / 256;
+        uint8_t *img = a.image;
+        float *sd = reinterpret_cast<float *>(img + nb_row * 272);
+        int16_t *bsum = reinterpret_cast<int16_t *>(img + ((nb_row * 272 + nb_row * 4 + 15) & ~15u));
+        int16_t *sum16 = bsum + nb_row * 8;
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int c = tid % NCH + rd * THREADS;
+            const bool active = tid / NCH == 0;
+            const float4 v = res[rd];
+            float amax = active ? fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))) : 0.0f;
+            amax = warp_max(amax);
+            __syncthreads();
+            if (lane == 0) sm.red[warp] = amax;
+            __syncthreads();
+            amax = fmaxf(sm.red[warp & ~1], sm.red[warp | 1]);
+            if (active) {
+                const float scale = __fdiv_rn(amax, 127.0f);
+                const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+                const uint32_t blk = head0 * HD / 256 + c / 64, e = (c % 64) * 4;  // block of the row, first element inside it
+                const int q0 = quantize_value(v.x, inv), q1 = quantize_value(v.y, inv), q2 = quantize_value(v.z, inv), q3 = quantize_value(v.w, inv);
+                *reinterpret_cast<uint32_t *>(img + blk * 272 + e) = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                int s = q0 + q1 + q2 + q3;
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                if ((lane & 3) == 0) sum16[blk * 16 + e / 16] = (int16_t)s;
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                if ((lane & 7) == 0) bsum[blk * 8 + e / 32] = (int16_t)s;
+                if ((c % 64) == 0) sd[blk] = scale;
+            }
+        }
+    }
+    AF_STAMP(7);
+}
+
+template <int HD, int G>
+bool launch_fused_instance(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
+    static bool configured = false;
+    const size_t smem = sizeof(AttnFusedSmem<HD, G>);
+    if (!configured) {
+        cudaFuncSetAttribute(attn_decode_fused_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.n_splits, a.n_head_kv, a.n_seq);
+    cfg.blockDim = dim3(AF_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<HD, G>, a, programmatic, programmatic && a.n_seq == 1);
+    return true;
+}
+
 }  // namespace
 
 void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st) {
@@ -320,6 +756,36 @@ void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st) {
         else if (a.head_dim == 64) done = launch_hd<64>(a, group, st);
     }
     if (!done) attn_generic_kernel<<<dim3(a.n_head, a.n_seq), 32, 0, st>>>(a);
+}
+
+#ifdef OB_ATTN_PROF
+extern "C" __attribute__((visibility("default"))) int ob_debug_attn_prof(unsigned long long *dst, size_t n) {
+    return (int)cudaMemcpyFromSymbol(dst, g_attn_prof, n * sizeof(unsigned long long));
+}
+#endif
+
+bool launch_attn_decode_fused(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
+    if (a.n_seq == 0) return true;
+    if (!a.counters || !a.part_o || a.n_head % a.n_head_kv) return false;
+    const uint32_t group = a.n_head / a.n_head_kv;
+    if (a.head_dim == 128) {
+        switch (group) {
+        case 1: return launch_fused_instance<128, 1>(a, programmatic, st);
+        case 2: return launch_fused_instance<128, 2>(a, programmatic, st);
+        case 4: return launch_fused_instance<128, 4>(a, programmatic, st);
+        case 8: return launch_fused_instance<128, 8>(a, programmatic, st);
+        default: return false;
+        }
+    }
+    if (a.head_dim == 64) {
+        switch (group) {
+        case 2: return launch_fused_instance<64, 2>(a, programmatic, st);
+        case 4: return launch_fused_instance<64, 4>(a, programmatic, st);
+        case 8: return launch_fused_instance<64, 8>(a, programmatic, st);
+        default: return false;
+        }
+    }
+    return false;
 }
 
 }  // namespace ob

@@ -133,8 +133,14 @@ struct AttnDecodeArgs {
     float *part_o;             // [n_seq][n_head][n_splits][head_dim]
     float *part_ml;            // [n_seq][n_head][n_splits][2]
     uint32_t max_pos;          // upper bound of n_pos (sizes nothing on the device; bounds the split length)
+    // launch_attn_decode_fused only:
+    uint32_t *counters;        // [n_seq][n_head_kv], zero before the first launch; the kernel leaves them zero
+    uint8_t *image;            // optional, n_seq == 1: the output quantized per 256 for the product that follows (stream_gemv.cu)
 };
 void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st);
+// One kernel: every warp streams its own pages, the CTAs of a (sequence, kv head) leave partials and the last of them to
+// finish merges them (and quantizes the result when `image` is set).  False when the shape is not covered.
+bool launch_attn_decode_fused(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st);
 
 // Exact-order attention (three kernels: scores, softmax, output); see attention.cu.
 struct AttnExactArgs {

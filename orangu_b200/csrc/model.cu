@@ -78,6 +78,7 @@ struct ob_model {
           *logits = nullptr;
     ActPair act_embd, act_attn, act_ff;
     float *part_o = nullptr, *part_ml = nullptr;
+    uint32_t *attn_counters = nullptr;  // [rows][kv heads] arrival counters of the fused attention kernel, zero between launches
     float *norm_scale = nullptr;      // [2] RMSNorm scales for the fused decode kernels (attention norm, FFN / output norm)
     uint8_t *ready_embd = nullptr, *ready_attn = nullptr, *ready_ff = nullptr;  // quantized activations of the single decode token
     float *scores = nullptr;          // exact-order attention scratch [T][n_head_l][score_stride]
@@ -93,6 +94,7 @@ struct ob_model {
     std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
     obtp::Comm *comm = nullptr;
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
+    bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
 };
 
 struct ob_kv {
@@ -273,7 +275,8 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
     return a;
 }
 
-void run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32_t pos_bound, const int32_t *const *d_tables,
+// Returns true when `image` (the quantized output, for the single-token product kernels) has been written.
+bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32_t pos_bound, uint8_t *image, const int32_t *const *d_tables,
                    const uint32_t *d_npos, cudaStream_t st) {
     const uint32_t hd = m->cfg.head_dim;
     const __half *k_pool = m->k_pool + (size_t)li * m->layer_stride, *v_pool = m->v_pool + (size_t)li * m->layer_stride;
@@ -295,6 +298,7 @@ void run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
         at.max_pos = pos_bound;
         launch_attn_exact(at, st);
         m->ctx->launches += 3;
+        return false;
     } else {
         AttnDecodeArgs at{};
         at.q = m->q;
@@ -312,8 +316,17 @@ void run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
         at.part_o = m->part_o;
         at.part_ml = m->part_ml;
         at.max_pos = m->cfg.max_seq_len;
+        at.counters = m->attn_counters;
+        at.image = image;
+        AttnDecodeArgs fused = at;
+        fused.n_splits = std::max(1u, std::min(m->max_splits, (uint32_t)m->ctx->sm_count / (T * m->n_head_kv_l)));  // one CTA per SM
+        if (m->use_fused_attn && launch_attn_decode_fused(fused, true, st)) {
+            m->ctx->launches += 1;
+            return image != nullptr && (m->n_head_l / m->n_head_kv_l * hd) % 256 == 0;
+        }
         launch_attn_decode(at, st);
         m->ctx->launches += 2;
+        return false;
     }
 }
 
@@ -348,14 +361,16 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         if (stream_layer) {
             launch_norm_quant(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 1), m->ctx->sm_count, true, st);
-            run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
-            launch_quant_image(m->attn, q_dim, m->ready_attn, true, st);
+            if (!run_attention(m, li, T, exact_attn, pos_bound, m->ready_attn, d_tables, d_npos, st)) {
+                launch_quant_image(m->attn, q_dim, m->ready_attn, true, st);
+                m->ctx->launches++;
+            }
             launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
             launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
             launch_quant_image(m->gate, n_ff, m->ready_ff, true, st);
             launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
-            m->ctx->launches += 8;
+            m->ctx->launches += 7;
             continue;
         }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
@@ -378,7 +393,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         launch_rope_kv(rk, st);
         m->ctx->launches++;
 
-        run_attention(m, li, T, exact_attn, pos_bound, d_tables, d_npos, st);
+        run_attention(m, li, T, exact_attn, pos_bound, nullptr, d_tables, d_npos, st);
 
         quantize_into(m, ACT_PLAIN, m->attn, nullptr, T, q_dim, m->act_attn, needs_k({L.wo}), needs_flat({L.wo}), st);
         if (!tp) {
@@ -515,6 +530,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     if (m->cfg.max_seq_len == 0) m->cfg.max_seq_len = 4096;
     if (m->cfg.max_batch_tokens == 0) m->cfg.max_batch_tokens = 1;
     if (const char *e = getenv("OB_STREAM_GEMV")) m->use_stream = !(e[0] == '0' && e[1] == 0);
+    if (const char *e = getenv("OB_FUSED_ATTN")) m->use_fused_attn = !(e[0] == '0' && e[1] == 0);
     m->tp_rank = rank;
     m->tp_size = tp;
     m->n_head_l = c.n_head / tp;
@@ -603,6 +619,8 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         const size_t row_splits = (size_t)4 * ctx->sm_count + T;
         if ((rc = dev_alloc(m, &m->part_o, row_splits * m->n_head_l * hd))) return bail(rc);
         if ((rc = dev_alloc(m, &m->part_ml, row_splits * m->n_head_l * 2))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->attn_counters, (size_t)T * m->n_head_kv_l))) return bail(rc);
+        OB_CUDA(ctx, cudaMemset(m->attn_counters, 0, (size_t)T * m->n_head_kv_l * 4));
     }
     m->exact_attn_max_pos = attn_exact_supported(m->n_head_l, m->n_head_kv_l, hd) ? std::min(m->cfg.max_seq_len, c.exact_attention_max_pos ? c.exact_attention_max_pos : 1024u) : 0u;
     m->score_stride = (m->exact_attn_max_pos + 63) / 64 * 64;

@@ -208,3 +208,29 @@ def test_flash_decode_path_through_the_model(backend):
     got = model.forward(kv, [5], 100)
     want = ref.forward(rkv, [5], 100)
     assert np.abs(got - want).max() < LOGIT_TOL
+
+
+@pytest.mark.parametrize("name,n_ctx", [("small", 100), ("1b", 200), ("8b", 333)])
+def test_fused_flash_decode_agrees_with_the_split_kernels_and_the_oracle(backend, name, n_ctx, monkeypatch):
+    """The one-kernel flash-decode (split + merge + int8 output) against the two-kernel form and the CPU oracle, on one
+    layer, teacher-forced: a few decode steps past the exact-order bound."""
+    cfg = dict(synth.CONFIGS[name])
+    cfg["n_layer"] = 1
+    cfg["n_vocab"] = min(cfg["n_vocab"], 4096)
+    tensors = synth.model_tensors(cfg, seed=29)
+    kw = dict(max_seq_len=512, max_batch_tokens=64, kv_pool_tokens=1024, exact_attention_max_pos=16)
+    fused = LlamaModel(backend, cfg, tensors, **kw)
+    monkeypatch.setenv("OB_FUSED_ATTN", "0")
+    split = LlamaModel(backend, cfg, tensors, **kw)
+    monkeypatch.delenv("OB_FUSED_ATTN")
+    ref = O.Model(cfg, tensors)
+    toks = prompt(cfg, n_ctx, 9)
+    kf, ks, rkv = fused.new_kv_cache(400), split.new_kv_cache(400), ref.new_kv(400, f16=True)
+    a, b, want = fused.forward(kf, toks, 0), split.forward(ks, toks, 0), ref.forward(rkv, toks, 0)
+    assert np.abs(a - want).max() < LOGIT_TOL and np.abs(b - want).max() < LOGIT_TOL
+    for step in range(4):
+        tok = int(toks[step])
+        a, b, want = fused.forward(kf, [tok], n_ctx + step), split.forward(ks, [tok], n_ctx + step), ref.forward(rkv, [tok], n_ctx + step)
+        assert np.abs(a - want).max() < LOGIT_TOL, step
+        assert np.abs(b - want).max() < LOGIT_TOL, step
+        assert np.abs(a - b).max() < LOGIT_TOL, step
