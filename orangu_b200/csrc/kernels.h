@@ -75,6 +75,9 @@ struct StreamArgs {
     float eps;
     const uint8_t *ready;    // READY: the token's quantized activations as launch_norm_quant / launch_quant_image left them
     const float *residual;   // RESIDUAL: y = residual + product (may alias y)
+    // one SWIGLU segment whose row count is a multiple of 256: also leave the outputs quantized per 256 (the next product's READY input)
+    uint8_t *out_image;
+    uint32_t *out_counters;  // [rows / 256], zero before the launch and after it
     // RoPE + KV append (ROPE_Q / ROPE_K / V)
     const float *rope_table; // [pos][rope_dim/2](sin, cos)
     const uint32_t *position;        // device: position of the token

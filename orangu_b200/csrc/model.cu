@@ -78,6 +78,7 @@ struct ob_model {
           *logits = nullptr;
     ActPair act_embd, act_attn, act_ff;
     float *part_o = nullptr, *part_ml = nullptr;
+    uint32_t *ff_counters = nullptr;    // [n_ff / 256] arrival counters of the SwiGLU outputs, zero between launches
     uint32_t *attn_counters = nullptr;  // [rows][kv heads] arrival counters of the fused attention kernel, zero between launches
     float *norm_scale = nullptr;      // [2] RMSNorm scales for the fused decode kernels (attention norm, FFN / output norm)
     uint8_t *ready_embd = nullptr, *ready_attn = nullptr, *ready_ff = nullptr;  // quantized activations of the single decode token
@@ -255,6 +256,8 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.prologue = SG_PRO_READY;
         a.ready = m->ready_embd;
         a.seg[0] = StreamSeg{L.gate->w, L.up->w, m->gate, SG_EP_SWIGLU};
+        a.out_image = m->ready_ff;
+        a.out_counters = m->ff_counters;
         break;
     case 4:
         a.n_seg = 1;
@@ -368,9 +371,8 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
             launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
-            launch_quant_image(m->gate, n_ff, m->ready_ff, true, st);
             launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
-            m->ctx->launches += 7;
+            m->ctx->launches += 6;
             continue;
         }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
@@ -630,6 +632,8 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         if ((rc = dev_alloc(m, &m->ready_embd, act_image_bytes(c.n_embd)))) return bail(rc);
         if ((rc = dev_alloc(m, &m->ready_attn, act_image_bytes(m->n_head_l * c.head_dim)))) return bail(rc);
         if ((rc = dev_alloc(m, &m->ready_ff, act_image_bytes(m->n_ff_l)))) return bail(rc);
+        if ((rc = dev_alloc(m, &m->ff_counters, m->n_ff_l / 256))) return bail(rc);
+        OB_CUDA(ctx, cudaMemset(m->ff_counters, 0, (size_t)m->n_ff_l / 256 * 4));
     }
     const MetaLayout ml(T);
     if ((rc = dev_alloc(m, &m->d_meta, ml.bytes))) return bail(rc);

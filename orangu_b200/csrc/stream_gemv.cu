@@ -41,11 +41,13 @@ constexpr uint32_t ACT_BLOCK_STRIDE = 272;  // bytes per 256 int8 activations: 1
 // bytes of `lp` blocks of one row inside a slot
 __host__ __device__ inline uint32_t part_bytes(uint32_t type, uint32_t lp) { return type == TYPE_Q4_K ? lp * 144u : lp * 208u + ((lp * 2u + 15u) & ~15u); }
 
-// lanes per pair of rows: the smallest power of two that covers min(nb, 32) blocks; at least 2, because each pair also
-// needs two lanes for the ordered sums of its two rows
+// lanes per pair of rows (= blocks of a unit): the smallest power of two that covers the row, at least 2 because each pair
+// also needs two lanes for the ordered sums of its two rows; rows longer than 32 blocks are cut into chunks of 16, which
+// spreads a matrix with few rows (the FFN down projection) over more warps than chunks of 32 would
 __host__ __device__ inline uint32_t lanes_per_pair(uint32_t nb) {
+    if (nb > 32) return 16;
     uint32_t lp = 2;
-    while (lp < nb && lp < 32) lp <<= 1;
+    while (lp < nb) lp <<= 1;
     return lp;
 }
 
@@ -74,9 +76,9 @@ struct SgSmem {  // byte offsets inside dynamic shared memory
     uint32_t off_act, off_d, off_bsum, off_sum16, off_terms, off_ring, slot_bytes, total;
 };
 
-__host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6) {
+__host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6, uint32_t lp) {
     SgSmem s;
-    const uint32_t nb = in_dim / 256, nw = (uint32_t)sg_warps(has_q6), lp = lanes_per_pair(nb);
+    const uint32_t nb = in_dim / 256, nw = (uint32_t)sg_warps(has_q6);
     s.off_act = SEG_TABLE_BYTES;  // [0, SEG_TABLE_BYTES): the segment table
     const ActImage im = act_image(nb);
     s.off_d = s.off_act + im.off_d;
@@ -308,14 +310,31 @@ __device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, cons
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
+#ifdef OB_SG_PROF
+__device__ unsigned long long g_sg_prof[8][512 * 8];  // [kernel tag][cta][stamp]
+#define SG_STAMP(i)                                                                          \
+    do {                                                                                     \
+        if (threadIdx.x == 0 && blockIdx.x < 512) {                                          \
+            unsigned long long t;                                                            \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));                            \
+            g_sg_prof[a.n_seg == 3 ? 1 : (a.in_dim > 8192 ? 4 : (a.seg[0].w2.data ? 3 : (a.seg[0].epilogue == SG_EP_RESIDUAL ? 2 : 5)))][blockIdx.x * 8 + (i)] = t; \
+        }                                                                                    \
+    } while (0)
+extern "C" __attribute__((visibility("default"))) int ob_debug_sg_prof(unsigned long long *dst, size_t n) {
+    return (int)cudaMemcpyFromSymbol(dst, g_sg_prof, n * sizeof(unsigned long long));
+}
+#else
+#define SG_STAMP(i)
+#endif
 template <int LP, bool Q6>  // LP: lanes (= blocks per unit) of a row pair; Q6: the launch has Q6_K segments (three warps, larger slots)
 __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int NW = Q6 ? 3 : 4, PPU = 32 / LP, HL = LP / 2;
     constexpr uint32_t PB4 = LP * 144u, PB6 = LP * 208u + ((LP * 2u + 15u) & ~15u);
     constexpr uint32_t SLOT = 2u * PPU * (Q6 ? PB6 : PB4);
-    const SgSmem L = sg_smem(a.in_dim, Q6);
+    const SgSmem L = sg_smem(a.in_dim, Q6, LP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    SG_STAMP(0);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t terms = sbase + L.off_terms + warp * 256;
     const uint32_t slots = sbase + L.off_ring + warp * 2 * SLOT;
@@ -353,7 +372,8 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
     // this warp's contiguous share of the groups
     const uint32_t n_warps = gridDim.x * NW, gw = blockIdx.x * NW + warp;
     const uint32_t g_end = (uint32_t)(((uint64_t)G * (gw + 1)) / n_warps);
-    uint32_t ig = (uint32_t)(((uint64_t)G * gw) / n_warps), ic = 0;  // next unit to request: group, chunk
+    const uint32_t g_first = (uint32_t)(((uint64_t)G * gw) / n_warps);
+    uint32_t ig = g_first, ic = 0;  // next unit to request: group, chunk
     uint32_t cg = ig, cc = 0;                                        // next unit to compute
 
     const uint32_t q = lane / HL, sub = lane % HL, cj = q >> 1, cr = q & 1;  // copy role: part q = (pair cj, row cr), chunks sub + HL * k
@@ -411,10 +431,12 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
     advance(ig, ic);
 
     // ---- prologue ---------------------------------------------------------------------------------------------
+    SG_STAMP(1);
     if (a.wait_dependency) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the successor may start requesting its weights
         asm volatile("griddepcontrol.wait;" ::: "memory");               // the predecessor's output is complete and visible
     }
+    SG_STAMP(2);
     if (a.prologue == SG_PRO_READY) {  // the producer left the image in global memory
         const uint32_t n16 = (L.off_terms - L.off_act) / 16;
         for (uint32_t c = threadIdx.x; c < n16; c += NW * 32) {
@@ -426,6 +448,7 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         quantize_image(a.x, norm ? a.norm_w : nullptr, norm ? *a.norm_scale : 1.0f, nb, smem + L.off_act, warp, NW);
     }
     __syncthreads();
+    SG_STAMP(3);
 
     // ---- main loop ------------------------------------------------------------------------------------------------
     float tot = 0.0f;  // lanes 2j, 2j+1: rows A, B of the group's pair j, running over the chunks of the row
@@ -538,6 +561,36 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         }
     }
     __pipeline_wait_prior(0);
+
+    // ---- SwiGLU outputs as the next product's int8 input: the warp that completes a block of 256 quantizes it ---------
+    // Every warp adds the number of outputs it stored to the counters of the blocks they belong to; the add that brings a
+    // counter to 256 tells its warp that the whole block is in memory.  The counters are left at zero.
+    if (a.out_image) {
+        const uint32_t pairs = pairs_of[0];
+        const uint32_t p0 = min(g_first * PPU, pairs), p1 = min(g_end * PPU, pairs);
+        __syncwarp();
+        if (p1 > p0) {
+            uint32_t done_blocks = 0;  // bit i: block p0 / 256 + i is complete and ours to quantize
+            if (lane == 0) {
+                __threadfence();
+                for (uint32_t b = p0 / 256; b <= (p1 - 1) / 256; ++b) {
+                    const uint32_t cnt = min(p1, (b + 1) * 256) - max(p0, b * 256);
+                    if (atomicAdd(&a.out_counters[b], cnt) + cnt == 256) {
+                        done_blocks |= 1u << (b - p0 / 256);
+                        a.out_counters[b] = 0;
+                    }
+                }
+                if (done_blocks) __threadfence();
+            }
+            done_blocks = __shfl_sync(0xffffffffu, done_blocks, 0);
+            while (done_blocks) {
+                const uint32_t b = p0 / 256 + (uint32_t)(__ffs((int)done_blocks) - 1);
+                done_blocks &= done_blocks - 1;
+                quantize_image(a.seg[0].y, nullptr, 1.0f, pairs / 256, a.out_image, b, pairs / 256);  // stride = block count: block b only
+            }
+        }
+    }
+    SG_STAMP(4);
 }
 
 // 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.  With `image` set the
@@ -547,6 +600,8 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__r
                                                                 float *__restrict__ out, uint8_t *__restrict__ image, bool wait_dependency) {
     extern __shared__ float srow[];  // the row, one pad word per 16
     __shared__ SeqSumWorkspace<NS_THREADS> ws;
+    if (norm_w)  // the weights do not depend on the predecessor: have them in L2 by the time the scale is known
+        for (uint32_t i = threadIdx.x * 32; i < dim; i += NS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(norm_w + i));
     if (wait_dependency) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -570,6 +625,8 @@ __global__ void __launch_bounds__(128) quant_image_kernel(const float *__restric
 
 }  // namespace
 
+static uint32_t pick_lp(uint32_t nb) { return lanes_per_pair(nb); }
+
 bool stream_gemv_supported(const StreamArgs &a) {
     if (a.n_seg < 1 || a.n_seg > 3 || a.in_dim % 256) return false;
     bool q6 = false;
@@ -581,7 +638,7 @@ bool stream_gemv_supported(const StreamArgs &a) {
         if (g.epilogue >= SG_EP_ROPE_Q && (g.w.out_dim & 1)) return false;
         q6 = q6 || g.w.type == TYPE_Q6_K;
     }
-    return sg_smem(a.in_dim, q6).total <= 108 * 1024;
+    return sg_smem(a.in_dim, q6, pick_lp(a.in_dim / 256)).total <= 108 * 1024;
 }
 
 size_t act_image_bytes(uint32_t dim) { return act_image(dim / 256).bytes; }
@@ -647,13 +704,13 @@ void launch_lp(uint32_t lp, const cudaLaunchConfig_t &cfg, const StreamArgs &arg
 void launch_stream_gemv(const StreamArgs &a, int sm_count, bool programmatic, cudaStream_t st) {
     bool q6 = false;
     uint32_t groups = 0;
-    const uint32_t lp = lanes_per_pair(a.in_dim / 256), ppu = 32 / lp;
+    const uint32_t lp = pick_lp(a.in_dim / 256), ppu = 32 / lp;
     for (int s = 0; s < a.n_seg; ++s) {
         q6 = q6 || a.seg[s].w.type == TYPE_Q6_K;
         const uint32_t pairs = a.seg[s].w2.data ? a.seg[s].w.out_dim : (a.seg[s].w.out_dim + 1) / 2;
         groups += (pairs + ppu - 1) / ppu;
     }
-    const SgSmem L = sg_smem(a.in_dim, q6);
+    const SgSmem L = sg_smem(a.in_dim, q6, lp);
     StreamArgs args = a;
     args.wait_dependency = programmatic;
     const uint32_t nw = (uint32_t)sg_warps(q6);
