@@ -595,7 +595,7 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
 
 // 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.  With `image` set the
 // CTA goes on to quantize (x * scale) * norm_w per 256, so that the product kernels that follow only copy the result.
-constexpr int NS_THREADS = 1024;
+constexpr int NS_THREADS = 512;
 __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__restrict__ x, const float *__restrict__ norm_w, uint32_t dim, float eps,
                                                                 float *__restrict__ out, uint8_t *__restrict__ image, bool wait_dependency) {
     extern __shared__ float srow[];  // the row, one pad word per 16
