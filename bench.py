@@ -325,15 +325,32 @@ def main():
     # ---- roofline of the dominant kernel --------------------------------------------------------------
     peak, peak_kind = measured_peak_gbs()
     iters = 20
-    ms, nbytes, nl = model.profile_gemv(12, iters)
-    per_launch_s = ms * 1e-3 / (iters * nl)
-    achieved = nbytes / nl / per_launch_s / 1e9
     step_bytes = algorithmic_bytes_per_token(cfg, len(kv)) // world
-    roofline = {"bound": "hbm", "kernel": "gemv_kernel<Q4_K, 1 token>", "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "launches_timed": iters * nl, "avg_launch_us": per_launch_s * 1e6,
-                "algorithmic_bytes_per_launch": nbytes // nl,
+    kernels = None
+    if world == 1:
+        # the fused decode kernels, each timed back to back over all layers (every launch streams its own layer's weights);
+        # the gate/up kernel carries 43% of a token's bytes and is the one reported
+        names = {1: "attn_q/k/v + RoPE + KV append", 2: "attn_output + residual", 3: "ffn_gate + ffn_up + SwiGLU + int8 output",
+                 4: "ffn_down + residual", 5: "output projection"}
+        kernels = {}
+        for v in (1, 2, 3, 4, 5):
+            ms, nbytes, nl = model.profile_gemv(12, iters, v)
+            us = ms * 1e3 / (iters * nl)
+            kernels[names[v]] = {"avg_launch_us": us, "algorithmic_bytes_per_launch": nbytes // nl, "GB/s": nbytes / nl / us / 1e3,
+                                 "launches_per_token": nl}
+        dom = kernels[names[3]]
+        kname, per_launch_s, bytes_per_launch, timed = "stream_gemv_kernel<16, Q4_K> (" + names[3] + ")", dom["avg_launch_us"] * 1e-6, dom["algorithmic_bytes_per_launch"], iters * cfg["n_layer"]
+    else:
+        ms, nbytes, nl = model.profile_gemv(12, iters)
+        kname, per_launch_s, bytes_per_launch, timed = "gemv_kernel<Q4_K, 1 token>", ms * 1e-3 / (iters * nl), nbytes // nl, iters * nl
+    achieved = bytes_per_launch / per_launch_s / 1e9
+    roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "launches_timed": timed, "avg_launch_us": per_launch_s * 1e6,
+                "algorithmic_bytes_per_launch": bytes_per_launch,
                 "step": {"algorithmic_bytes_per_token_per_gpu": step_bytes, "achieved": step_bytes / (dev_ms * 1e-3 / K) / 1e9,
                          "frac": step_bytes / (dev_ms * 1e-3 / K) / 1e9 / peak}}
+    if kernels:
+        roofline["kernels"] = kernels
 
     # ---- batch 64 extra ---------------------------------------------------------------------------------
     batch64 = None

@@ -837,10 +837,17 @@ __global__ void __launch_bounds__(SC_THREADS) attn_scores_kernel(AttnExactArgs a
         for (int g = 0; g < G; ++g) acc[g] = 0.0f;
         if (live) {
             const __half *kp = a.k_pool + (((uint64_t)table[p / KV_PAGE] * a.n_head_kv + kvh) * KV_PAGE + p % KV_PAGE) * hd;
-            for (uint32_t c = 0; c < chunks; ++c) {
-                const float kf = __half2float(kp[8 * c + j]);
+            __half kv[32];  // head_dim <= 256: all loads first, so that they overlap
 #pragma unroll
-                for (int g = 0; g < G; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(sq[g * hd + 8 * c + j], kf));
+            for (uint32_t c = 0; c < 32; ++c)
+                if (c < chunks) kv[c] = kp[8 * c + j];
+#pragma unroll
+            for (uint32_t c = 0; c < 32; ++c) {
+                if (c < chunks) {
+                    const float kf = __half2float(kv[c]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc[g] = __fadd_rn(acc[g], __fmul_rn(sq[g * hd + 8 * c + j], kf));
+                }
             }
         }
 #pragma unroll
@@ -883,30 +890,68 @@ __global__ void __launch_bounds__(128) attn_softmax_kernel(AttnExactArgs a) {
         for (uint32_t p = threadIdx.x; p < n_pos; p += blockDim.x) s[p] = __fdiv_rn(s[p], sum);
 }
 
-// grid (hd / 16, n_head_kv, n_rows), G * 16 threads: thread (g, d) carries out[h][d]
+// grid (hd / 16, n_head_kv, n_rows), G * 16 threads: thread (g, d) carries out[h][d] = (..((0 + w_0 v_0[d]) + w_1 v_1[d]) + ..).
+// The chain reads its operands from shared memory; the CTA brings them there a tile of 2 * threads positions at a time,
+// the next tile's global loads in flight while the current tile is being added.
 template <int G>
 __global__ void __launch_bounds__(G * 16) attn_output_kernel(AttnExactArgs a) {
+    constexpr int NT = G * 16, TILE = 2 * NT;
+    __shared__ __align__(16) __half sv[2][TILE][16];
+    __shared__ __align__(16) float sw[2][G][TILE];
     const uint32_t slice = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const uint32_t n_pos = a.n_pos[row], hd = a.head_dim;
-    const uint32_t g = threadIdx.x >> 4, d = slice * 16 + (threadIdx.x & 15);
-    const uint32_t head = kvh * G + g;
-    const float *w = a.scores + ((uint64_t)row * a.n_head + head) * a.score_stride;
+    const uint32_t tid = threadIdx.x, g = tid >> 4, d = tid & 15;
+    const uint32_t head0 = kvh * G;
+    const float *w0 = a.scores + ((uint64_t)row * a.n_head + head0) * a.score_stride;
     const int32_t *table = a.page_tables[row];
-    float o = 0.0f;
-    for (uint32_t pg = 0; pg * KV_PAGE < n_pos; ++pg) {
-        const __half *vp = a.v_pool + ((uint64_t)table[pg] * a.n_head_kv + kvh) * KV_PAGE * hd + d;
-        const uint32_t cnt = min((uint32_t)KV_PAGE, n_pos - pg * KV_PAGE);
-        float wv[KV_PAGE], vv[KV_PAGE];
+    const uint32_t n_tiles = (n_pos + TILE - 1) / TILE;
+
+    uint4 rv[4];      // this thread's share of a tile: positions 2 tid, 2 tid + 1, two 16-byte halves each
+    float rw[2 * G];  // and weights tid + NT * i of head i / 2 ... see the index below
+    auto load_tile = [&](uint32_t t) {
+        const uint32_t p0 = t * TILE;
 #pragma unroll
-        for (int t = 0; t < KV_PAGE; ++t) {  // the loads do not depend on the chain: issue them all first
-            wv[t] = t < (int)cnt ? w[pg * KV_PAGE + t] : 0.0f;
-            vv[t] = t < (int)cnt ? __half2float(vp[(uint32_t)t * hd]) : 0.0f;
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t p = p0 + 2 * tid + i;
+            if (p < n_pos) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(a.v_pool + (((uint64_t)table[p / KV_PAGE] * a.n_head_kv + kvh) * KV_PAGE + p % KV_PAGE) * hd + slice * 16);
+                rv[2 * i] = src[0];
+                rv[2 * i + 1] = src[1];
+            } else {
+                rv[2 * i] = rv[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            }
         }
 #pragma unroll
-        for (int t = 0; t < KV_PAGE; ++t)
-            if (t < (int)cnt) o = __fadd_rn(o, __fmul_rn(wv[t], vv[t]));
+        for (int i = 0; i < 2 * G; ++i) {  // element (head i / 2, position tid + NT * (i % 2)) of the tile's weights
+            const uint32_t p = p0 + tid + NT * (i & 1);
+            rw[i] = p < n_pos ? w0[(uint64_t)(i >> 1) * a.score_stride + p] : 0.0f;
+        }
+    };
+    auto store_tile = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            *reinterpret_cast<uint4 *>(&sv[buf][2 * tid + i][0]) = rv[2 * i];
+            *reinterpret_cast<uint4 *>(&sv[buf][2 * tid + i][8]) = rv[2 * i + 1];
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * G; ++i) sw[buf][i >> 1][tid + NT * (i & 1)] = rw[i];
+    };
+
+    float o = 0.0f;
+    if (n_tiles) {
+        load_tile(0);
+        store_tile(0);
     }
-    a.out[(uint64_t)row * a.n_head * hd + (uint64_t)head * hd + d] = o;
+    __syncthreads();
+    for (uint32_t t = 0; t < n_tiles; ++t) {
+        const int buf = (int)(t & 1);
+        if (t + 1 < n_tiles) load_tile(t + 1);
+        const uint32_t cnt = min((uint32_t)TILE, n_pos - t * TILE);
+        for (uint32_t p = 0; p < cnt; ++p) o = __fadd_rn(o, __fmul_rn(sw[buf][g][p], __half2float(sv[buf][p][d])));
+        if (t + 1 < n_tiles) store_tile(buf ^ 1);
+        __syncthreads();
+    }
+    a.out[(uint64_t)row * a.n_head * hd + (uint64_t)(head0 + g) * hd + slice * 16 + d] = o;
 }
 
 template <int G>
