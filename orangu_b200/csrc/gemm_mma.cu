@@ -27,15 +27,28 @@ namespace ob {
 
 namespace {
 
-constexpr int MM_WARPS = 4, MM_ROWS = 16 * MM_WARPS, MM_TOK = 64, MM_NT = MM_TOK / 8;
-constexpr uint32_t MM_A_BYTES = MM_ROWS * 144, MM_B_ROW = 272, MM_B_BYTES = MM_TOK * MM_B_ROW;
-constexpr uint32_t MM_S16_BYTES = MM_TOK * 32, MM_AD_BYTES = MM_TOK * 4, MM_BS_BYTES = MM_TOK * 16;
-constexpr uint32_t MM_STAGE = MM_A_BYTES + MM_B_BYTES + MM_S16_BYTES + MM_AD_BYTES + MM_BS_BYTES;  // 30,208 bytes
+constexpr int MM_WARPS = 4, MM_ROWS = 16 * MM_WARPS;
+constexpr uint32_t MM_B_ROW = 272;
+
+// shared-memory stage of one super-block: weight blocks of 64 rows | activations of TOK tokens | per-16 sums | token scales |
+// per-32 sums | (Q6_K) the rows' d
+template <uint32_t TYPE, int NT>
+struct MmStage {
+    static constexpr uint32_t TOK = 8 * NT;
+    static constexpr uint32_t BLK = TYPE == TYPE_Q4_K ? 144 : 208;
+    static constexpr uint32_t A = 0, B = MM_ROWS * BLK, S16 = B + TOK * MM_B_ROW, AD = S16 + TOK * 32, BS = AD + TOK * 4, DW = BS + TOK * 16;
+    static constexpr uint32_t BYTES = DW + MM_ROWS * 4;
+};
 
 __device__ __forceinline__ void mma_u8s8_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0));
 }
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
     uint32_t v;
@@ -61,9 +74,12 @@ __device__ __forceinline__ int dp2a_hi_su(uint32_t a, uint32_t b, int c) {  // c
     return d;
 }
 
-// GEMM: the prefill association (two passes); otherwise every (row, token) is the single-token product.
-template <bool GEMM>
-__global__ void __launch_bounds__(MM_WARPS * 32) gemm_q4k_mma_kernel(GemvArgs a) {
+// GEMM: the prefill association (Q4_K: two passes); otherwise every (row, token) is the single-token product.
+// NT: n-tiles of 8 tokens per CTA.
+template <uint32_t TYPE, bool GEMM, int NT>
+__global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
+    using S = MmStage<TYPE, NT>;
+    constexpr uint32_t TOK = S::TOK, BLK = S::BLK;
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
@@ -77,46 +93,53 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_q4k_mma_kernel(GemvArgs a)
     }
     const GemvSegment &seg = a.seg[si];
     const uint32_t out_dim = seg.w.out_dim, nb = seg.w.nb;
-    const uint32_t row0 = tile * MM_ROWS, tok0 = blockIdx.y * MM_TOK;
-    const uint32_t n_tok = min((uint32_t)MM_TOK, a.n_tokens - tok0);
+    const uint32_t row0 = tile * MM_ROWS, tok0 = blockIdx.y * TOK;
+    const uint32_t n_tok = min(TOK, a.n_tokens - tok0);
 
     // activation rows of tokens past the end stay zero in both stages
-    for (uint32_t i = tid; i < 2 * MM_STAGE / 16; i += MM_WARPS * 32) *reinterpret_cast<uint4 *>(smem + i * 16) = make_uint4(0, 0, 0, 0);
+    for (uint32_t i = tid; i < 2 * S::BYTES / 16; i += MM_WARPS * 32) *reinterpret_cast<uint4 *>(smem + i * 16) = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
     auto stage_block = [&](uint32_t b, int st, bool codes) {
-        const uint32_t base = sbase + st * MM_STAGE;
+        const uint32_t base = sbase + st * S::BYTES;
         if (codes) {
-            for (uint32_t c = tid; c < MM_ROWS * 9; c += MM_WARPS * 32) {  // weights: 64 rows x 144 bytes
-                const uint32_t r = c / 9, j = c % 9, row = min(row0 + r, out_dim - 1);
-                cp16(base + r * 144 + j * 16, seg.w.data + (uint64_t)row * seg.w.row_stride + (uint64_t)b * 144 + j * 16);
+            constexpr uint32_t CPR = BLK / 16;  // 16-byte chunks per row block
+            for (uint32_t c = tid; c < MM_ROWS * CPR; c += MM_WARPS * 32) {
+                const uint32_t r = c / CPR, j = c % CPR, row = min(row0 + r, out_dim - 1);
+                cp16(base + S::A + r * BLK + j * 16, seg.w.data + (uint64_t)row * seg.w.row_stride + (uint64_t)b * BLK + j * 16);
             }
             for (uint32_t c = tid; c < n_tok * 16; c += MM_WARPS * 32) {  // activations: tokens x 256 int8
                 const uint32_t t = c >> 4, j = c & 15;
-                cp16(base + MM_A_BYTES + t * MM_B_ROW + j * 16, a.act.q + (uint64_t)(tok0 + t) * a.act.dim_cap + (uint64_t)b * 256 + j * 16);
+                cp16(base + S::B + t * MM_B_ROW + j * 16, a.act.q + (uint64_t)(tok0 + t) * a.act.dim_cap + (uint64_t)b * 256 + j * 16);
+            }
+            if (TYPE == TYPE_Q6_K && tid < MM_ROWS) {  // the rows' f16 d of this block, from the plane behind the blocks
+                const uint32_t row = min(row0 + tid, out_dim - 1);
+                const uint16_t bits = *reinterpret_cast<const uint16_t *>(seg.w.data + (uint64_t)row * seg.w.row_stride + seg.w.d_off + 2 * b);
+                *reinterpret_cast<float *>(smem + st * S::BYTES + S::DW + tid * 4) = f16_bits_to_f32(bits);
             }
         } else {
             for (uint32_t r = tid; r < MM_ROWS; r += MM_WARPS * 32) {  // only the 16-byte headers: d, dmin, scales and mins
                 const uint32_t row = min(row0 + r, out_dim - 1);
-                cp16(base + r * 144, seg.w.data + (uint64_t)row * seg.w.row_stride + (uint64_t)b * 144);
+                cp16(base + S::A + r * BLK, seg.w.data + (uint64_t)row * seg.w.row_stride + (uint64_t)b * BLK);
             }
         }
-        for (uint32_t c = tid; c < n_tok * 2; c += MM_WARPS * 32) {  // per-16 sums: 16 int16 per token
-            const uint32_t t = c >> 1, j = c & 1;
-            cp16(base + MM_A_BYTES + MM_B_BYTES + t * 32 + j * 16, a.act.sums + (uint64_t)(tok0 + t) * (a.act.dim_cap / 16) + (uint64_t)b * 16 + j * 8);
+        if (TYPE == TYPE_Q4_K) {
+            for (uint32_t c = tid; c < n_tok * 2; c += MM_WARPS * 32) {  // per-16 sums: 16 int16 per token
+                const uint32_t t = c >> 1, j = c & 1;
+                cp16(base + S::S16 + t * 32 + j * 16, a.act.sums + (uint64_t)(tok0 + t) * (a.act.dim_cap / 16) + (uint64_t)b * 16 + j * 8);
+            }
         }
         if (tid < (int)n_tok)
-            *reinterpret_cast<float *>(smem + st * MM_STAGE + MM_A_BYTES + MM_B_BYTES + MM_S16_BYTES + tid * 4) =
-                a.act.d[(uint64_t)(tok0 + tid) * (a.act.dim_cap / 256) + b];
+            *reinterpret_cast<float *>(smem + st * S::BYTES + S::AD + tid * 4) = a.act.d[(uint64_t)(tok0 + tid) * (a.act.dim_cap / 256) + b];
     };
 
-    float acc[MM_NT][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < MM_NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
 
-    const int n_pass = GEMM ? 2 : 1;
-    for (int pass = 0; pass < n_pass; ++pass) {
-        const bool min_pass = GEMM && pass == 0;  // pass 1 of the prefill order: the min terms of all super-blocks
+    constexpr int N_PASS = GEMM && TYPE == TYPE_Q4_K ? 2 : 1;
+    for (int pass = 0; pass < N_PASS; ++pass) {
+        const bool min_pass = N_PASS == 2 && pass == 0;  // pass 1 of the Q4_K prefill order: the min terms of all super-blocks
         stage_block(0, 0, !min_pass);
         __pipeline_commit();
         for (uint32_t b = 0; b < nb; ++b) {
@@ -125,95 +148,152 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_q4k_mma_kernel(GemvArgs a)
             __pipeline_commit();
             __pipeline_wait_prior(1);
             __syncthreads();  // block b has landed
-            const uint32_t base = sbase + st * MM_STAGE;
-            // per-32 sums from the per-16 sums: token t, pair j
-            for (uint32_t i = tid; i < MM_TOK * 8; i += MM_WARPS * 32) {
-                const uint32_t w = lds_u32(base + MM_A_BYTES + MM_B_BYTES + i * 4);
-                reinterpret_cast<int16_t *>(smem + st * MM_STAGE + MM_A_BYTES + MM_B_BYTES + MM_S16_BYTES + MM_AD_BYTES)[i] =
-                    (int16_t)((int)(int16_t)(w & 0xffff) + (int)(int16_t)(w >> 16));
-            }
-            __syncthreads();
-
-            // this warp's rows gid and gid + 8 of the tile: header words
-            const uint32_t arow[2] = {base + (warp * 16 + gid) * 144, base + (warp * 16 + gid + 8) * 144};
-            uint32_t scl[2], sch[2], ml[2], mh[2];
-            float dd[2], dmin[2];
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const uint4 hd = lds_u128(arow[r]);
-                dd[r] = f16_bits_to_f32(hd.x & 0xffffu);
-                dmin[r] = f16_bits_to_f32(hd.x >> 16);
-                scl[r] = hd.y & 0x3f3f3f3fu;  // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of four words
-                ml[r] = hd.z & 0x3f3f3f3fu;
-                sch[r] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
-                mh[r] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
-            }
-            int isum[MM_NT][4];
-#pragma unroll
-            for (int nt = 0; nt < MM_NT; ++nt) isum[nt][0] = isum[nt][1] = isum[nt][2] = isum[nt][3] = 0;
-            if (!min_pass) {
-#pragma unroll
-                for (int g = 0; g < 4; ++g) {  // sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles) of bytes 32g .. 32g + 31
-                    uint32_t w[2][2];
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        w[r][0] = lds_u32(arow[r] + 16 + 32 * g + 4 * tig);
-                        w[r][1] = lds_u32(arow[r] + 16 + 32 * g + 16 + 4 * tig);
-                    }
-                    const uint32_t M = 0x0f0f0f0fu;
-                    const uint32_t lo0 = w[0][0] & M, lo1 = w[1][0] & M, lo2 = w[0][1] & M, lo3 = w[1][1] & M;
-                    const uint32_t hi0 = (w[0][0] >> 4) & M, hi1 = (w[1][0] >> 4) & M, hi2 = (w[0][1] >> 4) & M, hi3 = (w[1][1] >> 4) & M;
-                    const uint32_t scw0 = g < 2 ? scl[0] : sch[0], scw1 = g < 2 ? scl[1] : sch[1];
-                    const int sa0 = (int)((scw0 >> (16 * (g & 1))) & 0xff), sb0 = (int)((scw0 >> (16 * (g & 1) + 8)) & 0xff);
-                    const int sa1 = (int)((scw1 >> (16 * (g & 1))) & 0xff), sb1 = (int)((scw1 >> (16 * (g & 1) + 8)) & 0xff);
-#pragma unroll
-                    for (int nt = 0; nt < MM_NT; ++nt) {
-                        const uint32_t xb = base + MM_A_BYTES + (8 * nt + gid) * MM_B_ROW + 64 * g + 4 * tig;
-                        int c[4] = {0, 0, 0, 0};
-                        mma_u8s8_k32(c, lo0, lo1, lo2, lo3, lds_u32(xb), lds_u32(xb + 16));
-                        isum[nt][0] += sa0 * c[0];
-                        isum[nt][1] += sa0 * c[1];
-                        isum[nt][2] += sa1 * c[2];
-                        isum[nt][3] += sa1 * c[3];
-                        int e[4] = {0, 0, 0, 0};
-                        mma_u8s8_k32(e, hi0, hi1, hi2, hi3, lds_u32(xb + 32), lds_u32(xb + 48));
-                        isum[nt][0] += sb0 * e[0];
-                        isum[nt][1] += sb0 * e[1];
-                        isum[nt][2] += sb1 * e[2];
-                        isum[nt][3] += sb1 * e[3];
-                    }
+            const uint32_t base = sbase + st * S::BYTES;
+            if (TYPE == TYPE_Q4_K) {  // per-32 sums from the per-16 sums: token t, pair j
+                for (uint32_t i = tid; i < TOK * 8; i += MM_WARPS * 32) {
+                    const uint32_t w = lds_u32(base + S::S16 + i * 4);
+                    reinterpret_cast<int16_t *>(smem + st * S::BYTES + S::BS)[i] = (int16_t)((int)(int16_t)(w & 0xffff) + (int)(int16_t)(w >> 16));
                 }
+                __syncthreads();
             }
-            // fp32 terms of this super-block for elements (row gid | gid + 8, token 8 nt + 2 tig | + 1)
+
+            // this warp's rows gid and gid + 8 of the tile
+            const uint32_t arow[2] = {base + S::A + (warp * 16 + gid) * BLK, base + S::A + (warp * 16 + gid + 8) * BLK};
+            int isum[NT][4];
 #pragma unroll
-            for (int nt = 0; nt < MM_NT; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) isum[nt][0] = isum[nt][1] = isum[nt][2] = isum[nt][3] = 0;
+
+            if constexpr (TYPE == TYPE_Q4_K) {
+                uint32_t scl[2], sch[2], ml[2], mh[2];
+                float dd[2], dmin[2];
 #pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint32_t t = 8 * nt + 2 * tig + k;
-                    const float ad = __uint_as_float(lds_u32(base + MM_A_BYTES + MM_B_BYTES + MM_S16_BYTES + t * 4));
-                    int imin[2] = {0, 0};
-                    if (!GEMM || min_pass) {
-                        const uint4 bsv = lds_u128(base + MM_A_BYTES + MM_B_BYTES + MM_S16_BYTES + MM_AD_BYTES + t * 16);
+                for (int r = 0; r < 2; ++r) {
+                    const uint4 hd = lds_u128(arow[r]);
+                    dd[r] = f16_bits_to_f32(hd.x & 0xffffu);
+                    dmin[r] = f16_bits_to_f32(hd.x >> 16);
+                    scl[r] = hd.y & 0x3f3f3f3fu;  // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of four words
+                    ml[r] = hd.z & 0x3f3f3f3fu;
+                    sch[r] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
+                    mh[r] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+                }
+                if (!min_pass) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {  // sub-blocks 2g (low nibbles) and 2g + 1 (high nibbles) of bytes 32g .. 32g + 31
+                        uint32_t w[2][2];
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
-                            int v = dp2a_lo_su(bsv.x, ml[r], 0);
-                            v = dp2a_hi_su(bsv.y, ml[r], v);
-                            v = dp2a_lo_su(bsv.z, mh[r], v);
-                            imin[r] = dp2a_hi_su(bsv.w, mh[r], v);
+                            w[r][0] = lds_u32(arow[r] + 16 + 32 * g + 4 * tig);
+                            w[r][1] = lds_u32(arow[r] + 16 + 32 * g + 16 + 4 * tig);
                         }
-                    }
+                        const uint32_t M = 0x0f0f0f0fu;
+                        const uint32_t lo0 = w[0][0] & M, lo1 = w[1][0] & M, lo2 = w[0][1] & M, lo3 = w[1][1] & M;
+                        const uint32_t hi0 = (w[0][0] >> 4) & M, hi1 = (w[1][0] >> 4) & M, hi2 = (w[0][1] >> 4) & M, hi3 = (w[1][1] >> 4) & M;
+                        const uint32_t scw0 = g < 2 ? scl[0] : sch[0], scw1 = g < 2 ? scl[1] : sch[1];
+                        const int sa0 = (int)((scw0 >> (16 * (g & 1))) & 0xff), sb0 = (int)((scw0 >> (16 * (g & 1) + 8)) & 0xff);
+                        const int sa1 = (int)((scw1 >> (16 * (g & 1))) & 0xff), sb1 = (int)((scw1 >> (16 * (g & 1) + 8)) & 0xff);
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        float &o = acc[nt][2 * r + k];
-                        if (!GEMM) {
-                            o = __fadd_rn(o, __fmul_rn(ad, __fsub_rn(__fmul_rn(dd[r], (float)isum[nt][2 * r + k]), __fmul_rn(dmin[r], (float)imin[r]))));
-                        } else if (min_pass) {
-                            o = __fsub_rn(o, __fmul_rn(__fmul_rn(ad, dmin[r]), (float)imin[r]));
-                        } else {
-                            o = __fadd_rn(o, __fmul_rn(ad, __fmul_rn(dd[r], (float)isum[nt][2 * r + k])));
+                        for (int nt = 0; nt < NT; ++nt) {
+                            const uint32_t xb = base + S::B + (8 * nt + gid) * MM_B_ROW + 64 * g + 4 * tig;
+                            int c[4] = {0, 0, 0, 0};
+                            mma_u8s8_k32(c, lo0, lo1, lo2, lo3, lds_u32(xb), lds_u32(xb + 16));
+                            isum[nt][0] += sa0 * c[0];
+                            isum[nt][1] += sa0 * c[1];
+                            isum[nt][2] += sa1 * c[2];
+                            isum[nt][3] += sa1 * c[3];
+                            int e[4] = {0, 0, 0, 0};
+                            mma_u8s8_k32(e, hi0, hi1, hi2, hi3, lds_u32(xb + 32), lds_u32(xb + 48));
+                            isum[nt][0] += sb0 * e[0];
+                            isum[nt][1] += sb0 * e[1];
+                            isum[nt][2] += sb1 * e[2];
+                            isum[nt][3] += sb1 * e[3];
                         }
                     }
                 }
+                // fp32 terms of this super-block for elements (row gid | gid + 8, token 8 nt + 2 tig | + 1)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint32_t t = 8 * nt + 2 * tig + k;
+                        const float ad = __uint_as_float(lds_u32(base + S::AD + t * 4));
+                        int imin[2] = {0, 0};
+                        if (!GEMM || min_pass) {
+                            const uint4 bsv = lds_u128(base + S::BS + t * 16);
+#pragma unroll
+                            for (int r = 0; r < 2; ++r) {
+                                int v = dp2a_lo_su(bsv.x, ml[r], 0);
+                                v = dp2a_hi_su(bsv.y, ml[r], v);
+                                v = dp2a_lo_su(bsv.z, mh[r], v);
+                                imin[r] = dp2a_hi_su(bsv.w, mh[r], v);
+                            }
+                        }
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            float &o = acc[nt][2 * r + k];
+                            if (!GEMM) {
+                                o = __fadd_rn(o, __fmul_rn(ad, __fsub_rn(__fmul_rn(dd[r], (float)isum[nt][2 * r + k]), __fmul_rn(dmin[r], (float)imin[r]))));
+                            } else if (min_pass) {
+                                o = __fsub_rn(o, __fmul_rn(__fmul_rn(ad, dmin[r]), (float)imin[r]));
+                            } else {
+                                o = __fadd_rn(o, __fmul_rn(ad, __fmul_rn(dd[r], (float)isum[nt][2 * r + k])));
+                            }
+                        }
+                    }
+                }
+            } else {  // Q6_K: block = [ql 128 | qh 64 | signed scales 16]; sixteen sub-blocks of 16 elements
+                uint32_t scw[2][4];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const uint4 v = lds_u128(arow[r] + 192);
+                    scw[r][0] = v.x;
+                    scw[r][1] = v.y;
+                    scw[r][2] = v.z;
+                    scw[r][3] = v.w;
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int is = 0; is < 2; ++is) {
+                        // codes l = 16 is + 4 tig .. + 3 of this half: ql bytes l (runs 0, 2) and 32 + l (runs 1, 3), qh bytes l
+                        uint32_t v[2][4];
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const uint32_t qa = lds_u32(arow[r] + 64 * h + 16 * is + 4 * tig), qb = lds_u32(arow[r] + 64 * h + 32 + 16 * is + 4 * tig);
+                            const uint32_t qh = lds_u32(arow[r] + 128 + 32 * h + 16 * is + 4 * tig);
+                            v[r][0] = __vsub4((qa & 0x0f0f0f0fu) | ((qh << 4) & 0x30303030u), 0x20202020u);  // q - 32 as signed bytes
+                            v[r][1] = __vsub4((qb & 0x0f0f0f0fu) | ((qh << 2) & 0x30303030u), 0x20202020u);
+                            v[r][2] = __vsub4(((qa >> 4) & 0x0f0f0f0fu) | (qh & 0x30303030u), 0x20202020u);
+                            v[r][3] = __vsub4(((qb >> 4) & 0x0f0f0f0fu) | ((qh >> 2) & 0x30303030u), 0x20202020u);
+                        }
+#pragma unroll
+                        for (int run = 0; run < 4; ++run) {
+                            const int sidx = 8 * h + 2 * run + is;  // scale of elements 128 h + 32 run + 16 is ..
+                            const int s0 = (int)(int8_t)((scw[0][sidx >> 2] >> (8 * (sidx & 3))) & 0xff), s1 = (int)(int8_t)((scw[1][sidx >> 2] >> (8 * (sidx & 3))) & 0xff);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                int c[4] = {0, 0, 0, 0};
+                                mma_s8s8_k16(c, v[0][run], v[1][run], lds_u32(base + S::B + (8 * nt + gid) * MM_B_ROW + 128 * h + 32 * run + 16 * is + 4 * tig));
+                                isum[nt][0] += s0 * c[0];
+                                isum[nt][1] += s0 * c[1];
+                                isum[nt][2] += s1 * c[2];
+                                isum[nt][3] += s1 * c[3];
+                            }
+                        }
+                    }
+                }
+                const float dw[2] = {__uint_as_float(lds_u32(base + S::DW + (warp * 16 + gid) * 4)), __uint_as_float(lds_u32(base + S::DW + (warp * 16 + gid + 8) * 4))};
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const float ad = __uint_as_float(lds_u32(base + S::AD + (8 * nt + 2 * tig + k) * 4));
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const float fi = (float)isum[nt][2 * r + k];
+                            const float term = GEMM ? __fmul_rn(ad, __fmul_rn(dw[r], fi)) : __fmul_rn(__fmul_rn(ad, dw[r]), fi);
+                            acc[nt][2 * r + k] = __fadd_rn(acc[nt][2 * r + k], term);
+                        }
+                    }
             }
             __syncthreads();  // everyone is done with this stage before it is refilled
         }
@@ -222,7 +302,7 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_q4k_mma_kernel(GemvArgs a)
 
     // ---- store
 #pragma unroll
-    for (int nt = 0; nt < MM_NT; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t row = row0 + warp * 16 + gid + 8 * (i >> 1), t = 8 * nt + 2 * tig + (i & 1);
@@ -235,27 +315,50 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_q4k_mma_kernel(GemvArgs a)
         }
 }
 
+template <uint32_t TYPE, bool GEMM, int NT>
+void launch_mma_instance(const GemvArgs &a, uint32_t tiles, cudaStream_t st) {
+    static bool configured = false;
+    constexpr uint32_t smem = 2 * MmStage<TYPE, NT>::BYTES;
+    if (!configured) {
+        cudaFuncSetAttribute(gemm_mma_kernel<TYPE, GEMM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        configured = true;
+    }
+    const dim3 grid(tiles, (a.n_tokens + 8 * NT - 1) / (8 * NT));
+    gemm_mma_kernel<TYPE, GEMM, NT><<<grid, MM_WARPS * 32, smem, st>>>(a);
+}
+
+template <uint32_t TYPE, bool GEMM>
+void launch_mma_nt(const GemvArgs &a, uint32_t tiles, int nt, cudaStream_t st) {
+    if (nt == 8) launch_mma_instance<TYPE, GEMM, 8>(a, tiles, st);
+    else if (nt == 4) launch_mma_instance<TYPE, GEMM, 4>(a, tiles, st);
+    else launch_mma_instance<TYPE, GEMM, 2>(a, tiles, st);
+}
+
 }  // namespace
 
 bool gemm_mma_supported(const GemvArgs &a) {
     if (a.n_seg < 1 || a.n_tokens < 9 || a.isum_out) return false;
+    const uint32_t type = a.seg[0].w.type;
+    if (type != TYPE_Q4_K && type != TYPE_Q6_K) return false;
     for (int s = 0; s < a.n_seg; ++s)
-        if (a.seg[s].w.type != TYPE_Q4_K || a.seg[s].w.in_dim != a.seg[0].w.in_dim) return false;
+        if (a.seg[s].w.type != type || a.seg[s].w.in_dim != a.seg[0].w.in_dim) return false;
     return true;
 }
 
-void launch_gemm_mma(const GemvArgs &a, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(gemm_q4k_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * MM_STAGE);
-        cudaFuncSetAttribute(gemm_q4k_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * MM_STAGE);
-        configured = true;
-    }
+void launch_gemm_mma(const GemvArgs &a, int sm_count, cudaStream_t st) {
     uint32_t tiles = 0;
     for (int s = 0; s < a.n_seg; ++s) tiles += (a.seg[s].w.out_dim + MM_ROWS - 1) / MM_ROWS;
-    const dim3 grid(tiles, (a.n_tokens + MM_TOK - 1) / MM_TOK);
-    if (a.gemm_order) gemm_q4k_mma_kernel<true><<<grid, MM_WARPS * 32, 2 * MM_STAGE, st>>>(a);
-    else gemm_q4k_mma_kernel<false><<<grid, MM_WARPS * 32, 2 * MM_STAGE, st>>>(a);
+    // 64 tokens per CTA reuse every weight fragment eight times; fewer when that would leave SMs without a CTA
+    int nt = 8;
+    while (nt > 2 && (a.n_tokens <= 4u * nt || tiles * ((a.n_tokens + 8 * nt - 1) / (8 * nt)) < 2u * (uint32_t)sm_count)) nt /= 2;
+    const bool q4 = a.seg[0].w.type == TYPE_Q4_K;
+    if (q4) {
+        if (a.gemm_order) launch_mma_nt<TYPE_Q4_K, true>(a, tiles, nt, st);
+        else launch_mma_nt<TYPE_Q4_K, false>(a, tiles, nt, st);
+    } else {
+        if (a.gemm_order) launch_mma_nt<TYPE_Q6_K, true>(a, tiles, nt, st);
+        else launch_mma_nt<TYPE_Q6_K, false>(a, tiles, nt, st);
+    }
 }
 
 }  // namespace ob

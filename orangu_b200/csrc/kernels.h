@@ -55,9 +55,9 @@ void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st);
 size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, bool gemm_order);
 uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order);  // kernels launch_gemv issues
 
-// ---- gemm_mma.cu: many-token products on the tensor cores (Q4_K; 9 tokens or more)
+// ---- gemm_mma.cu: many-token products on the tensor cores (Q4_K and Q6_K; 9 tokens or more)
 bool gemm_mma_supported(const GemvArgs &a);
-void launch_gemm_mma(const GemvArgs &a, cudaStream_t st);
+void launch_gemm_mma(const GemvArgs &a, int sm_count, cudaStream_t st);
 
 // ---- stream_gemv.cu: fused single-token products for decode (Q4_K / Q6_K weights)
 enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1, SG_PRO_READY = 2 };
