@@ -38,6 +38,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))  # tests/oracle.py: the ctypes binding of the CPU oracle
 
+# torch.distributed.run exports OMP_NUM_THREADS=1; the synthetic-weight generator and the CPU oracle are OpenMP code and
+# would take minutes on one thread.  Give every rank its share of the host cores (before any OpenMP runtime starts).
+if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS", "1") == "1":
+    os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", os.environ["WORLD_SIZE"]))))
+
 import numpy as np  # noqa: E402
 
 METRIC = "decode tok/s (8B-shape Q4_K_M, bs1 & bs64); quantized GEMV HBM GB/s vs peak"
@@ -127,31 +132,11 @@ def model_config(args):
 
 
 def build_tensors(cfg, rank: int, world: int, barrier):
-    """Seeded synthetic tensors.  With several ranks, rank 0 writes them to /dev/shm once and the others map them."""
+    """Seeded synthetic tensors.  The generator is deterministic, so with several ranks every rank makes its own copy
+    (the library keeps only the rank's slices on the device)."""
     from orangu_b200 import synth
 
-    if world == 1:
-        return synth.model_tensors(cfg, seed=20240)
-    path = f"/dev/shm/ob_bench_{os.environ.get('MASTER_PORT', '0')}_{cfg['n_layer']}_{cfg['n_embd']}.npz.d"
-    if rank == 0:
-        tensors = synth.model_tensors(cfg, seed=20240)
-        os.makedirs(path, exist_ok=True)
-        index = {}
-        for name, t in tensors.items():
-            fn = os.path.join(path, name.replace(".", "_") + ".bin")
-            t["data"].tofile(fn)
-            index[name] = {k: v for k, v in t.items() if k != "data"}
-            index[name]["dtype"] = str(t["data"].dtype)
-        json.dump(index, open(os.path.join(path, "index.json"), "w"))
-        barrier()
-        return tensors
-    barrier()
-    index = json.load(open(os.path.join(path, "index.json")))
-    tensors = {}
-    for name, meta in index.items():
-        data = np.fromfile(os.path.join(path, name.replace(".", "_") + ".bin"), dtype=meta.pop("dtype"))
-        tensors[name] = dict(meta, data=data)
-    return tensors
+    return synth.model_tensors(cfg, seed=20240)
 
 
 def algorithmic_bytes_per_token(cfg, context: int) -> int:
@@ -282,7 +267,7 @@ def main():
         uid = bytes(buf.cpu().tolist())
 
     ctx_len, K, W = args.context, args.steps, args.warmup
-    b64 = args.batch64_steps if world == 1 else 0
+    b64 = args.batch64_steps
     margin = 2 * (K + W) + 96
     per_seq = ctx_len + margin
     model = orangu_b200.LlamaModel(be, cfg, tensors, max_seq_len=per_seq, max_batch_tokens=512,
@@ -366,12 +351,14 @@ def main():
         kv.truncate(ctx_len)
         firsts = [int(first)] * 64
         model.decode_loop(caches, firsts, 3)
+        barrier()
         out64 = model.decode_loop(caches, firsts, b64)
-        ms64 = be.last_device_ms()
+        ms64 = max_over_ranks(be.last_device_ms())
         batch64 = {"value": 64 * b64 / (ms64 * 1e-3), "unit": UNIT, "steps": b64, "ms_per_step": ms64 / b64, "sequences": 64,
                    "context": ctx_len, "kv": "63 sequences share the first one's prefilled pages by device copy (KvCache::copy_prefix_from)",
                    "algorithmic_bytes_per_step": algorithmic_bytes_per_token(cfg, 0) + 64 * (algorithmic_bytes_per_token(cfg, ctx_len) - algorithmic_bytes_per_token(cfg, 0))}
-        batch64["hbm_frac"] = batch64["algorithmic_bytes_per_step"] / (ms64 / b64 * 1e-3) / 1e9 / peak
+        batch64["hbm_frac_per_gpu"] = batch64["algorithmic_bytes_per_step"] / world / (ms64 / b64 * 1e-3) / 1e9 / peak
+        batch64["parallelism"] = f"tp{world}"
 
     # ---- CPU baseline (rank 0, single GPU runs only) --------------------------------------------------------
     cpu = None

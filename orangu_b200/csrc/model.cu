@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <cmath>
 #include <map>
 #include <vector>
 
@@ -322,7 +323,21 @@ bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
         at.counters = m->attn_counters;
         at.image = image;
         AttnDecodeArgs fused = at;
-        fused.n_splits = std::max(1u, std::min(m->max_splits, (uint32_t)m->ctx->sm_count / (T * m->n_head_kv_l)));  // one CTA per SM
+        {   // one CTA per SM; with more (row, kv head) pairs than SMs, the split count that wastes least of the last wave
+            const uint32_t pairs = T * m->n_head_kv_l, sms = (uint32_t)m->ctx->sm_count;
+            uint32_t best = std::max(1u, sms / pairs);
+            if (pairs >= sms) {
+                double best_waste = 1e9;
+                for (uint32_t s = 1; s <= 4; ++s) {
+                    const double waves = (double)pairs * s / sms, waste = (std::ceil(waves) - waves) / std::ceil(waves) + 0.01 * s;
+                    if (waste < best_waste) {
+                        best_waste = waste;
+                        best = s;
+                    }
+                }
+            }
+            fused.n_splits = std::max(1u, std::min(m->max_splits, best));
+        }
         if (m->use_fused_attn && launch_attn_decode_fused(fused, true, st)) {
             m->ctx->launches += 1;
             return image != nullptr && (m->n_head_l / m->n_head_kv_l * hd) % 256 == 0;
