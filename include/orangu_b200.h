@@ -152,8 +152,10 @@ int ob_quantize_act(ob_ctx *ctx, const float *x, uint32_t n, int per_256, int8_t
  * can dispatch to, VulkanBackend::gpu_attention_split (B/vulkan.rs:6330-6342, 10788): one query
  * token q [n_head*head_dim] against n_pos cached positions k,v [n_pos, n_head_kv*head_dim] f32,
  * which are stored as fp16 pages exactly as the KV mirror holds them (E/kv_cache.rs:26-32).
- * exact_order != 0 evaluates in the CPU loop's operation order (bit-identical to it); 0 takes the
- * split flash-decode kernel, whose result differs from the CPU's in the last bits. */
+ * exact_order 1 evaluates in the CPU loop's operation order (bit-identical to it); 0 takes the
+ * split flash-decode kernels and 2 the one-kernel tensor-core flash-decode that the decode step uses
+ * (head_dim 64 or 128; 1, 2, 4 or 8 query heads per kv head); their results differ from the CPU's in
+ * the last bits. */
 int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos,
                         uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, int exact_order, float *out);
 /* The split flash-decode attention of ob_attention_decode for callers that must not allocate: a slot's worker

@@ -205,12 +205,12 @@ class CudaBackend:
         capi.check(self._h, self._lib.ob_quantize_act(self._h, x.ctypes.data, x.size, 1 if per_256 else 0, q.ctypes.data, d.ctypes.data, sums.ctypes.data))
         return q, d, sums
 
-    def attention_decode(self, q, k, v, n_head: int, n_head_kv: int, head_dim: int, scale: float, exact_order: bool = True) -> np.ndarray:
+    def attention_decode(self, q, k, v, n_head: int, n_head_kv: int, head_dim: int, scale: float, exact_order: bool | int = True) -> np.ndarray:
         q = np.ascontiguousarray(q, np.float32).reshape(-1)
         k = np.ascontiguousarray(k, np.float32).reshape(-1, n_head_kv * head_dim)
         v = np.ascontiguousarray(v, np.float32).reshape(-1, n_head_kv * head_dim)
         out = np.empty(n_head * head_dim, np.float32)
-        capi.check(self._h, self._lib.ob_attention_decode(self._h, q.ctypes.data, k.ctypes.data, v.ctypes.data, k.shape[0], n_head, n_head_kv, head_dim, scale, 1 if exact_order else 0, out.ctypes.data))
+        capi.check(self._h, self._lib.ob_attention_decode(self._h, q.ctypes.data, k.ctypes.data, v.ctypes.data, k.shape[0], n_head, n_head_kv, head_dim, scale, int(exact_order), out.ctypes.data))
         return out
 
     def argmax(self, logits, recent=None, repeat_last_n: int = 64, penalty: float = 1.0) -> int:

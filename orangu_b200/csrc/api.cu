@@ -525,7 +525,7 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
     const uint32_t n_splits = std::max(1u, std::min(16u, n_pages / 4));
     const size_t pool_b = kp.size() * 2, part_o_b = (size_t)n_head * n_splits * head_dim * 4, part_ml_b = (size_t)n_head * n_splits * 8;
     const size_t meta_b = 256 + (size_t)n_pages * 4;
-    if (exact_order && !attn_exact_supported(n_head, n_head_kv, head_dim))
+    if (exact_order == 1 && !attn_exact_supported(n_head, n_head_kv, head_dim))
         return fail(ctx, OB_ERR_UNSUPPORTED, "attention_decode: exact order needs head_dim % 16 == 0 and a group of 1, 2, 3, 4 or 8 heads");
     int rc;
     if ((rc = ensure(ctx, ctx->sx, (size_t)q_dim * 4))) return rc;
@@ -561,7 +561,7 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
     a.part_o = static_cast<float *>(ctx->saux2.p);
     a.part_ml = reinterpret_cast<float *>(static_cast<uint8_t *>(ctx->saux2.p) + part_o_b);
     a.max_pos = n_pos;
-    if (exact_order) {
+    if (exact_order == 1) {
         const uint32_t stride = (n_pos + 63) / 64 * 64;
         if ((rc = ensure(ctx, ctx->sq, (size_t)n_head * stride * 4))) return rc;
         AttnExactArgs e{};
@@ -581,6 +581,12 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
         e.max_pos = n_pos;
         launch_attn_exact(e, ctx->stream);
         ctx->launches += 3;
+    } else if (exact_order == 2) {  // the one-kernel form the decode step uses
+        a.counters = reinterpret_cast<uint32_t *>(meta + 128);
+        OB_CUDA(ctx, cudaMemsetAsync(a.counters, 0, 128, ctx->stream));
+        if (n_head_kv > 32 || !launch_attn_decode_fused(a, false, ctx->stream))
+            return fail(ctx, OB_ERR_UNSUPPORTED, "attention_decode: the fused kernel needs head_dim 64 or 128 and 1, 2, 4 or 8 heads per kv head");
+        ctx->launches += 1;
     } else {
         launch_attn_decode(a, ctx->stream);
         ctx->launches += 2;

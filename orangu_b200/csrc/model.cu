@@ -96,6 +96,7 @@ struct ob_model {
     std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
     obtp::Comm *comm = nullptr;
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
+    bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
 };
 
@@ -250,6 +251,7 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.ready = m->ready_attn;
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
+        if (m->tp_size > 1) a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->proj, SG_EP_STORE};  // this rank's partial; summed over ranks afterwards
         break;
     case 3:
         a.n_seg = 1;
@@ -267,13 +269,14 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.ready = m->ready_ff;
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
+        if (m->tp_size > 1) a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->proj, SG_EP_STORE};
         break;
     default:
         a.n_seg = 1;
         a.in_dim = c.n_embd;
         a.prologue = SG_PRO_READY;
         a.ready = m->ready_embd;
-        a.seg[0] = StreamSeg{m->output->w, DevWeight{}, m->logits, SG_EP_STORE};
+        a.seg[0] = StreamSeg{m->output->w, DevWeight{}, m->logits + m->vocab0, SG_EP_STORE};  // this rank's vocabulary rows
         break;
     }
     return a;
@@ -369,12 +372,12 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
 
     // Batch-1 decode on one GPU with K-type weights takes the fused streaming kernels (stream_gemv.cu):
     // norm / quantize as prologue, RoPE + KV append, residual and SwiGLU as epilogues, 5 product kernels per layer.
-    const bool stream = T == 1 && !tp && m->use_stream && m->ready_embd;
+    const bool stream = T == 1 && m->use_stream && m->ready_embd;
     auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
 
     for (uint32_t li = 0; li < c.n_layer; ++li) {
         const LayerDev &L = m->layers[li];
-        const bool stream_layer = stream && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
+        const bool stream_layer = stream && m->stream_ok && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
                                   k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
         if (stream_layer) {
             launch_norm_quant(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
@@ -384,9 +387,19 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
                 m->ctx->launches++;
             }
             launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
+            if (tp) {
+                obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
+                launch_add(m->x, m->proj, n_embd, st);
+                m->ctx->launches += 2;
+            }
             launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
             launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
+            if (tp) {
+                obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
+                launch_add(m->x, m->proj, n_embd, st);
+                m->ctx->launches += 2;
+            }
             m->ctx->launches += 6;
             continue;
         }
@@ -435,11 +448,15 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         }
     }
 
-    if (n_logit_rows == 1 && stream && k_type(m->output)) {
+    if (n_logit_rows == 1 && stream && m->stream_ok && k_type(m->output)) {
         StreamArgs la = stream_args(m, 0, 5);
         launch_norm_quant(m->x + (size_t)logit_row0 * n_embd, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
         m->ctx->launches += 2;
+        if (tp) {
+            obtp::all_gather_logits(m->comm, m->logits, 1, c.n_vocab, m->vocab0, m->vocab_l, st);
+            m->ctx->launches++;
+        }
         if (want_argmax) {
             ArgmaxArgs am{};
             am.logits = m->logits;
@@ -667,6 +684,15 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) return bail(fail(ctx, OB_ERR_CUDA, std::string("model_create: ") + cudaGetErrorString(e)));
+    if (m->ready_embd && c.n_layer) {  // do the fused decode kernels cover this model's shapes?
+        m->stream_ok = true;
+        for (int v = 1; v <= 5; ++v) {
+            const StreamArgs sa = stream_args(m, 0, v);
+            bool k_types = true;
+            for (int sgi = 0; sgi < sa.n_seg; ++sgi) k_types = k_types && (sa.seg[sgi].w.type == TYPE_Q4_K || sa.seg[sgi].w.type == TYPE_Q6_K);
+            if (k_types && !stream_gemv_supported(sa)) m->stream_ok = false;
+        }
+    }
     *out = m;
     return OB_OK;
 }

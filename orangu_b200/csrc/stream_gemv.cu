@@ -36,6 +36,8 @@ namespace ob {
 
 namespace {
 
+// two CTAs of this much (plus the 1 KB the system reserves for each) fit the 228 KB of an SM
+constexpr uint32_t SG_MAX_SMEM = 112 * 1024;
 constexpr uint32_t ACT_BLOCK_STRIDE = 272;  // bytes per 256 int8 activations: 17 sixteen-byte chunks, so lanes one block apart hit different banks
 
 // bytes of `lp` blocks of one row inside a slot
@@ -638,7 +640,7 @@ bool stream_gemv_supported(const StreamArgs &a) {
         if (g.epilogue >= SG_EP_ROPE_Q && (g.w.out_dim & 1)) return false;
         q6 = q6 || g.w.type == TYPE_Q6_K;
     }
-    return sg_smem(a.in_dim, q6, pick_lp(a.in_dim / 256)).total <= 108 * 1024;
+    return sg_smem(a.in_dim, q6, pick_lp(a.in_dim / 256)).total <= SG_MAX_SMEM;
 }
 
 size_t act_image_bytes(uint32_t dim) { return act_image(dim / 256).bytes; }
@@ -684,7 +686,7 @@ template <int LP, bool Q6>
 void launch_instance(const cudaLaunchConfig_t &cfg, const StreamArgs &args) {
     static bool configured = false;  // one flag per instantiation
     if (!configured) {
-        cudaFuncSetAttribute(stream_gemv_kernel<LP, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 108 * 1024);
+        cudaFuncSetAttribute(stream_gemv_kernel<LP, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, SG_MAX_SMEM);
         configured = true;
     }
     cudaLaunchKernelEx(&cfg, stream_gemv_kernel<LP, Q6>, args);

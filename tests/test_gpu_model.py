@@ -234,3 +234,21 @@ def test_fused_flash_decode_agrees_with_the_split_kernels_and_the_oracle(backend
         assert np.abs(a - want).max() < LOGIT_TOL, step
         assert np.abs(b - want).max() < LOGIT_TOL, step
         assert np.abs(a - b).max() < LOGIT_TOL, step
+
+
+def test_70b_shape_layer_is_bit_exact(backend):
+    """One layer of the 70B shape (d_model 8192, 64 query heads on 8 kv heads, FFN 28672): rows of 32 and 112 super-blocks
+    and 8 query heads per kv head go through the fused decode kernels and the tensor-core prefill, bit for bit."""
+    cfg = dict(synth.CONFIGS["70b"])
+    cfg["n_layer"] = 1
+    cfg["n_vocab"] = 2048
+    tensors = synth.model_tensors(cfg, seed=31)
+    model, ref = LlamaModel(backend, cfg, tensors, max_seq_len=128, max_batch_tokens=64, kv_pool_tokens=256), O.Model(cfg, tensors)
+    toks = prompt(cfg, 40, 4)
+    kv, rkv = model.new_kv_cache(64), ref.new_kv(64, f16=True)
+    assert_bit_equal(model.forward(kv, toks, 0), ref.forward(rkv, toks, 0), "prefill logits")
+    tok = 7
+    for step in range(3):
+        got, want = model.forward(kv, [tok], 40 + step), ref.forward(rkv, [tok], 40 + step)
+        assert_bit_equal(got, want, f"decode step {step}")
+        tok = O.argmax(want)
