@@ -5,6 +5,7 @@
 #include <stdint.h>
 
 #include "common.cuh"
+#include "tp.h"
 
 namespace ob {
 
@@ -61,7 +62,7 @@ void launch_gemm_mma(const GemvArgs &a, int sm_count, cudaStream_t st);
 
 // ---- stream_gemv.cu: fused single-token products for decode (Q4_K / Q6_K weights)
 enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1, SG_PRO_READY = 2 };
-enum StreamEpilogue { SG_EP_STORE = 0, SG_EP_RESIDUAL = 1, SG_EP_SWIGLU = 2, SG_EP_ROPE_Q = 3, SG_EP_ROPE_K = 4, SG_EP_V = 5 };
+enum StreamEpilogue { SG_EP_STORE = 0, SG_EP_RESIDUAL = 1, SG_EP_SWIGLU = 2, SG_EP_ROPE_Q = 3, SG_EP_ROPE_K = 4, SG_EP_V = 5, SG_EP_XCHG = 6 };
 struct StreamSeg {
     DevWeight w;       // rows 2p, 2p+1 form pair p ...
     DevWeight w2;      // ... unless w2.data != nullptr: then pair p is (w row p, w2 row p)  (gate / up)
@@ -88,6 +89,9 @@ struct StreamArgs {
     const int32_t *const *page_table; // device: pointer to the sequence's page table
     __half *k_pool, *v_pool;
     uint32_t n_head_kv, head_dim, rope_dim;
+    // XCHG: the rows are this rank's partial of a contraction-split product; they go into every rank's exchange slot and
+    // the last CTA raises this rank's flag everywhere (tp.h).  px.size == 0: unused.
+    obtp::PeerXchg px;
     bool wait_dependency;    // launched with programmatic stream serialisation: wait for the predecessor before reading x
 };
 bool stream_gemv_supported(const StreamArgs &a);
@@ -97,6 +101,9 @@ void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool
 size_t act_image_bytes(uint32_t dim);
 // RMSNorm scale as launch_norm_scale (also stored to *scale_out), then (x * scale) * norm_w quantized per 256 into `image`.
 void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, bool programmatic, cudaStream_t st);
+// The same, but first the pending peer exchange is completed: x += the ranks' partials, added in rank order (x is written).
+void launch_norm_quant_consume(float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, const obtp::PeerXchg &px,
+                               bool programmatic, cudaStream_t st);
 // x quantized per 256 into `image`.
 void launch_quant_image(const float *x, uint32_t dim, uint8_t *image, bool programmatic, cudaStream_t st);
 

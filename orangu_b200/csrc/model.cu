@@ -95,6 +95,7 @@ struct ob_model {
     std::map<uint64_t, cudaGraphExec_t> graphs;
     std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
     obtp::Comm *comm = nullptr;
+    obtp::PeerXchg px{};         // size > 1: the single-token step exchanges partials through peer memory instead of NCCL
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
     bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
@@ -211,6 +212,8 @@ void quantize_into(ob_model *m, int source, const float *x, const float *aux, ui
     m->ctx->launches++;
 }
 
+int check_peer(ob_model *m);
+
 uint32_t pick_splits(const ob_model *m, uint32_t n_rows) {
     const uint32_t pairs = std::max(1u, n_rows * m->n_head_kv_l);
     uint32_t s = (4u * (uint32_t)m->ctx->sm_count + pairs - 1) / pairs;
@@ -252,6 +255,10 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
         if (m->tp_size > 1) a.seg[0] = StreamSeg{L.wo->w, DevWeight{}, m->proj, SG_EP_STORE};  // this rank's partial; summed over ranks afterwards
+        if (m->px.size > 1) {
+            a.seg[0].epilogue = SG_EP_XCHG;
+            a.px = m->px;
+        }
         break;
     case 3:
         a.n_seg = 1;
@@ -270,6 +277,10 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         a.residual = m->x;
         a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->x, SG_EP_RESIDUAL};
         if (m->tp_size > 1) a.seg[0] = StreamSeg{L.down->w, DevWeight{}, m->proj, SG_EP_STORE};
+        if (m->px.size > 1) {
+            a.seg[0].epilogue = SG_EP_XCHG;
+            a.px = m->px;
+        }
         break;
     default:
         a.n_seg = 1;
@@ -375,33 +386,48 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
     const bool stream = T == 1 && m->use_stream && m->ready_embd;
     auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
 
+    bool pending_exchange = false;  // a peer exchange has been started and the residual stream does not hold its sum yet
     for (uint32_t li = 0; li < c.n_layer; ++li) {
         const LayerDev &L = m->layers[li];
         const bool stream_layer = stream && m->stream_ok && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
                                   k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
         if (stream_layer) {
-            launch_norm_quant(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
+            const bool peer = tp && m->px.size > 1;
+            if (pending_exchange) launch_norm_quant_consume(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
+            else launch_norm_quant(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
+            pending_exchange = false;
             launch_stream_gemv(stream_args(m, li, 1), m->ctx->sm_count, true, st);
             if (!run_attention(m, li, T, exact_attn, pos_bound, m->ready_attn, d_tables, d_npos, st)) {
                 launch_quant_image(m->attn, q_dim, m->ready_attn, true, st);
                 m->ctx->launches++;
             }
             launch_stream_gemv(stream_args(m, li, 2), m->ctx->sm_count, true, st);
-            if (tp) {
-                obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
-                launch_add(m->x, m->proj, n_embd, st);
-                m->ctx->launches += 2;
+            if (peer) {
+                launch_norm_quant_consume(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
+            } else {
+                if (tp) {
+                    obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
+                    launch_add(m->x, m->proj, n_embd, st);
+                    m->ctx->launches += 2;
+                }
+                launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             }
-            launch_norm_quant(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
             launch_stream_gemv(stream_args(m, li, 3), m->ctx->sm_count, true, st);
             launch_stream_gemv(stream_args(m, li, 4), m->ctx->sm_count, true, st);
-            if (tp) {
+            if (peer) {
+                pending_exchange = true;  // completed by the next norm kernel
+            } else if (tp) {
                 obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
                 launch_add(m->x, m->proj, n_embd, st);
                 m->ctx->launches += 2;
             }
             m->ctx->launches += 6;
             continue;
+        }
+        if (pending_exchange) {  // an unfused layer after a fused one: complete the exchange on its own
+            launch_norm_quant_consume(m->x, nullptr, n_embd, c.rms_eps, m->norm_scale, nullptr, m->px, true, st);
+            m->ctx->launches++;
+            pending_exchange = false;
         }
         quantize_into(m, ACT_RMSNORM, m->x, L.attn_norm, T, n_embd, m->act_embd, needs_k({L.wq, L.wk, L.wv}), needs_flat({L.wq, L.wk, L.wv}), st);
         run_products(m, m->act_embd, {{L.wq, m->q, q_dim, nullptr}, {L.wk, m->k, kv_dim, nullptr}, {L.wv, m->v, kv_dim, nullptr}}, T, gemm_order, st);
@@ -450,7 +476,9 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
 
     if (n_logit_rows == 1 && stream && m->stream_ok && k_type(m->output)) {
         StreamArgs la = stream_args(m, 0, 5);
-        launch_norm_quant(m->x + (size_t)logit_row0 * n_embd, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
+        if (pending_exchange) launch_norm_quant_consume(m->x, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
+        else launch_norm_quant(m->x + (size_t)logit_row0 * n_embd, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, true, st);
+        pending_exchange = false;
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
         m->ctx->launches += 2;
         if (tp) {
@@ -467,7 +495,12 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             launch_argmax(am, st);
             m->ctx->launches += 3;
         }
-    } else if (n_logit_rows) {
+    } else if (pending_exchange) {
+        launch_norm_quant_consume(m->x, nullptr, n_embd, c.rms_eps, m->norm_scale, nullptr, m->px, true, st);
+        m->ctx->launches++;
+        pending_exchange = false;
+    }
+    if (n_logit_rows && !(n_logit_rows == 1 && stream && m->stream_ok && k_type(m->output))) {
         const float *xl = m->x + (size_t)logit_row0 * n_embd;
         quantize_into(m, ACT_RMSNORM, xl, m->output_norm, n_logit_rows, n_embd, m->act_embd, needs_k({m->output}), needs_flat({m->output}), st);
         // Always the single-token kernel: forward() projects one row (llama.rs:1026-1030).
@@ -680,6 +713,11 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         std::string err;
         m->comm = obtp::create(c.tp_unique_id, (int)rank, (int)tp, ctx->device, &err);
         if (!m->comm) return bail(fail(ctx, OB_ERR_COMM, "model_create: " + err));
+        const char *pe = getenv("OB_TP_PEER");
+        if (!(pe && pe[0] == '0' && pe[1] == 0) && tp <= 8) {
+            std::string perr;
+            if (!obtp::peer_init(m->comm, c.n_embd, ctx->device, &m->px, &perr)) m->px = obtp::PeerXchg{};  // no peer access: NCCL all-reduce
+        }
     }
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaGetLastError();
@@ -952,7 +990,7 @@ int run_rows(ob_model *m, const std::vector<ob_kv *> &row_kv, const uint32_t *to
     cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1);
     ctx->last_ms += ms;
     if (out_token) memcpy(out_token, m->h_out_tokens, (size_t)n_logit_rows * 4);
-    return OB_OK;
+    return check_peer(m);
 }
 
 }  // namespace
@@ -1038,6 +1076,16 @@ int ob_last_hidden(ob_model *m, uint32_t n_tokens, float *out) {
 
 namespace {
 
+// After a synchronisation: did a peer exchange of the tensor-parallel step run out of time?
+int check_peer(ob_model *m) {
+    if (m->px.size < 2) return OB_OK;
+    uint32_t e = 0;
+    if (cudaMemcpy(&e, m->px.err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(m->ctx, OB_ERR_CUDA, "reading the exchange status failed");
+    if (!e) return OB_OK;
+    cudaMemset(m->px.err, 0, 4);
+    return fail(m->ctx, OB_ERR_COMM, "tensor-parallel exchange: a rank did not deliver its partial within 4 s");
+}
+
 // kind 0: H2D metadata + step + D2H token (one host round trip per step)
 // kind 1: step + advance (device-resident loop)
 // exact: every window stays within exact_attn_max_pos for as long as the graph is replayed
@@ -1117,7 +1165,7 @@ int ob_decode_greedy(ob_model *m, ob_kv *kv, uint32_t token, uint32_t *out_token
     ctx->launches += m->graph_launches[key];
     kv->len += 1;
     *out_token = m->h_out_tokens[0];
-    return OB_OK;
+    return check_peer(m);
 }
 
 int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens, uint32_t n_seq, uint32_t n_steps, uint32_t *out_tokens) {
@@ -1174,7 +1222,7 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
     cudaEventElapsedTime(&ctx->last_ms, ctx->ev0, ctx->ev1);
     ctx->launches += m->graph_launches[key] * n_steps;
     for (uint32_t s = 0; s < n_seq; ++s) kvs[s]->len += n_steps;
-    return OB_OK;
+    return check_peer(m);
 }
 
 int ob_tp_unique_id(void *out128) {

@@ -439,6 +439,7 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         asm volatile("griddepcontrol.wait;" ::: "memory");               // the predecessor's output is complete and visible
     }
     SG_STAMP(2);
+    const uint32_t xk = a.px.size > 1 ? *reinterpret_cast<const volatile uint32_t *>(a.px.seq) : 0u;  // number of this exchange
     if (a.prologue == SG_PRO_READY) {  // the producer left the image in global memory
         const uint32_t n16 = (L.off_terms - L.off_act) / 16;
         for (uint32_t c = threadIdx.x; c < n16; c += NW * 32) {
@@ -540,6 +541,17 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         case SG_EP_SWIGLU:
             y[pair] = silu_mul_exact(tA, tB);
             break;
+        case SG_EP_XCHG: {  // this rank's partial rows, tagged, into every rank's slot [parity][this rank]
+            const uint64_t off = (uint64_t)((xk & 1u) * a.px.size + a.px.rank) * a.px.n + 2 * pair;
+            for (uint32_t r = 0; r < a.px.size; ++r) {
+                uint2 *dst = a.px.slots[r] + off;
+                if (hasB)
+                    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(__float_as_uint(tA)), "r"(xk + 1u), "r"(__float_as_uint(tB)), "r"(xk + 1u) : "memory");
+                else
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(dst), "r"(__float_as_uint(tA)), "r"(xk + 1u) : "memory");
+            }
+            break;
+        }
         default: {  // q, k, v rows of the token: rotate (q, k) and append (k, v) to the page as f16
             const uint32_t row = 2 * pair, hd = a.head_dim, head = row / hd, idx = (row % hd) / 2;
             const uint32_t pos = *a.position;
@@ -598,8 +610,8 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
 // 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.  With `image` set the
 // CTA goes on to quantize (x * scale) * norm_w per 256, so that the product kernels that follow only copy the result.
 constexpr int NS_THREADS = 512;
-__global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__restrict__ x, const float *__restrict__ norm_w, uint32_t dim, float eps,
-                                                                float *__restrict__ out, uint8_t *__restrict__ image, bool wait_dependency) {
+__global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restrict__ x, const float *__restrict__ norm_w, uint32_t dim, float eps,
+                                                                float *__restrict__ out, uint8_t *__restrict__ image, obtp::PeerXchg px, bool wait_dependency) {
     extern __shared__ float srow[];  // the row, one pad word per 16
     __shared__ SeqSumWorkspace<NS_THREADS> ws;
     if (norm_w)  // the weights do not depend on the predecessor: have them in L2 by the time the scale is known
@@ -608,8 +620,43 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(const float *__r
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) srow[i + (i >> 4)] = __ldcg(x + i);
-    __syncthreads();
+    if (px.size > 1) {
+        // complete the pending exchange: every element is read until it carries this exchange's tag (bounded), then
+        // x += (p_0 + p_1 + ..) in rank order
+        const uint32_t k = *reinterpret_cast<const volatile uint32_t *>(px.seq), tag = k + 1u;
+        const uint2 *mine = px.slots[px.rank] + (uint64_t)(k & 1u) * px.size * px.n;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        bool gave_up = false;
+        for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) {
+            float sum = 0.0f;
+            for (uint32_t r = 0; r < px.size; ++r) {
+                const uint2 *src = mine + (uint64_t)r * px.n + i;
+                uint2 w;
+                for (uint32_t spin = 0;; ++spin) {
+                    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(src) : "memory");
+                    if (w.y == tag || gave_up) break;
+                    if ((spin & 1023u) == 1023u) {
+                        unsigned long long t1;
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                        if (t1 - t0 > 4000000000ull) {  // four seconds: a rank is gone; report and go on with what is there
+                            *px.err = 1u;
+                            gave_up = true;
+                        }
+                    }
+                }
+                sum = r == 0 ? __uint_as_float(w.x) : __fadd_rn(sum, __uint_as_float(w.x));
+            }
+            const float v = __fadd_rn(__ldcg(x + i), sum);
+            x[i] = v;
+            srow[i + (i >> 4)] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) *px.seq = k + 1u;
+    } else {
+        for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) srow[i + (i >> 4)] = __ldcg(x + i);
+        __syncthreads();
+    }
     const float t = cta_sequential_sum<NS_THREADS>([&](uint32_t i) { const float v = srow[i + (i >> 4)]; return __fmul_rn(v, v); }, dim, ws);
     const float scale = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
     if (threadIdx.x == 0 && out) *out = scale;
@@ -645,7 +692,8 @@ bool stream_gemv_supported(const StreamArgs &a) {
 
 size_t act_image_bytes(uint32_t dim) { return act_image(dim / 256).bytes; }
 
-void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, bool programmatic, cudaStream_t st) {
+void launch_norm_quant_consume(float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, const obtp::PeerXchg &px,
+                               bool programmatic, cudaStream_t st) {
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(norm_scale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -661,7 +709,11 @@ void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, norm_scale_kernel, x, norm_w, dim, eps, scale_out, image, programmatic);
+    cudaLaunchKernelEx(&cfg, norm_scale_kernel, x, norm_w, dim, eps, scale_out, image, px, programmatic);
+}
+
+void launch_norm_quant(const float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, bool programmatic, cudaStream_t st) {
+    launch_norm_quant_consume(const_cast<float *>(x), norm_w, dim, eps, scale_out, image, obtp::PeerXchg{}, programmatic, st);  // no exchange: x is only read
 }
 
 void launch_norm_scale(const float *x, uint32_t dim, float eps, float *out, bool programmatic, cudaStream_t st) {

@@ -6,6 +6,8 @@
 #include <dlfcn.h>
 #include <string.h>
 
+#include <vector>
+
 namespace obtp {
 
 namespace {
@@ -75,6 +77,8 @@ struct Comm {
     NcclComm comm = nullptr;
     int rank = 0, size = 1;
     std::string err;
+    void *peer_region = nullptr;    // this rank's exchange region
+    void *peer_mapped[8] = {};      // the peers' regions as mapped here
 };
 
 bool unique_id(void *out128, std::string *err) {
@@ -116,6 +120,9 @@ Comm *create(const void *id128, int rank, int size, int device, std::string *err
 
 void destroy(Comm *c) {
     if (!c) return;
+    for (void *p : c->peer_mapped)
+        if (p) cudaIpcCloseMemHandle(p);
+    if (c->peer_region) cudaFree(c->peer_region);
     Api *a = api();
     if (a && c->comm) a->CommDestroy(c->comm);
     delete c;
@@ -148,5 +155,49 @@ bool all_gather_logits(Comm *c, float *logits, uint32_t rows, uint32_t n_vocab, 
 }
 
 const char *last_error(Comm *c) { return c ? c->err.c_str() : ""; }
+
+bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
+    auto bail = [&](const std::string &m) {
+        if (err) *err = m;
+        return false;
+    };
+    Api *a = api();
+    if (!a || !c || c->size < 2 || c->size > 8) return bail("peer exchange needs 2 to 8 ranks");
+    cudaSetDevice(device);
+    constexpr size_t kFlagBytes = 256, kLocalBytes = 256;
+    const size_t slot_bytes = (size_t)2 * c->size * n * sizeof(uint2), total = kFlagBytes + kLocalBytes + slot_bytes;
+    if (cudaMalloc(&c->peer_region, total) != cudaSuccess) return bail("cudaMalloc of the exchange region failed");
+    cudaMemset(c->peer_region, 0, total);
+    cudaIpcMemHandle_t mine;
+    if (cudaIpcGetMemHandle(&mine, c->peer_region) != cudaSuccess) return bail(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError()));
+    // all-gather the 64-byte handles through the communicator
+    unsigned char *stage = nullptr;
+    if (cudaMalloc(reinterpret_cast<void **>(&stage), (size_t)c->size * sizeof(mine)) != cudaSuccess) return bail("cudaMalloc failed");
+    cudaMemcpy(stage + (size_t)c->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    NcclResult r = a->AllGather(stage + (size_t)c->rank * sizeof(mine), stage, sizeof(mine), /* ncclChar */ 0, c->comm, nullptr);
+    cudaError_t e = cudaStreamSynchronize(nullptr);
+    std::vector<cudaIpcMemHandle_t> all((size_t)c->size);
+    if (r == 0 && e == cudaSuccess) e = cudaMemcpy(all.data(), stage, all.size() * sizeof(mine), cudaMemcpyDeviceToHost);
+    cudaFree(stage);
+    if (r != 0 || e != cudaSuccess) return bail("exchange of the IPC handles failed");
+    PeerXchg px{};
+    px.rank = (uint32_t)c->rank;
+    px.size = (uint32_t)c->size;
+    px.n = n;
+    for (int p = 0; p < c->size; ++p) {
+        void *base = c->peer_region;
+        if (p != c->rank) {
+            if (cudaIpcOpenMemHandle(&base, all[(size_t)p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+                return bail(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(cudaGetLastError()));
+            c->peer_mapped[p] = base;
+        }
+        px.slots[p] = reinterpret_cast<uint2 *>(static_cast<unsigned char *>(base) + kFlagBytes + kLocalBytes);
+    }
+    uint32_t *local = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(c->peer_region) + kFlagBytes);
+    px.seq = local;
+    px.err = local + 32;
+    *out = px;
+    return true;
+}
 
 }  // namespace obtp

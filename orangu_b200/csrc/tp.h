@@ -23,4 +23,22 @@ bool all_reduce_sum(Comm *, float *buf, size_t count, cudaStream_t st);
 bool all_gather_logits(Comm *, float *logits, uint32_t rows, uint32_t n_vocab, uint32_t vocab0, uint32_t vocab_l, cudaStream_t st);
 const char *last_error(Comm *);
 
+// One-shot exchange of the ranks' partial vectors through peer memory (NVLink stores between the GPUs of one node), for
+// the single-token decode step where an NCCL all-reduce of 16 KB costs more than the product it follows.
+// Every rank owns 2 x size slots of n (value, tag) pairs.  In exchange number k (counted per rank in *seq, the same on
+// all ranks) a rank's product kernel stores each element of its partial, together with the tag k + 1 in the same 8-byte
+// word, into slot [k & 1][its rank] of EVERY rank; the consumer reads each word until its tag is k + 1 (an 8-byte store
+// arrives whole, so no fence or separate flag is needed), adds the values in rank order -- every rank gets the same
+// bits -- and increments *seq.  Two parities suffice: nobody can start exchange k + 2 before everybody has finished
+// reading exchange k.  A POD: it is passed to kernels by value.
+struct PeerXchg {
+    uint2 *slots[8];     // slots[r]: rank r's slot array [2][size][n] of (value bits, tag)
+    uint32_t *seq;       // this rank: exchanges completed
+    uint32_t *err;       // this rank: set to 1 when a wait ran out of time
+    uint32_t rank, size, n;
+};
+// Allocates this rank's region, exchanges CUDA IPC handles over the communicator and maps the peers' regions.
+// False (with *err) when peer access is not available; the caller then keeps to NCCL.
+bool peer_init(Comm *, uint32_t n, int device, PeerXchg *out, std::string *err);
+
 }  // namespace obtp
