@@ -221,7 +221,43 @@ typedef struct ob_model_desc {
      * tensors and the model keeps its own shard.  tp_size <= 1 means single GPU. */
     uint32_t tp_rank, tp_size;
     const void *tp_unique_id;   /* tp_size > 1: the 128-byte id from ob_tp_unique_id, identical on every rank */
+    const float *rope_freqs;    /* optional rope_freqs.weight: rope_dim / 2 factors that divide the rotation frequencies
+                                 * (E/arch/llama.rs:186-200, E/tensor.rs:1143-1145); NULL: none */
 } ob_model_desc;
+
+/* ------------------------------------------------- GGUF files
+ * GgufFile::open (src/gguf.rs:206-275): header, typed metadata, tensor table; the file is mapped read-only and the
+ * tensor data pointers below point into the mapping (valid until ob_gguf_close).  Works without a GPU.  A failed call
+ * leaves its message in ob_gguf_last_error() (per thread). */
+typedef struct ob_gguf ob_gguf;
+typedef struct ob_gguf_tensor_info { /* TensorInfo, src/gguf.rs:121-130 */
+    const char *name;
+    uint32_t ggml_type;
+    uint32_t n_dims;
+    uint64_t dims[4];   /* GGUF order: dims[0] is the contiguous one (in_dim of a matrix), dims[1] the number of rows */
+    const void *data;   /* data section start + offset */
+    uint64_t n_bytes;   /* 0 for a type this build does not size */
+} ob_gguf_tensor_info;
+int ob_gguf_open(const char *path, ob_gguf **out);
+void ob_gguf_close(ob_gguf *g);
+const char *ob_gguf_last_error(void);
+uint32_t ob_gguf_version(const ob_gguf *g);
+uint64_t ob_gguf_alignment(const ob_gguf *g);   /* general.alignment, 32 when absent (src/gguf.rs:47) */
+uint64_t ob_gguf_data_offset(const ob_gguf *g); /* end of the tensor table rounded up to the alignment (src/gguf.rs:258-266) */
+uint64_t ob_gguf_n_tensors(const ob_gguf *g);
+int ob_gguf_tensor(const ob_gguf *g, uint64_t index, ob_gguf_tensor_info *out);
+int ob_gguf_find_tensor(const ob_gguf *g, const char *name, ob_gguf_tensor_info *out);
+int ob_gguf_get_u64(const ob_gguf *g, const char *key, uint64_t *out);   /* any integer or bool value */
+int ob_gguf_get_f32(const ob_gguf *g, const char *key, float *out);
+int ob_gguf_get_string(const ob_gguf *g, const char *key, const char **out);
+/* read_model_config (E/loader.rs:1652-1712) and the tensor lookup of LlamaModel::load_with_backend
+ * (E/arch/llama.rs:125-200) for general.architecture == "llama": fills every field of *desc from the file -- required
+ * keys embedding_length, block_count, attention.head_count; head_count_kv, key_length, rope.dimension_count,
+ * rope.freq_base, layer_norm_rms_epsilon and vocab_size default as the reference's do; output.weight may be absent
+ * (tied); rope_freqs.weight is optional.  max_seq_len is set to context_length and max_batch_tokens to 512; the caller
+ * adjusts the run-time sizing and the tensor-parallel fields and passes desc to ob_model_create.  desc->layers is
+ * owned by g. */
+int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *desc);
 
 /* Stands in for LlamaModel::load_with_backend (E/arch/llama.rs:125-230) on the device side:
  * uploads (and shards) every tensor, sizes scratch, builds the RoPE table. */

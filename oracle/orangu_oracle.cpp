@@ -741,11 +741,19 @@ void oref_rope_table(float *sin_cos, size_t n_pos, size_t rope_dim, float freq_b
 }
 
 /* E/tensor.rs:1162-1176, RopeLayout::Norm */
+static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors);
+
 void oref_rope_norm(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base) {
+    rope_norm_ff(x, n_head, head_dim, pos, rope_dim, freq_base, nullptr);
+}
+
+/* E/tensor.rs:1140-1176 with optional frequency factors (freq /= ff[i], :1143-1145) */
+static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors) {
     size_t half = rope_dim / 2;
     std::vector<float> rot(half * 2);
     for (size_t i = 0; i < half; ++i) {
         float freq = powf(freq_base, -2.0f * (float)i / (float)rope_dim);
+        if (freq_factors) freq /= freq_factors[i];
         float theta = 1.0f * ((float)pos * freq);
         rot[2 * i] = sinf(theta) * 1.0f;
         rot[2 * i + 1] = cosf(theta) * 1.0f;
@@ -924,8 +932,8 @@ int oref_forward(const oref_model *m, oref_kv *kv, const uint32_t *tokens, size_
         std::vector<float> &ck = kv->k[li], &cv = kv->v[li];
         for (size_t t = 0; t < n_tokens; ++t) { /* E/arch/llama.rs:787-809 */
             size_t pos = start_pos + t;
-            oref_rope_norm(&q[t * q_dim], n_head, head_dim, pos, c.rope_dim, c.rope_freq_base);
-            oref_rope_norm(&k[t * kv_dim], n_head_kv, head_dim, pos, c.rope_dim, c.rope_freq_base);
+            rope_norm_ff(&q[t * q_dim], n_head, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs);
+            rope_norm_ff(&k[t * kv_dim], n_head_kv, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs);
             for (size_t i = 0; i < kv_dim; ++i) {
                 float kk = k[t * kv_dim + i], vv = v[t * kv_dim + i];
                 if (kv->f16) {

@@ -111,6 +111,7 @@ typedef struct {
 typedef struct {
     uint32_t n_vocab, n_embd, n_layer, n_head, n_head_kv, head_dim, rope_dim, n_ff;
     float rope_freq_base, rms_eps;
+    const float *rope_freqs; /* optional rope_freqs.weight, rope_dim / 2 factors dividing the frequencies (E/arch/llama.rs:186-200); NULL: none */
 } oref_config;
 
 typedef struct oref_model oref_model;

@@ -32,7 +32,8 @@ class ModelDesc(C.Structure):
         ("rope_freq_base", C.c_float), ("rms_eps", C.c_float),
         ("max_seq_len", C.c_uint32), ("max_batch_tokens", C.c_uint32), ("kv_pool_tokens", C.c_uint64), ("exact_attention_max_pos", C.c_uint32),
         ("token_embd", MatrixDesc), ("output_norm", C.c_void_p), ("output", MatrixDesc),
-        ("layers", C.POINTER(LayerDesc)), ("tp_rank", C.c_uint32), ("tp_size", C.c_uint32), ("tp_unique_id", C.c_void_p)]
+        ("layers", C.POINTER(LayerDesc)), ("tp_rank", C.c_uint32), ("tp_size", C.c_uint32), ("tp_unique_id", C.c_void_p),
+        ("rope_freqs", C.c_void_p)]
 
 
 class MatmulOpC(C.Structure):
@@ -46,7 +47,24 @@ class Greedy(C.Structure):
 # name -> (restype, argtypes); every symbol the header declares
 _vp, _u32, _u64, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_float
 _PP = C.POINTER(C.c_void_p)
+class GgufTensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_uint32), ("n_dims", C.c_uint32), ("dims", C.c_uint64 * 4), ("data", C.c_void_p), ("n_bytes", C.c_uint64)]
+
+
 SIGNATURES = {
+    "ob_gguf_open": (_i32, [C.c_char_p, _PP]),
+    "ob_gguf_close": (None, [_vp]),
+    "ob_gguf_last_error": (C.c_char_p, []),
+    "ob_gguf_version": (C.c_uint32, [_vp]),
+    "ob_gguf_alignment": (_u64, [_vp]),
+    "ob_gguf_data_offset": (_u64, [_vp]),
+    "ob_gguf_n_tensors": (_u64, [_vp]),
+    "ob_gguf_tensor": (_i32, [_vp, _u64, C.POINTER(GgufTensorInfo)]),
+    "ob_gguf_find_tensor": (_i32, [_vp, C.c_char_p, C.POINTER(GgufTensorInfo)]),
+    "ob_gguf_get_u64": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "ob_gguf_get_f32": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_float)]),
+    "ob_gguf_get_string": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_char_p)]),
+    "ob_gguf_model_desc": (_i32, [_vp, C.POINTER(ModelDesc)]),
     "ob_init": (_i32, [_i32, _PP]),
     "ob_destroy": (None, [_vp]),
     "ob_last_error": (C.c_char_p, [_vp]),

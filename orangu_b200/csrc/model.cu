@@ -593,6 +593,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     m->cfg.layers = nullptr;
     m->cfg.output_norm = nullptr;
     m->cfg.tp_unique_id = nullptr;
+    m->cfg.rope_freqs = nullptr;
     if (m->cfg.rope_dim == 0) m->cfg.rope_dim = c.head_dim;
     if (m->cfg.max_seq_len == 0) m->cfg.max_seq_len = 4096;
     if (m->cfg.max_batch_tokens == 0) m->cfg.max_batch_tokens = 1;
@@ -644,7 +645,10 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     {
         const uint32_t half = m->cfg.rope_dim / 2, n_pos = m->cfg.max_seq_len;
         std::vector<float> freq(half), tab((size_t)n_pos * half * 2);
-        for (uint32_t i = 0; i < half; ++i) freq[i] = powf(c.rope_freq_base, -2.0f * (float)i / (float)m->cfg.rope_dim);
+        for (uint32_t i = 0; i < half; ++i) {
+            freq[i] = powf(c.rope_freq_base, -2.0f * (float)i / (float)m->cfg.rope_dim);
+            if (c.rope_freqs) freq[i] /= c.rope_freqs[i];  // tensor.rs:1143-1145
+        }
         for (uint32_t p = 0; p < n_pos; ++p)
             for (uint32_t i = 0; i < half; ++i) {
                 const float theta = 1.0f * ((float)p * freq[i]);

@@ -91,11 +91,41 @@ class LlamaModel:
         d.tp_rank, d.tp_size = tp_rank, tp_size
         self._id = C.create_string_buffer(tp_unique_id, 128) if tp_unique_id else None
         d.tp_unique_id = C.addressof(self._id) if self._id else None
+        if "rope_freqs.weight" in tensors:  # llama.rs:186-200
+            self._rope_freqs = np.ascontiguousarray(tensors["rope_freqs.weight"]["data"], np.float32)
+            if self._rope_freqs.size < d.rope_dim // 2:
+                raise ValueError("rope_freqs.weight is shorter than rope_dim / 2")
+            d.rope_freqs = self._rope_freqs.ctypes.data
         self._h = C.c_void_p()
         capi.check(backend._h, self._lib.ob_model_create(backend._h, C.byref(d), C.byref(self._h)))
         self.n_vocab = cfg["n_vocab"]
         self.kv_dim_local = cfg["n_head_kv"] // max(1, tp_size) * cfg["head_dim"]
         self.max_batch_tokens = max_batch_tokens
+
+    @classmethod
+    def from_gguf(cls, backend: CudaBackend, path: str, max_seq_len: int = 0, max_batch_tokens: int = 512, kv_pool_tokens: int = 0,
+                  exact_attention_max_pos: int = 0, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: bytes | None = None) -> "LlamaModel":
+        """LlamaModel::load_with_backend (arch/llama.rs:125-230) from a .gguf file: the library maps the file, reads the
+        configuration and the tensor table (ob_gguf_open, ob_gguf_model_desc) and uploads its share of every tensor."""
+        from .gguf import GgufFile
+
+        self = cls.__new__(cls)
+        self.backend, self._lib = backend, backend._lib
+        with GgufFile(path) as g:
+            d = g.model_desc()
+            if max_seq_len:
+                d.max_seq_len = max_seq_len
+            d.max_batch_tokens, d.kv_pool_tokens, d.exact_attention_max_pos = max_batch_tokens, kv_pool_tokens, exact_attention_max_pos
+            d.tp_rank, d.tp_size = tp_rank, tp_size
+            self._id = C.create_string_buffer(tp_unique_id, 128) if tp_unique_id else None
+            d.tp_unique_id = C.addressof(self._id) if self._id else None
+            self.cfg = {k: getattr(d, k) for k in ("n_vocab", "n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "rope_dim", "n_ff", "rope_freq_base", "rms_eps")}
+            self._h = C.c_void_p()
+            capi.check(backend._h, self._lib.ob_model_create(backend._h, C.byref(d), C.byref(self._h)))  # copies what it needs out of the mapping
+        self.n_vocab = self.cfg["n_vocab"]
+        self.kv_dim_local = self.cfg["n_head_kv"] // max(1, tp_size) * self.cfg["head_dim"]
+        self.max_batch_tokens = max_batch_tokens
+        return self
 
     def new_kv_cache(self, capacity: int) -> KvCache:
         return KvCache(self, capacity)

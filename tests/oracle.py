@@ -43,6 +43,7 @@ class Config(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_vocab", "n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "rope_dim", "n_ff")] + [
         ("rope_freq_base", C.c_float),
         ("rms_eps", C.c_float),
+        ("rope_freqs", C.c_void_p),
     ]
 
 
@@ -246,7 +247,8 @@ class Model:
         self._keep = tensors
         self.cfg = cfg
         c = Config(cfg["n_vocab"], cfg["n_embd"], cfg["n_layer"], cfg["n_head"], cfg["n_head_kv"], cfg["head_dim"],
-                   cfg.get("rope_dim", cfg["head_dim"]), cfg["n_ff"], cfg["rope_freq_base"], cfg["rms_eps"])
+                   cfg.get("rope_dim", cfg["head_dim"]), cfg["n_ff"], cfg["rope_freq_base"], cfg["rms_eps"],
+                   tensors["rope_freqs.weight"]["data"].ctypes.data if "rope_freqs.weight" in tensors else None)
 
         def mat(name):
             t = tensors[name]

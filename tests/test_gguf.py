@@ -1,0 +1,149 @@
+"""GGUF files: the library's reader against files written here (layout of src/gguf.rs:206-275), the model description
+it derives (engine/loader.rs:1652-1712, engine/arch/llama.rs:125-200), and -- on a GPU -- a model loaded from a file
+against the same model built from the tensors and against the oracle."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from orangu_b200 import capi, synth
+from orangu_b200.gguf import GgufFile, write_gguf
+
+
+def tiny(seed=5, with_output=True, rope_freqs=False):
+    cfg = dict(synth.CONFIGS["tiny"])
+    tensors = synth.model_tensors(cfg, seed=seed)
+    if not with_output:
+        del tensors["output.weight"]
+    if rope_freqs:
+        tensors["rope_freqs.weight"] = {"data": np.linspace(1.0, 8.0, cfg["head_dim"] // 2).astype(np.float32), "type": 0}
+    return cfg, tensors
+
+
+@pytest.mark.parametrize("alignment", [32, 64, 4096])
+def test_reader_sees_what_the_writer_wrote(tmp_path, alignment):
+    cfg, tensors = tiny(rope_freqs=True)
+    path = str(tmp_path / "tiny.gguf")
+    write_gguf(path, cfg, tensors, alignment=alignment, extra_metadata=[("tokenizer.ggml.tokens", "arr", ("str", ["a", "bc", "def"])), ("general.name", "str", "tiny")])
+    with GgufFile(path) as g:
+        assert g.version == 3 and g.alignment == alignment and g.data_offset % alignment == 0
+        assert g.get_string("general.architecture") == "llama" and g.get_string("general.name") == "tiny"
+        assert g.get_u64("llama.block_count") == cfg["n_layer"] and abs(g.get_f32("llama.rope.freq_base") - cfg["rope_freq_base"]) < 1e-3
+        infos = {t["name"]: t for t in g.tensors()}
+        assert set(infos) == set(tensors)
+        for name, t in tensors.items():
+            raw = np.ascontiguousarray(t["data"]).view(np.uint8).reshape(-1)
+            assert infos[name]["type"] == t["type"] and infos[name]["n_bytes"] == raw.size
+            assert infos[name]["address"] % alignment == (g.data_offset % alignment)  # mapping is page aligned; offsets keep the alignment
+            assert (g.tensor_bytes(name) == raw).all(), name
+            if "in_dim" in t:
+                assert infos[name]["dims"] == [t["in_dim"], t["out_dim"]]  # dims[0] is the contiguous one
+        d = g.model_desc()
+        for k in ("n_vocab", "n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "n_ff"):
+            assert getattr(d, k) == cfg[k], k
+        assert d.rope_dim == cfg["head_dim"] and abs(d.rms_eps - cfg["rms_eps"]) < 1e-12 and d.rope_freqs
+        assert d.layers[1].w_down.in_dim == cfg["n_ff"] and d.layers[1].w_down.out_dim == cfg["n_embd"] and d.layers[0].wv.ggml_type == 14
+
+
+def test_defaults_and_tied_output(tmp_path):
+    """head_count_kv, key_length, rope.dimension_count, freq_base, eps and vocab_size default as the reference's loader does."""
+    cfg, tensors = tiny(with_output=False)
+    cfg["n_head_kv"] = cfg["n_head"]  # so that the default (== n_head) matches the k/v tensors
+    tensors = synth.model_tensors(cfg, seed=5)
+    del tensors["output.weight"]
+    path = str(tmp_path / "min.gguf")
+    write_gguf(path, cfg, tensors)
+    # rewrite with only the required keys
+    from orangu_b200 import gguf as G
+
+    meta = [("general.architecture", "str", "llama"), ("llama.embedding_length", "u32", cfg["n_embd"]), ("llama.block_count", "u64", cfg["n_layer"]),
+            ("llama.attention.head_count", "i32", cfg["n_head"]), ("tokenizer.ggml.tokens", "arr", ("str", ["t%d" % i for i in range(cfg["n_vocab"])]))]
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(meta))
+    for k, kind, v in meta:
+        head += G._string(k) + G._value(kind, v)
+    infos, blobs, off = b"", [], 0
+    for name, t in tensors.items():
+        raw = np.ascontiguousarray(t["data"]).view(np.uint8).reshape(-1)
+        dims = [t["in_dim"], t["out_dim"]] if "in_dim" in t else [int(np.asarray(t["data"]).size)]
+        infos += G._string(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", x) for x in dims) + struct.pack("<IQ", t["type"], off)
+        blobs.append((off, raw))
+        off = (off + raw.size + 31) // 32 * 32
+    start = (len(head) + len(infos) + 31) // 32 * 32
+    with open(path, "wb") as f:
+        f.write(head + infos + b"\0" * (start - len(head) - len(infos)))
+        pos = 0
+        for o, raw in blobs:
+            f.write(b"\0" * (o - pos) + raw.tobytes())
+            pos = o + raw.size
+    with GgufFile(path) as g:
+        assert g.alignment == 32
+        d = g.model_desc()
+        assert d.n_head_kv == cfg["n_head"] and d.head_dim == cfg["n_embd"] // cfg["n_head"] and d.rope_dim == d.head_dim
+        assert d.n_vocab == cfg["n_vocab"] and abs(d.rope_freq_base - 10000.0) < 1e-3 and abs(d.rms_eps - 1e-5) < 1e-12
+        assert d.n_ff == cfg["n_ff"] and not d.output.data and not d.rope_freqs  # tied output, no frequency factors
+
+
+def test_malformed_files_are_refused_with_a_message(tmp_path):
+    cfg, tensors = tiny()
+    good = str(tmp_path / "good.gguf")
+    write_gguf(good, cfg, tensors)
+    blob = open(good, "rb").read()
+
+    def refused(data, needle):
+        p = str(tmp_path / "bad.gguf")
+        open(p, "wb").write(data)
+        with pytest.raises(capi.OranguError) as e:
+            GgufFile(p)
+        assert needle in str(e.value), str(e.value)
+
+    refused(b"GGML" + blob[4:], "bad magic")
+    refused(blob[:4] + struct.pack("<I", 1) + blob[8:], "version 1")
+    refused(blob[:16], "shorter than")
+    refused(blob[:len(blob) // 2], "past the end")                                     # tensor data cut off
+    refused(blob[:24] + struct.pack("<Q", 1 << 40) + blob[32:], "malformed metadata")  # a key length of a terabyte
+    refused(blob[:8] + struct.pack("<Q", 1 << 40) + blob[16:], "implausible")
+    with pytest.raises(capi.OranguError):
+        GgufFile(str(tmp_path / "missing.gguf"))
+    # a model whose architecture or tensor types are outside the build is named, not crashed on
+    p = str(tmp_path / "arch.gguf")
+    write_gguf(p, cfg, tensors)
+    data = open(p, "rb").read().replace(b"\x05\x00\x00\x00\x00\x00\x00\x00llama", b"\x05\x00\x00\x00\x00\x00\x00\x00qwen2", 1)
+    open(p, "wb").write(data)
+    with GgufFile(p) as g, pytest.raises(capi.OranguError) as e:
+        g.model_desc()
+    assert "qwen2" in str(e.value)
+    bad = dict(tensors)
+    bad["blk.0.attn_q.weight"] = dict(tensors["blk.0.attn_q.weight"], type=13)  # Q5_K: sized, but no kernel
+    bad["blk.0.attn_q.weight"]["data"] = np.zeros(cfg["n_head"] * cfg["head_dim"] * cfg["n_embd"] // 256 * 176, np.uint8)
+    write_gguf(p, cfg, bad)
+    with GgufFile(p) as g, pytest.raises(capi.OranguError) as e:
+        g.model_desc()
+    assert "blk.0.attn_q.weight" in str(e.value) and "13" in str(e.value)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("with_output,rope_freqs", [(True, False), (False, True)])
+def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(tmp_path, with_output, rope_freqs):
+    import oracle as O
+    import orangu_b200
+    from gpu_common import assert_bit_equal
+
+    be = orangu_b200.CudaBackend.init(0)
+    cfg, tensors = tiny(seed=9, with_output=with_output, rope_freqs=rope_freqs)
+    path = str(tmp_path / "m.gguf")
+    write_gguf(path, cfg, tensors, alignment=64)
+    from_file = orangu_b200.LlamaModel.from_gguf(be, path, max_seq_len=64, max_batch_tokens=16)
+    from_mem = orangu_b200.LlamaModel(be, cfg, tensors, max_seq_len=64, max_batch_tokens=16)
+    ref = O.Model(cfg, tensors)
+    toks = np.random.default_rng(1).integers(0, cfg["n_vocab"], 11).astype(np.uint32)
+    ka, kb, kr = from_file.new_kv_cache(32), from_mem.new_kv_cache(32), ref.new_kv(32, f16=True)
+    a, b, want = from_file.forward(ka, toks, 0), from_mem.forward(kb, toks, 0), ref.forward(kr, toks, 0)
+    assert_bit_equal(a, want, "prefill logits, model from the file")
+    assert_bit_equal(b, want, "prefill logits, model from tensors")
+    tok = O.argmax(want)
+    for step in range(4):
+        a, want = from_file.forward(ka, [tok], 11 + step), ref.forward(kr, [tok], 11 + step)
+        assert_bit_equal(a, want, f"decode step {step}")
+        tok = O.argmax(want)
+    be.close()
