@@ -7,6 +7,7 @@ import struct
 import numpy as np
 import pytest
 
+from gpu_common import backend  # noqa: F401
 from orangu_b200 import capi, synth
 from orangu_b200.gguf import GgufFile, write_gguf
 
@@ -124,12 +125,12 @@ def test_malformed_files_are_refused_with_a_message(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("with_output,rope_freqs", [(True, False), (False, True)])
-def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(tmp_path, with_output, rope_freqs):
+def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(backend, tmp_path, with_output, rope_freqs):
     import oracle as O
     import orangu_b200
     from gpu_common import assert_bit_equal
 
-    be = orangu_b200.CudaBackend.init(0)
+    be = backend
     cfg, tensors = tiny(seed=9, with_output=with_output, rope_freqs=rope_freqs)
     path = str(tmp_path / "m.gguf")
     write_gguf(path, cfg, tensors, alignment=64)
@@ -146,4 +147,3 @@ def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(tmp_path
         a, want = from_file.forward(ka, [tok], 11 + step), ref.forward(kr, [tok], 11 + step)
         assert_bit_equal(a, want, f"decode step {step}")
         tok = O.argmax(want)
-    be.close()
