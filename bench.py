@@ -363,7 +363,7 @@ def main():
     # ---- CPU baseline (rank 0, single GPU runs only) --------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, cores, sample = cpu_decode_tokens_per_s(cfg, tensors, budget_s=15.0, max_tokens=24)
+        v, cores, sample = cpu_decode_tokens_per_s(cfg, tensors, budget_s=15.0, max_tokens=400)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
 
     if rank == 0:
