@@ -6,19 +6,19 @@
 // and can issue at most four warp instructions in that clock, so the whole loop (copy, dot, sums, bookkeeping)
 // has to stay near one instruction per 15-20 bytes.  Hence:
 //
-//   * one lane owns one whole super-block, for two rows at once: the six-bit scales of the block are unpacked
-//     once (10 instructions for all eight scales and mins), the activations are read once per pair of rows,
-//     and no cross-lane reduction is needed for the integer sums;
+//   * two lanes share one super-block, for two rows at once (each takes 128 of its 256 elements and adds its integer
+//     sums to the other's with one shuffle): the six-bit scales a lane needs are unpacked into one word, the
+//     activations are read once per pair of rows, and the fp32 term is formed once per row;
 //   * every warp owns two shared-memory slots and fills them with cp.async (16-byte, L1-bypassing) copies of
-//     its next "units" (32 lanes' worth of blocks, two rows each), so the bytes in flight do not occupy
-//     registers; the first units are requested before anything else happens in the kernel.  A lane copies
-//     from one row only, at a fixed stride, so a unit costs it one pointer computation and 18 copies;
+//     its next "units" (16 blocks x two rows = 4.6 KB), so the bytes in flight do not occupy registers and sixteen
+//     warps fit an SM; the first units are requested before anything else happens in the kernel.  A lane copies
+//     from one row only, at a fixed stride, so a unit costs it one pointer computation and 9 copies;
 //   * the lanes-per-row-pair count is a template parameter and the work is split statically over all warps of
 //     the grid, so the loop has no divisions, no atomics and no per-unit descriptors;
 //   * the operator that produces the activations is the kernel's prologue (RMSNorm scaling and the int8
 //     quantisation, written straight into shared memory in a conflict-free layout), and the operator that
 //     consumes the product is its epilogue (residual add, silu(gate) * up, or RoPE and the fp16 KV append);
-//   * two small CTAs fit one SM, and the kernel is launched with programmatic stream serialisation: it may
+//   * two CTAs of eight warps fit one SM, and the kernel is launched with programmatic stream serialisation: it may
 //     start, and request weights, while its predecessor is still running, and waits on the grid dependency
 //     only before it reads the predecessor's output.
 //
@@ -40,20 +40,21 @@ namespace {
 constexpr uint32_t SG_MAX_SMEM = 112 * 1024;
 constexpr uint32_t ACT_BLOCK_STRIDE = 272;  // bytes per 256 int8 activations: 17 sixteen-byte chunks, so lanes one block apart hit different banks
 
-// bytes of `lp` blocks of one row inside a slot
-__host__ __device__ inline uint32_t part_bytes(uint32_t type, uint32_t lp) { return type == TYPE_Q4_K ? lp * 144u : lp * 208u + ((lp * 2u + 15u) & ~15u); }
+// bytes of `bpc` blocks of one row inside a slot
+__host__ __device__ inline uint32_t part_bytes(uint32_t type, uint32_t bpc) { return type == TYPE_Q4_K ? bpc * 144u : bpc * 208u + ((bpc * 2u + 15u) & ~15u); }
 
-// lanes per pair of rows (= blocks of a unit): the smallest power of two that covers the row, at least 2 because each pair
-// also needs two lanes for the ordered sums of its two rows; rows longer than 32 blocks are cut into chunks of 16, which
-// spreads a matrix with few rows (the FFN down projection) over more warps than chunks of 32 would
+// Two lanes share one super-block of a row pair (each takes half of its 256 elements), so a unit -- 32 lanes -- is 16
+// (block, pair) cells = 4.6 KB, half of what one lane per cell would make it: the two-slot ring of a warp is 9 KB and
+// sixteen warps fit an SM.  Lanes per pair of rows = 2 x blocks per chunk; a chunk is the smallest power of two that
+// covers the row, at most 16 blocks (longer rows are cut into chunks, which also spreads a matrix with few rows over
+// more warps).
 __host__ __device__ inline uint32_t lanes_per_pair(uint32_t nb) {
-    if (nb > 32) return 16;
-    uint32_t lp = 2;
-    while (lp < nb) lp <<= 1;
-    return lp;
+    uint32_t bpc = 1;
+    while (bpc < nb && bpc < 16) bpc <<= 1;
+    return 2 * bpc;
 }
 
-__host__ __device__ inline int sg_warps(bool has_q6) { return has_q6 ? 3 : 4; }
+__host__ __device__ inline int sg_warps(bool has_q6) { return has_q6 ? 6 : 8; }
 
 // The "image" is what the dot loop reads from shared memory: [nb][272] int8 (256 used), [nb] f32 scales, [nb][8] int16
 // sums per 32, [nb][16] int16 sums per 16.  A kernel either builds it in its own shared memory from the fp32 row, or a
@@ -86,9 +87,9 @@ __host__ __device__ inline SgSmem sg_smem(uint32_t in_dim, bool has_q6, uint32_t
     s.off_d = s.off_act + im.off_d;
     s.off_bsum = s.off_act + im.off_bsum;    // int16 [nb][8]  sums per 32
     s.off_sum16 = s.off_act + im.off_sum16;  // int16 [nb][16] sums per 16
-    s.off_terms = s.off_act + im.bytes;      // float [warp][pair slot][row][lp]  = [warp][64]
-    s.off_ring = s.off_terms + nw * 64 * 4;
-    s.slot_bytes = (32 / lp) * 2 * part_bytes(has_q6 ? TYPE_Q6_K : TYPE_Q4_K, lp);
+    s.off_terms = s.off_act + im.bytes;      // float [warp][pair slot][row][blocks per chunk]  = [warp][32]
+    s.off_ring = s.off_terms + nw * 32 * 4;
+    s.slot_bytes = (32 / lp) * 2 * part_bytes(has_q6 ? TYPE_Q6_K : TYPE_Q4_K, lp / 2);
     s.total = s.off_ring + nw * 2 * s.slot_bytes;
     return s;
 }
@@ -187,9 +188,10 @@ __device__ void quantize_image(const float *x, const float *norm_w, float norm_s
 }
 
 // ---- units ---------------------------------------------------------------------------------------------------
-// A unit is what one warp processes at a time: PPU = 32 / LP consecutive pairs of rows of one segment x up to LP
-// blocks [b0, b0 + nblk).  In the dot, lane l works on pair l / LP, block b0 + l % LP.  In the copy, the 2 * PPU
-// row parts of the unit get LP / 2 lanes each: lane l copies chunks l % (LP/2), + LP/2, ... of part l / (LP/2).
+// A unit is what one warp processes at a time: PPU = 32 / LP consecutive pairs of rows of one segment x up to LP / 2
+// blocks [b0, b0 + nblk).  In the dot, lane l works on pair l / LP, block b0 + (l % LP) / 2, half l % 2 of the block.  In
+// the copy, the 2 * PPU row parts of the unit get LP / 2 lanes each: lane l copies chunks l % (LP/2), + LP/2, ... of part
+// l / (LP/2).
 // A "group" is the PPU pairs of a unit over all blocks of their rows; a warp processes whole groups, chunk by chunk,
 // so that the running totals of the rows stay in its registers.
 
@@ -205,26 +207,27 @@ __device__ __forceinline__ int dp2a_hi(uint32_t a, uint32_t b, int c) {  // c + 
     return d;
 }
 
-__device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, uint32_t xa, uint32_t bs, float ad, float term[2]) {
+// Lane `half` (0 or 1) of the two that share a cell: elements 128 half .. 128 half + 127 of the super-block, i.e. sub-blocks
+// 4 half .. 4 half + 3, for rows A and B.  Returns this lane's part of the integer sums; the caller adds the two lanes'.
+__device__ __forceinline__ void dot_half_q4k(uint32_t blk0, uint32_t blk1, uint32_t half, uint32_t xa, uint32_t bs, int isum[2], int imin[2], uint32_t dd[2]) {
     const uint32_t blk[2] = {blk0, blk1};
-    uint32_t scl[2], sch[2], ml[2], mh[2], dd[2];
-    int isum[2] = {0, 0};
+    uint32_t sc[2], mn[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const uint4 hd = lds128(blk[r]);
         dd[r] = hd.x;
-        // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of four words
-        scl[r] = hd.y & 0x3f3f3f3fu;
-        ml[r] = hd.z & 0x3f3f3f3fu;
-        sch[r] = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u);
-        mh[r] = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+        // the 6-bit scales and mins (engine/quant.rs:653-662) of this lane's four sub-blocks as bytes of one word each
+        sc[r] = half ? ((hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u)) : (hd.y & 0x3f3f3f3fu);
+        mn[r] = half ? (((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u)) : (hd.z & 0x3f3f3f3fu);
+        isum[r] = 0;
     }
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // 64 elements: sub-blocks 2g (low nibbles) and 2g+1 (high nibbles)
-        const uint4 x0 = lds128(xa + 64 * g), x1 = lds128(xa + 64 * g + 16), x2 = lds128(xa + 64 * g + 32), x3 = lds128(xa + 64 * g + 48);
+    for (int gg = 0; gg < 2; ++gg) {  // 64 elements: sub-blocks 4 half + 2 gg (low nibbles) and + 1 (high nibbles)
+        const uint32_t xo = xa + 128 * half + 64 * gg, qo = 16 + 64 * half + 32 * gg;
+        const uint4 x0 = lds128(xo), x1 = lds128(xo + 16), x2 = lds128(xo + 32), x3 = lds128(xo + 48);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-            const uint4 qa = lds128(blk[r] + 16 + 32 * g), qb = lds128(blk[r] + 32 + 32 * g);
+            const uint4 qa = lds128(blk[r] + qo), qb = lds128(blk[r] + qo + 16);
             const uint32_t Lm = 0x0f0f0f0fu, Hm = 0xf0f0f0f0u;
             int lo0 = dp4a_us(qa.x & Lm, x0.x, 0), lo1 = dp4a_us(qa.y & Lm, x0.y, 0);
             lo0 = dp4a_us(qa.z & Lm, x0.z, lo0);
@@ -241,74 +244,62 @@ __device__ __forceinline__ void dot_block_q4k(uint32_t blk0, uint32_t blk1, uint
             hi0 = dp4a_us(qb.z & Hm, x3.z, hi0);
             hi1 = dp4a_us(qb.w & Hm, x3.w, hi1);
             const int lo = lo0 + lo1, hi = (hi0 + hi1) >> 4;  // the high nibbles stayed in place: every product carried a factor 16
-            const uint32_t scw = g < 2 ? scl[r] : sch[r];
-            const int sca = (int)((scw >> (16 * (g & 1))) & 0xff), scb = (int)((scw >> (16 * (g & 1) + 8)) & 0xff);
+            const int sca = (int)((sc[r] >> (16 * gg)) & 0xff), scb = (int)((sc[r] >> (16 * gg + 8)) & 0xff);
             isum[r] += sca * lo + scb * hi;
         }
     }
-    const uint4 bsv = lds128(bs);  // eight int16 sums as four pairs
+    const uint2 bsv = lds64(bs + 8 * half);  // this lane's four per-32 sums as two pairs
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        int imin = dp2a_lo(bsv.x, ml[r], 0);
-        imin = dp2a_hi(bsv.y, ml[r], imin);
-        imin = dp2a_lo(bsv.z, mh[r], imin);
-        imin = dp2a_hi(bsv.w, mh[r], imin);
-        const float d = f16_bits_to_f32(dd[r] & 0xffffu), dmin = f16_bits_to_f32(dd[r] >> 16);
-        term[r] = __fmul_rn(ad, __fsub_rn(__fmul_rn(d, (float)isum[r]), __fmul_rn(dmin, (float)imin)));
-    }
+    for (int r = 0; r < 2; ++r) imin[r] = dp2a_hi(bsv.y, mn[r], dp2a_lo(bsv.x, mn[r], 0));
 }
 
-// blk0/blk1: the 208-byte blocks [ql 128 | qh 64 | scales 16]; dsup[r]: their f16 d; s16p: the block's sixteen per-16 sums.
-__device__ __forceinline__ void dot_block_q6k(uint32_t blk0, uint32_t blk1, const float dsup[2], uint32_t xa, uint32_t s16p, float ad, float term[2]) {
+// blk0/blk1: the 208-byte blocks [ql 128 | qh 64 | scales 16]; lane `h` takes elements 128 h .. 128 h + 127 (eight groups of 16).
+__device__ __forceinline__ void dot_half_q6k(uint32_t blk0, uint32_t blk1, uint32_t h, uint32_t xa, uint32_t s16p, int isum[2]) {
     const uint32_t blk[2] = {blk0, blk1};
-    int isum[2] = {0, 0};
+    uint32_t xw[32];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {  // 128 elements: runs 0..3 of 32
-        uint32_t xw[32];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint4 v = lds128(xa + 128 * h + 16 * k);
-            xw[4 * k] = v.x;
-            xw[4 * k + 1] = v.y;
-            xw[4 * k + 2] = v.z;
-            xw[4 * k + 3] = v.w;
-        }
-        const uint4 sv = lds128(s16p + 16 * h);  // eight int16 sums, groups 8h .. 8h+7
-        const int s16[8] = {(int16_t)(sv.x & 0xffff), (int16_t)(sv.x >> 16), (int16_t)(sv.y & 0xffff), (int16_t)(sv.y >> 16),
-                            (int16_t)(sv.z & 0xffff), (int16_t)(sv.z >> 16), (int16_t)(sv.w & 0xffff), (int16_t)(sv.w >> 16)};
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const uint2 scw = lds64(blk[r] + 192 + 8 * h);  // signed scales of groups 8h .. 8h+7
-            int dots[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // group 2 * run + k
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {  // k: 16-byte chunk of l (elements l = 16k .. 16k+15 of each run)
-                const uint4 qla = lds128(blk[r] + 64 * h + 16 * k);       // runs 0 (low nibble) and 2 (high)
-                const uint4 qlb = lds128(blk[r] + 64 * h + 32 + 16 * k);  // runs 1 and 3
-                const uint4 qhv = lds128(blk[r] + 128 + 32 * h + 16 * k);
-                const uint32_t A[4] = {qla.x, qla.y, qla.z, qla.w}, B[4] = {qlb.x, qlb.y, qlb.z, qlb.w}, Hh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint32_t v0 = (A[w] & 0x0f0f0f0fu) | ((Hh[w] << 4) & 0x30303030u);
-                    const uint32_t v1 = (B[w] & 0x0f0f0f0fu) | ((Hh[w] << 2) & 0x30303030u);
-                    const uint32_t v2 = ((A[w] >> 4) & 0x0f0f0f0fu) | (Hh[w] & 0x30303030u);
-                    const uint32_t v3 = ((B[w] >> 4) & 0x0f0f0f0fu) | ((Hh[w] >> 2) & 0x30303030u);
-                    const int wi = 4 * k + w;  // word index inside a 32-element run
-                    dots[0 + k] = dp4a_us(v0, xw[wi], dots[0 + k]);
-                    dots[2 + k] = dp4a_us(v1, xw[8 + wi], dots[2 + k]);
-                    dots[4 + k] = dp4a_us(v2, xw[16 + wi], dots[4 + k]);
-                    dots[6 + k] = dp4a_us(v3, xw[24 + wi], dots[6 + k]);
-                }
-            }
-            const uint32_t scb[2] = {scw.x, scw.y};
-#pragma unroll
-            for (int gi = 0; gi < 8; ++gi) {
-                const int sc = (int)(int8_t)((scb[gi >> 2] >> (8 * (gi & 3))) & 0xff);
-                isum[r] += sc * (dots[gi] - 32 * s16[gi]);
-            }
-        }
+    for (int k = 0; k < 8; ++k) {
+        const uint4 v = lds128(xa + 128 * h + 16 * k);
+        xw[4 * k] = v.x;
+        xw[4 * k + 1] = v.y;
+        xw[4 * k + 2] = v.z;
+        xw[4 * k + 3] = v.w;
     }
+    const uint4 sv = lds128(s16p + 16 * h);  // eight int16 sums, groups 8h .. 8h+7
+    const int s16[8] = {(int16_t)(sv.x & 0xffff), (int16_t)(sv.x >> 16), (int16_t)(sv.y & 0xffff), (int16_t)(sv.y >> 16),
+                        (int16_t)(sv.z & 0xffff), (int16_t)(sv.z >> 16), (int16_t)(sv.w & 0xffff), (int16_t)(sv.w >> 16)};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) term[r] = __fmul_rn(__fmul_rn(ad, dsup[r]), (float)isum[r]);
+    for (int r = 0; r < 2; ++r) {
+        const uint2 scw = lds64(blk[r] + 192 + 8 * h);  // signed scales of groups 8h .. 8h+7
+        int dots[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // group 2 * run + k
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {  // k: 16-byte chunk of l (elements l = 16k .. 16k+15 of each run)
+            const uint4 qla = lds128(blk[r] + 64 * h + 16 * k);       // runs 0 (low nibble) and 2 (high)
+            const uint4 qlb = lds128(blk[r] + 64 * h + 32 + 16 * k);  // runs 1 and 3
+            const uint4 qhv = lds128(blk[r] + 128 + 32 * h + 16 * k);
+            const uint32_t A[4] = {qla.x, qla.y, qla.z, qla.w}, B[4] = {qlb.x, qlb.y, qlb.z, qlb.w}, Hh[4] = {qhv.x, qhv.y, qhv.z, qhv.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t v0 = (A[w] & 0x0f0f0f0fu) | ((Hh[w] << 4) & 0x30303030u);
+                const uint32_t v1 = (B[w] & 0x0f0f0f0fu) | ((Hh[w] << 2) & 0x30303030u);
+                const uint32_t v2 = ((A[w] >> 4) & 0x0f0f0f0fu) | (Hh[w] & 0x30303030u);
+                const uint32_t v3 = ((B[w] >> 4) & 0x0f0f0f0fu) | ((Hh[w] >> 2) & 0x30303030u);
+                const int wi = 4 * k + w;  // word index inside a 32-element run
+                dots[0 + k] = dp4a_us(v0, xw[wi], dots[0 + k]);
+                dots[2 + k] = dp4a_us(v1, xw[8 + wi], dots[2 + k]);
+                dots[4 + k] = dp4a_us(v2, xw[16 + wi], dots[4 + k]);
+                dots[6 + k] = dp4a_us(v3, xw[24 + wi], dots[6 + k]);
+            }
+        }
+        const uint32_t scb[2] = {scw.x, scw.y};
+        int acc = 0;
+#pragma unroll
+        for (int gi = 0; gi < 8; ++gi) {
+            const int sc = (int)(int8_t)((scb[gi >> 2] >> (8 * (gi & 3))) & 0xff);
+            acc += sc * (dots[gi] - 32 * s16[gi]);
+        }
+        isum[r] = acc;
+    }
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
@@ -329,18 +320,18 @@ extern "C" __attribute__((visibility("default"))) int ob_debug_sg_prof(unsigned 
 #define SG_STAMP(i)
 #endif
 template <int LP, bool Q6>  // LP: lanes (= blocks per unit) of a row pair; Q6: the launch has Q6_K segments (three warps, larger slots)
-__global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArgs a) {
+__global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
-    constexpr int NW = Q6 ? 3 : 4, PPU = 32 / LP, HL = LP / 2;
-    constexpr uint32_t PB4 = LP * 144u, PB6 = LP * 208u + ((LP * 2u + 15u) & ~15u);
+    constexpr int NW = Q6 ? 6 : 8, PPU = 32 / LP, BPC = LP / 2, HL = BPC;  // BPC: blocks per chunk; HL: lanes copying one row part
+    constexpr uint32_t PB4 = BPC * 144u, PB6 = BPC * 208u + ((BPC * 2u + 15u) & ~15u);
     constexpr uint32_t SLOT = 2u * PPU * (Q6 ? PB6 : PB4);
     const SgSmem L = sg_smem(a.in_dim, Q6, LP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     SG_STAMP(0);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t terms = sbase + L.off_terms + warp * 256;
+    const uint32_t terms = sbase + L.off_terms + warp * 128;
     const uint32_t slots = sbase + L.off_ring + warp * 2 * SLOT;
-    const uint32_t nb = a.in_dim / 256, nchunk = (nb + LP - 1) / LP;
+    const uint32_t nb = a.in_dim / 256, nchunk = (nb + BPC - 1) / BPC;
 
     // groups of PPU pairs, segments concatenated (a group never straddles two segments)
     uint32_t pairs_of[3], first_of[4];
@@ -379,7 +370,7 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
     uint32_t cg = ig, cc = 0;                                        // next unit to compute
 
     const uint32_t q = lane / HL, sub = lane % HL, cj = q >> 1, cr = q & 1;  // copy role: part q = (pair cj, row cr), chunks sub + HL * k
-    const uint32_t pj = lane / LP, bl = lane % LP;                          // dot role
+    const uint32_t pj = lane / LP, bl = (lane % LP) >> 1, half = lane & 1;   // dot role: pair, block of the chunk, half of the block
 
     auto issue = [&](uint32_t slot, uint32_t g, uint32_t ch) {
         const uint32_t e = sbase + ((g >= gb1) + (g >= gb2)) * (SEG_WORDS * 4);
@@ -390,31 +381,31 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
         const uint32_t row_index = dual ? pair : min(2 * pair + cr, m.z - 1);
         const uint2 wp = dual && cr ? wb : wa;
         const uint8_t *row = reinterpret_cast<const uint8_t *>(((uint64_t)wp.y << 32) | wp.x) + (uint64_t)row_index * m.x;
-        const uint32_t b0 = ch * LP, nblk = min((uint32_t)LP, nb - b0);
+        const uint32_t b0 = ch * BPC, nblk = min((uint32_t)BPC, nb - b0);
         if (!Q6 || m.y == TYPE_Q4_K) {
             const uint8_t *src = row + b0 * 144 + sub * 16;
             const uint32_t dst = slot + q * PB4 + sub * 16;
-            if (nblk == LP) {
+            if (nblk == BPC) {
 #pragma unroll
-                for (int k = 0; k < 18; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
+                for (int k = 0; k < 9; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
             } else {
 #pragma unroll
-                for (int k = 0; k < 18; ++k)
+                for (int k = 0; k < 9; ++k)
                     if (sub + HL * k < nblk * 9) cp_async16(dst + k * HL * 16, src + k * HL * 16);
             }
         } else {
             const uint8_t *src = row + b0 * 208 + sub * 16;
             const uint32_t dst = slot + q * PB6 + sub * 16;
-            if (nblk == LP) {
+            if (nblk == BPC) {
 #pragma unroll
-                for (int k = 0; k < 26; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
+                for (int k = 0; k < 13; ++k) cp_async16(dst + k * HL * 16, src + k * HL * 16);
             } else {
 #pragma unroll
-                for (int k = 0; k < 26; ++k)
+                for (int k = 0; k < 13; ++k)
                     if (sub + HL * k < nblk * 13) cp_async16(dst + k * HL * 16, src + k * HL * 16);
             }
             // the f16 d values of these blocks; b0 is 0 or a multiple of 8, so the source is 16-byte aligned
-            if (sub < (nblk * 2 + 15) / 16) cp_async16(slot + q * PB6 + LP * 208 + sub * 16, row + lds32(e + 32) + 2 * b0 + sub * 16);
+            if (sub < (nblk * 2 + 15) / 16) cp_async16(slot + q * PB6 + BPC * 208 + sub * 16, row + lds32(e + 32) + 2 * b0 + sub * 16);
         }
     };
     auto advance = [&](uint32_t &g, uint32_t &c) {
@@ -459,40 +450,53 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
     while (cg < g_end) {
         const uint32_t slot = slots + par * SLOT;
         const uint32_t e = sbase + ((cg >= gb1) + (cg >= gb2)) * (SEG_WORDS * 4);
-        const uint32_t b0 = cc * LP, nblk = min((uint32_t)LP, nb - b0);
+        const uint32_t b0 = cc * BPC, nblk = min((uint32_t)BPC, nb - b0);
         __pipeline_wait_prior(1);
         __syncwarp();
         {
             const uint32_t gb = min(b0 + bl, nb - 1);  // lanes past the row's end recompute its last block; nobody reads their terms
             const uint32_t xa = sbase + L.off_act + gb * ACT_BLOCK_STRIDE;
             const float ad = __uint_as_float(lds32(sbase + L.off_d + gb * 4));
-            float term[2];
+            int isum[2], imin[2] = {0, 0};
+            float term;  // lane `half` ends up with the term of row `half` of the pair
             if (!Q6 || lds32(e + 20) == TYPE_Q4_K) {
                 const uint32_t pA = slot + (2 * pj) * PB4 + bl * 144;
-                dot_block_q4k(pA, pA + PB4, xa, sbase + L.off_bsum + gb * 16, ad, term);
+                uint32_t dd[2];
+                dot_half_q4k(pA, pA + PB4, half, xa, sbase + L.off_bsum + gb * 16, isum, imin, dd);
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {  // the two lanes of the cell add their halves: exact integers, any order
+                    isum[r] += __shfl_xor_sync(0xffffffffu, isum[r], 1);
+                    imin[r] += __shfl_xor_sync(0xffffffffu, imin[r], 1);
+                }
+                const int is = half ? isum[1] : isum[0], im = half ? imin[1] : imin[0];
+                const uint32_t dw = half ? dd[1] : dd[0];
+                const float d = f16_bits_to_f32(dw & 0xffffu), dmin = f16_bits_to_f32(dw >> 16);
+                term = __fmul_rn(ad, __fsub_rn(__fmul_rn(d, (float)is), __fmul_rn(dmin, (float)im)));
             } else {
                 const uint32_t pA = slot + (2 * pj) * PB6, pB = pA + PB6;
-                const float dsup[2] = {f16_bits_to_f32(lds16(pA + LP * 208 + 2 * bl)), f16_bits_to_f32(lds16(pB + LP * 208 + 2 * bl))};
-                dot_block_q6k(pA + bl * 208, pB + bl * 208, dsup, xa, sbase + L.off_sum16 + gb * 32, ad, term);
+                dot_half_q6k(pA + bl * 208, pB + bl * 208, half, xa, sbase + L.off_sum16 + gb * 32, isum);
+                isum[0] += __shfl_xor_sync(0xffffffffu, isum[0], 1);
+                isum[1] += __shfl_xor_sync(0xffffffffu, isum[1], 1);
+                const float dsup = f16_bits_to_f32(lds16((half ? pB : pA) + BPC * 208 + 2 * bl));
+                term = __fmul_rn(__fmul_rn(ad, dsup), (float)(half ? isum[1] : isum[0]));
             }
-            sts32(terms + ((2 * pj) * LP + bl) * 4, term[0]);
-            sts32(terms + ((2 * pj + 1) * LP + bl) * 4, term[1]);
+            sts32(terms + ((2 * pj + half) * BPC + bl) * 4, term);
         }
         __syncwarp();
         // ordered sum: lane s < 2 * PPU continues the running total of (pair s / 2, row s % 2) over this chunk's blocks, in order
         if (cc == 0) tot = 0.0f;
         if (lane < 2 * PPU) {
-            const uint32_t tp = terms + lane * LP * 4;
-            if constexpr (LP >= 4) {
-                if (nblk == LP) {
+            const uint32_t tp = terms + lane * BPC * 4;
+            if constexpr (BPC >= 4) {
+                if (nblk == BPC) {
 #pragma unroll
-                    for (int b = 0; b < LP; b += 4) {
+                    for (int b = 0; b < BPC; b += 4) {
                         const uint4 v = lds128(tp + b * 4);
                         tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, __uint_as_float(v.x)), __uint_as_float(v.y)), __uint_as_float(v.z)), __uint_as_float(v.w));
                     }
                 } else {
 #pragma unroll
-                    for (int b = 0; b < LP; b += 4) {
+                    for (int b = 0; b < BPC; b += 4) {
                         if (b < (int)nblk) {
                             const uint4 v = lds128(tp + b * 4);
                             tot = __fadd_rn(tot, __uint_as_float(v.x));
@@ -502,10 +506,12 @@ __global__ void __launch_bounds__(Q6 ? 96 : 128, 2) stream_gemv_kernel(StreamArg
                         }
                     }
                 }
-            } else {
+            } else if constexpr (BPC == 2) {
                 const uint2 v = lds64(tp);
                 tot = __fadd_rn(tot, __uint_as_float(v.x));
                 if (nblk > 1) tot = __fadd_rn(tot, __uint_as_float(v.y));
+            } else {
+                tot = __fadd_rn(tot, __uint_as_float(lds32(tp)));
             }
         }
         __syncwarp();
