@@ -331,7 +331,7 @@ def main():
     achieved = bytes_per_launch / per_launch_s / 1e9
     # DRAM read + write bytes of one launch of the gate/up kernel of the 8B shape, from the ncu capture summarised in
     # profiles/decode_step_kernels_8b_ncu_full.md (a capture cannot run inside a timed bench)
-    traffic = 66131968 + 615168 if world == 1 and (cfg["n_embd"], cfg["n_ff"]) == (4096, 14336) else None
+    traffic = 66128896 + 896000 if world == 1 and (cfg["n_embd"], cfg["n_ff"]) == (4096, 14336) else None
     roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "launches_timed": timed, "avg_launch_us": per_launch_s * 1e6,
                 "algorithmic_bytes_per_launch": bytes_per_launch,
