@@ -327,7 +327,6 @@ bool launch_hd(const AttnDecodeArgs &a, uint32_t group, cudaStream_t st) {
 // 256 exactly as the activation quantizer does (engine/vecdot.rs:3030-3053), so the attention-output product can
 // start from int8 without another launch.
 // ====================================================================================================
-constexpr int AF_WARPS = 8;
 
 #ifdef OB_ATTN_PROF
 __device__ unsigned long long g_attn_prof[4096 * 8];
@@ -343,7 +342,7 @@ __device__ unsigned long long g_attn_prof[4096 * 8];
 #define AF_STAMP(i)
 #endif
 
-template <int HD, int G>
+template <int HD, int G, int AF_WARPS>
 struct AttnFusedSmem {
     static constexpr int ROW = HD * 2 + 16;             // bytes per token row: the pad spreads eight rows over all banks
     uint8_t kv[AF_WARPS][2][2][KV_PAGE * ROW];          // [warp][slot][k|v]
@@ -379,10 +378,12 @@ __device__ __forceinline__ uint32_t pack_half2_rest(float x, float y) {
     return pack_half2(x - f.x, y - f.y);
 }
 
-template <int HD, int G>
+// AF_WARPS: 8 (one CTA per SM; single-token decode, where every SM should be streaming pages) or 4 (two CTAs per SM, whose
+// start-up and merge phases overlap each other's streaming; large batches).
+template <int HD, int G, int AF_WARPS>
 __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDecodeArgs a, bool wait_dependency, bool early_pages) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    using Smem = AttnFusedSmem<HD, G>;
+    using Smem = AttnFusedSmem<HD, G, AF_WARPS>;
     Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
     constexpr int ROW = Smem::ROW;
     constexpr int THREADS = AF_WARPS * 32;
@@ -723,17 +724,17 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
     AF_STAMP(7);
 }
 
-template <int HD, int G>
-bool launch_fused_instance(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
+template <int HD, int G, int W>
+bool launch_fused_warps(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
     static bool configured = false;
-    const size_t smem = sizeof(AttnFusedSmem<HD, G>);
+    const size_t smem = sizeof(AttnFusedSmem<HD, G, W>);
     if (!configured) {
-        cudaFuncSetAttribute(attn_decode_fused_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_decode_fused_kernel<HD, G, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.n_splits, a.n_head_kv, a.n_seq);
-    cfg.blockDim = dim3(AF_WARPS * 32);
+    cfg.blockDim = dim3(W * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -741,8 +742,15 @@ bool launch_fused_instance(const AttnDecodeArgs &a, bool programmatic, cudaStrea
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = programmatic ? 1 : 0;
-    cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<HD, G>, a, programmatic, programmatic && a.n_seq == 1);
+    cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<HD, G, W>, a, programmatic, programmatic && a.n_seq == 1);
     return true;
+}
+
+template <int HD, int G>
+bool launch_fused_instance(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
+    // G * HD must be a multiple of the CTA size and the merge maps one 16-byte piece to a thread: 4 warps need G * HD >= 512
+    if (a.small_ctas && G * HD >= 512) return launch_fused_warps<HD, G, 4>(a, programmatic, st);
+    return launch_fused_warps<HD, G, 8>(a, programmatic, st);
 }
 
 }  // namespace

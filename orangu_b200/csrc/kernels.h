@@ -150,6 +150,7 @@ struct AttnDecodeArgs {
     // launch_attn_decode_fused only:
     uint32_t *counters;        // [n_seq][n_head_kv], zero before the first launch; the kernel leaves them zero
     uint8_t *image;            // optional, n_seq == 1: the output quantized per 256 for the product that follows (stream_gemv.cu)
+    bool small_ctas;           // many (row, kv head) pairs: CTAs of four warps, two per SM
 };
 void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st);
 // One kernel: every warp streams its own pages, the CTAs of a (sequence, kv head) leave partials and the last of them to

@@ -337,13 +337,16 @@ bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
         at.counters = m->attn_counters;
         at.image = image;
         AttnDecodeArgs fused = at;
-        {   // one CTA per SM; with more (row, kv head) pairs than SMs, the split count that wastes least of the last wave
+        {   // one 8-warp CTA per SM; with at least two (row, kv head) pairs per SM, 4-warp CTAs, two per SM, and the split
+            // count that wastes least of the last wave
             const uint32_t pairs = T * m->n_head_kv_l, sms = (uint32_t)m->ctx->sm_count;
             uint32_t best = std::max(1u, sms / pairs);
+            fused.small_ctas = pairs >= 2 * sms;
             if (pairs >= sms) {
+                const uint32_t slots = fused.small_ctas ? 2 * sms : sms;
                 double best_waste = 1e9;
                 for (uint32_t s = 1; s <= 4; ++s) {
-                    const double waves = (double)pairs * s / sms, waste = (std::ceil(waves) - waves) / std::ceil(waves) + 0.01 * s;
+                    const double waves = (double)pairs * s / slots, waste = (std::ceil(waves) - waves) / std::ceil(waves) + 0.01 * s;
                     if (waste < best_waste) {
                         best_waste = waste;
                         best = s;

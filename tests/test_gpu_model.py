@@ -252,3 +252,35 @@ def test_70b_shape_layer_is_bit_exact(backend):
         got, want = model.forward(kv, [tok], 40 + step), ref.forward(rkv, [tok], 40 + step)
         assert_bit_equal(got, want, f"decode step {step}")
         tok = O.argmax(want)
+
+
+def test_large_decode_batch_takes_the_small_cta_attention_and_agrees_with_single_decodes(backend):
+    """40 sequences x 8 kv heads is more than two (row, kv head) pairs per SM: the flash-decode runs as 4-warp CTAs.  Every
+    sequence's logits have to agree with the same sequence decoded alone (8-warp CTAs, more splits) and with the oracle."""
+    cfg = dict(synth.CONFIGS["8b"])
+    cfg["n_layer"] = 1
+    cfg["n_vocab"] = 2048
+    tensors = synth.model_tensors(cfg, seed=37)
+    n_seq, n_ctx = 40, 70
+    model = LlamaModel(backend, cfg, tensors, max_seq_len=128, max_batch_tokens=64, kv_pool_tokens=(n_seq + 2) * 128, exact_attention_max_pos=16)
+    ref = O.Model(cfg, tensors)
+    toks = prompt(cfg, n_ctx, 12)
+    base = model.new_kv_cache(96)
+    model.forward(base, toks, 0)
+    rkv = ref.new_kv(96, f16=True)
+    ref.forward(rkv, toks, 0)
+    caches = []
+    for _ in range(n_seq):
+        c = model.new_kv_cache(96)
+        c.copy_prefix_from(base, n_ctx)
+        caches.append(c)
+    nxt = [int(t) for t in prompt(cfg, n_seq, 13)]
+    _, logits = model.forward_batch_decode(caches, nxt, want_logits=True)
+    for i in (0, 7, 39):
+        alone = model.new_kv_cache(96)
+        alone.copy_prefix_from(base, n_ctx)
+        got_alone = model.forward(alone, [nxt[i]], n_ctx)
+        want = ref.forward(rkv, [nxt[i]], n_ctx)
+        rkv.truncate(n_ctx)
+        assert np.abs(logits[i] - got_alone).max() < LOGIT_TOL, i
+        assert np.abs(logits[i] - want).max() < LOGIT_TOL, i
