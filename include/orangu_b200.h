@@ -154,8 +154,8 @@ int ob_quantize_act(ob_ctx *ctx, const float *x, uint32_t n, int per_256, int8_t
  * which are stored as fp16 pages exactly as the KV mirror holds them (E/kv_cache.rs:26-32).
  * exact_order 1 evaluates in the CPU loop's operation order (bit-identical to it); 0 takes the
  * split flash-decode kernels and 2 the one-kernel tensor-core flash-decode that the decode step uses
- * (head_dim 64 or 128; 1, 2, 4 or 8 query heads per kv head); their results differ from the CPU's in
- * the last bits. */
+ * (head_dim 64 or 128; 1, 2, 4 or 8 query heads per kv head; 3 is the same kernel in the four-warp CTA shape it
+ * takes for large decode batches); their results differ from the CPU's in the last bits. */
 int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float *v, uint32_t n_pos,
                         uint32_t n_head, uint32_t n_head_kv, uint32_t head_dim, float scale, int exact_order, float *out);
 /* The split flash-decode attention of ob_attention_decode for callers that must not allocate: a slot's worker

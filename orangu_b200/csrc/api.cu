@@ -581,7 +581,8 @@ int ob_attention_decode(ob_ctx *ctx, const float *q, const float *k, const float
         e.max_pos = n_pos;
         launch_attn_exact(e, ctx->stream);
         ctx->launches += 3;
-    } else if (exact_order == 2) {  // the one-kernel form the decode step uses
+    } else if (exact_order == 2 || exact_order == 3) {  // the one-kernel form the decode step uses (3: its large-batch shape, CTAs of four warps)
+        a.small_ctas = exact_order == 3;
         a.counters = reinterpret_cast<uint32_t *>(meta + 128);
         OB_CUDA(ctx, cudaMemsetAsync(a.counters, 0, 128, ctx->stream));
         if (n_head_kv > 32 || !launch_attn_decode_fused(a, false, ctx->stream))

@@ -46,7 +46,8 @@ class KvCache:
 
     def close(self):
         if self._h:
-            self._lib.ob_kv_destroy(self._h)
+            if self.model._h and self.model.backend._h:  # after the backend is gone the handle is no longer valid: leave it
+                self._lib.ob_kv_destroy(self._h)
             self._h = None
 
     def __del__(self):

@@ -107,13 +107,14 @@ def test_flash_decode_attention_within_rounding(backend, n_head, n_head_kv, head
 @pytest.mark.parametrize("n_head,n_head_kv", [(4, 4), (8, 4), (8, 2), (32, 8), (8, 1), (64, 8)])
 @pytest.mark.parametrize("head_dim", [64, 128])
 @pytest.mark.parametrize("n_pos", [1, 17, 40, 331, 1500])
-def test_fused_tensor_core_flash_decode_within_rounding(backend, n_head, n_head_kv, head_dim, n_pos):
+@pytest.mark.parametrize("mode", [2, 3])
+def test_fused_tensor_core_flash_decode_within_rounding(backend, n_head, n_head_kv, head_dim, n_pos, mode):
     """The one-kernel flash-decode: scores and outputs on the tensor cores with q and the probabilities split into two
     fp16 parts -- the result has to stay at fp32 rounding level, not fp16."""
     if n_head // n_head_kv == 1 and head_dim == 64:
         pytest.skip("one head of 64 dims per kv head is not a shape of the fused kernel")
     q, k, v, want = attention_case(n_head, n_head_kv, head_dim, n_pos)
-    got = backend.attention_decode(q, k, v, n_head, n_head_kv, head_dim, 0.125, exact_order=2)
+    got = backend.attention_decode(q, k, v, n_head, n_head_kv, head_dim, 0.125, exact_order=mode)  # 3: CTAs of four warps
     assert np.abs(got - want).max() < 2e-5
 
 
