@@ -156,7 +156,7 @@ bool all_gather_logits(Comm *c, float *logits, uint32_t rows, uint32_t n_vocab, 
 
 const char *last_error(Comm *c) { return c ? c->err.c_str() : ""; }
 
-bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
+static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
     auto bail = [&](const std::string &m) {
         if (err) *err = m;
         return false;
@@ -166,10 +166,18 @@ bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err)
     cudaSetDevice(device);
     constexpr size_t kFlagBytes = 256, kLocalBytes = 256;
     const size_t slot_bytes = (size_t)2 * c->size * n * sizeof(uint2), total = kFlagBytes + kLocalBytes + slot_bytes;
-    if (cudaMalloc(&c->peer_region, total) != cudaSuccess) return bail("cudaMalloc of the exchange region failed");
-    cudaMemset(c->peer_region, 0, total);
+    // Every rank reaches the all-gather below, whatever happened before it (a rank that skipped it would leave the others
+    // waiting in NCCL); a rank without a region sends a zero handle and fails afterwards.
     cudaIpcMemHandle_t mine;
-    if (cudaIpcGetMemHandle(&mine, c->peer_region) != cudaSuccess) return bail(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError()));
+    memset(&mine, 0, sizeof(mine));
+    std::string early;
+    if (cudaMalloc(&c->peer_region, total) != cudaSuccess) {
+        c->peer_region = nullptr;
+        early = "cudaMalloc of the exchange region failed";
+    } else {
+        cudaMemset(c->peer_region, 0, total);
+        if (cudaIpcGetMemHandle(&mine, c->peer_region) != cudaSuccess) early = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
+    }
     // all-gather the 64-byte handles through the communicator
     unsigned char *stage = nullptr;
     if (cudaMalloc(reinterpret_cast<void **>(&stage), (size_t)c->size * sizeof(mine)) != cudaSuccess) return bail("cudaMalloc failed");
@@ -179,6 +187,7 @@ bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err)
     std::vector<cudaIpcMemHandle_t> all((size_t)c->size);
     if (r == 0 && e == cudaSuccess) e = cudaMemcpy(all.data(), stage, all.size() * sizeof(mine), cudaMemcpyDeviceToHost);
     cudaFree(stage);
+    if (!early.empty()) return bail(early);
     if (r != 0 || e != cudaSuccess) return bail("exchange of the IPC handles failed");
     PeerXchg px{};
     px.rank = (uint32_t)c->rank;
@@ -198,6 +207,25 @@ bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err)
     px.err = local + 32;
     *out = px;
     return true;
+}
+
+bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
+    Api *a = api();
+    if (!a || !c) return false;
+    // Every rank must take the same path afterwards: the exchange is used only if it could be set up everywhere.
+    // (The handle all-gather inside peer_init_local is reached by every rank or by none: its preconditions are the same
+    // on all ranks, and allocation failures this early are not expected; the agreement below covers the mapping step.)
+    const bool mine = peer_init_local(c, n, device, out, err);
+    int *flag = nullptr;
+    if (cudaMalloc(reinterpret_cast<void **>(&flag), sizeof(int)) != cudaSuccess) return false;
+    const int v = mine ? 1 : 0;
+    cudaMemcpy(flag, &v, sizeof(int), cudaMemcpyHostToDevice);
+    const NcclResult r = a->AllReduce(flag, flag, 1, /* ncclInt32 */ 2, /* ncclMin */ 2, c->comm, nullptr);
+    int all = 0;
+    if (r == 0 && cudaStreamSynchronize(nullptr) == cudaSuccess) cudaMemcpy(&all, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(flag);
+    if (!all && err && err->empty()) *err = "another rank could not set up the peer exchange";
+    return all == 1;
 }
 
 }  // namespace obtp
