@@ -329,8 +329,9 @@ def main():
         ms, nbytes, nl = model.profile_gemv(12, iters)
         kname, per_launch_s, bytes_per_launch, timed = "gemv_kernel<Q4_K, 1 token>", ms * 1e-3 / (iters * nl), nbytes // nl, iters * nl
     achieved = bytes_per_launch / per_launch_s / 1e9
-    # DRAM read + write bytes of one launch of the gate/up kernel of the 8B shape, from the ncu capture summarised in
-    # profiles/decode_step_kernels_8b_ncu_full.md (a capture cannot run inside a timed bench)
+    # DRAM read + write bytes of one launch of the gate/up kernel of the 8B shape, taken from an ncu capture of this kernel
+    # on a two-layer model of the same shape (dram__bytes_read.sum + dram__bytes_write.sum; a capture cannot run inside a
+    # timed bench)
     traffic = 66128896 + 896000 if world == 1 and (cfg["n_embd"], cfg["n_ff"]) == (4096, 14336) else None
     roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": traffic, "launches_timed": timed, "avg_launch_us": per_launch_s * 1e6,
