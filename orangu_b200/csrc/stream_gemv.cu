@@ -126,14 +126,36 @@ __device__ __forceinline__ float silu_mul_exact(float g, float u) {
 }
 
 // ---- activations of the single token, quantized per 256 ------------------------------------------------------
+// One warp, block b of the image: lane l holds elements 8l .. 8l+7 of the block in v.
+__device__ __forceinline__ void quantize_block(const float (&v)[8], uint32_t b, uint8_t *img, const ActImage &im) {
+    const int lane = threadIdx.x & 31;
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = warp_max(amax);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+    int q[8], s8 = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        q[i] = quantize_value(v[i], inv);
+        s8 += q[i];
+    }
+    const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+    const uint32_t lo = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    const uint32_t hi = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(img + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
+    if ((lane & 1) == 0) reinterpret_cast<int16_t *>(img + im.off_sum16)[b * 16 + (lane >> 1)] = (int16_t)s16;
+    if ((lane & 3) == 0) reinterpret_cast<int16_t *>(img + im.off_bsum)[b * 8 + (lane >> 2)] = (int16_t)s32;
+    if (lane == 0) reinterpret_cast<float *>(img + im.off_d)[b] = scale;
+}
+
 // Warps `warp`, `warp + n_warps`, ... of the callers take blocks round-robin; a lane owns 8 consecutive elements of the block.
 // x * norm_scale * norm_w is quantized when norm_w != nullptr (tensor.rs:747), x itself otherwise.
 __device__ void quantize_image(const float *x, const float *norm_w, float norm_scale, uint32_t nb, uint8_t *img, uint32_t warp, uint32_t n_warps) {
     const int lane = threadIdx.x & 31;
     const ActImage im = act_image(nb);
-    float *sd = reinterpret_cast<float *>(img + im.off_d);
-    int16_t *bsum = reinterpret_cast<int16_t *>(img + im.off_bsum);
-    int16_t *sum16 = reinterpret_cast<int16_t *>(img + im.off_sum16);
     // four blocks per pass, all their loads issued before any arithmetic: the pass costs one memory latency, not four
     for (uint32_t bb = warp; bb < nb; bb += 4 * n_warps) {
         float v[4][8];
@@ -163,26 +185,7 @@ __device__ void quantize_image(const float *x, const float *norm_w, float norm_s
         for (int k = 0; k < 4; ++k) {
             const uint32_t b = bb + k * n_warps;
             if (b >= nb) break;  // warp-uniform
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[k][i]));
-            amax = warp_max(amax);
-            const float scale = __fdiv_rn(amax, 127.0f);
-            const float inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
-            int q[8], s8 = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                q[i] = quantize_value(v[k][i], inv);
-                s8 += q[i];
-            }
-            const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
-            const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-            const uint32_t lo = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-            const uint32_t hi = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-            *reinterpret_cast<uint2 *>(img + b * ACT_BLOCK_STRIDE + lane * 8) = make_uint2(lo, hi);
-            if ((lane & 1) == 0) sum16[b * 16 + (lane >> 1)] = (int16_t)s16;
-            if ((lane & 3) == 0) bsum[b * 8 + (lane >> 2)] = (int16_t)s32;
-            if (lane == 0) sd[b] = scale;
+            quantize_block(v[k], b, img, im);
         }
     }
 }
@@ -620,8 +623,22 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
                                                                 float *__restrict__ out, uint8_t *__restrict__ image, obtp::PeerXchg px, bool wait_dependency) {
     extern __shared__ float srow[];  // the row, one pad word per 16
     __shared__ SeqSumWorkspace<NS_THREADS> ws;
-    if (norm_w)  // the weights do not depend on the predecessor: have them in L2 by the time the scale is known
-        for (uint32_t i = threadIdx.x * 32; i < dim; i += NS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(norm_w + i));
+    // The weights do not depend on the predecessor: those of this warp's first two blocks are in registers, the others in
+    // L2, by the time the scale is known.
+    constexpr uint32_t NS_WARPS = NS_THREADS / 32, NS_PRE = 2;
+    const uint32_t nb = dim / 256, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float wpre[NS_PRE][8];
+    if (norm_w && image) {
+#pragma unroll
+        for (uint32_t k = 0; k < NS_PRE; ++k) {
+            const uint32_t b = warp + k * NS_WARPS;
+            if (b < nb) {
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + b * 256 + lane * 8)), w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + b * 256 + lane * 8 + 4));
+                wpre[k][0] = w0.x; wpre[k][1] = w0.y; wpre[k][2] = w0.z; wpre[k][3] = w0.w; wpre[k][4] = w1.x; wpre[k][5] = w1.y; wpre[k][6] = w1.z; wpre[k][7] = w1.w;
+            }
+        }
+        for (uint32_t i = NS_PRE * NS_WARPS * 256 + threadIdx.x * 32; i < dim; i += NS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(norm_w + i));
+    }
     if (wait_dependency) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -666,7 +683,28 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
     const float t = cta_sequential_sum<NS_THREADS>([&](uint32_t i) { const float v = srow[i + (i >> 4)]; return __fmul_rn(v, v); }, dim, ws);
     const float scale = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
     if (threadIdx.x == 0 && out) *out = scale;
-    if (image) quantize_image(x, norm_w, scale, dim / 256, image, threadIdx.x >> 5, NS_THREADS / 32);
+    if (!image) return;
+    if (!norm_w) {
+        quantize_image(x, nullptr, scale, nb, image, warp, NS_WARPS);
+        return;
+    }
+    // (x * scale) * w per 256, the row taken from shared memory (the pad keeps a lane's 8 elements together)
+    const ActImage im = act_image(nb);
+    for (uint32_t k = 0, b = warp; b < nb; ++k, b += NS_WARPS) {
+        const uint32_t e0 = b * 256 + lane * 8;
+        const float *sv = srow + e0 + (e0 >> 4);
+        float v[8], w[8];
+        if (k < NS_PRE) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = k == 0 ? wpre[0][i] : wpre[1][i];
+        } else {
+            const float4 w0 = __ldg(reinterpret_cast<const float4 *>(norm_w + e0)), w1 = __ldg(reinterpret_cast<const float4 *>(norm_w + e0 + 4));
+            w[0] = w0.x; w[1] = w0.y; w[2] = w0.z; w[3] = w0.w; w[4] = w1.x; w[5] = w1.y; w[6] = w1.z; w[7] = w1.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(sv[i], scale), w[i]);  // tensor.rs:747
+        quantize_block(v, b, image, im);
+    }
 }
 
 // x quantized per 256 into the image, one warp per block.
