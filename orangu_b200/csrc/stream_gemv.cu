@@ -640,7 +640,6 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
         for (uint32_t i = NS_PRE * NS_WARPS * 256 + threadIdx.x * 32; i < dim; i += NS_THREADS * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(norm_w + i));
     }
     if (wait_dependency) {
-        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
     if (px.size > 1) {
@@ -680,6 +679,9 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
         for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) srow[i + (i >> 4)] = __ldcg(x + i);
         __syncthreads();
     }
+    // The successor is let in only now: its CTAs start by requesting weights, and that traffic would stand in the way of
+    // the loads above, which are on the critical path.
+    if (wait_dependency) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const float t = cta_sequential_sum<NS_THREADS>([&](uint32_t i) { const float v = srow[i + (i >> 4)]; return __fmul_rn(v, v); }, dim, ws);
     const float scale = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(t, (float)dim), eps)));
     if (threadIdx.x == 0 && out) *out = scale;
