@@ -112,6 +112,47 @@ void dequantize_q8_0(const uint8_t *bytes, size_t n, float *out) {
     }
 }
 
+/* The per-32 symmetric family (Q4_0, Q5_0, IQ4_NL): block = f16 d, [Q5_0: 4 bytes of fifth bits,] 16 bytes of nibbles;
+ * the low nibbles are elements 0..15, the high nibbles 16..31.  E/vecdot.rs:1001-1016 (the shared bit extraction),
+ * :1019-1025 (Q4_0: bias 8), :1036-1038 (Q5_0: bias 16), E/quant.rs:1320-1336 + E/iq_grids.rs:5941 (IQ4_NL: the
+ * nibble indexes the format's 16 non-uniform levels). */
+const int8_t IQ4NL_LEVELS[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+inline bool is_sym32(uint32_t type) { return type == OREF_TYPE_Q4_0 || type == OREF_TYPE_Q5_0 || type == OREF_TYPE_IQ4_NL; }
+inline size_t sym32_block_bytes(uint32_t type) { return type == OREF_TYPE_Q5_0 ? 22 : 18; }
+
+/* writes the block's 32 signed codes, returns its scale */
+float unpack_sym32(uint32_t type, const uint8_t *blk, int8_t *w) {
+    const float d = read_f16(blk);
+    if (type == OREF_TYPE_IQ4_NL) {
+        for (int j = 0; j < 16; ++j) {
+            w[j] = IQ4NL_LEVELS[blk[2 + j] & 0x0F];
+            w[16 + j] = IQ4NL_LEVELS[blk[2 + j] >> 4];
+        }
+        return d;
+    }
+    const bool five = type == OREF_TYPE_Q5_0;
+    const uint32_t qh = five ? ((uint32_t)blk[2] | ((uint32_t)blk[3] << 8) | ((uint32_t)blk[4] << 16) | ((uint32_t)blk[5] << 24)) : 0u;
+    const uint8_t *qs = blk + (five ? 6 : 2);
+    const int bias = five ? 16 : 8;
+    for (int j = 0; j < 16; ++j) {
+        const uint32_t hi_lo = ((qh >> j) << 4) & 0x10, hi_hi = (qh >> (j + 12)) & 0x10;
+        w[j] = (int8_t)((int)((qs[j] & 0x0Fu) | hi_lo) - bias);
+        w[16 + j] = (int8_t)((int)((uint32_t)(qs[j] >> 4) | hi_hi) - bias);
+    }
+    return d;
+}
+
+/* E/quant.rs:537-555 (Q4_0), :560-580 (Q5_0), :1320-1336 (IQ4_NL): code times scale, one rounding */
+void dequantize_sym32(uint32_t type, const uint8_t *bytes, size_t n, float *out) {
+    size_t nb = (n + 31) / 32, o = 0;
+    int8_t w[32];
+    for (size_t b = 0; b < nb; ++b) {
+        const float d = unpack_sym32(type, bytes + b * sym32_block_bytes(type), w);
+        for (size_t i = 0; i < 32 && o < n; ++i, ++o) out[o] = (float)w[i] * d;
+    }
+}
+
 /* E/quant.rs:666-697 */
 void dequantize_q4_k(const uint8_t *bytes, size_t n, float *out) {
     size_t nb = (n + 255) / 256;
@@ -238,6 +279,18 @@ float dot_q8_0(const uint8_t *row, size_t in_dim, const ActRow &a) {
         const uint8_t *blk = row + b * 34;
         float dw = read_f16(blk);
         total += dw * a.d[b] * (float)dot32((const int8_t *)(blk + 2), a.q + b * 32);
+    }
+    return total;
+}
+
+/* E/vecdot.rs:2842-2852 (IQ4_NL), :2856-2867 (Q5_0), :2871-2881 (Q4_0): the Q8_0 loop over the unpacked codes */
+float dot_sym32(uint32_t type, const uint8_t *row, size_t in_dim, const ActRow &a) {
+    float total = 0.0f;
+    int8_t w[32];
+    const size_t nb = in_dim / 32, bb = sym32_block_bytes(type);
+    for (size_t b = 0; b < nb; ++b) {
+        const float dw = unpack_sym32(type, row + b * bb, w);
+        total += dw * a.d[b] * (float)dot32(w, a.q + b * 32);
     }
     return total;
 }
@@ -510,6 +563,28 @@ void gemm_flat_q8_0(const uint8_t *row, const ActQ8Flat &a, float *out) {
     }
 }
 
+/* The same accumulation over a row unpacked to (codes, per-32 scale): E/vecdot.rs:1277-1292 (Q4_0), :1246-1275 (Q5_0 and
+ * Q8_0), :1318-1340 (IQ4_NL) feed E/vecdot.rs:2598-2629 */
+void gemm_flat_sym32(uint32_t type, const uint8_t *row, const ActQ8Flat &a, float *out) {
+    const size_t bb = sym32_block_bytes(type);
+    std::vector<int8_t> codes(a.n_block * 32);
+    std::vector<float> scale(a.n_block);
+    for (size_t b = 0; b < a.n_block; ++b) scale[b] = unpack_sym32(type, row + b * bb, &codes[b * 32]);
+    for (size_t tl = 0; tl < a.n_tile; ++tl) {
+        float acc[TOKEN_TILE] = {0, 0, 0, 0};
+        const int8_t *qtile = &a.q[tl * a.n_block * TOKEN_TILE * ACT_BLOCK];
+        const float *dtile = &a.d[tl * a.n_block * TOKEN_TILE];
+        for (size_t b = 0; b < a.n_block; ++b) {
+            const float s0 = scale[b];
+            const int8_t *q0 = &codes[b * 32];
+            const int8_t *xq = qtile + b * TOKEN_TILE * ACT_BLOCK;
+            const float *ad = dtile + b * TOKEN_TILE;
+            for (size_t k = 0; k < TOKEN_TILE; ++k) acc[k] += ad[k] * s0 * (float)dot32(q0, xq + k * ACT_BLOCK);
+        }
+        store_tile(tl, acc, out, a.n_tokens);
+    }
+}
+
 int set_threads(int n_threads) {
 #ifdef _OPENMP
     int n = n_threads > 0 ? n_threads : omp_get_num_procs();
@@ -522,7 +597,7 @@ int set_threads(int n_threads) {
 }
 
 bool supported(uint32_t type, size_t in_dim) {
-    if (type == OREF_TYPE_Q8_0) return in_dim % 32 == 0;
+    if (type == OREF_TYPE_Q8_0 || is_sym32(type)) return in_dim % 32 == 0;
     if (type == OREF_TYPE_Q4_K || type == OREF_TYPE_Q6_K) return in_dim % 256 == 0;
     return false;
 }
@@ -532,12 +607,17 @@ void gemv_token(const float *x, const uint8_t *raw, uint32_t type, size_t in_dim
     size_t rb = (size_t)oref_row_bytes(type, in_dim);
     std::vector<int8_t> q(in_dim);
     std::vector<int32_t> sums(in_dim / GROUP);
-    if (type == OREF_TYPE_Q8_0) {
+    if (type == OREF_TYPE_Q8_0 || is_sym32(type)) {
         std::vector<float> d(in_dim / 32);
         oref_quantize_act(x, in_dim, q.data(), d.data(), sums.data());
         ActRow a{q.data(), d.data(), sums.data()};
+        if (type == OREF_TYPE_Q8_0) {
 #pragma omp parallel for schedule(static)
-        for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_q8_0(raw + o * rb, in_dim, a);
+            for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_q8_0(raw + o * rb, in_dim, a);
+        } else {
+#pragma omp parallel for schedule(static)
+            for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_sym32(type, raw + o * rb, in_dim, a);
+        }
     } else {
         std::vector<float> d(in_dim / 256);
         oref_quantize_act_k_row(x, in_dim, q.data(), d.data(), sums.data());
@@ -563,6 +643,8 @@ int oref_block_layout(uint32_t type, uint32_t *bb, uint32_t *be) {
     switch (type) {
     case OREF_TYPE_F32: *bb = 4; *be = 1; return 0;
     case OREF_TYPE_Q8_0: *bb = 34; *be = 32; return 0;
+    case OREF_TYPE_Q4_0: case OREF_TYPE_IQ4_NL: *bb = 18; *be = 32; return 0;
+    case OREF_TYPE_Q5_0: *bb = 22; *be = 32; return 0;
     case OREF_TYPE_Q4_K: *bb = 144; *be = 256; return 0;
     case OREF_TYPE_Q6_K: *bb = 210; *be = 256; return 0;
     default: return -1;
@@ -580,6 +662,7 @@ int oref_dequantize(uint32_t type, const uint8_t *bytes, size_t n, float *out) {
     switch (type) {
     case OREF_TYPE_F32: memcpy(out, bytes, n * 4); return 0;
     case OREF_TYPE_Q8_0: dequantize_q8_0(bytes, n, out); return 0;
+    case OREF_TYPE_Q4_0: case OREF_TYPE_Q5_0: case OREF_TYPE_IQ4_NL: dequantize_sym32(type, bytes, n, out); return 0;
     case OREF_TYPE_Q4_K: dequantize_q4_k(bytes, n, out); return 0;
     case OREF_TYPE_Q6_K: dequantize_q6_k(bytes, n, out); return 0;
     default: return -1;
@@ -603,6 +686,13 @@ float oref_dot_q8_0(const uint8_t *row, size_t in_dim, const int8_t *q, const fl
     return dot_q8_0(row, in_dim, a);
 }
 
+float oref_dot_row32(uint32_t type, const uint8_t *row, size_t in_dim, const int8_t *q, const float *d) {
+    ActRow a{q, d, nullptr};
+    if (type == OREF_TYPE_Q8_0) return dot_q8_0(row, in_dim, a);
+    if (is_sym32(type)) return dot_sym32(type, row, in_dim, a);
+    return NAN;
+}
+
 float oref_dot_k_row(uint32_t type, const uint8_t *row, size_t in_dim, const int8_t *q, const float *d, const int32_t *sums) {
     ActRow a{q, d, sums};
     if (type == OREF_TYPE_Q4_K) return dot_k_row_q4_k(row, in_dim, a, nullptr, nullptr);
@@ -614,11 +704,14 @@ int oref_row_partials(uint32_t type, const uint8_t *row, size_t in_dim, const fl
     if (!supported(type, in_dim)) return -1;
     std::vector<int8_t> q(in_dim);
     std::vector<int32_t> sums(in_dim / GROUP);
-    if (type == OREF_TYPE_Q8_0) {
+    if (type == OREF_TYPE_Q8_0 || is_sym32(type)) {
         std::vector<float> d(in_dim / 32);
         oref_quantize_act(x, in_dim, q.data(), d.data(), sums.data());
+        int8_t w[32];
         for (size_t b = 0; b < in_dim / 32; ++b) {
-            isum[b] = dot32((const int8_t *)(row + b * 34 + 2), q.data() + b * 32);
+            if (type == OREF_TYPE_Q8_0) memcpy(w, row + b * 34 + 2, 32);
+            else unpack_sym32(type, row + b * sym32_block_bytes(type), w);
+            isum[b] = dot32(w, q.data() + b * 32);
             if (imin) imin[b] = 0;
         }
         return 0;
@@ -650,6 +743,11 @@ int oref_matmul(const float *x, size_t n_tokens, const uint8_t *raw, uint32_t ty
         a.quantize(x, in_dim, n_tokens);
 #pragma omp parallel for schedule(static)
         for (size_t o = 0; o < out_dim; ++o) gemm_flat_q8_0(raw + o * rb, a, &yt[o * n_tokens]);
+    } else if (is_sym32(type)) {
+        ActQ8Flat a;
+        a.quantize(x, in_dim, n_tokens);
+#pragma omp parallel for schedule(static)
+        for (size_t o = 0; o < out_dim; ++o) gemm_flat_sym32(type, raw + o * rb, a, &yt[o * n_tokens]);
     } else {
         ActQ8K a;
         a.quantize(x, in_dim, n_tokens);

@@ -35,6 +35,9 @@ extern "C" {
 
 /* ggml type ids, E/quant.rs:50-112 */
 #define OREF_TYPE_F32 0u
+#define OREF_TYPE_Q4_0 2u   /* the per-32 symmetric family beside Q8_0: one f16 scale, 32 signed codes, no min term */
+#define OREF_TYPE_Q5_0 6u
+#define OREF_TYPE_IQ4_NL 20u
 #define OREF_TYPE_Q8_0 8u
 #define OREF_TYPE_Q4_K 12u
 #define OREF_TYPE_Q6_K 14u
@@ -55,6 +58,8 @@ void oref_quantize_act_k_row(const float *x, size_t n, int8_t *q, float *d, int3
 
 /* ---- GEMV rows ------------------------------------------------------------ */
 float oref_dot_q8_0(const uint8_t *row, size_t in_dim, const int8_t *q, const float *d);   /* E/vecdot.rs:2829-2838 */
+/* any per-32 type (Q8_0, Q4_0, Q5_0, IQ4_NL) against per-32 quantized activations; E/vecdot.rs:2842-2881 */
+float oref_dot_row32(uint32_t type, const uint8_t *row, size_t in_dim, const int8_t *q, const float *d);
 float oref_dot_k_row(uint32_t type, const uint8_t *row, size_t in_dim, const int8_t *q,
                      const float *d, const int32_t *sums);                                /* E/vecdot.rs:3152-3178, 3215-3241 */
 /* The integer partial sums the GEMV forms before touching fp32: per Q8_0 block the

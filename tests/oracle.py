@@ -15,7 +15,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(ROOT, "oracle", "_build", "liborangu_oracle.so")
 
 F32, Q8_0, Q4_K, Q6_K = 0, 8, 12, 14
-BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), F32: (4, 1)}
+Q4_0, Q5_0, IQ4_NL = 2, 6, 20   # per-32 symmetric types: one f16 scale and 32 signed codes per block, like Q8_0
+PER_32 = (Q8_0, Q4_0, Q5_0, IQ4_NL)
+BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), F32: (4, 1), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32)}
 
 
 def build(force: bool = False) -> str:
@@ -66,6 +68,8 @@ def lib():
         L.oref_get_scale_min_k4.argtypes = [i32, vp, vp, vp]
         L.oref_quantize_act.argtypes = [vp, u64, vp, vp, vp]
         L.oref_quantize_act_k_row.argtypes = [vp, u64, vp, vp, vp]
+        L.oref_dot_row32.restype = f32
+        L.oref_dot_row32.argtypes = [C.c_uint32, vp, u64, vp, vp]
         L.oref_dot_q8_0.restype = f32
         L.oref_dot_q8_0.argtypes = [vp, u64, vp, vp]
         L.oref_dot_k_row.restype = f32
@@ -145,6 +149,9 @@ def dot_row(t, row, x):
     if t == Q8_0:
         q, d, _ = quantize_act(x)
         return float(lib().oref_dot_q8_0(_p(row), x.size, _p(q), _p(d)))
+    if t in PER_32:
+        q, d, _ = quantize_act(x)
+        return float(lib().oref_dot_row32(t, _p(row), x.size, _p(q), _p(d)))
     q, d, s = quantize_act(x, True)
     return float(lib().oref_dot_k_row(t, _p(row), x.size, _p(q), _p(d), _p(s)))
 

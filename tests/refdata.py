@@ -4,7 +4,7 @@ E = src/bin/orangu-server/engine in the reference tree.
 """
 import numpy as np
 
-BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 0: (4, 1)}
+BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 0: (4, 1), 2: (18, 32), 6: (22, 32), 20: (18, 32)}
 
 
 def fixture_bytes(n):
@@ -73,7 +73,7 @@ def activations(n):
 def _pin_scales(raw, t):
     bb = BLOCK[t][0]
     blocks = raw.reshape(-1, bb)
-    if t == 8:
+    if t in (8, 2, 6, 20):  # one leading f16 scale (E/vecdot.rs:3459-3461)
         blocks[:, 0:2] = [0x00, 0x30]
     elif t == 12:
         blocks[:, 0:2] = [0x00, 0x30]

@@ -12,12 +12,16 @@ import oracle as O
 from refdata import activations, fixture_bytes, bit_checksum, fixture_row, k_fixture, pseudo_bytes, xorshift32_kv
 
 Q8_0, Q4_K, Q6_K = O.Q8_0, O.Q4_K, O.Q6_K
+Q4_0, Q5_0, IQ4_NL = O.Q4_0, O.Q5_0, O.IQ4_NL
 
 
 # ---- E/quant.rs:1389-1463 -------------------------------------------------
 GOLDEN = [
     (O.F32, 64, 0x1EB2_B799_2AE6_E834),
     (Q8_0, 256, 0xC5D5_8782_F54E_52E5),
+    (Q4_0, 256, 0x1623_25C9_68C1_0725),
+    (Q5_0, 256, 0x813F_8949_E12B_3725),
+    (IQ4_NL, 256, 0x7956_C82F_EBA1_2125),
     (Q4_K, 512, 0x9A72_68A4_32A5_C5FA),
     (Q6_K, 512, 0x6100_1D33_3CB0_CFD1),
 ]
@@ -200,6 +204,47 @@ def test_q8_0_gemv_within_int8_budget(in_dim, seed):
     ref, mag = dequant_reference(Q8_0, row, x)
     got = O.dot_row(Q8_0, row, x)
     assert abs(got - ref) <= 0.01 * max(mag, 1e-6)
+
+
+# E/vecdot.rs:4176-4180 (Q4_0), :3854 (Q5_0), :3891 (IQ4_NL) run the same check on the per-32 symmetric types
+@pytest.mark.parametrize("t", [Q4_0, Q5_0, IQ4_NL])
+@pytest.mark.parametrize("in_dim", [32, 896, 4864])
+@pytest.mark.parametrize("seed", [1, 7, 99])
+def test_per_32_symmetric_gemv_within_int8_budget(t, in_dim, seed):
+    row = fixture_row(t, in_dim, seed)
+    x = activations(in_dim)
+    ref, mag = dequant_reference(t, row, x)
+    got = O.dot_row(t, row, x)
+    assert abs(got - ref) <= 0.01 * max(mag, 1e-6)
+
+
+# E/vecdot.rs:4226-4235: an all-zero Q4_0 payload unpacks to -8 everywhere (its own zero point, not Q5_0's -16)
+def test_q4_0_zero_payload_is_minus_eight():
+    block = np.zeros(18, np.uint8)
+    block[0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    assert (O.dequantize(Q4_0, block, 32) == -8.0).all()
+    q5 = np.zeros(22, np.uint8)
+    q5[0:2] = block[0:2]
+    assert (O.dequantize(Q5_0, q5, 32) == -16.0).all()
+
+
+def test_per_32_symmetric_types_equal_q8_0_on_the_unpacked_codes():
+    """Their dot is the Q8_0 loop over the unpacked codes (E/vecdot.rs:2842-2881), so a Q8_0 row holding those codes
+    must give the same bits, single token and batched."""
+    x1 = activations(896)
+    xb = activations(896 * 5).reshape(5, 896)
+    for t in (Q4_0, Q5_0, IQ4_NL):
+        raw = fixture_row(t, 896 * 6, 3)  # six rows
+        codes = O.dequantize(t, raw, 896 * 6) / np.float32(0.125)
+        assert (codes == np.round(codes)).all() and np.abs(codes).max() <= 127
+        as_q8 = np.zeros((896 * 6 // 32, 34), np.uint8)
+        as_q8[:, 0:2] = [0x00, 0x30]
+        as_q8[:, 2:] = codes.astype(np.int8).view(np.uint8).reshape(-1, 32)
+        for x in (x1, xb):
+            n_tok = 1 if x.ndim == 1 else x.shape[0]
+            a = O.matmul(x, n_tok, raw, t, 896, 6)
+            b = O.matmul(x, n_tok, as_q8.reshape(-1), Q8_0, 896, 6)
+            assert a.tobytes() == b.tobytes()
 
 
 @pytest.mark.parametrize("t", [Q4_K, Q6_K])
