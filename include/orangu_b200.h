@@ -47,6 +47,12 @@ typedef enum ob_status {
 #define OB_TYPE_Q8_0 8u
 #define OB_TYPE_Q4_K 12u
 #define OB_TYPE_Q6_K 14u
+/* Per-32 symmetric types (one f16 scale, 32 signed codes).  The CPU kernels for them are the Q8_0 loops over the unpacked
+ * codes (E/vecdot.rs:2842-2881 decode, :1277-1340 + :2598-2629 batched), so the library unpacks them once, at registration,
+ * into its Q8_0 layout: results equal the CPU's bit for bit; the device reads 34 bytes per block instead of 18 or 22. */
+#define OB_TYPE_Q4_0 2u
+#define OB_TYPE_Q5_0 6u
+#define OB_TYPE_IQ4_NL 20u
 
 typedef struct ob_ctx ob_ctx;
 typedef struct ob_weight ob_weight;
@@ -66,7 +72,7 @@ const char *ob_last_error(const ob_ctx *ctx);
 
 unsigned ob_abi_version(void);
 
-/* Replaces Backend::supports_type (B/mod.rs:479-495): 1 for Q8_0, Q4_K, Q6_K (and F32
+/* Replaces Backend::supports_type (B/mod.rs:479-495): 1 for Q8_0, Q4_K, Q6_K, Q4_0, Q5_0, IQ4_NL (and F32
  * for norm vectors), 0 otherwise, so a missing kernel is a named start-up error. */
 int ob_supports_type(uint32_t ggml_type);
 

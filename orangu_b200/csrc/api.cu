@@ -44,7 +44,7 @@ int ensure(ob_ctx *ctx, Scratch &s, size_t bytes) {
     return OB_OK;
 }
 
-bool type_supported(uint32_t t) { return t == TYPE_Q8_0 || t == TYPE_Q4_K || t == TYPE_Q6_K; }
+bool type_supported(uint32_t t) { return t == TYPE_Q8_0 || t == TYPE_Q4_K || t == TYPE_Q6_K || is_sym32_source(t); }
 
 }  // namespace obrt
 
@@ -138,13 +138,13 @@ int make_weight(ob_ctx *ctx, const uint8_t *raw, uint64_t row_bytes, uint32_t ty
     ob_weight *w = new ob_weight;
     w->ctx = ctx;
     DevWeight &d = w->w;
-    d.type = type;
+    d.type = is_sym32_source(type) ? TYPE_Q8_0 : type;  // Q4_0, Q5_0, IQ4_NL are held as their unpacked int8 codes + f16 scale
     d.in_dim = n_cols;
     d.out_dim = n_rows;
     d.nb = n_cols / be;
-    const uint32_t main_bytes = type == TYPE_Q4_K ? 144u : (type == TYPE_Q6_K ? 208u : 32u);
+    const uint32_t main_bytes = d.type == TYPE_Q4_K ? 144u : (d.type == TYPE_Q6_K ? 208u : 32u);
     d.d_off = d.nb * main_bytes;
-    const uint64_t row_size = (uint64_t)d.nb * bb;
+    const uint64_t row_size = (uint64_t)d.nb * block_bytes_gguf(d.type);
     d.row_stride = (row_size + 15) & ~(uint64_t)15;
     w->bytes = d.row_stride * n_rows;
     void *mem = nullptr;
@@ -171,7 +171,7 @@ int make_weight(ob_ctx *ctx, const uint8_t *raw, uint64_t row_bytes, uint32_t ty
         src_dev = static_cast<const uint8_t *>(staging);
     }
     if (d.row_stride != row_size) cudaMemsetAsync(mem, 0, w->bytes, ctx->stream);
-    launch_repack(src_dev, row_bytes, 0, col0 / be, d, ctx->stream);
+    launch_repack(src_dev, row_bytes, type, 0, col0 / be, d, ctx->stream);
     ctx->launches++;
     e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaGetLastError();

@@ -15,6 +15,12 @@
 namespace ob {
 
 constexpr uint32_t TYPE_F32 = 0, TYPE_Q8_0 = 8, TYPE_Q4_K = 12, TYPE_Q6_K = 14;
+// Source-only types: per-32 symmetric formats (one f16 scale, 32 signed codes, no min term) whose CPU kernels are the
+// Q8_0 loops over the unpacked codes (engine/vecdot.rs:2842-2881, :1277-1340).  They are unpacked to the device's Q8_0
+// layout at registration, so every kernel sees TYPE_Q8_0 and gives the CPU's bits; the price is 34 instead of 18 or 22
+// bytes per block of HBM traffic.
+constexpr uint32_t TYPE_Q4_0 = 2, TYPE_Q5_0 = 6, TYPE_IQ4_NL = 20;
+__host__ __device__ inline bool is_sym32_source(uint32_t t) { return t == TYPE_Q4_0 || t == TYPE_Q5_0 || t == TYPE_IQ4_NL; }
 constexpr int KV_PAGE = 16;  // tokens per KV page
 
 // ---- device helpers ----------------------------------------------------------------
@@ -88,8 +94,10 @@ struct DevWeight {
     uint64_t row_stride;  // bytes
 };
 
-__host__ __device__ inline uint32_t block_elems(uint32_t type) { return type == TYPE_Q8_0 ? 32u : 256u; }
-__host__ __device__ inline uint32_t block_bytes_gguf(uint32_t type) { return type == TYPE_Q8_0 ? 34u : (type == TYPE_Q4_K ? 144u : 210u); }
+__host__ __device__ inline uint32_t block_elems(uint32_t type) { return type == TYPE_Q8_0 || is_sym32_source(type) ? 32u : 256u; }
+__host__ __device__ inline uint32_t block_bytes_gguf(uint32_t type) {
+    return type == TYPE_Q8_0 ? 34u : type == TYPE_Q4_K ? 144u : type == TYPE_Q5_0 ? 22u : is_sym32_source(type) ? 18u : 210u;
+}
 
 // Quantized activations of one token row, natural element order.
 //   q     int8  [in_dim]

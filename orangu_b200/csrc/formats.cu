@@ -10,14 +10,37 @@ namespace ob {
 
 // One thread per destination block.  src rows are GGUF rows of `src_row_bytes`; the
 // destination takes blocks [blk0, blk0+nb) of rows [row0, row0+n_rows).
-__global__ void repack_kernel(const uint8_t *__restrict__ src, uint64_t src_row_bytes, uint32_t row0, uint32_t blk0, DevWeight w) {
+// The 16 levels an IQ4_NL nibble indexes (engine/iq_grids.rs:5941; a constant of the format).
+__constant__ int8_t IQ4NL_LEVELS[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+__global__ void repack_kernel(const uint8_t *__restrict__ src, uint64_t src_row_bytes, uint32_t src_type, uint32_t row0, uint32_t blk0, DevWeight w) {
     uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     uint64_t total = (uint64_t)w.out_dim * w.nb;
     if (idx >= total) return;
     uint32_t r = (uint32_t)(idx / w.nb), b = (uint32_t)(idx % w.nb);
-    const uint8_t *s = src + (uint64_t)(row0 + r) * src_row_bytes + (uint64_t)(blk0 + b) * block_bytes_gguf(w.type);
+    const uint8_t *s = src + (uint64_t)(row0 + r) * src_row_bytes + (uint64_t)(blk0 + b) * block_bytes_gguf(src_type);
     uint8_t *drow = const_cast<uint8_t *>(w.data) + (uint64_t)r * w.row_stride;
-    if (w.type == TYPE_Q4_K) {
+    if (is_sym32_source(src_type)) {
+        // low nibbles are elements 0..15, high nibbles 16..31; Q5_0 adds a fifth bit per element from the 32-bit qh and
+        // subtracts 16, Q4_0 subtracts 8, IQ4_NL looks the nibble up (engine/vecdot.rs:1001-1016, :1019-1038)
+        int8_t *d = reinterpret_cast<int8_t *>(drow + (uint64_t)b * 32);
+        const bool five = src_type == TYPE_Q5_0;
+        const uint32_t qh = five ? ((uint32_t)s[2] | ((uint32_t)s[3] << 8) | ((uint32_t)s[4] << 16) | ((uint32_t)s[5] << 24)) : 0u;
+        const uint8_t *qs = s + (five ? 6 : 2);
+        const int bias = five ? 16 : 8;
+        for (int j = 0; j < 16; ++j) {
+            if (src_type == TYPE_IQ4_NL) {
+                d[j] = IQ4NL_LEVELS[qs[j] & 0x0F];
+                d[16 + j] = IQ4NL_LEVELS[qs[j] >> 4];
+            } else {
+                const uint32_t hi_lo = ((qh >> j) << 4) & 0x10, hi_hi = (qh >> (j + 12)) & 0x10;
+                d[j] = (int8_t)((int)((qs[j] & 0x0Fu) | hi_lo) - bias);
+                d[16 + j] = (int8_t)((int)((uint32_t)(qs[j] >> 4) | hi_hi) - bias);
+            }
+        }
+        drow[w.d_off + 2 * b] = s[0];
+        drow[w.d_off + 2 * b + 1] = s[1];
+    } else if (w.type == TYPE_Q4_K) {
         uint8_t *d = drow + (uint64_t)b * 144;
         for (int i = 0; i < 144; ++i) d[i] = s[i];
     } else if (w.type == TYPE_Q6_K) {
@@ -90,9 +113,9 @@ __global__ void embed_kernel(DevWeight w, const uint32_t *__restrict__ tokens, u
     out[(uint64_t)t * w.in_dim + e] = dequant_element(w, tokens[t], e);
 }
 
-void launch_repack(const uint8_t *src, uint64_t src_row_bytes, uint32_t row0, uint32_t blk0, const DevWeight &w, cudaStream_t st) {
+void launch_repack(const uint8_t *src, uint64_t src_row_bytes, uint32_t src_type, uint32_t row0, uint32_t blk0, const DevWeight &w, cudaStream_t st) {
     uint64_t total = (uint64_t)w.out_dim * w.nb;
-    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src, src_row_bytes, row0, blk0, w);
+    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(src, src_row_bytes, src_type, row0, blk0, w);
 }
 
 void launch_dequant_rows(const DevWeight &w, uint32_t first_row, uint32_t n_rows, float *out, cudaStream_t st) {

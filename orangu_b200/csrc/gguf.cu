@@ -63,6 +63,7 @@ uint64_t tensor_bytes(uint32_t type, uint64_t n) {
     case 11: return n / 256 * 110;    // Q3_K
     case 13: return n / 256 * 176;    // Q5_K
     case 15: return n / 256 * 292;    // Q8_K
+    case 20: return n / 32 * 18;      // IQ4_NL
     default: return 0;
     }
 }

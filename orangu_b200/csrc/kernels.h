@@ -10,7 +10,8 @@
 namespace ob {
 
 // ---- formats.cu
-void launch_repack(const uint8_t *src, uint64_t src_row_bytes, uint32_t row0, uint32_t blk0, const DevWeight &w, cudaStream_t st);
+// src_type: the GGUF type of `src`; w.type is what the device holds (TYPE_Q8_0 for the per-32 symmetric source types).
+void launch_repack(const uint8_t *src, uint64_t src_row_bytes, uint32_t src_type, uint32_t row0, uint32_t blk0, const DevWeight &w, cudaStream_t st);
 void launch_dequant_rows(const DevWeight &w, uint32_t first_row, uint32_t n_rows, float *out, cudaStream_t st);
 void launch_embed(const DevWeight &w, const uint32_t *tokens, uint32_t n_tokens, float *out, cudaStream_t st);
 

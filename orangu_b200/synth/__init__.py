@@ -10,7 +10,10 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(os.path.dirname(HERE), "_lib", "libob_synth.so")
 F32, Q8_0, Q4_K, Q6_K = 0, 8, 12, 14
-BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256)}
+Q4_0, Q5_0, IQ4_NL = 2, 6, 20
+BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32)}
+# standard deviation of a uniformly random code of the per-32 symmetric types (sets the block scale for a wanted std)
+_CODE_STD = {Q4_0: 4.61, Q5_0: 9.23, IQ4_NL: 70.2}
 
 _lib = None
 
@@ -53,6 +56,15 @@ def quantize(w: np.ndarray, ggml_type: int) -> np.ndarray:
 def matrix(ggml_type: int, out_dim: int, in_dim: int, seed: int, std: float = 0.02) -> dict:
     """[out_dim, in_dim] ~ N(0, std^2), quantized; the fp32 matrix is never materialised."""
     bb, be = BLOCK[ggml_type]
+    if ggml_type in _CODE_STD:
+        # uniformly random codes; block scales spread over [0.5, 1.5] x the value that gives the wanted std
+        if in_dim % be:
+            raise ValueError("in_dim is not a whole number of blocks")
+        rng = np.random.default_rng(seed & 0xFFFFFFFFFFFF)
+        blocks = rng.integers(0, 256, (out_dim * (in_dim // be), bb), dtype=np.uint8)
+        d = (std / _CODE_STD[ggml_type] * rng.uniform(0.5, 1.5, blocks.shape[0])).astype(np.float16)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        return {"data": blocks.reshape(-1), "type": ggml_type, "in_dim": in_dim, "out_dim": out_dim}
     out = np.empty(out_dim * (in_dim // be) * bb, np.uint8)
     if _load().obs_synth_matrix(ggml_type, seed, std, out_dim, in_dim, out.ctypes.data):
         raise ValueError("in_dim is not a whole number of blocks")

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import numpy as np
 
-BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256)}  # ggml type -> (bytes, elements) per block
+BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 2: (18, 32), 6: (22, 32), 20: (18, 32)}  # ggml type -> (bytes, elements) per block
 
 
 def check(cfg: dict, tp_size: int) -> None:

@@ -182,7 +182,7 @@ def test_weight_slices_for_tensor_parallel(backend):
     from orangu_b200 import capi
 
     L = capi.load()
-    for t in TYPES:
+    for t in TYPES + SYM32:
         in_dim, out_dim = 2048, 24
         w = gauss_matrix(t, out_dim, in_dim, 77)
         x = synth.normal(in_dim, 3)
@@ -197,6 +197,53 @@ def test_weight_slices_for_tensor_parallel(backend):
         rows = w.raw.reshape(out_dim, -1)[8:16]
         sub = np.ascontiguousarray(rows[:, (512 // be) * bb:(1536 // be) * bb])
         assert_bit_equal(y, O.matmul(xs, 1, sub, t, 1024, 8), f"slice type {t}")
+
+
+# ---- Q4_0, Q5_0, IQ4_NL: per-32 symmetric types, unpacked at registration into the Q8_0 layout ------------
+SYM32 = [2, 6, 20]
+SYM32_GOLDEN = {2: 0x162325C968C10725, 6: 0x813F8949E12B3725, 20: 0x7956C82FEBA12125}  # E/quant.rs:1389-1420, 256 elements
+
+
+@pytest.mark.parametrize("t", SYM32)
+def test_per_32_symmetric_types_dequantize_to_the_reference_checksums(backend, t):
+    from refdata import bit_checksum
+
+    bb, be = O.BLOCK[t]
+    raw = fixture_bytes(256 // be * bb)
+    got = backend.row(QuantMatrix(raw, t, 256, 1), 0)
+    want = O.dequantize(t, raw, 256)
+    nan = np.isnan(want)
+    assert (np.isnan(got[0]) == nan).all()
+    assert (bits(got[0])[~nan] == bits(want)[~nan]).all()
+    if not nan.any():
+        assert bit_checksum(got[0]) == SYM32_GOLDEN[t]
+
+
+@pytest.mark.parametrize("t", SYM32)
+@pytest.mark.parametrize("in_dim,out_dim", [(32, 3), (896, 7), (4864, 33)])
+def test_per_32_symmetric_rows_partials_and_gemv_are_bit_exact(backend, t, in_dim, out_dim):
+    for w, x in ((lcg_matrix(t, out_dim, in_dim, 17), activations(in_dim)),
+                 (gauss_matrix(t, out_dim, in_dim, 3), synth.normal(in_dim, 7))):
+        want_rows = O.dequantize(t, w.raw, in_dim * out_dim).reshape(out_dim, in_dim)
+        assert_bit_equal(backend.row(w, 0, out_dim), want_rows, f"rows, type {t}")
+        isum, _ = backend.matmul_partials(x, w)
+        rb = w.row_bytes()
+        for o in range(out_dim):
+            wi, _ = O.row_partials(t, w.raw[o * rb:(o + 1) * rb], x)
+            assert (isum[o] == wi).all(), f"isum row {o}"
+        assert_bit_equal(backend.matmul(x, 1, w), O.matmul(x, 1, w.raw, t, in_dim, out_dim), f"gemv type {t} [{out_dim}x{in_dim}]")
+
+
+@pytest.mark.parametrize("t", SYM32)
+def test_per_32_symmetric_batches_are_bit_exact(backend, t):
+    in_dim, out_dim = 896, 37
+    w = gauss_matrix(t, out_dim, in_dim, 21)
+    for n in (2, 7, 64):
+        x = synth.normal(n * in_dim, 40 + n)
+        assert_bit_equal(backend.matmul(x, n, w), O.matmul(x, n, w.raw, t, in_dim, out_dim), f"prefill, {n} tokens")
+        assert_bit_equal(backend.matmul_decode(x, n, w), O.matmul_decode(x, n, w.raw, t, in_dim, out_dim), f"decode batch, {n} rows")
+    raw, x = k_fixture(t, 2048, 5, 7, 4242)  # the reference's 5-row, 7-token fixture shape
+    assert_bit_equal(backend.matmul(x, 7, QuantMatrix(raw, t, 2048, 5)), O.matmul(x, 7, raw, t, 2048, 5), "fixture")
 
 
 # ---- error behaviour ---------------------------------------------------------------------------------

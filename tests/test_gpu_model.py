@@ -30,7 +30,10 @@ def prompt(cfg, n, seed):
 
 
 @pytest.mark.parametrize("name,types", [("tiny", None), ("small", None), ("tiny", {"attn_q": 8, "ffn_down": 8, "output": 8}),
-                                         ("small", {"attn_k": 14, "ffn_gate": 14, "token_embd": 14})])
+                                         ("small", {"attn_k": 14, "ffn_gate": 14, "token_embd": 14}),
+                                         # Q4_0 / Q5_0 / IQ4_NL everywhere
+                                         ("tiny", {"token_embd": 2, "output": 6, "attn_q": 2, "attn_k": 20, "attn_v": 6, "attn_output": 2,
+                                                   "ffn_gate": 20, "ffn_up": 2, "ffn_down": 6})])
 def test_prefill_then_greedy_decode_matches_the_oracle(backend, name, types):
     cfg, tensors, model, ref = build(backend, name, seed=3, types=types, max_seq_len=256, max_batch_tokens=32, kv_pool_tokens=512)
     toks = prompt(cfg, 45, 1)
