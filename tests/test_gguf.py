@@ -12,9 +12,12 @@ from orangu_b200 import capi, synth
 from orangu_b200.gguf import GgufFile, write_gguf
 
 
-def tiny(seed=5, with_output=True, rope_freqs=False):
+PER_32_MIX = {"token_embd": 2, "output": 6, "attn_q": 2, "attn_k": 20, "attn_v": 6, "attn_output": 2, "ffn_gate": 20, "ffn_up": 2, "ffn_down": 6}
+
+
+def tiny(seed=5, with_output=True, rope_freqs=False, types=None):
     cfg = dict(synth.CONFIGS["tiny"])
-    tensors = synth.model_tensors(cfg, seed=seed)
+    tensors = synth.model_tensors(cfg, seed=seed, types=types)
     if not with_output:
         del tensors["output.weight"]
     if rope_freqs:
@@ -45,6 +48,18 @@ def test_reader_sees_what_the_writer_wrote(tmp_path, alignment):
             assert getattr(d, k) == cfg[k], k
         assert d.rope_dim == cfg["head_dim"] and abs(d.rms_eps - cfg["rms_eps"]) < 1e-12 and d.rope_freqs
         assert d.layers[1].w_down.in_dim == cfg["n_ff"] and d.layers[1].w_down.out_dim == cfg["n_embd"] and d.layers[0].wv.ggml_type == 14
+
+
+def test_per_32_symmetric_tensors_are_sized_and_described(tmp_path):
+    cfg, tensors = tiny(types=PER_32_MIX)
+    path = str(tmp_path / "mix.gguf")
+    write_gguf(path, cfg, tensors)
+    with GgufFile(path) as g:
+        infos = {t["name"]: t for t in g.tensors()}
+        for name, t in tensors.items():
+            assert infos[name]["type"] == t["type"] and infos[name]["n_bytes"] == np.ascontiguousarray(t["data"]).view(np.uint8).size, name
+        desc = g.model_desc()  # every tensor type has a kernel
+        assert desc is not None
 
 
 def test_defaults_and_tied_output(tmp_path):
@@ -124,14 +139,14 @@ def test_malformed_files_are_refused_with_a_message(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("with_output,rope_freqs", [(True, False), (False, True)])
-def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(backend, tmp_path, with_output, rope_freqs):
+@pytest.mark.parametrize("with_output,rope_freqs,types", [(True, False, None), (False, True, None), (True, False, PER_32_MIX)])
+def test_model_from_a_file_equals_the_model_from_tensors_and_the_oracle(backend, tmp_path, with_output, rope_freqs, types):
     import oracle as O
     import orangu_b200
     from gpu_common import assert_bit_equal
 
     be = backend
-    cfg, tensors = tiny(seed=9, with_output=with_output, rope_freqs=rope_freqs)
+    cfg, tensors = tiny(seed=9, with_output=with_output, rope_freqs=rope_freqs, types=types)
     path = str(tmp_path / "m.gguf")
     write_gguf(path, cfg, tensors, alignment=64)
     from_file = orangu_b200.LlamaModel.from_gguf(be, path, max_seq_len=64, max_batch_tokens=16)
