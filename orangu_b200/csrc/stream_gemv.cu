@@ -650,28 +650,48 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
         unsigned long long t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
         bool gave_up = false;
-        for (uint32_t i = threadIdx.x; i < dim; i += NS_THREADS) {
-            float sum = 0.0f;
-            for (uint32_t r = 0; r < px.size; ++r) {
-                const uint2 *src = mine + (uint64_t)r * px.n + i;
-                uint2 w;
-                for (uint32_t spin = 0;; ++spin) {
-                    asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w.x), "=r"(w.y) : "l"(src) : "memory");
-                    if (w.y == tag || gave_up) break;
-                    if ((spin & 1023u) == 1023u) {
-                        unsigned long long t1;
-                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                        if (t1 - t0 > 4000000000ull) {  // four seconds: a rank is gone; report and go on with what is there
-                            *px.err = 1u;
-                            gave_up = true;
+        // Four elements x all ranks at a time: every word is requested before any is examined, so a batch costs one
+        // trip to memory when the partials are already there (the usual case); words that do not carry the tag yet are
+        // read again, one after the other.
+        constexpr uint32_t EB = 4, MAX_RANKS = 8;
+        for (uint32_t i0 = threadIdx.x; i0 < dim; i0 += EB * NS_THREADS) {
+            uint2 w[EB][MAX_RANKS];
+            float xv[EB];
+#pragma unroll
+            for (uint32_t e = 0; e < EB; ++e) {
+                const uint32_t i = i0 + e * NS_THREADS;
+#pragma unroll
+                for (uint32_t r = 0; r < MAX_RANKS; ++r)
+                    if (i < dim && r < px.size)
+                        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w[e][r].x), "=r"(w[e][r].y) : "l"(mine + (uint64_t)r * px.n + i) : "memory");
+                if (i < dim) xv[e] = __ldcg(x + i);
+            }
+#pragma unroll
+            for (uint32_t e = 0; e < EB; ++e) {
+                const uint32_t i = i0 + e * NS_THREADS;
+                if (i >= dim) continue;
+                float sum = 0.0f;
+#pragma unroll
+                for (uint32_t r = 0; r < MAX_RANKS; ++r) {
+                    if (r >= px.size) continue;
+                    const uint2 *src = mine + (uint64_t)r * px.n + i;
+                    for (uint32_t spin = 0; w[e][r].y != tag && !gave_up; ++spin) {
+                        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(w[e][r].x), "=r"(w[e][r].y) : "l"(src) : "memory");
+                        if ((spin & 1023u) == 1023u) {
+                            unsigned long long t1;
+                            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                            if (t1 - t0 > 4000000000ull) {  // four seconds: a rank is gone; report and go on with what is there
+                                *px.err = 1u;
+                                gave_up = true;
+                            }
                         }
                     }
+                    sum = r == 0 ? __uint_as_float(w[e][r].x) : __fadd_rn(sum, __uint_as_float(w[e][r].x));
                 }
-                sum = r == 0 ? __uint_as_float(w.x) : __fadd_rn(sum, __uint_as_float(w.x));
+                const float v = __fadd_rn(xv[e], sum);
+                x[i] = v;
+                srow[i + (i >> 4)] = v;
             }
-            const float v = __fadd_rn(__ldcg(x + i), sum);
-            x[i] = v;
-            srow[i + (i >> 4)] = v;
         }
         __syncthreads();
         if (threadIdx.x == 0) *px.seq = k + 1u;
