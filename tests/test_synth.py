@@ -27,6 +27,17 @@ def test_quantizers_round_trip_through_the_reference_decode_rules(t, tol):
     assert rms < tol, rms
 
 
+@pytest.mark.parametrize("t", [synth.Q4_0, synth.Q5_0, synth.IQ4_NL])
+def test_per_32_symmetric_matrices_are_seeded_finite_and_of_the_wanted_scale(t):
+    m = synth.matrix(t, 64, 1024, 21, std=0.02)
+    assert m["data"].size == 64 * O.row_bytes(t, 1024)
+    assert (m["data"] == synth.matrix(t, 64, 1024, 21, std=0.02)["data"]).all()
+    assert not (m["data"] == synth.matrix(t, 64, 1024, 22, std=0.02)["data"]).all()
+    w = O.dequantize(t, m["data"], 64 * 1024)
+    assert np.isfinite(w).all()
+    assert 0.5 * 0.02 < w.std() < 2.0 * 0.02, w.std()
+
+
 def test_q6_k_scales_take_both_signs_and_q4_k_uses_all_six_bits():
     w = synth.normal(64 * 256, 5, 0.02).reshape(64, 256)
     q6 = synth.quantize(w, synth.Q6_K).reshape(64, 210)
