@@ -179,6 +179,35 @@ void dequantize_q4_k(const uint8_t *bytes, size_t n, float *out) {
     }
 }
 
+/* E/quant.rs:703-742: block = d, dmin, scales[12], qh[32], qs[128]; code = nibble + 16 * (bit of qh[l] for the sub-block) */
+void dequantize_q5_k(const uint8_t *bytes, size_t n, float *out) {
+    size_t nb = (n + 255) / 256;
+    float tmp[256];
+    for (size_t b = 0; b < nb; ++b) {
+        const uint8_t *blk = bytes + b * 176;
+        float d = read_f16(blk), dmin = read_f16(blk + 2);
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        size_t w = 0;
+        int is = 0;
+        uint8_t u1 = 1, u2 = 2;
+        for (size_t q_offset = 0; q_offset < 256; q_offset += 64) {
+            uint8_t sc1, m1, sc2, m2;
+            scale_min_k4(is, scales, &sc1, &m1);
+            scale_min_k4(is + 1, scales, &sc2, &m2);
+            float d1 = d * (float)sc1, mm1 = dmin * (float)m1;
+            float d2 = d * (float)sc2, mm2 = dmin * (float)m2;
+            const uint8_t *q = qs + q_offset / 2;
+            for (int l = 0; l < 32; ++l) tmp[w++] = d1 * (float)((int)(q[l] & 0x0F) + ((qh[l] & u1) ? 16 : 0)) - mm1;
+            for (int l = 0; l < 32; ++l) tmp[w++] = d2 * (float)((int)(q[l] >> 4) + ((qh[l] & u2) ? 16 : 0)) - mm2;
+            is += 2;
+            u1 = (uint8_t)(u1 << 2);
+            u2 = (uint8_t)(u2 << 2);
+        }
+        size_t take = std::min<size_t>(256, n - b * 256);
+        memcpy(out + b * 256, tmp, take * sizeof(float));
+    }
+}
+
 /* E/quant.rs:746-787 */
 void dequantize_q6_k(const uint8_t *bytes, size_t n, float *out) {
     size_t nb = (n + 255) / 256;
@@ -325,6 +354,37 @@ float dot_k_row_q4_k(const uint8_t *row, size_t in_dim, const ActRow &a, int32_t
     return total;
 }
 
+/* E/vecdot.rs:3181-3210: the Q4_K loop over five-bit codes */
+float dot_k_row_q5_k(const uint8_t *row, size_t in_dim, const ActRow &a, int32_t *isum_out, int32_t *imin_out) {
+    float total = 0.0f;
+    int8_t w[32];
+    size_t ns = in_dim / 256;
+    for (size_t s = 0; s < ns; ++s) {
+        const uint8_t *blk = row + s * 176;
+        float d = read_f16(blk), dmin = read_f16(blk + 2);
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        size_t sb = s * SUBS;
+        int32_t isum = 0, imin = 0;
+        for (int g = 0; g < 4; ++g) {
+            const uint8_t *bytes = qs + g * 32;
+            for (int half = 0; half < 2; ++half) {
+                int shift = half * 4;
+                uint8_t sc, m;
+                scale_min_k4(g * 2 + half, scales, &sc, &m);
+                const uint8_t hi_mask = (uint8_t)(1u << (g * 2 + half));
+                size_t b = sb + g * 2 + half;
+                for (int j = 0; j < 32; ++j) w[j] = (int8_t)(((bytes[j] >> shift) & 0x0F) + ((qh[j] & hi_mask) ? 16 : 0));
+                isum += (int32_t)sc * dot32(w, a.q + b * 32);
+                imin += (int32_t)m * (a.sums[b * 2] + a.sums[b * 2 + 1]);
+            }
+        }
+        if (isum_out) isum_out[s] = isum;
+        if (imin_out) imin_out[s] = imin;
+        total += a.d[s] * (d * (float)isum - dmin * (float)imin);
+    }
+    return total;
+}
+
 /* E/vecdot.rs:3215-3241 */
 float dot_k_row_q6_k(const uint8_t *row, size_t in_dim, const ActRow &a, int32_t *isum_out) {
     float total = 0.0f;
@@ -420,6 +480,37 @@ struct KRow {
     std::vector<float> d, dmin;
     bool q6 = false;
 };
+
+/* E/vecdot.rs:2064-2089: as unpack_k_q4_k, codes carry their fifth bit; the row then takes the Q4_K GEMM (:2119-2143) */
+void unpack_k_q5_k(const uint8_t *row, size_t in_dim, KRow &out) {
+    size_t ns = in_dim / 256;
+    out.q6 = false;
+    out.q.resize(in_dim);
+    out.sc.resize(in_dim / 32);
+    out.mins.resize(in_dim / 32);
+    out.d.resize(ns);
+    out.dmin.resize(ns);
+    size_t sb = 0;
+    for (size_t s = 0; s < ns; ++s) {
+        const uint8_t *blk = row + s * 176;
+        out.d[s] = read_f16(blk);
+        out.dmin[s] = read_f16(blk + 2);
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        for (int g = 0; g < 4; ++g) {
+            const uint8_t *bytes = qs + g * 32;
+            for (int half = 0; half < 2; ++half) {
+                uint8_t sc, m;
+                scale_min_k4(g * 2 + half, scales, &sc, &m);
+                const uint8_t hi_mask = (uint8_t)(1u << (g * 2 + half));
+                int8_t *w = &out.q[(sb + half) * 32];
+                for (int j = 0; j < 32; ++j) w[j] = (int8_t)(((bytes[j] >> (half * 4)) & 0x0F) + ((qh[j] & hi_mask) ? 16 : 0));
+                out.sc[sb + half] = sc;
+                out.mins[sb + half] = m;
+            }
+            sb += 2;
+        }
+    }
+}
 
 /* E/vecdot.rs:2036-2058 */
 void unpack_k_q4_k(const uint8_t *row, size_t in_dim, KRow &out) {
@@ -598,7 +689,7 @@ int set_threads(int n_threads) {
 
 bool supported(uint32_t type, size_t in_dim) {
     if (type == OREF_TYPE_Q8_0 || is_sym32(type)) return in_dim % 32 == 0;
-    if (type == OREF_TYPE_Q4_K || type == OREF_TYPE_Q6_K) return in_dim % 256 == 0;
+    if (type == OREF_TYPE_Q4_K || type == OREF_TYPE_Q6_K || type == OREF_TYPE_Q5_K) return in_dim % 256 == 0;
     return false;
 }
 
@@ -625,6 +716,9 @@ void gemv_token(const float *x, const uint8_t *raw, uint32_t type, size_t in_dim
         if (type == OREF_TYPE_Q4_K) {
 #pragma omp parallel for schedule(static)
             for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_k_row_q4_k(raw + o * rb, in_dim, a, nullptr, nullptr);
+        } else if (type == OREF_TYPE_Q5_K) {
+#pragma omp parallel for schedule(static)
+            for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_k_row_q5_k(raw + o * rb, in_dim, a, nullptr, nullptr);
         } else {
 #pragma omp parallel for schedule(static)
             for (size_t o = 0; o < out_dim; ++o) y[o * y_stride] = dot_k_row_q6_k(raw + o * rb, in_dim, a, nullptr);
@@ -646,6 +740,7 @@ int oref_block_layout(uint32_t type, uint32_t *bb, uint32_t *be) {
     case OREF_TYPE_Q4_0: case OREF_TYPE_IQ4_NL: *bb = 18; *be = 32; return 0;
     case OREF_TYPE_Q5_0: *bb = 22; *be = 32; return 0;
     case OREF_TYPE_Q4_K: *bb = 144; *be = 256; return 0;
+    case OREF_TYPE_Q5_K: *bb = 176; *be = 256; return 0;
     case OREF_TYPE_Q6_K: *bb = 210; *be = 256; return 0;
     default: return -1;
     }
@@ -664,6 +759,7 @@ int oref_dequantize(uint32_t type, const uint8_t *bytes, size_t n, float *out) {
     case OREF_TYPE_Q8_0: dequantize_q8_0(bytes, n, out); return 0;
     case OREF_TYPE_Q4_0: case OREF_TYPE_Q5_0: case OREF_TYPE_IQ4_NL: dequantize_sym32(type, bytes, n, out); return 0;
     case OREF_TYPE_Q4_K: dequantize_q4_k(bytes, n, out); return 0;
+    case OREF_TYPE_Q5_K: dequantize_q5_k(bytes, n, out); return 0;
     case OREF_TYPE_Q6_K: dequantize_q6_k(bytes, n, out); return 0;
     default: return -1;
     }
@@ -696,6 +792,7 @@ float oref_dot_row32(uint32_t type, const uint8_t *row, size_t in_dim, const int
 float oref_dot_k_row(uint32_t type, const uint8_t *row, size_t in_dim, const int8_t *q, const float *d, const int32_t *sums) {
     ActRow a{q, d, sums};
     if (type == OREF_TYPE_Q4_K) return dot_k_row_q4_k(row, in_dim, a, nullptr, nullptr);
+    if (type == OREF_TYPE_Q5_K) return dot_k_row_q5_k(row, in_dim, a, nullptr, nullptr);
     if (type == OREF_TYPE_Q6_K) return dot_k_row_q6_k(row, in_dim, a, nullptr);
     return NAN;
 }
@@ -721,6 +818,8 @@ int oref_row_partials(uint32_t type, const uint8_t *row, size_t in_dim, const fl
     ActRow a{q.data(), d.data(), sums.data()};
     if (type == OREF_TYPE_Q4_K) {
         dot_k_row_q4_k(row, in_dim, a, isum, imin);
+    } else if (type == OREF_TYPE_Q5_K) {
+        dot_k_row_q5_k(row, in_dim, a, isum, imin);
     } else {
         dot_k_row_q6_k(row, in_dim, a, isum);
         if (imin) memset(imin, 0, (in_dim / 256) * sizeof(int32_t));
@@ -756,8 +855,9 @@ int oref_matmul(const float *x, size_t n_tokens, const uint8_t *raw, uint32_t ty
             KRow w;
 #pragma omp for schedule(static)
             for (size_t o = 0; o < out_dim; ++o) {
-                if (type == OREF_TYPE_Q4_K) {
-                    unpack_k_q4_k(raw + o * rb, in_dim, w);
+                if (type == OREF_TYPE_Q4_K || type == OREF_TYPE_Q5_K) {
+                    if (type == OREF_TYPE_Q4_K) unpack_k_q4_k(raw + o * rb, in_dim, w);
+                    else unpack_k_q5_k(raw + o * rb, in_dim, w);
                     gemm_k_q4_k(w, a, &yt[o * n_tokens]);
                 } else {
                     unpack_k_q6_k(raw + o * rb, in_dim, w);

@@ -41,6 +41,7 @@ extern "C" {
 #define OREF_TYPE_Q8_0 8u
 #define OREF_TYPE_Q4_K 12u
 #define OREF_TYPE_Q6_K 14u
+#define OREF_TYPE_Q5_K 13u  /* Q4_K with a fifth bit per code; oracle only so far: the device library has no kernel for it */
 
 /* ---- formats ------------------------------------------------------------ */
 float oref_f16_to_f32(uint16_t bits);                       /* E/quant.rs:511-528 */

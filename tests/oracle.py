@@ -15,9 +15,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(ROOT, "oracle", "_build", "liborangu_oracle.so")
 
 F32, Q8_0, Q4_K, Q6_K = 0, 8, 12, 14
+Q5_K = 13  # oracle only: no device kernel yet
 Q4_0, Q5_0, IQ4_NL = 2, 6, 20   # per-32 symmetric types: one f16 scale and 32 signed codes per block, like Q8_0
 PER_32 = (Q8_0, Q4_0, Q5_0, IQ4_NL)
-BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), F32: (4, 1), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32)}
+BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), F32: (4, 1), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32), Q5_K: (176, 256)}
 
 
 def build(force: bool = False) -> str:

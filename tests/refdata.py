@@ -4,7 +4,7 @@ E = src/bin/orangu-server/engine in the reference tree.
 """
 import numpy as np
 
-BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 0: (4, 1), 2: (18, 32), 6: (22, 32), 20: (18, 32)}
+BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 0: (4, 1), 2: (18, 32), 6: (22, 32), 20: (18, 32), 13: (176, 256)}
 
 
 def fixture_bytes(n):
@@ -75,7 +75,7 @@ def _pin_scales(raw, t):
     blocks = raw.reshape(-1, bb)
     if t in (8, 2, 6, 20):  # one leading f16 scale (E/vecdot.rs:3459-3461)
         blocks[:, 0:2] = [0x00, 0x30]
-    elif t == 12:
+    elif t in (12, 13):  # Q5_K shares Q4_K's leading d / dmin pair (E/vecdot.rs:3467-3471)
         blocks[:, 0:2] = [0x00, 0x30]
         blocks[:, 2:4] = [0x00, 0x2C]
     elif t == 14:

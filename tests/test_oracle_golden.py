@@ -13,6 +13,7 @@ from refdata import activations, fixture_bytes, bit_checksum, fixture_row, k_fix
 
 Q8_0, Q4_K, Q6_K = O.Q8_0, O.Q4_K, O.Q6_K
 Q4_0, Q5_0, IQ4_NL = O.Q4_0, O.Q5_0, O.IQ4_NL
+Q5_K = O.Q5_K
 
 
 # ---- E/quant.rs:1389-1463 -------------------------------------------------
@@ -23,6 +24,7 @@ GOLDEN = [
     (Q5_0, 256, 0x813F_8949_E12B_3725),
     (IQ4_NL, 256, 0x7956_C82F_EBA1_2125),
     (Q4_K, 512, 0x9A72_68A4_32A5_C5FA),
+    (Q5_K, 512, 0x41C7_0B9B_E169_6E6D),
     (Q6_K, 512, 0x6100_1D33_3CB0_CFD1),
 ]
 
@@ -287,8 +289,39 @@ def test_row_partials_reassemble_to_the_row_total():
         assert np.float32(O.dot_row(t, row, x)).view(np.uint32) == total.view(np.uint32)
 
 
+# ---- Q5_K (oracle only so far): E/quant.rs:1872-1888, E/vecdot.rs:4127-4133, 4141-4166 ----------------------
+def q5_k_high_bit_block():
+    block = np.zeros(176, np.uint8)
+    block[0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)  # d = 1, dmin = 0
+    block[4:16] = [1, 1, 1, 1, 0, 0, 0, 0, 1, 1, 1, 1]                # every scale 1, every min 0
+    block[16:48] = 0xFF                                               # qh: every high bit set; qs: every nibble 0
+    return block
+
+
+def test_q5_k_high_bit_reaches_every_sub_block():
+    block = q5_k_high_bit_block()
+    assert (O.dequantize(Q5_K, block, 256) == 16.0).all()
+    # decode and batched forms see the same codes: with x = 1 everywhere a row sums 256 * 16 * (quantized 1.0)
+    x = np.ones(256, np.float32)
+    one = O.matmul(x, 1, block, Q5_K, 256, 1)[0, 0]
+    many = O.matmul(np.tile(x, 5), 5, block, Q5_K, 256, 1)[:, 0]
+    assert abs(one - 4096.0) < 1e-2 and (np.abs(many - 4096.0) < 1e-2).all()
+
+
+@pytest.mark.parametrize("in_dim", [256, 3072, 4864])
+@pytest.mark.parametrize("seed", [1, 7, 99])
+def test_q5_k_gemv_within_int8_budget(in_dim, seed):
+    row = fixture_row(Q5_K, in_dim, seed)
+    x = activations(in_dim)
+    ref, mag = dequant_reference(Q5_K, row, x)
+    got = O.dot_row(Q5_K, row, x)
+    assert abs(got - ref) <= 0.02 * max(mag, 1e-6)
+    isum, imin = O.row_partials(Q5_K, row, x)
+    assert isum.size == in_dim // 256 and imin.size == in_dim // 256
+
+
 # ---- E/vecdot.rs:4416-4549 -------------------------------------------------
-@pytest.mark.parametrize("t", [Q4_K, Q6_K])
+@pytest.mark.parametrize("t", [Q4_K, Q6_K, Q5_K])
 @pytest.mark.parametrize("in_dim", [256, 2048, 8192])
 def test_k_gemm_matches_dequantize_reference(t, in_dim):
     out_dim, n_tokens = 5, 7
