@@ -29,7 +29,8 @@ extern "C" {
 #pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
 #endif
 
-#define OB_ABI_VERSION 1u
+/* 2: ob_model_desc gained rope_freqs (layout change); the GGUF, static-attention and KV-copy entry points were added. */
+#define OB_ABI_VERSION 2u
 
 typedef enum ob_status {
     OB_OK = 0,

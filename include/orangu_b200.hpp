@@ -26,9 +26,16 @@ struct QuantMatrix {
     uint32_t ggml_type = 0;
     uint32_t in_dim = 0;   // dims[0], contiguous
     uint32_t out_dim = 0;  // dims[1]
+    // block_layout (engine/quant.rs:132-169): elements and bytes per block of the types this backend takes
     uint64_t row_bytes() const {
-        const uint32_t be = ggml_type == OB_TYPE_Q8_0 ? 32 : 256;
-        const uint32_t bb = ggml_type == OB_TYPE_Q8_0 ? 34 : (ggml_type == OB_TYPE_Q4_K ? 144 : 210);
+        uint32_t be = 256, bb = 210;  // Q6_K
+        switch (ggml_type) {
+        case OB_TYPE_Q8_0: be = 32; bb = 34; break;
+        case OB_TYPE_Q4_0: case OB_TYPE_IQ4_NL: be = 32; bb = 18; break;
+        case OB_TYPE_Q5_0: be = 32; bb = 22; break;
+        case OB_TYPE_Q4_K: be = 256; bb = 144; break;
+        default: break;
+        }
         return (uint64_t)(in_dim / be) * bb;
     }
     // loader.rs:627-646

@@ -138,11 +138,8 @@ void launch_quantize(int source, const QuantArgs &a, cudaStream_t st) {
     case ACT_PLAIN: quantize_kernel<ACT_PLAIN><<<a.n_rows, QT, 0, st>>>(a); break;
     case ACT_RMSNORM: {
         const size_t smem = ((size_t)a.dim + a.dim / 16 + 16) * 4;
-        static bool configured = false;
-        if (!configured) {
-            cudaFuncSetAttribute(quantize_kernel<ACT_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-            configured = true;
-        }
+        static PerDeviceOnce once;
+        if (once.run([] { return cudaFuncSetAttribute(quantize_kernel<ACT_RMSNORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); }) != cudaSuccess) return;
         quantize_kernel<ACT_RMSNORM><<<a.n_rows, QT, smem, st>>>(a);
         break;
     }

@@ -287,12 +287,9 @@ __global__ void attn_generic_kernel(AttnDecodeArgs a) {
 
 template <int HD, int G>
 void launch_fast(const AttnDecodeArgs &a, cudaStream_t st) {
-    static bool configured = false;
+    static PerDeviceOnce once;  // one per instantiation
     const size_t smem = sizeof(AttnSmem<HD, G>);
-    if (!configured) {
-        cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured = true;
-    }
+    if (once.run([] { return cudaFuncSetAttribute(attn_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnSmem<HD, G>)); }) != cudaSuccess) return;
     dim3 grid(a.n_splits, a.n_head_kv, a.n_seq);
     attn_decode_kernel<HD, G><<<grid, AT_THREADS, smem, st>>>(a);
     attn_merge_kernel<<<dim3(a.n_head, a.n_seq), HD, 0, st>>>(a);
@@ -328,19 +325,6 @@ bool launch_hd(const AttnDecodeArgs &a, uint32_t group, cudaStream_t st) {
 // start from int8 without another launch.
 // ====================================================================================================
 
-#ifdef OB_ATTN_PROF
-__device__ unsigned long long g_attn_prof[4096 * 8];
-#define AF_STAMP(i)                                                                                      \
-    do {                                                                                                 \
-        if (threadIdx.x == 0) {                                                                          \
-            unsigned long long t;                                                                        \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));                                        \
-            g_attn_prof[((blockIdx.y * gridDim.x + blockIdx.x) % 4096) * 8 + (i)] = t;                    \
-        }                                                                                                \
-    } while (0)
-#else
-#define AF_STAMP(i)
-#endif
 
 template <int HD, int G, int AF_WARPS>
 struct AttnFusedSmem {
@@ -394,7 +378,6 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;  // the fragment's row (group) and column pair
     const uint32_t head0 = kvh * G;
-    AF_STAMP(0);
 
     // ---- before the grid dependency: everything that the predecessor (which appends this token's K and V and writes q)
     // does not produce -- the window, the page table and all pages but the one the new token lands in
@@ -432,16 +415,13 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
-    AF_STAMP(1);
     if (pg < page_end && defer0) stage_page(pg, 0);
     __pipeline_commit();
     if (pg + AF_WARPS < page_end && defer1) stage_page(pg + AF_WARPS, 1);
     __pipeline_commit();
-    AF_STAMP(2);
 
     for (int i = tid; i < G * HD; i += THREADS) sm.q[i / HD][i % HD] = __ldcg(a.q + (uint64_t)seq * a.n_head * HD + (uint64_t)head0 * HD + i);
     __syncthreads();
-    AF_STAMP(3);
 
     // A fragments of q: row gid holds the rounded q of head gid, row gid + 4 (or + 8) its remainder
     const int my_head = LO8 ? gid : (gid & 3);
@@ -555,7 +535,6 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
         __pipeline_commit();
     }
     __pipeline_wait_prior(0);
-    AF_STAMP(4);
 
     // ---- the warps' partials meet in shared memory (rounded-row part + remainder-row part)
 #pragma unroll
@@ -596,7 +575,6 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
         }
     }
     // ---- who is last for this (sequence, kv head)?
-    AF_STAMP(5);
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -605,7 +583,6 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
         if (sm.is_last) a.counters[seq * a.n_head_kv + kvh] = 0;  // ready for the next launch
     }
     __syncthreads();
-    AF_STAMP(6);
     if (!sm.is_last) return;
     __threadfence();
 
@@ -721,17 +698,15 @@ __global__ void __launch_bounds__(AF_WARPS * 32) attn_decode_fused_kernel(AttnDe
             }
         }
     }
-    AF_STAMP(7);
 }
 
 template <int HD, int G, int W>
 bool launch_fused_warps(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
-    static bool configured = false;
+    static PerDeviceOnce once;  // one per instantiation
     const size_t smem = sizeof(AttnFusedSmem<HD, G, W>);
-    if (!configured) {
-        cudaFuncSetAttribute(attn_decode_fused_kernel<HD, G, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        configured = true;
-    }
+    if (once.run([] { return cudaFuncSetAttribute(attn_decode_fused_kernel<HD, G, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(AttnFusedSmem<HD, G, W>)); }) !=
+        cudaSuccess)
+        return false;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(a.n_splits, a.n_head_kv, a.n_seq);
     cfg.blockDim = dim3(W * 32);
@@ -766,11 +741,6 @@ void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st) {
     if (!done) attn_generic_kernel<<<dim3(a.n_head, a.n_seq), 32, 0, st>>>(a);
 }
 
-#ifdef OB_ATTN_PROF
-extern "C" __attribute__((visibility("default"))) int ob_debug_attn_prof(unsigned long long *dst, size_t n) {
-    return (int)cudaMemcpyFromSymbol(dst, g_attn_prof, n * sizeof(unsigned long long));
-}
-#endif
 
 bool launch_attn_decode_fused(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st) {
     if (a.n_seq == 0) return true;

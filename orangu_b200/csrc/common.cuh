@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 
 namespace ob {
@@ -22,6 +23,28 @@ constexpr uint32_t TYPE_F32 = 0, TYPE_Q8_0 = 8, TYPE_Q4_K = 12, TYPE_Q6_K = 14;
 constexpr uint32_t TYPE_Q4_0 = 2, TYPE_Q5_0 = 6, TYPE_IQ4_NL = 20;
 __host__ __device__ inline bool is_sym32_source(uint32_t t) { return t == TYPE_Q4_0 || t == TYPE_Q5_0 || t == TYPE_IQ4_NL; }
 constexpr int KV_PAGE = 16;  // tokens per KV page
+
+// ---- one-time kernel set-up, per device ---------------------------------------------
+// cudaFuncSetAttribute applies to the device that is current when it is called, and one process may hold
+// contexts on several GPUs, so "configured" is a bit per device ordinal, not one flag.  Holds its own lock:
+// contexts on the same GPU may launch from different threads.
+struct PerDeviceOnce {
+    std::mutex mu;
+    uint64_t done[4] = {0, 0, 0, 0};  // device ordinals 0..255
+    template <class F>
+    cudaError_t run(F &&configure) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        std::lock_guard<std::mutex> g(mu);
+        uint64_t &word = done[(dev >> 6) & 3];
+        const uint64_t bit = 1ull << (dev & 63);
+        if (word & bit) return cudaSuccess;
+        e = configure();
+        if (e == cudaSuccess) word |= bit;
+        return e;
+    }
+};
 
 // ---- device helpers ----------------------------------------------------------------
 

@@ -317,12 +317,9 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
 
 template <uint32_t TYPE, bool GEMM, int NT>
 void launch_mma_instance(const GemvArgs &a, uint32_t tiles, cudaStream_t st) {
-    static bool configured = false;
+    static PerDeviceOnce once;  // one per instantiation
     constexpr uint32_t smem = 2 * MmStage<TYPE, NT>::BYTES;
-    if (!configured) {
-        cudaFuncSetAttribute(gemm_mma_kernel<TYPE, GEMM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
-    }
+    if (once.run([] { return cudaFuncSetAttribute(gemm_mma_kernel<TYPE, GEMM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); }) != cudaSuccess) return;
     const dim3 grid(tiles, (a.n_tokens + 8 * NT - 1) / (8 * NT));
     gemm_mma_kernel<TYPE, GEMM, NT><<<grid, MM_WARPS * 32, smem, st>>>(a);
 }

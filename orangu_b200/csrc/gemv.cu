@@ -361,11 +361,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(GemvArgs a, uint3
 
 template <uint32_t TYPE, int T, bool GEMM>
 void launch_tile(const GemvArgs &a, int grid, size_t smem, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(gemv_kernel<TYPE, T, GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        configured = true;
-    }
+    static PerDeviceOnce once;  // one per instantiation
+    if (once.run([] { return cudaFuncSetAttribute(gemv_kernel<TYPE, T, GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess) return;
     for (uint32_t tok0 = 0; tok0 < a.n_tokens; tok0 += T) gemv_kernel<TYPE, T, GEMM><<<grid, GEMV_THREADS, smem, st>>>(a, tok0);
 }
 

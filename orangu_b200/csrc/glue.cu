@@ -150,11 +150,8 @@ __global__ void repeat_penalty_kernel(float *logits, uint32_t n_vocab, const uin
 
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st) {
     if (!n_tokens) return;
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    if (once.run([] { return cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); }) != cudaSuccess) return;
     rmsnorm_kernel<<<n_tokens, 512, ((size_t)dim + dim / 16 + 16) * 4, st>>>(x, w, dim, eps, out);
 }
 void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st) {

@@ -86,6 +86,7 @@ struct ob_model {
     float *scores = nullptr;          // exact-order attention scratch [T][n_head_l][score_stride]
     uint32_t score_stride = 0, exact_attn_max_pos = 0;
     uint32_t max_splits = 1;
+    size_t row_splits_cap = 0;  // (row, split) pairs part_o / part_ml hold
     uint8_t *d_meta = nullptr, *h_meta = nullptr;
     uint32_t *d_out_tokens = nullptr, *h_out_tokens = nullptr;
     unsigned long long *argmax_scratch = nullptr;
@@ -99,6 +100,7 @@ struct ob_model {
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
     bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
+    bool comm_failed = false;    // a collective could not be enqueued during the last step (reported by check_peer)
 };
 
 struct ob_kv {
@@ -354,7 +356,9 @@ bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
                 }
             }
             fused.n_splits = std::max(1u, std::min(m->max_splits, best));
+            while (fused.n_splits > 1 && (size_t)T * fused.n_splits > m->row_splits_cap) --fused.n_splits;  // never past the partial buffers
         }
+        while (at.n_splits > 1 && (size_t)T * at.n_splits > m->row_splits_cap) --at.n_splits;
         if (m->use_fused_attn && launch_attn_decode_fused(fused, true, st)) {
             m->ctx->launches += 1;
             return image != nullptr && (m->n_head_l / m->n_head_kv_l * hd) % 256 == 0;
@@ -409,7 +413,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
                 launch_norm_quant_consume(m->x, L.ffn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
             } else {
                 if (tp) {
-                    obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
+                    if (!obtp::all_reduce_sum(m->comm, m->proj, n_embd, st)) m->comm_failed = true;
                     launch_add(m->x, m->proj, n_embd, st);
                     m->ctx->launches += 2;
                 }
@@ -420,7 +424,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             if (peer) {
                 pending_exchange = true;  // completed by the next norm kernel
             } else if (tp) {
-                obtp::all_reduce_sum(m->comm, m->proj, n_embd, st);
+                if (!obtp::all_reduce_sum(m->comm, m->proj, n_embd, st)) m->comm_failed = true;
                 launch_add(m->x, m->proj, n_embd, st);
                 m->ctx->launches += 2;
             }
@@ -459,7 +463,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             run_products(m, m->act_attn, {{L.wo, m->x, n_embd, m->x}}, T, gemm_order, st);
         } else {
             run_products(m, m->act_attn, {{L.wo, m->proj, n_embd, nullptr}}, T, gemm_order, st);
-            obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st);
+            if (!obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st)) m->comm_failed = true;
             launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
             m->ctx->launches += 2;
         }
@@ -471,7 +475,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             run_products(m, m->act_ff, {{L.down, m->x, n_embd, m->x}}, T, gemm_order, st);
         } else {
             run_products(m, m->act_ff, {{L.down, m->proj, n_embd, nullptr}}, T, gemm_order, st);
-            obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st);
+            if (!obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st)) m->comm_failed = true;
             launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
             m->ctx->launches += 2;
         }
@@ -485,7 +489,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
         m->ctx->launches += 2;
         if (tp) {
-            obtp::all_gather_logits(m->comm, m->logits, 1, c.n_vocab, m->vocab0, m->vocab_l, st);
+            if (!obtp::all_gather_logits(m->comm, m->logits, 1, c.n_vocab, m->vocab0, m->vocab_l, st)) m->comm_failed = true;
             m->ctx->launches++;
         }
         if (want_argmax) {
@@ -509,7 +513,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         // Always the single-token kernel: forward() projects one row (llama.rs:1026-1030).
         run_products(m, m->act_embd, {{m->output, m->logits + m->vocab0, c.n_vocab, nullptr}}, n_logit_rows, false, st);
         if (tp) {
-            obtp::all_gather_logits(m->comm, m->logits, n_logit_rows, c.n_vocab, m->vocab0, m->vocab_l, st);
+            if (!obtp::all_gather_logits(m->comm, m->logits, n_logit_rows, c.n_vocab, m->vocab0, m->vocab_l, st)) m->comm_failed = true;
             m->ctx->launches++;
         }
         if (want_argmax) {
@@ -689,8 +693,10 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     if ((rc = alloc_act(m, &m->act_attn, T, q_dim))) return bail(rc);
     if ((rc = alloc_act(m, &m->act_ff, T, m->n_ff_l))) return bail(rc);
     m->max_splits = std::max(1u, std::min(64u, (m->cfg.max_seq_len + 63) / 64));
-    {   // rows * pick_splits(rows) never exceeds 4 * SMs + rows
-        const size_t row_splits = (size_t)4 * ctx->sm_count + T;
+    {   // rows * pick_splits(rows) never exceeds 4 * SMs + rows; the fused kernel's own rule (run_attention) takes up to
+        // four splits per row however many rows there are
+        const size_t row_splits = std::max((size_t)4 * ctx->sm_count + T, (size_t)4 * T);
+        m->row_splits_cap = row_splits;
         if ((rc = dev_alloc(m, &m->part_o, row_splits * m->n_head_l * hd))) return bail(rc);
         if ((rc = dev_alloc(m, &m->part_ml, row_splits * m->n_head_l * 2))) return bail(rc);
         if ((rc = dev_alloc(m, &m->attn_counters, (size_t)T * m->n_head_kv_l))) return bail(rc);
@@ -1085,6 +1091,10 @@ namespace {
 
 // After a synchronisation: did a peer exchange of the tensor-parallel step run out of time?
 int check_peer(ob_model *m) {
+    if (m->comm_failed) {
+        m->comm_failed = false;
+        return fail(m->ctx, OB_ERR_COMM, std::string("tensor-parallel collective failed: ") + obtp::last_error(m->comm));
+    }
     if (m->px.size < 2) return OB_OK;
     uint32_t e = 0;
     if (cudaMemcpy(&e, m->px.err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(m->ctx, OB_ERR_CUDA, "reading the exchange status failed");

@@ -306,22 +306,6 @@ __device__ __forceinline__ void dot_half_q6k(uint32_t blk0, uint32_t blk1, uint3
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
-#ifdef OB_SG_PROF
-__device__ unsigned long long g_sg_prof[8][512 * 8];  // [kernel tag][cta][stamp]
-#define SG_STAMP(i)                                                                          \
-    do {                                                                                     \
-        if (threadIdx.x == 0 && blockIdx.x < 512) {                                          \
-            unsigned long long t;                                                            \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));                            \
-            g_sg_prof[a.n_seg == 3 ? 1 : (a.in_dim > 8192 ? 4 : (a.seg[0].w2.data ? 3 : (a.seg[0].epilogue == SG_EP_RESIDUAL ? 2 : 5)))][blockIdx.x * 8 + (i)] = t; \
-        }                                                                                    \
-    } while (0)
-extern "C" __attribute__((visibility("default"))) int ob_debug_sg_prof(unsigned long long *dst, size_t n) {
-    return (int)cudaMemcpyFromSymbol(dst, g_sg_prof, n * sizeof(unsigned long long));
-}
-#else
-#define SG_STAMP(i)
-#endif
 template <int LP, bool Q6>  // LP: lanes (= blocks per unit) of a row pair; Q6: the launch has Q6_K segments (three warps, larger slots)
 __global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
@@ -330,7 +314,6 @@ __global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamAr
     constexpr uint32_t SLOT = 2u * PPU * (Q6 ? PB6 : PB4);
     const SgSmem L = sg_smem(a.in_dim, Q6, LP);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    SG_STAMP(0);
     const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t terms = sbase + L.off_terms + warp * 128;
     const uint32_t slots = sbase + L.off_ring + warp * 2 * SLOT;
@@ -427,12 +410,10 @@ __global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamAr
     advance(ig, ic);
 
     // ---- prologue ---------------------------------------------------------------------------------------------
-    SG_STAMP(1);
     if (a.wait_dependency) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the successor may start requesting its weights
         asm volatile("griddepcontrol.wait;" ::: "memory");               // the predecessor's output is complete and visible
     }
-    SG_STAMP(2);
     const uint32_t xk = a.px.size > 1 ? *reinterpret_cast<const volatile uint32_t *>(a.px.seq) : 0u;  // number of this exchange
     if (a.prologue == SG_PRO_READY) {  // the producer left the image in global memory
         const uint32_t n16 = (L.off_terms - L.off_act) / 16;
@@ -453,7 +434,6 @@ __global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamAr
         quantize_image(a.x, norm ? a.norm_w : nullptr, norm ? *a.norm_scale : 1.0f, nb, smem + L.off_act, warp, NW);
     }
     __syncthreads();
-    SG_STAMP(3);
 
     // ---- main loop ------------------------------------------------------------------------------------------------
     float tot = 0.0f;  // lanes 2j, 2j+1: rows A, B of the group's pair j, running over the chunks of the row
@@ -621,7 +601,6 @@ __global__ void __launch_bounds__(Q6 ? 192 : 256, 2) stream_gemv_kernel(StreamAr
             }
         }
     }
-    SG_STAMP(4);
 }
 
 // 1 / sqrt(mean(x^2) + eps) with the squares added left to right (engine/tensor.rs:743-745), one CTA.  With `image` set the
@@ -768,11 +747,8 @@ size_t act_image_bytes(uint32_t dim) { return act_image(dim / 256).bytes; }
 
 void launch_norm_quant_consume(float *x, const float *norm_w, uint32_t dim, float eps, float *scale_out, uint8_t *image, const obtp::PeerXchg &px,
                                bool programmatic, cudaStream_t st) {
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(norm_scale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        configured = true;
-    }
+    static PerDeviceOnce once;
+    if (once.run([] { return cudaFuncSetAttribute(norm_scale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); }) != cudaSuccess) return;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(NS_THREADS);
@@ -810,11 +786,8 @@ void launch_quant_image(const float *x, uint32_t dim, uint8_t *image, bool progr
 
 template <int LP, bool Q6>
 void launch_instance(const cudaLaunchConfig_t &cfg, const StreamArgs &args) {
-    static bool configured = false;  // one flag per instantiation
-    if (!configured) {
-        cudaFuncSetAttribute(stream_gemv_kernel<LP, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, SG_MAX_SMEM);
-        configured = true;
-    }
+    static PerDeviceOnce once;  // one per instantiation
+    if (once.run([] { return cudaFuncSetAttribute(stream_gemv_kernel<LP, Q6>, cudaFuncAttributeMaxDynamicSharedMemorySize, SG_MAX_SMEM); }) != cudaSuccess) return;
     cudaLaunchKernelEx(&cfg, stream_gemv_kernel<LP, Q6>, args);
 }
 

@@ -33,7 +33,7 @@ def test_header_and_binding_agree(lib):
 
 
 def test_constants_without_a_device(lib):
-    assert lib.ob_abi_version() == 1
+    assert lib.ob_abi_version() == 2
     assert [lib.ob_supports_type(t) for t in (0, 8, 12, 14, 2, 6, 20)] == [1, 1, 1, 1, 1, 1, 1]
     assert [lib.ob_supports_type(t) for t in (1, 3, 7, 10, 13, 30)] == [0, 0, 0, 0, 0, 0]
     assert lib.ob_reduced_surface() is None
@@ -72,3 +72,91 @@ def test_cpp_host_wrapper_compiles():
         open(src, "w").write('#include "orangu_b200.hpp"\nint main(){ return orangu::CudaBackend::try_init_index(0) ? 0 : 0; }\n')
         r = subprocess.run(["/usr/bin/g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), src], capture_output=True, text=True)
         assert r.returncode == 0, r.stderr
+
+
+def _compile_and_run(source: str, extra=(), run=True):
+    import subprocess, tempfile
+
+    from orangu_b200 import capi
+
+    with tempfile.TemporaryDirectory() as d:
+        src, exe = os.path.join(d, "t.cpp"), os.path.join(d, "t")
+        open(src, "w").write(source)
+        libdir = os.path.dirname(capi.lib_path())
+        cmd = ["/usr/bin/g++", "-std=c++17", "-O1", "-I", os.path.join(ROOT, "include"), src, "-o", exe, *extra]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        if not run:
+            return ""
+        r = subprocess.run([exe], capture_output=True, text=True, env={**os.environ, "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", "")})
+        assert r.returncode == 0, r.stdout + r.stderr
+        return r.stdout
+
+
+def test_struct_layouts_agree_between_header_binding_and_integration_notes(lib):
+    """sizeof / offsetof as the C compiler sees the header == the ctypes binding == the figures INTEGRATION.md quotes for
+    the Rust #[repr(C)] structs (a binding that is one field short hands the library a truncated struct)."""
+    from orangu_b200 import capi
+
+    out = _compile_and_run(
+        '#include <cstdio>\n#include <cstddef>\n#include "orangu_b200.h"\n'
+        'int main(){ std::printf("%zu %zu %zu %zu %zu %zu %u\\n", sizeof(ob_model_desc), sizeof(ob_layer_desc), sizeof(ob_matrix_desc),'
+        ' offsetof(ob_model_desc, rope_freqs), sizeof(ob_greedy), sizeof(ob_gguf_tensor_info), OB_ABI_VERSION); }\n')
+    model, layer, matrix, off_rope, greedy, tinfo, abi = (int(v) for v in out.split())
+    assert (model, layer, matrix, off_rope) == (C.sizeof(capi.ModelDesc), C.sizeof(capi.LayerDesc), C.sizeof(capi.MatrixDesc), capi.ModelDesc.rope_freqs.offset)
+    assert greedy == C.sizeof(capi.Greedy) and tinfo == C.sizeof(capi.GgufTensorInfo)
+    assert abi == lib.ob_abi_version()
+    notes = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    quoted = re.search(r"size_of::<ob_model_desc>\(\) == (\d+).*?size_of::<ob_layer_desc>\(\) == (\d+).*?OB_ABI_VERSION: u32 = (\d+)", notes, flags=re.S)
+    assert quoted, "INTEGRATION.md must quote the struct sizes its Rust binding is checked against"
+    assert tuple(int(v) for v in quoted.groups()) == (model, layer, abi)
+    # every field of the C struct appears in the written Rust struct
+    rust = notes[notes.index("pub struct ob_model_desc"):]
+    rust = rust[:rust.index("}")]
+    for name, _ in capi.ModelDesc._fields_:
+        assert f"pub {name}:" in rust, f"INTEGRATION.md's ob_model_desc lacks {name}"
+    header = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "orangu_b200.h")).read(), flags=re.S)
+    for name in declared_symbols():
+        assert f"pub fn {name}(" in notes, f"INTEGRATION.md does not declare {name}"
+    assert header
+
+
+def test_row_bytes_of_the_cpp_wrapper_for_every_type():
+    out = _compile_and_run(
+        '#include <cstdio>\n#include "orangu_b200.hpp"\n'
+        'int main(){ for (unsigned t : {8u, 12u, 14u, 2u, 6u, 20u}) { orangu::QuantMatrix m{nullptr, t, 4096, 3}; std::printf("%llu ", (unsigned long long)m.row_bytes()); } }\n',
+        extra=["-L", os.path.dirname(__import__("orangu_b200").capi.lib_path()), "-lorangu_b200"])
+    assert [int(v) for v in out.split()] == [4096 // 32 * 34, 4096 // 256 * 144, 4096 // 256 * 210, 4096 // 32 * 18, 4096 // 32 * 22, 4096 // 32 * 18]
+
+
+@pytest.mark.gpu
+def test_cpp_host_wrapper_runs_a_matmul_on_the_gpu():
+    """The C++ mirror of the Backend trait, compiled and run: one Q4_0 and one Q4_K product through the class equal the
+    oracle's (the Q4_0 row size is what the wrapper once got wrong)."""
+    import numpy as np
+
+    import oracle as O
+    from orangu_b200 import capi, synth
+
+    out_dim, in_dim = 6, 512
+    cases = []
+    with __import__("tempfile").TemporaryDirectory() as d:
+        for t in (2, 12):
+            raw = synth.matrix(t, out_dim, in_dim, 5 + t)["data"]
+            x = synth.normal(in_dim, 9 + t)
+            raw.tofile(os.path.join(d, f"w{t}.bin"))
+            x.tofile(os.path.join(d, f"x{t}.bin"))
+            cases.append((t, raw, x))
+        src = (
+            '#include <cstdio>\n#include <vector>\n#include <fstream>\n#include <iterator>\n#include "orangu_b200.hpp"\n'
+            'static std::vector<char> rd(const std::string &p){ std::ifstream f(p, std::ios::binary); return {std::istreambuf_iterator<char>(f), {}}; }\n'
+            'int main(int, char **argv){ std::string d = "%s"; auto be = orangu::CudaBackend::try_init_index(0); if (!be) return 3;\n'
+            ' for (unsigned t : {2u, 12u}) { auto w = rd(d + "/w" + std::to_string(t) + ".bin"); auto x = rd(d + "/x" + std::to_string(t) + ".bin");\n'
+            '  orangu::QuantMatrix m{reinterpret_cast<const uint8_t *>(w.data()), t, %du, %du}; if (m.row_bytes() * m.out_dim != w.size()) return 4;\n'
+            '  auto y = be->matmul(reinterpret_cast<const float *>(x.data()), 1, m); std::ofstream o(d + "/y" + std::to_string(t) + ".bin", std::ios::binary);\n'
+            '  o.write(reinterpret_cast<const char *>(y.data()), y.size() * 4); }\n return 0; }\n' % (d, in_dim, out_dim))
+        _compile_and_run(src, extra=["-L", os.path.dirname(capi.lib_path()), "-lorangu_b200"])
+        for t, raw, x in cases:
+            got = np.fromfile(os.path.join(d, f"y{t}.bin"), dtype=np.float32)
+            want = O.matmul(x, 1, raw, t, in_dim, out_dim)
+            assert (got.view(np.uint32) == want.view(np.uint32)).all()

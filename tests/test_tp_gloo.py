@@ -25,7 +25,8 @@ def rank_main(rank, world, port, results):
     import torch.distributed as dist
 
     import oracle as O
-    from orangu_b200 import synth, tp_shard
+    from orangu_b200 import synth
+    import tp_shard
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -105,7 +106,8 @@ def test_two_ranks_reproduce_the_single_process_products():
 
 
 def test_plan_rejects_shapes_that_do_not_split():
-    from orangu_b200 import synth, tp_shard
+    from orangu_b200 import synth
+    import tp_shard
 
     with pytest.raises(ValueError):
         tp_shard.plan(dict(synth.CONFIGS["tiny"]), 2, 0)  # 2 heads x 64 per rank is not a multiple of 256
