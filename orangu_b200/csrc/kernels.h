@@ -108,6 +108,31 @@ void launch_norm_quant_consume(float *x, const float *norm_w, uint32_t dim, floa
 // x quantized per 256 into `image`.
 void launch_quant_image(const float *x, uint32_t dim, uint8_t *image, bool programmatic, cudaStream_t st);
 
+// ---- layer_stream.cu: the single-token products between two attention kernels as phases of one persistent launch
+struct alignas(16) LsPhase {
+    StreamArgs a;        // as for launch_stream_gemv; prologue SG_PRO_READY, or SG_PRO_RMSNORM (x: the fp32 row; the exact scale is computed by the phase)
+    uint32_t lp;         // lanes per row pair (kernel shape of this phase)
+    uint32_t q6;         // the phase has Q6_K segments
+    uint32_t nw;         // warps of the CTA that take part in the product
+    uint32_t l2_ahead;   // units per warp sent to L2 ahead of the ring while the prologue runs
+};
+struct LsLayout {  // byte offsets inside the kernel's dynamic shared memory
+    uint32_t off_desc;   // two phase descriptors (ping-pong)
+    uint32_t off_tab;    // two segment tables (ping-pong)
+    uint32_t off_ctrl;   // control words
+    uint32_t off_img;    // the activation image of the running phase
+    uint32_t off_norm;   // RMSNorm prologue: the fp32 row (one pad word per 16) and the exact-sum workspace
+    uint32_t off_terms;  // [warp][32] fp32 terms
+    uint32_t off_ring;   // per-warp two-slot weight ring
+    uint32_t total;
+};
+bool layer_stream_phase(const StreamArgs &a, LsPhase *out);              // false: the shape does not take this kernel
+LsLayout layer_stream_layout(const LsPhase *phases, uint32_t n);         // host copy of the phases
+bool layer_stream_fits(const LsLayout &L);
+// barrier: one zeroed word per launch; status: set to 1 when a barrier wait gave up after timeout_ms
+bool launch_layer_stream(const LsPhase *dev_phases, uint32_t n, const LsLayout &L, int sm_count, uint32_t *barrier, uint32_t *status, uint32_t timeout_ms,
+                         bool programmatic, cudaStream_t st);
+
 // ---- glue.cu
 void launch_rmsnorm(const float *x, const float *w, uint32_t n_tokens, uint32_t dim, float eps, float *out, cudaStream_t st);
 void launch_swiglu(const float *gate, const float *up, uint64_t n, float *out, cudaStream_t st);

@@ -101,6 +101,19 @@ struct ob_model {
     bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
     bool comm_failed = false;    // a collective could not be enqueued during the last step (reported by check_peer)
+    // Persistent layer kernel (layer_stream.cu): the single-token products between two attention kernels as one launch.
+    // Phase list: [q/k/v of layer 0] then per layer [attention-output, gate/up, down, q/k/v of the next layer | output projection].
+    bool use_persist = true;     // OB_PERSIST=0 keeps one launch per product
+    bool persist_ok = false;
+    bool launch_failed = false;  // a launch of the persistent kernel was refused (reported after the step)
+    std::vector<LsPhase> h_phases;
+    LsPhase *d_phases = nullptr;
+    LsLayout ls_layout{};
+    uint32_t *ls_barriers = nullptr;  // one word per launch of a step, zeroed when the step starts
+    uint32_t *ls_status = nullptr;    // set by the kernel when a barrier wait ran out of time
+    uint32_t *h_ls_status = nullptr;  // pinned host copy, fetched with every step's results
+    uint32_t ls_timeout_ms = 2000;
+    bool ls_split = false;            // OB_LS_SPLIT=1: every phase is its own launch
 };
 
 struct ob_kv {
@@ -215,6 +228,12 @@ void quantize_into(ob_model *m, int source, const float *x, const float *aux, ui
 }
 
 int check_peer(ob_model *m);
+// Before the synchronisation that ends a step: the persistent kernel's status word comes down with the results.
+inline void fetch_status(ob_model *m, cudaStream_t st) {
+    if (m->persist_ok) cudaMemcpyAsync(m->h_ls_status, m->ls_status, 4, cudaMemcpyDeviceToHost, st);
+}
+int build_persistent_phases(ob_model *m);
+StreamArgs stream_args(const ob_model *m, uint32_t li, int which);
 
 uint32_t pick_splits(const ob_model *m, uint32_t n_rows) {
     const uint32_t pairs = std::max(1u, n_rows * m->n_head_kv_l);
@@ -293,6 +312,56 @@ StreamArgs stream_args(const ob_model *m, uint32_t li, int which) {
         break;
     }
     return a;
+}
+
+// The phase list of the persistent layer kernel, when every layer's products take it and the shared memory fits.
+int build_persistent_phases(ob_model *m) {
+    const ob_model_desc &c = m->cfg;
+    auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
+    for (const LayerDev &L : m->layers)
+        if (!(k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) && k_type(L.down) && L.gate->w.type == L.up->w.type))
+            return OB_OK;
+    if (!k_type(m->output) || (c.head_dim & 1)) return OB_OK;
+    uint32_t l2_norm = 8, l2_ready = 2;  // units per warp sent to L2 ahead of the ring (OB_LS_L2_AHEAD overrides both)
+    if (const char *e = getenv("OB_LS_L2_AHEAD")) l2_norm = l2_ready = (uint32_t)atoi(e);
+    std::vector<LsPhase> ph;
+    auto add = [&](uint32_t li, int which) {
+        StreamArgs a = stream_args(m, li, which);
+        if (which == 1 || which == 3 || which == 5) {  // the norm is the phase's own prologue
+            a.prologue = SG_PRO_RMSNORM;
+            a.x = m->x;
+            a.norm_w = which == 1 ? m->layers[li].attn_norm : which == 3 ? m->layers[li].ffn_norm : m->output_norm;
+            a.ready = nullptr;
+        }
+        LsPhase d;
+        if (!layer_stream_phase(a, &d)) return false;
+        d.l2_ahead = a.prologue == SG_PRO_RMSNORM ? l2_norm : l2_ready;
+        ph.push_back(d);
+        return true;
+    };
+    bool ok = add(0, 1);
+    for (uint32_t li = 0; ok && li < c.n_layer; ++li) {
+        ok = add(li, 2) && add(li, 3) && add(li, 4);
+        if (ok) ok = li + 1 < c.n_layer ? add(li + 1, 1) : add(0, 5);
+    }
+    if (!ok) return OB_OK;
+    const LsLayout L = layer_stream_layout(ph.data(), (uint32_t)ph.size());
+    if (!layer_stream_fits(L)) return OB_OK;
+    int rc;
+    if ((rc = dev_alloc(m, &m->d_phases, ph.size()))) return rc;
+    if ((rc = dev_alloc(m, &m->ls_barriers, (size_t)c.n_layer + 2))) return rc;
+    if ((rc = dev_alloc(m, &m->ls_status, 4))) return rc;
+    OB_CUDA(m->ctx, cudaMemcpy(m->d_phases, ph.data(), ph.size() * sizeof(LsPhase), cudaMemcpyHostToDevice));
+    OB_CUDA(m->ctx, cudaMemset(m->ls_barriers, 0, ((size_t)c.n_layer + 2) * 4));
+    OB_CUDA(m->ctx, cudaMemset(m->ls_status, 0, 16));
+    OB_CUDA(m->ctx, cudaMallocHost(reinterpret_cast<void **>(&m->h_ls_status), 4));
+    *m->h_ls_status = 0;
+    if (const char *e = getenv("OB_LS_SPLIT")) m->ls_split = e[0] == '1';
+    if (const char *e = getenv("OB_LS_TIMEOUT_MS")) m->ls_timeout_ms = (uint32_t)std::max(1, atoi(e));
+    m->h_phases = std::move(ph);
+    m->ls_layout = L;
+    m->persist_ok = true;
+    return OB_OK;
 }
 
 // Returns true when `image` (the quantized output, for the single-token product kernels) has been written.
@@ -392,6 +461,46 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
     // norm / quantize as prologue, RoPE + KV append, residual and SwiGLU as epilogues, 5 product kernels per layer.
     const bool stream = T == 1 && m->use_stream && m->ready_embd;
     auto k_type = [](const ob_weight *w) { return w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K; };
+
+    // One sequence, one GPU, K-type weights throughout: the products between two attention kernels are one persistent launch
+    // (layer_stream.cu) -- a layer is that launch plus the attention kernel.
+    if (stream && m->persist_ok && n_logit_rows == 1 && logit_row0 == 0) {
+        const uint32_t n_launch = c.n_layer + 1;
+        cudaMemsetAsync(m->ls_barriers, 0, (size_t)n_launch * 4, st);
+        auto launch = [&](uint32_t first, uint32_t n, uint32_t slot, bool programmatic) {
+            if (m->ls_split) {  // one phase per launch (no grid barrier is crossed): isolates the cost of the phases
+                for (uint32_t i = 0; i < n; ++i) {
+                    if (!launch_layer_stream(m->d_phases + first + i, 1, m->ls_layout, m->ctx->sm_count, m->ls_barriers + slot, m->ls_status, m->ls_timeout_ms, programmatic, st))
+                        m->launch_failed = true;
+                    m->ctx->launches++;
+                }
+                return;
+            }
+            if (!launch_layer_stream(m->d_phases + first, n, m->ls_layout, m->ctx->sm_count, m->ls_barriers + slot, m->ls_status, m->ls_timeout_ms, programmatic, st))
+                m->launch_failed = true;
+            m->ctx->launches++;
+        };
+        launch(0, 1, 0, false);
+        for (uint32_t li = 0; li < c.n_layer; ++li) {
+            if (!run_attention(m, li, T, exact_attn, pos_bound, m->ready_attn, d_tables, d_npos, st)) {
+                launch_quant_image(m->attn, q_dim, m->ready_attn, true, st);
+                m->ctx->launches++;
+            }
+            launch(1 + 4 * li, 4, 1 + li, true);
+        }
+        if (want_argmax) {
+            ArgmaxArgs am{};
+            am.logits = m->logits;
+            am.n_seq = 1;
+            am.n_vocab = c.n_vocab;
+            am.out = m->d_out_tokens;
+            am.scratch = m->argmax_scratch;
+            launch_argmax(am, st);
+            m->ctx->launches += 3;
+        }
+        m->last_T = T;
+        return;
+    }
 
     bool pending_exchange = false;  // a peer exchange has been started and the residual stream does not hold its sum yet
     for (uint32_t li = 0; li < c.n_layer; ++li) {
@@ -555,6 +664,7 @@ void ob_model_destroy(ob_model *m) {
     for (void *p : m->owned) cudaFree(p);
     if (m->h_meta) cudaFreeHost(m->h_meta);
     if (m->h_out_tokens) cudaFreeHost(m->h_out_tokens);
+    if (m->h_ls_status) cudaFreeHost(m->h_ls_status);
     delete m;
 }
 
@@ -743,6 +853,10 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
             for (int sgi = 0; sgi < sa.n_seg; ++sgi) k_types = k_types && (sa.seg[sgi].w.type == TYPE_Q4_K || sa.seg[sgi].w.type == TYPE_Q6_K);
             if (k_types && !stream_gemv_supported(sa)) m->stream_ok = false;
         }
+    }
+    if (const char *e = getenv("OB_PERSIST")) m->use_persist = !(e[0] == '0' && e[1] == 0);
+    if (m->stream_ok && m->use_persist && tp == 1) {
+        if ((rc = build_persistent_phases(m))) return bail(rc);
     }
     *out = m;
     return OB_OK;
@@ -997,6 +1111,7 @@ int run_rows(ob_model *m, const std::vector<ob_kv *> &row_kv, const uint32_t *to
     if (out_token) OB_CUDA(ctx, cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_logit_rows * 4, cudaMemcpyDeviceToHost, st));
     if (out_logits) OB_CUDA(ctx, cudaMemcpyAsync(out_logits, m->logits, (size_t)n_logit_rows * m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, st));
     OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
+    fetch_status(m, st);
     OB_CUDA(ctx, cudaStreamSynchronize(st));
     OB_CUDA(ctx, cudaGetLastError());
     float ms = 0.0f;
@@ -1091,6 +1206,17 @@ namespace {
 
 // After a synchronisation: did a peer exchange of the tensor-parallel step run out of time?
 int check_peer(ob_model *m) {
+    if (m->launch_failed) {
+        m->launch_failed = false;
+        return fail(m->ctx, OB_ERR_CUDA, std::string("launching the persistent layer kernel failed: ") + cudaGetErrorString(cudaGetLastError()));
+    }
+    if (m->persist_ok) {
+        if (*m->h_ls_status) {  // copied down with the step's results (fetch_status)
+            *m->h_ls_status = 0;
+            cudaMemset(m->ls_status, 0, 4);
+            return fail(m->ctx, OB_ERR_CUDA, "the persistent layer kernel gave up at a grid barrier (not every CTA was resident)");
+        }
+    }
     if (m->comm_failed) {
         m->comm_failed = false;
         return fail(m->ctx, OB_ERR_COMM, std::string("tensor-parallel collective failed: ") + obtp::last_error(m->comm));
@@ -1133,6 +1259,7 @@ int get_graph(ob_model *m, uint32_t n_seq, int kind, bool exact, cudaGraphExec_t
     enqueue_step(m, n_seq, false, 0, n_seq, true, exact, pos_bound, st);
     if (kind == 0) {
         cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, st);
+        fetch_status(m, st);
     } else {
         advance_kernel<<<(n_seq + 127) / 128, 128, 0, st>>>(reinterpret_cast<uint32_t *>(m->d_meta + ml.off_tokens),
                                                              reinterpret_cast<uint32_t *>(m->d_meta + ml.off_positions),
@@ -1234,6 +1361,7 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
     for (uint32_t i = 0; i < n_steps; ++i) OB_CUDA(ctx, cudaGraphLaunch(exec, st));
     OB_CUDA(ctx, cudaEventRecord(ctx->ev1, st));
     OB_CUDA(ctx, cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * n_seq * 4, cudaMemcpyDeviceToHost, st));
+    fetch_status(m, st);
     OB_CUDA(ctx, cudaStreamSynchronize(st));
     OB_CUDA(ctx, cudaGetLastError());
     cudaEventElapsedTime(&ctx->last_ms, ctx->ev0, ctx->ev1);

@@ -128,6 +128,31 @@ def test_sweep_shape_batch_64(backend, t):
     assert_bit_equal(backend.matmul_decode(x, n, w), O.matmul_decode(x, n, w.raw, t, in_dim, out_dim), "decode batch 64")
 
 
+@pytest.mark.parametrize("t", [Q4_K, Q6_K])
+@pytest.mark.parametrize("out_dim,in_dim", [(4096, 4096), (14336, 4096), (4096, 14336)])
+def test_sweep_shapes_batch_512(backend, t, out_dim, in_dim):
+    """The sweep's largest batch on all three shapes: the prefill GEMM (two-pass order for Q4_K) and, on a slice of the
+    rows, the decode contract (every row equals the single-token kernel)."""
+    n = 512
+    w = gauss_matrix(t, out_dim, in_dim, 46)
+    x = synth.normal(n * in_dim, 47)
+    assert_bit_equal(backend.matmul(x, n, w), O.matmul(x, n, w.raw, t, in_dim, out_dim), f"prefill batch 512, type {t} [{out_dim}x{in_dim}]")
+    got = np.asarray(backend.matmul_decode(x, n, w)).reshape(n, out_dim)
+    for tok in (0, 255, 511):
+        alone = O.matmul(x[tok * in_dim:(tok + 1) * in_dim], 1, w.raw, t, in_dim, out_dim)
+        assert_bit_equal(got[tok], np.asarray(alone).reshape(-1), f"decode batch 512 row {tok}")
+
+
+@pytest.mark.parametrize("n", [64, 512])
+def test_q8_0_4096_batches_64_and_512(backend, n):
+    """Q8_0 at many tokens: the flat GEMM (engine/vecdot.rs:2598-2629) and the decode batch, kernels backend/cpu.rs:76-90 picks."""
+    out_dim = in_dim = 4096
+    w = gauss_matrix(Q8_0, out_dim, in_dim, 48)
+    x = synth.normal(n * in_dim, 49)
+    assert_bit_equal(backend.matmul(x, n, w), O.matmul(x, n, w.raw, Q8_0, in_dim, out_dim), f"Q8_0 prefill batch {n}")
+    assert_bit_equal(backend.matmul_decode(x, n, w), O.matmul_decode(x, n, w.raw, Q8_0, in_dim, out_dim), f"Q8_0 decode batch {n}")
+
+
 # ---- decode batches and prefill ---------------------------------------------------------------------
 @pytest.mark.parametrize("t", TYPES)
 @pytest.mark.parametrize("out_dim", [5, 8, 11])

@@ -257,6 +257,89 @@ def test_70b_shape_layer_is_bit_exact(backend):
         tok = O.argmax(want)
 
 
+def test_8b_shape_two_layers_bit_exact(backend):
+    """Two layers of the 8B shape with the full 14336-wide FFN: ffn_down rows are 56 super-blocks = 3.5 chunks of 16, the
+    only shape of the configurations that ends a row on a partial chunk in the single-token product kernels.  Prefill,
+    then decode steps through forward(), the captured graph and the device loop, all bit for bit."""
+    cfg = dict(synth.CONFIGS["8b"])
+    cfg["n_layer"] = 2
+    cfg["n_vocab"] = 4096
+    tensors = synth.model_tensors(cfg, seed=41)
+    model, ref = LlamaModel(backend, cfg, tensors, max_seq_len=256, max_batch_tokens=64, kv_pool_tokens=1024), O.Model(cfg, tensors)
+    toks = prompt(cfg, 70, 14)
+    kv, kv2, rkv = model.new_kv_cache(128), model.new_kv_cache(128), ref.new_kv(128, f16=True)
+    want = ref.forward(rkv, toks, 0)
+    assert_bit_equal(model.forward(kv, toks, 0), want, "prefill logits")
+    model.forward(kv2, toks, 0)
+    tok = O.argmax(want)
+    first = tok
+    ref_tokens = []
+    for step in range(6):
+        got, want = model.forward(kv, [tok], 70 + step), ref.forward(rkv, [tok], 70 + step)
+        assert_bit_equal(got, want, f"decode step {step}")
+        tok = O.argmax(want)
+        ref_tokens.append(tok)
+    assert model.decode_loop([kv2], [first], 6)[:, 0].tolist() == ref_tokens
+
+
+@pytest.mark.parametrize("n_layer", [2, 4])
+def test_8b_shape_at_context_4096_fused_flash_decode_error_is_measured(backend, n_layer, capsys):
+    """The configuration the decode throughput is quoted on: 8B shape, context past 4096, the one-kernel flash-decode
+    attention.  Teacher-forced against the oracle; the largest logit error per layer count is printed.  Flash-decode
+    differs from the CPU loop in the last bits of the attention output; every later int8 quantisation can turn such a
+    difference into a one-code difference, so on random weights the error is the int8 noise of the layers behind it, not
+    2e-2: measured 0.10 at 2 layers and 0.18 at 4 (logits of magnitude 4.5).  What is asserted is that bound (a wrong page,
+    split or merge would show as errors of the logits' own magnitude) and the same greedy token on every step."""
+    cfg = dict(synth.CONFIGS["8b"])
+    cfg["n_layer"] = n_layer
+    cfg["n_vocab"] = 4096
+    tensors = synth.model_tensors(cfg, seed=43)
+    n_ctx = 4096 + 37
+    model = LlamaModel(backend, cfg, tensors, max_seq_len=n_ctx + 32, max_batch_tokens=512, kv_pool_tokens=n_ctx + 64)
+    ref = O.Model(cfg, tensors)
+    toks = prompt(cfg, n_ctx, 15)
+    kv, rkv = model.new_kv_cache(n_ctx + 16), ref.new_kv(n_ctx + 16, f16=True)
+    got, want = model.forward(kv, toks, 0), ref.forward(rkv, toks, 0)
+    errs = [float(np.abs(got - want).max())]
+    scale = float(np.abs(want).max())
+    tok, same_top1 = O.argmax(want), 0
+    for step in range(6):
+        got, want = model.forward(kv, [tok], n_ctx + step), ref.forward(rkv, [tok], n_ctx + step)
+        errs.append(float(np.abs(got - want).max()))
+        same_top1 += int(np.argmax(got)) == O.argmax(want)
+        tok = O.argmax(want)
+    with capsys.disabled():
+        print(f"\n[8B shape, {n_layer} layers, context {n_ctx}, fused flash-decode] max-abs logit error: prefill {errs[0]:.3e}, "
+              f"decode steps {max(errs[1:]):.3e} (logit scale {scale:.2f}); greedy top-1 equal on {same_top1}/6 steps")
+    assert max(errs) < 0.15 * n_layer ** 0.5 + 0.05, errs
+    assert same_top1 == 6
+
+
+def test_flash_prefill_chunks_of_210_and_300_rows_stay_inside_the_partial_buffers(backend):
+    """Prefill chunks whose (row, kv head) pairs exceed the SM count pick their own split count (up to four per row): with
+    8 kv heads a 210-row chunk takes 4 splits = 840 (row, split) pairs and a 300-row chunk 3 = 900, which the buffers for the
+    splits' partial results have to hold.  One 8B-shape layer, windows past the exact-order bound, against the oracle."""
+    cfg = dict(synth.CONFIGS["8b"])
+    cfg["n_layer"] = 1
+    cfg["n_vocab"] = 2048
+    tensors = synth.model_tensors(cfg, seed=47)
+    model = LlamaModel(backend, cfg, tensors, max_seq_len=640, max_batch_tokens=300, kv_pool_tokens=1280, exact_attention_max_pos=16)
+    ref = O.Model(cfg, tensors)
+    toks = prompt(cfg, 40 + 210 + 300, 16)
+    kv, rkv = model.new_kv_cache(600), ref.new_kv(600, f16=True)
+    pos = 0
+    for n in (40, 210, 300):
+        got, want = model.forward(kv, toks[pos:pos + n], pos), ref.forward(rkv, toks[pos:pos + n], pos)
+        assert np.isfinite(got).all()
+        # one layer of int8 re-quantisation behind flash attention on random weights: errors up to ~0.1 on logits of
+        # magnitude 4; a damaged buffer would show as errors of the logits' own size
+        assert np.abs(got - want).max() < 0.2, (n, float(np.abs(got - want).max()))
+        pos += n
+    # one more step on the same context still computes the same thing (nothing next to the buffers was damaged)
+    got, want = model.forward(kv, [3], pos), ref.forward(rkv, [3], pos)
+    assert np.abs(got - want).max() < 0.2
+
+
 def test_large_decode_batch_takes_the_small_cta_attention_and_agrees_with_single_decodes(backend):
     """40 sequences x 8 kv heads is more than two (row, kv head) pairs per SM: the flash-decode runs as 4-warp CTAs.  Every
     sequence's logits have to agree with the same sequence decoded alone (8-warp CTAs, more splits) and with the oracle."""

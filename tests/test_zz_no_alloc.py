@@ -4,8 +4,9 @@ Some callers of this library cannot allocate device memory while they run: a slo
 of a request (cudaMalloc / cudaFree synchronise the whole device and would stall the other slots), or a server
 whose KV pool has already taken the remaining memory.  For them the split flash-decode attention exists in a
 form whose only scratch is a fixed array inside the library image.  This test calls it through the C ABI with
-caller-owned device buffers and checks it against the allocating entry point, ob_attention_decode, twice in a
-row (the array is shared between calls and keeps the previous call's contents).
+caller-owned device buffers and checks it, twice in a row (the array is shared between calls and keeps the previous
+call's contents), against two things: the CPU oracle's attention over the same fp16-rounded K and V (the values), and
+the allocating entry point, ob_attention_decode (the plumbing).
 
 Collected last on purpose (file name), so a run that stops at the first failure has already run everything else.
 It needs no state from the other tests and passes alone in a fresh process too.
@@ -34,6 +35,7 @@ def pages_from_rows(x, n_head_kv, head_dim):
 def test_static_scratch_attention_matches_the_allocating_entry_point(n_head, n_head_kv, head_dim, n_pos_pair):
     import torch
 
+    import oracle as O
     import orangu_b200
     from orangu_b200 import capi, synth
 
@@ -47,6 +49,8 @@ def test_static_scratch_attention_matches_the_allocating_entry_point(n_head, n_h
             q = synth.normal(n_head * head_dim, 300 + call)
             scale = float(1.0 / np.sqrt(head_dim))
             want = be.attention_decode(q, k, v, n_head, n_head_kv, head_dim, scale, exact_order=False)
+            f16 = lambda a: a.astype(np.float16).astype(np.float32)  # the cache holds f16 (engine/kv_cache.rs:26-32)
+            cpu = O.attention(q, f16(k), f16(v), n_head, n_head_kv, head_dim, scale, 1, n_pos - 1)[0]
 
             q_d = torch.from_numpy(q).cuda()
             k_d = torch.from_numpy(pages_from_rows(k, n_head_kv, head_dim)).cuda()
@@ -60,7 +64,8 @@ def test_static_scratch_attention_matches_the_allocating_entry_point(n_head, n_h
             be.synchronize()
             got = out_d.cpu().numpy()
             assert np.isfinite(got).all()
-            assert np.abs(got - want).max() < TOL, f"call {call}, {n_pos} positions"
+            assert np.abs(got - cpu).max() < TOL, f"call {call}, {n_pos} positions: differs from the CPU oracle"
+            assert np.abs(got - want).max() < TOL, f"call {call}, {n_pos} positions: differs from ob_attention_decode"
     finally:
         be.close()
 
