@@ -103,7 +103,7 @@ struct ob_model {
     bool comm_failed = false;    // a collective could not be enqueued during the last step (reported by check_peer)
     // Persistent layer kernel (layer_stream.cu): the single-token products between two attention kernels as one launch.
     // Phase list: [q/k/v of layer 0] then per layer [attention-output, gate/up, down, q/k/v of the next layer | output projection].
-    bool use_persist = true;     // OB_PERSIST=0 keeps one launch per product
+    bool use_persist = false;    // OB_PERSIST=1; measured slower than one launch per product (barrier waits and the synchronous norm outweigh the launches saved)
     bool persist_ok = false;
     bool launch_failed = false;  // a launch of the persistent kernel was refused (reported after the step)
     std::vector<LsPhase> h_phases;
@@ -854,7 +854,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
             if (k_types && !stream_gemv_supported(sa)) m->stream_ok = false;
         }
     }
-    if (const char *e = getenv("OB_PERSIST")) m->use_persist = !(e[0] == '0' && e[1] == 0);
+    if (const char *e = getenv("OB_PERSIST")) m->use_persist = e[0] == '1' && e[1] == 0;
     if (m->stream_ok && m->use_persist && tp == 1) {
         if ((rc = build_persistent_phases(m))) return bail(rc);
     }

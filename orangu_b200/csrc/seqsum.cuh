@@ -132,32 +132,53 @@ __device__ float warp_sequential_sum(F term, uint32_t n) {
 // ----------------------------------------------------------------------------------------------------
 // The same sum by a whole CTA, with the sequential part reduced to a few dozen steps.
 //
-// The binade of every partial sum is known in advance, up to a rigorous margin: with E_i the exact prefix
-// sum (taken in double), the sequentially rounded s_i satisfies |s_i - E_i| <= i * 2^-24 * s_i.  A term whose
-// two neighbouring partial sums are, with that margin, inside one binade is "safe": its increment function
-// can be formed without knowing S.  All safe functions are formed in parallel; a thread whose terms are all
-// safe composes them; runs of such threads are composed by a segmented warp scan; and only the threads that
-// hold an unsafe term (the start of the sum and the ~log2(n) binade crossings) are added with real float
-// additions, one after the other.  Every application checks that s really is in the assumed binade; if that
-// ever failed the warp-level routine above recomputes the sum from scratch.
+// The binade of every partial sum is known in advance, up to a rigorous margin: with E_i the exact prefix sum, the
+// sequentially rounded s_i satisfies |s_i - E_i| <= i * 2^-24 * s_i; E_i itself is taken from an fp32 scan (a few dozen
+// additions of non-negative values: relative error below 4e-6, which the margin includes).  A thread whose partial
+// sums are, with that margin, inside one binade is "safe": its terms' increment functions can be formed without
+// knowing S.  All safe functions are formed in parallel; a thread whose terms are all safe composes them; runs of such
+// threads are composed by a segmented warp scan; and only the threads that hold an unsafe term (the start of the sum
+// and the ~log2(n) binade crossings) are added with real float additions, one after the other.  Every application
+// checks that s really is in the assumed binade -- the margins only decide how often that holds, never the result:
+// if it ever failed the warp-level routine above recomputes the sum from scratch.
+//
+// The increment function of a term comes from the adder itself: inside a binade the bit pattern of s is its
+// significand, so with s_even = 2^e (significand 2^23) and s_odd = 2^e + ulp,
+//     a[0] = bits(fl(s_even + t)) - bits(s_even),   a[1] = bits(fl(s_odd + t)) - bits(s_odd)
+// are exactly the integers by which a sum of even / odd significand grows (round to nearest, ties to even), and a
+// difference of 2^23 - 1 or more says that the term alone leaves the binade.
 // ----------------------------------------------------------------------------------------------------
 constexpr int SEQSUM_MAX_EVENTS = 256;
 
-template <int THREADS>
+template <int THREADS, int MAX_EVENTS = SEQSUM_MAX_EVENTS>
 struct SeqSumWorkspace {
     // The serial part of the sum as a list of events in term order.  An event is either a composed increment function of
     // a run of safe terms (a0, a1 by parity; es = the binade it assumes) or up to four terms to be added for real.
-    uint4 ev_fn[SEQSUM_MAX_EVENTS];      // a0, a1, es, dirty
-    float4 ev_terms[SEQSUM_MAX_EVENTS];  // four terms, +0 where there is none (s + 0 == s)
-    float ev_s[SEQSUM_MAX_EVENTS];       // the sum after each event
-    double warp_tot[THREADS / 32];
+    uint4 ev_fn[MAX_EVENTS];      // a0, a1, es, dirty
+    float4 ev_terms[MAX_EVENTS];  // four terms, +0 where there is none (s + 0 == s)
+    float ev_s[MAX_EVENTS];       // the sum after each event
+    float warp_tot[THREADS / 32];
     uint32_t warp_events[THREADS / 32];
     float result;
 };
 
-// Every thread of the CTA must call this (it contains __syncthreads); every thread returns the sum.
-template <int THREADS, class F>
-__device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS> &ws) {
+namespace seqsum_detail {
+
+// a[parity] of term t in the binade whose biased exponent is es (1..254); t >= 0 or NaN
+__device__ __forceinline__ void term_function_add(float t, uint32_t es, uint32_t &a0, uint32_t &a1) {
+    const uint32_t be = es << 23, bo = be | 1u;
+    const uint32_t d0 = __float_as_uint(__fadd_rn(__uint_as_float(be), t)) - be;
+    const uint32_t d1 = __float_as_uint(__fadd_rn(__uint_as_float(bo), t)) - bo;
+    a0 = d0 >= (1u << 23) - 1u ? SAT : d0;  // leaves the binade (inf and NaN land here too)
+    a1 = d1 >= (1u << 23) - 1u ? SAT : d1;
+}
+
+}  // namespace seqsum_detail
+
+// E > 0: every thread has at most E terms and keeps them in registers (one evaluation of term() each, and loops of known
+// length); E == 0: any number of terms, re-evaluated where needed.
+template <int THREADS, int MAX_EVENTS, int E, class F>
+__device__ __forceinline__ float cta_sequential_sum_impl(F term, uint32_t n, SeqSumWorkspace<THREADS, MAX_EVENTS> &ws) {
     using namespace seqsum_detail;
     constexpr int NWARP = THREADS / 32;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -165,26 +186,35 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
     const uint32_t first = min(n, (uint32_t)tid * ept), last = min(n, first + ept);
 
     SEQSUM_MARK(0);
-    // ---- exact prefix sums in double ------------------------------------------------------------
-    double local = 0.0;
-    for (uint32_t i = first; i < last; ++i) local += (double)term(i);
-    double incl = local;
+    // ---- prefix sums (fp32, additions only: every partial is a sum of non-negative values) -----------------------
+    float tv[E > 0 ? E : 1];
+    float local = 0.0f;
+    if constexpr (E > 0) {
+#pragma unroll
+        for (int j = 0; j < E; ++j) tv[j] = first + j < last ? term(first + j) : 0.0f;  // + 0 changes no sum and composes as the identity
+#pragma unroll
+        for (int j = 0; j < E; ++j) local += tv[j];
+    } else {
+        for (uint32_t i = first; i < last; ++i) local += term(i);
+    }
+    float incl = local;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        const double up = __shfl_up_sync(0xffffffffu, incl, d);
+        const float up = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= d) incl += up;
     }
     if (lane == 31) ws.warp_tot[warp] = incl;
+    float base = __shfl_up_sync(0xffffffffu, incl, 1);  // the lanes before this one
+    if (lane == 0) base = 0.0f;
     __syncthreads();
-    double base = incl - local;
     {   // plus the totals of the warps before this one: a shuffle scan over the (at most 32) warp totals
-        double wt = lane < NWARP ? ws.warp_tot[lane] : 0.0;
+        float wt = lane < NWARP ? ws.warp_tot[lane] : 0.0f;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const double up = __shfl_up_sync(0xffffffffu, wt, d);
+            const float up = __shfl_up_sync(0xffffffffu, wt, d);
             if (lane >= d) wt += up;
         }
-        const double before = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
+        const float before = __shfl_sync(0xffffffffu, wt, warp > 0 ? warp - 1 : 0);
         if (warp > 0) base += before;
     }
 
@@ -194,20 +224,25 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
     // thread can see; if both ends are in one binade, every term of the thread is safe in that binade.
     uint32_t c0 = 0, c1 = 0, es_run = 0, dirty = 0;
     if (first < last) {
-        const double m_last = (double)(last + 1) * 6.1e-8;  // > last * 2^-24, with room for the double sum's own error
-        const float flo = __double2float_rd(base * (1.0 - m_last)), fhi = __double2float_ru((base + local) * (1.0 + m_last));
+        const float m_last = (float)(last + 1 + ept) * 6.1e-8f + 2.0e-6f;  // > last * 2^-24, plus the scan's own error (ept + ~11 additions)
+        const float flo = __fmul_rd(base, __fsub_rd(1.0f, m_last)), fhi = __fmul_ru(__fadd_ru(base, local), __fadd_ru(1.0f, m_last));
         const uint32_t elo = (__float_as_uint(flo) >> 23) & 0xff, ehi = (__float_as_uint(fhi) >> 23) & 0xff;
-        if (elo == ehi && elo != 0 && elo != 255 && !(m_last >= 0.25)) {
+        if (elo == ehi && elo != 0 && elo != 255 && !(m_last >= 0.25f)) {
             es_run = elo;
-            for (uint32_t i = first; i < last; ++i) {
-                const float t = term(i);
+            auto compose = [&](float t) {
                 if (!(t >= 0.0f)) dirty = 1;  // negative or NaN: not this routine's case, add for real
                 uint32_t a0, a1;
-                term_function(__float_as_uint(t), (int)elo, a0, a1);
+                term_function_add(t, elo, a0, a1);
                 const uint32_t n0 = sat_add(c0, (c0 & 1u) ? a1 : a0);
                 const uint32_t n1 = sat_add(c1, ((1u + c1) & 1u) ? a1 : a0);
                 c0 = n0;
                 c1 = n1;
+            };
+            if constexpr (E > 0) {
+#pragma unroll
+                for (int j = 0; j < E; ++j) compose(tv[j]);
+            } else {
+                for (uint32_t i = first; i < last; ++i) compose(term(i));
             }
         } else {
             dirty = 1;
@@ -257,11 +292,22 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
         total = __shfl_sync(0xffffffffu, we, 31);
         const uint32_t before = __shfl_sync(0xffffffffu, we, warp > 0 ? warp - 1 : 0);
         uint32_t pos = (warp > 0 ? before : 0u) + ev_incl - my_events;
-        if (total <= (uint32_t)SEQSUM_MAX_EVENTS && my_events) {
+        if (total <= (uint32_t)MAX_EVENTS && my_events) {
             if (dirty) {
-                for (uint32_t i = first; i < last; i += 4, ++pos) {
-                    ws.ev_fn[pos] = make_uint4(0u, 0u, 0u, 1u);
-                    ws.ev_terms[pos] = make_float4(term(i), i + 1 < last ? term(i + 1) : 0.0f, i + 2 < last ? term(i + 2) : 0.0f, i + 3 < last ? term(i + 3) : 0.0f);
+                if constexpr (E > 0) {
+#pragma unroll
+                    for (int j = 0; j < E; j += 4) {
+                        if (first + j < last) {
+                            ws.ev_fn[pos] = make_uint4(0u, 0u, 0u, 1u);
+                            ws.ev_terms[pos] = make_float4(tv[j], j + 1 < E ? tv[j + 1] : 0.0f, j + 2 < E ? tv[j + 2] : 0.0f, j + 3 < E ? tv[j + 3] : 0.0f);
+                            ++pos;
+                        }
+                    }
+                } else {
+                    for (uint32_t i = first; i < last; i += 4, ++pos) {
+                        ws.ev_fn[pos] = make_uint4(0u, 0u, 0u, 1u);
+                        ws.ev_terms[pos] = make_float4(term(i), i + 1 < last ? term(i + 1) : 0.0f, i + 2 < last ? term(i + 2) : 0.0f, i + 3 < last ? term(i + 3) : 0.0f);
+                    }
                 }
             } else {
                 ws.ev_fn[pos] = make_uint4(c0, c1, es_run, 0u);
@@ -275,11 +321,13 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
     SEQSUM_VALUE(10, total);
     // ---- warp 0 applies the events in order -----------------------------------------------------------------------
     // The dependent chain per event is four additions (dirty) or the increment added to the bit pattern (clean: inside a
-    // binade, adding a * ulp is adding a to the bits).  The loads run ahead; the value after every event is stored, and
-    // whether every clean event really found and left s in its binade is checked afterwards, by all lanes at once.
+    // binade, adding a * ulp is adding a to the bits).  The next event's load runs ahead; the value after every event is
+    // stored, and whether every clean event really found and left s in its binade is checked afterwards, by all lanes at
+    // once.  (One warp issues an instruction every five cycles or so, so the walk costs about 70 cycles per event;
+    // unrolled and shuffle-fed variants that compute both kinds of event were measured two to three times slower.)
     if (warp == 0) {
         float s = 0.0f;
-        bool ok = total <= (uint32_t)SEQSUM_MAX_EVENTS;
+        bool ok = total <= (uint32_t)MAX_EVENTS;
         if (ok) {
             uint4 fn = ws.ev_fn[0];
             float4 tm = ws.ev_terms[0];
@@ -310,11 +358,21 @@ __device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS>
             ok = !__any_sync(0xffffffffu, bad);
         }
         SEQSUM_MARK(4);
+        SEQSUM_VALUE(11, ok ? 1 : 0);
         if (!ok) s = warp_sequential_sum<16>(term, n);
         if (lane == 0) ws.result = s;
     }
     __syncthreads();
     return ws.result;
+}
+
+// Every thread of the CTA must call this (it contains __syncthreads); every thread returns the sum.
+template <int THREADS, int MAX_EVENTS, class F>
+__device__ float cta_sequential_sum(F term, uint32_t n, SeqSumWorkspace<THREADS, MAX_EVENTS> &ws) {
+    const uint32_t ept = (n + THREADS - 1) / THREADS;  // the same in every thread
+    if (ept <= 8) return cta_sequential_sum_impl<THREADS, MAX_EVENTS, 8>(term, n, ws);
+    if (ept <= 16) return cta_sequential_sum_impl<THREADS, MAX_EVENTS, 16>(term, n, ws);
+    return cta_sequential_sum_impl<THREADS, MAX_EVENTS, 0>(term, n, ws);
 }
 
 }  // namespace ob
