@@ -114,6 +114,7 @@ int ob_synchronize(ob_ctx *ctx) {
     if (!ctx) return OB_ERR_INVALID;
     Bind b(ctx);
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (gemm_tc5_take_status()) return fail(ctx, OB_ERR_CUDA, "a tensor-core product gave up a bounded wait (pipeline barrier); its output is not valid");
     return OB_OK;
 }
 
@@ -296,6 +297,7 @@ int matmul_host(ob_ctx *ctx, const float *x, uint32_t n_tokens, const ob_weight 
     if (rc) return rc;
     OB_CUDA(ctx, cudaMemcpyAsync(y, ctx->sy.p, yb, cudaMemcpyDeviceToHost, ctx->stream));
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (gemm_tc5_take_status()) return fail(ctx, OB_ERR_CUDA, "a tensor-core product gave up a bounded wait (pipeline barrier); its output is not valid");
     OB_CUDA(ctx, cudaGetLastError());
     return OB_OK;
 }
@@ -346,6 +348,7 @@ int ob_matmul_batch(ob_ctx *ctx, const ob_matmul_op *ops, uint32_t n_ops, int de
         yo += yi;
     }
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (gemm_tc5_take_status()) return fail(ctx, OB_ERR_CUDA, "a tensor-core product gave up a bounded wait (pipeline barrier); its output is not valid");
     OB_CUDA(ctx, cudaGetLastError());
     return OB_OK;
 }

@@ -1,0 +1,318 @@
+// Many-token products on the fifth-generation tensor cores: tcgen05.mma (kind::i8) with accumulators in tensor memory,
+// operands brought into shared memory by TMA (cp.async.bulk.tensor, no multicast: every tensor map covers this GPU's own
+// memory and every CTA fetches its own tiles).
+//
+// The arithmetic is the reference's, so the results equal the CPU's bit for bit at any batch size:
+//   Q8_0 (engine/vecdot.rs:2598-2629 flat GEMM, :2829-2838 decode): acc += (ad_b * s_b) * (f32)dot32_b per block of 32, in
+//   block order.  The int8 codes of a row are already a K-major int8 matrix, so TMA loads them straight into the
+//   128-byte-swizzled operand layout.  One fp32 rounding per 32 elements means every K = 32 step needs its own integer
+//   result: each tcgen05.mma (M = 128 rows, N = 64 tokens, K = 32) writes a fresh accumulator, four per pipeline step in
+//   one half of tensor memory while the epilogue warps drain the other half (tcgen05.ld), scale and accumulate in fp32.
+//
+// Roles in a CTA of ten warps: warps 0-7 epilogue (warp w reads the 32 tensor-memory lanes of quadrant w % 4, token columns
+// 32 * (w / 4) ..), warp 8 lane 0 issues the TMA loads, warp 9 allocates tensor memory and its lane 0 issues the MMAs.
+// Stages and accumulator halves are handed over through mbarriers; every wait is bounded -- a wait that runs out sets a
+// status word, makes all roles leave their loops, and the CTA frees its tensor memory and returns.
+#include <atomic>
+
+#include <cuda.h>  // CUtensorMap and its enums; cuTensorMapEncodeTiled is looked up through the runtime, libcuda is not linked
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ob {
+
+namespace {
+
+constexpr int TC_M = 128, TC_N = 64;
+constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_TMA_WARP = 8, TC_MMA_WARP = 9;
+constexpr int TC_THREADS = 10 * 32;
+constexpr uint32_t TC_POLL_LIMIT = 1u << 22;  // polls of one wait before it gives up (tens of milliseconds)
+
+__device__ uint32_t g_tc5_status;  // set to 1 when a wait ran out
+std::atomic<bool> g_tc5_launched{false};  // host: a kernel of this file has been launched since the status was last read
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---- mbarrier ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// False when the wait was abandoned: this one ran out of polls, or another role's did (*abort is then set).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort) {
+    for (uint32_t i = 0; i < TC_POLL_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63u) == 63u && *abort) return false;
+    }
+    *abort = 1u;
+    g_tc5_status = 1u;
+    return false;
+}
+
+// ---- TMA -----------------------------------------------------------------------------------------------------------
+// Tile at (x, y) of the tensor `tm` describes -> shared memory; completion counts on `bar`.  x * element size must be a
+// multiple of 16 bytes (all callers pass multiples of 128 bytes or of four floats).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, int32_t x, int32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+
+// ---- tensor memory and tcgen05 -----------------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {  // one whole warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {  // the same warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D (tensor memory, int32, 128 lanes x N columns) [+]= A (128 x 32 int8, K-major) * B (N x 32 int8, K-major)^T
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// All MMAs this thread has issued so far arrive on `bar` when they have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// This warp's 32 lanes x 32 consecutive columns: thread i gets lane i's words.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
+        "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+          "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+          "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups of eight rows 1024
+// bytes apart, tile base 1024-byte aligned.  A K = 32 step inside the 128-byte row advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3fffu) | (1ull << 16) /* leading byte offset: unused with a swizzle */ | (64ull << 32) /* 1024 B between row groups */ |
+           (1ull << 46) /* descriptor version of this architecture */ | (2ull << 61) /* 128-byte swizzle */;
+}
+// Instruction descriptor: int32 accumulator, A and B signed (1) or unsigned (0) 8-bit, both K-major, N columns, M = 128.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t a_signed, uint32_t b_signed, uint32_t n) {
+    return (2u << 4) | (a_signed << 7) | (b_signed << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// ---- Q8_0 ------------------------------------------------------------------------------------------------------------
+constexpr int Q8_STAGES = 4;
+constexpr uint32_t Q8_A_BYTES = TC_M * 128, Q8_B_BYTES = TC_N * 128, Q8_XD_BYTES = TC_N * 16;
+struct Q8Smem {  // offsets from the 1024-byte aligned base
+    static constexpr uint32_t A = 0, B = A + Q8_STAGES * Q8_A_BYTES, XD = B + Q8_STAGES * Q8_B_BYTES, BAR = XD + Q8_STAGES * Q8_XD_BYTES;
+    static constexpr uint32_t FULL = BAR, EMPTY = FULL + 8 * Q8_STAGES, ACC_FULL = EMPTY + 8 * Q8_STAGES, ACC_EMPTY = ACC_FULL + 16, SLOT = ACC_EMPTY + 16, ABORT = SLOT + 8;
+    static constexpr uint32_t BYTES = ABORT + 8, ALLOC = BYTES + 1024;
+};
+
+struct TcQ8Args {
+    GemvSegment seg;
+    uint32_t n_tokens, n_steps;  // steps of four blocks (128 elements)
+};
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc5_q8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xd, TcQ8Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (sbase - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * TC_N;
+    volatile uint32_t *abort = reinterpret_cast<volatile uint32_t *>(smem + Q8Smem::ABORT);
+    const uint32_t n_steps = a.n_steps;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Q8_STAGES; ++s) {
+            mbar_init(sbase + Q8Smem::FULL + 8 * s, 1);                  // the producer's expect_tx arrival
+            mbar_init(sbase + Q8Smem::EMPTY + 8 * s, 1 + TC_EPI_WARPS);  // MMA completion + the epilogue warps (they read the token scales)
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(sbase + Q8Smem::ACC_FULL + 8 * b, 1);
+            mbar_init(sbase + Q8Smem::ACC_EMPTY + 8 * b, TC_EPI_WARPS);
+        }
+        *abort = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == TC_MMA_WARP) tmem_alloc(sbase + Q8Smem::SLOT, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(smem + Q8Smem::SLOT);
+
+    if (warp == TC_TMA_WARP) {
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_steps; ++it) {
+                const uint32_t s = it % Q8_STAGES;
+                if (it >= Q8_STAGES && !mbar_wait(sbase + Q8Smem::EMPTY + 8 * s, ((it / Q8_STAGES) & 1u) ^ 1u, abort)) break;
+                const uint32_t full = sbase + Q8Smem::FULL + 8 * s;
+                mbar_expect_tx(full, Q8_A_BYTES + Q8_B_BYTES + Q8_XD_BYTES);
+                tma_load_2d(sbase + Q8Smem::A + s * Q8_A_BYTES, &tm_w, (int32_t)(it * 128), (int32_t)row0, full);
+                tma_load_2d(sbase + Q8Smem::B + s * Q8_B_BYTES, &tm_x, (int32_t)(it * 128), (int32_t)tok0, full);
+                tma_load_2d(sbase + Q8Smem::XD + s * Q8_XD_BYTES, &tm_xd, (int32_t)(it * 4), (int32_t)tok0, full);
+            }
+        }
+    } else if (warp == TC_MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(1, 1, TC_N);
+            for (uint32_t it = 0; it < n_steps; ++it) {
+                const uint32_t s = it % Q8_STAGES, buf = it & 1u;
+                if (!mbar_wait(sbase + Q8Smem::FULL + 8 * s, (it / Q8_STAGES) & 1u, abort)) break;
+                if (it >= 2 && !mbar_wait(sbase + Q8Smem::ACC_EMPTY + 8 * buf, ((it / 2) & 1u) ^ 1u, abort)) break;
+                tc_fence_after();
+                const uint64_t da = umma_desc_sw128(sbase + Q8Smem::A + s * Q8_A_BYTES), db = umma_desc_sw128(sbase + Q8Smem::B + s * Q8_B_BYTES);
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j)  // block j of the step: its own accumulator, nothing is added up on the tensor core
+                    umma_i8(tmem + buf * 256 + j * TC_N, da + 2 * j, db + 2 * j, idesc, 0u);
+                umma_commit(sbase + Q8Smem::EMPTY + 8 * s);
+                umma_commit(sbase + Q8Smem::ACC_FULL + 8 * buf);
+            }
+        }
+    } else {
+        // ---- epilogue: thread = one row x 32 tokens
+        const uint32_t quad = warp & 3u, half = warp >> 2;
+        const uint32_t row = row0 + quad * 32 + lane;
+        const bool row_ok = row < a.seg.w.out_dim;
+        const uint8_t *wrow = a.seg.w.data + (uint64_t)min(row, a.seg.w.out_dim - 1) * a.seg.w.row_stride + a.seg.w.d_off;
+        float acc[32];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) acc[t] = 0.0f;
+        uint2 sw_next = __ldg(reinterpret_cast<const uint2 *>(wrow));  // the row's four f16 block scales of step 0
+        for (uint32_t it = 0; it < n_steps; ++it) {
+            const uint32_t s = it % Q8_STAGES, buf = it & 1u;
+            const uint2 swb = sw_next;
+            if (it + 1 < n_steps) sw_next = __ldg(reinterpret_cast<const uint2 *>(wrow + 8 * (it + 1)));
+            if (!mbar_wait(sbase + Q8Smem::ACC_FULL + 8 * buf, (it / 2) & 1u, abort)) break;
+            tc_fence_after();
+            const float sw[4] = {f16_bits_to_f32(swb.x & 0xffffu), f16_bits_to_f32(swb.x >> 16), f16_bits_to_f32(swb.y & 0xffffu), f16_bits_to_f32(swb.y >> 16)};
+            const float4 *xd = reinterpret_cast<const float4 *>(smem + Q8Smem::XD + s * Q8_XD_BYTES) + half * 32;  // [token] the four block scales
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((quad * 32) << 16) + buf * 256 + j * TC_N + half * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 32; ++t) {
+                    const float4 d4 = xd[t];
+                    const float ad = j == 0 ? d4.x : j == 1 ? d4.y : j == 2 ? d4.z : d4.w;
+                    acc[t] = __fadd_rn(acc[t], __fmul_rn(__fmul_rn(ad, sw[j]), (float)(int)r[t]));  // (ad_b * s_b) * dot32_b, vecdot.rs:2620
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(sbase + Q8Smem::ACC_EMPTY + 8 * buf);
+                mbar_arrive(sbase + Q8Smem::EMPTY + 8 * s);
+            }
+        }
+        if (!*abort && row_ok) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+                const uint32_t tok = tok0 + half * 32 + t;
+                if (tok < a.n_tokens) {
+                    const uint64_t o = (uint64_t)tok * a.seg.y_stride + row;
+                    float v = acc[t];
+                    if (a.seg.epilogue == EPI_ADD_RESIDUAL) v = __fadd_rn(a.seg.residual[o], v);
+                    a.seg.y[o] = v;
+                }
+            }
+        }
+    }
+    if (*abort) {  // let copies that are still in flight land before the shared memory goes away
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TC_MMA_WARP) tmem_dealloc(tmem, 512);
+}
+
+// ---- host ------------------------------------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiled>(p);
+    }();
+    return fn;
+}
+
+// 2-D tensor of `rows` rows of `cols` elements, rows `pitch` bytes apart, read in boxes of box_cols x box_rows.
+bool make_map_2d(CUtensorMap *tm, CUtensorMapDataType type, uint32_t elem_bytes, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+                 uint32_t box_rows, CUtensorMapSwizzle swz) {
+    EncodeTiled fn = encode_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (pitch & 15) || ((uint64_t)box_cols * elem_bytes & 15)) return false;
+    const cuuint64_t dims[2] = {cols, rows}, strides[1] = {pitch};
+    const cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
+    return fn(tm, type, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool gemm_tc5_supported(const GemvArgs &a) {
+    static const bool enabled = [] { const char *e = getenv("OB_TC5"); return !(e && e[0] == '0' && e[1] == 0); }();
+    if (!enabled || a.n_seg < 1 || a.n_tokens < 16 || a.isum_out || !encode_fn()) return false;
+    const uint32_t type = a.seg[0].w.type, in_dim = a.seg[0].w.in_dim;
+    if (type != TYPE_Q8_0 || in_dim % 128 || a.act.dim_cap % 128) return false;
+    for (int s = 0; s < a.n_seg; ++s)
+        if (a.seg[s].w.type != type || a.seg[s].w.in_dim != in_dim || (a.seg[s].w.row_stride & 15) || (a.seg[s].w.d_off & 7)) return false;
+    return true;
+}
+
+bool launch_gemm_tc5(const GemvArgs &a, int sm_count, cudaStream_t st) {
+    (void)sm_count;
+    static PerDeviceOnce once;
+    if (once.run([] { return cudaFuncSetAttribute(gemm_tc5_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q8Smem::ALLOC); }) != cudaSuccess) return false;
+    const uint32_t in_dim = a.seg[0].w.in_dim;
+    CUtensorMap tm_x, tm_xd;
+    if (!make_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.act.q, in_dim, a.n_tokens, a.act.dim_cap, 128, TC_N, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(&tm_xd, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a.act.d, in_dim / 32, a.n_tokens, (uint64_t)(a.act.dim_cap / 32) * 4, 4, TC_N, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return false;
+    for (int s = 0; s < a.n_seg; ++s) {
+        const GemvSegment &g = a.seg[s];
+        CUtensorMap tm_w;
+        if (!make_map_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, in_dim, g.w.out_dim, g.w.row_stride, 128, TC_M, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        TcQ8Args k{};
+        k.seg = g;
+        k.n_tokens = a.n_tokens;
+        k.n_steps = in_dim / 128;
+        const dim3 grid((g.w.out_dim + TC_M - 1) / TC_M, (a.n_tokens + TC_N - 1) / TC_N);
+        gemm_tc5_q8_kernel<<<grid, TC_THREADS, Q8Smem::ALLOC, st>>>(tm_w, tm_x, tm_xd, k);
+        g_tc5_launched.store(true, std::memory_order_relaxed);
+    }
+    return true;
+}
+
+// 1 when a bounded wait of one of these kernels ran out since the last call (and clears it).  Synchronises with the device.
+int gemm_tc5_take_status() {
+    if (!g_tc5_launched.exchange(false)) return 0;
+    uint32_t v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc5_status, 4) != cudaSuccess) return 0;
+    if (v) {
+        const uint32_t z = 0;
+        cudaMemcpyToSymbol(g_tc5_status, &z, 4);
+    }
+    return (int)v;
+}
+
+}  // namespace ob

@@ -392,6 +392,7 @@ uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool g
 void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st) {
     if (a.n_tokens == 0 || a.n_seg == 0) return;
     static const bool use_mma = [] { const char *e = getenv("OB_MMA"); return !(e && e[0] == '0' && e[1] == 0); }();
+    if (gemm_tc5_supported(a) && launch_gemm_tc5(a, sm_count, st)) return;  // many tokens: tcgen05 tiles (gemm_tc5.cu)
     if (use_mma && gemm_mma_supported(a)) {  // many tokens: tensor-core tiles (gemm_mma.cu)
         launch_gemm_mma(a, sm_count, st);
         return;

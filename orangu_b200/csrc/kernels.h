@@ -61,6 +61,11 @@ uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool g
 bool gemm_mma_supported(const GemvArgs &a);
 void launch_gemm_mma(const GemvArgs &a, int sm_count, cudaStream_t st);
 
+// ---- gemm_tc5.cu: many-token products on tcgen05 tensor cores with TMEM accumulators, TMA-fed (16 tokens or more)
+bool gemm_tc5_supported(const GemvArgs &a);
+bool launch_gemm_tc5(const GemvArgs &a, int sm_count, cudaStream_t st);  // false: a tensor map could not be made (nothing was launched)
+int gemm_tc5_take_status();  // 1 when a bounded wait inside one of these kernels ran out since the last call
+
 // ---- stream_gemv.cu: fused single-token products for decode (Q4_K / Q6_K weights)
 enum StreamPrologue { SG_PRO_PLAIN = 0, SG_PRO_RMSNORM = 1, SG_PRO_READY = 2 };
 enum StreamEpilogue { SG_EP_STORE = 0, SG_EP_RESIDUAL = 1, SG_EP_SWIGLU = 2, SG_EP_ROPE_Q = 3, SG_EP_ROPE_K = 4, SG_EP_V = 5, SG_EP_XCHG = 6 };

@@ -1206,6 +1206,7 @@ namespace {
 
 // After a synchronisation: did a peer exchange of the tensor-parallel step run out of time?
 int check_peer(ob_model *m) {
+    if (gemm_tc5_take_status()) return fail(m->ctx, OB_ERR_CUDA, "a tensor-core product gave up a bounded wait (pipeline barrier); the step's output is not valid");
     if (m->launch_failed) {
         m->launch_failed = false;
         return fail(m->ctx, OB_ERR_CUDA, std::string("launching the persistent layer kernel failed: ") + cudaGetErrorString(cudaGetLastError()));
