@@ -100,6 +100,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes, groups of eight rows 1024
@@ -242,6 +249,246 @@ gemm_tc5_q8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (warp == TC_MMA_WARP) tmem_dealloc(tmem, 512);
 }
 
+// ---- Q4_K -----------------------------------------------------------------------------------------------------------
+// The 4-bit codes cannot go to the tensor core as they are: every 32-element sub-block has its own 6-bit scale, and
+// isum = sum_j sc_j * dot32_j has to be exact.  So the scale is folded into the operand, in two digits that keep every
+// product inside a byte: sc = 8 * sc_hi + sc_lo (both 0..7), code * digit <= 105, and
+//     isum = 8 * dot(code * sc_hi, x) + dot(code * sc_lo, x),      imin = dot(m_j(i), x)
+// (the min term sum_j m_j * bsum_j is itself a dot product with the sub-block's min as the "weight" of each of its
+// elements).  Eight expander warps turn each half super-block of 128 rows (TMA-loaded GGUF blocks) into those three
+// unsigned-byte planes in the swizzled operand layout -- a packed 32-bit multiply scales four codes at once -- the MMA
+// thread accumulates each plane over the super-block's eight K = 32 steps in its own tensor-memory accumulator, and the
+// epilogue warps form the super-block's fp32 term per (row, token) in the CPU's association and order:
+//   decode order   acc += ad * (d * isum - dmin * imin)                          (engine/vecdot.rs:3152-3178)
+//   prefill order  first for every super-block acc -= (ad * dmin) * imin, then acc += ad * (d * isum)
+//                  (engine/vecdot.rs:2119-2143, 2213-2255): two sweeps over K in one launch, the first over the block
+//                  headers only (min plane), the accumulators staying in registers.
+constexpr int K4_IN_STAGES = 3, K4_RING = 8;
+constexpr int K4_EXP_WARPS = 8;
+constexpr int K4_TMA_WARP = 16, K4_MMA_WARP = 17;
+constexpr int K4_THREADS = 18 * 32;
+constexpr uint32_t K4_RAW_BYTES = TC_M * 144, K4_B_BYTES = 2 * TC_N * 128, K4_PLANE_BYTES = TC_M * 128;
+struct K4Smem {
+    static constexpr uint32_t RAW = 0, B = RAW + K4_IN_STAGES * K4_RAW_BYTES;       // 55,296 is a multiple of 1024
+    static constexpr uint32_t PLANES = B + K4_IN_STAGES * K4_B_BYTES;               // [2 stages][3 planes][128 x 128]
+    static constexpr uint32_t XD = PLANES + 2 * 3 * K4_PLANE_BYTES;                  // [ring][64] token scales
+    static constexpr uint32_t DD = XD + K4_RING * TC_N * 4;                          // [ring][128] d | dmin << 16
+    static constexpr uint32_t BAR = DD + K4_RING * TC_M * 4;
+    static constexpr uint32_t IN_FULL = BAR, IN_EMPTY = IN_FULL + 8 * K4_IN_STAGES, PL_FULL = IN_EMPTY + 8 * K4_IN_STAGES, PL_EMPTY = PL_FULL + 16,
+                              ACC_FULL = PL_EMPTY + 16, ACC_EMPTY = ACC_FULL + 16, SLOT = ACC_EMPTY + 16, ABORT = SLOT + 8;
+    static constexpr uint32_t BYTES = ABORT + 8, ALLOC = BYTES + 1024;
+};
+static_assert((K4_IN_STAGES * K4_RAW_BYTES) % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+
+struct TcK4Args {
+    GemvSegment seg;
+    const float *act_d;    // [token][pitch] per-256 activation scales
+    uint32_t act_d_pitch;
+    uint32_t n_tokens, nb;
+};
+
+template <bool GEMM>
+__global__ void __launch_bounds__(K4_THREADS, 1)
+gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_constant__ CUtensorMap tm_hdr, const __grid_constant__ CUtensorMap tm_x, TcK4Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (sbase - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * TC_N;
+    volatile uint32_t *abort = reinterpret_cast<volatile uint32_t *>(smem + K4Smem::ABORT);
+    const uint32_t nb = a.nb;
+    const uint32_t n_visits = GEMM ? 2 * nb : nb;  // super-block visits; in the prefill order the first nb are the min sweep
+    // planes of a visit: decode order lo, hi, min; prefill order min alone, then lo, hi
+    auto n_planes = [&](uint32_t u) -> uint32_t { return GEMM ? (u < nb ? 1u : 2u) : 3u; };
+    constexpr uint32_t ACC_STRIDE = GEMM ? 128 : 192;  // tensor-memory columns per accumulator buffer
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < K4_IN_STAGES; ++s) {
+            mbar_init(sbase + K4Smem::IN_FULL + 8 * s, 1);
+            mbar_init(sbase + K4Smem::IN_EMPTY + 8 * s, 1 + K4_EXP_WARPS);  // MMA completion (activations) + the expanders (blocks)
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(sbase + K4Smem::PL_FULL + 8 * b, K4_EXP_WARPS);
+            mbar_init(sbase + K4Smem::PL_EMPTY + 8 * b, 1);
+            mbar_init(sbase + K4Smem::ACC_FULL + 8 * b, 1);
+            mbar_init(sbase + K4Smem::ACC_EMPTY + 8 * b, TC_EPI_WARPS);
+        }
+        *abort = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == K4_MMA_WARP) tmem_alloc(sbase + K4Smem::SLOT, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(smem + K4Smem::SLOT);
+
+    if (warp == K4_TMA_WARP) {
+        if (lane == 0) {
+            for (uint32_t u = 0; u < n_visits; ++u) {
+                const uint32_t slot = u % K4_IN_STAGES, s = u % nb;
+                const bool min_sweep = GEMM && u < nb;
+                if (u >= K4_IN_STAGES && !mbar_wait(sbase + K4Smem::IN_EMPTY + 8 * slot, ((u / K4_IN_STAGES) & 1u) ^ 1u, abort)) break;
+                const uint32_t full = sbase + K4Smem::IN_FULL + 8 * slot;
+                mbar_expect_tx(full, (min_sweep ? TC_M * 16u : K4_RAW_BYTES) + K4_B_BYTES);
+                if (min_sweep) tma_load_2d(sbase + K4Smem::RAW + slot * K4_RAW_BYTES, &tm_hdr, (int32_t)(s * 144), (int32_t)row0, full);  // the 16-byte headers
+                else tma_load_2d(sbase + K4Smem::RAW + slot * K4_RAW_BYTES, &tm_raw, (int32_t)(s * 144), (int32_t)row0, full);
+                tma_load_2d(sbase + K4Smem::B + slot * K4_B_BYTES, &tm_x, (int32_t)(s * 256), (int32_t)tok0, full);
+                tma_load_2d(sbase + K4Smem::B + slot * K4_B_BYTES + TC_N * 128, &tm_x, (int32_t)(s * 256 + 128), (int32_t)tok0, full);
+            }
+        }
+    } else if (warp == K4_MMA_WARP) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_i8(0, 1, TC_N);  // unsigned planes x signed activations
+            bool ok = true;
+            for (uint32_t u = 0; u < n_visits && ok; ++u) {
+                const uint32_t slot = u % K4_IN_STAGES, buf = u & 1u, np = n_planes(u);
+                for (uint32_t h = 0; h < 2; ++h) {
+                    const uint32_t v = 2 * u + h, ps = v & 1u;
+                    if (!(ok = mbar_wait(sbase + K4Smem::PL_FULL + 8 * ps, (v / 2) & 1u, abort))) break;
+                    if (h == 0) {
+                        if (!(ok = mbar_wait(sbase + K4Smem::IN_FULL + 8 * slot, (u / K4_IN_STAGES) & 1u, abort))) break;
+                        if (u >= 2 && !(ok = mbar_wait(sbase + K4Smem::ACC_EMPTY + 8 * buf, ((u / 2) & 1u) ^ 1u, abort))) break;
+                    }
+                    tc_fence_after();
+                    const uint64_t db = umma_desc_sw128(sbase + K4Smem::B + slot * K4_B_BYTES + h * TC_N * 128);
+                    for (uint32_t p = 0; p < np; ++p) {
+                        const uint64_t da = umma_desc_sw128(sbase + K4Smem::PLANES + (ps * 3 + p) * K4_PLANE_BYTES);
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) umma_i8(tmem + buf * ACC_STRIDE + p * TC_N, da + 2 * k, db + 2 * k, idesc, (h | k) ? 1u : 0u);
+                    }
+                    umma_commit(sbase + K4Smem::PL_EMPTY + 8 * ps);
+                    if (h == 1) {
+                        umma_commit(sbase + K4Smem::IN_EMPTY + 8 * slot);
+                        umma_commit(sbase + K4Smem::ACC_FULL + 8 * buf);
+                    }
+                }
+            }
+        }
+    } else if (warp >= TC_EPI_WARPS) {
+        // ---- expanders: thread = (row, 64 elements) of the half super-block in flight
+        const uint32_t et = threadIdx.x - TC_EPI_WARPS * 32, r = et >> 1, gl = et & 1u;
+        const uint32_t swz = r & 7u, row_off = (r >> 3) * 1024 + swz * 128;
+        bool ok = true;
+        for (uint32_t u = 0; u < n_visits && ok; ++u) {
+            const uint32_t slot = u % K4_IN_STAGES, s = u % nb;
+            const bool min_sweep = GEMM && u < nb, main_sweep = GEMM && u >= nb;
+            if (!(ok = mbar_wait(sbase + K4Smem::IN_FULL + 8 * slot, (u / K4_IN_STAGES) & 1u, abort))) break;
+            const uint8_t *raw = smem + K4Smem::RAW + slot * K4_RAW_BYTES + r * (min_sweep ? 16u : 144u);
+            const uint4 hd = *reinterpret_cast<const uint4 *>(raw);
+            if (gl == 0) reinterpret_cast<uint32_t *>(smem + K4Smem::DD)[(u % K4_RING) * TC_M + r] = hd.x;
+            if (et < TC_N) {
+                const uint32_t tok = tok0 + et;
+                reinterpret_cast<float *>(smem + K4Smem::XD)[(u % K4_RING) * TC_N + et] = tok < a.n_tokens ? __ldg(a.act_d + (uint64_t)tok * a.act_d_pitch + s) : 0.0f;
+            }
+            // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of two words each
+            const uint32_t scl = hd.y & 0x3f3f3f3fu, ml = hd.z & 0x3f3f3f3fu;
+            const uint32_t sch = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u), mh = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t v = 2 * u + h, ps = v & 1u, g = 2 * h + gl;  // 64 elements 64 g .. of the super-block: sub-blocks 2g (low nibbles), 2g + 1 (high)
+                if (v >= 2 && !(ok = mbar_wait(sbase + K4Smem::PL_EMPTY + 8 * ps, ((v / 2) & 1u) ^ 1u, abort))) break;
+                const uint32_t scw = g < 2 ? scl : sch, mw = g < 2 ? ml : mh, sh = 16 * (g & 1u);
+                const uint32_t sa = (scw >> sh) & 0xffu, sb = (scw >> (sh + 8)) & 0xffu, ma = (mw >> sh) & 0xffu, mb = (mw >> (sh + 8)) & 0xffu;
+                uint8_t *pl = smem + K4Smem::PLANES + ps * 3 * K4_PLANE_BYTES + row_off;
+                // 16-byte chunks 4 gl .. 4 gl + 3 of the row's 128 bytes, swizzled: low-nibble sub-block in the first two, high in the last two
+                const uint32_t c0 = ((4 * gl + 0) ^ swz) * 16, c1 = ((4 * gl + 1) ^ swz) * 16, c2 = ((4 * gl + 2) ^ swz) * 16, c3 = ((4 * gl + 3) ^ swz) * 16;
+                if (!min_sweep) {
+                    const uint4 qa = *reinterpret_cast<const uint4 *>(raw + 16 + 32 * g), qb = *reinterpret_cast<const uint4 *>(raw + 32 + 32 * g);
+                    const uint32_t M = 0x0f0f0f0fu;
+                    const uint32_t la[8] = {qa.x & M, qa.y & M, qa.z & M, qa.w & M, qb.x & M, qb.y & M, qb.z & M, qb.w & M};
+                    const uint32_t ha[8] = {(qa.x >> 4) & M, (qa.y >> 4) & M, (qa.z >> 4) & M, (qa.w >> 4) & M, (qb.x >> 4) & M, (qb.y >> 4) & M, (qb.z >> 4) & M, (qb.w >> 4) & M};
+                    const uint32_t sal = sa & 7u, sah = sa >> 3, sbl = sb & 7u, sbh = sb >> 3;
+                    uint8_t *plo = pl, *phi = pl + K4_PLANE_BYTES;
+                    // four codes (each <= 15) times a digit (<= 7) in one multiply: no byte reaches 256
+                    *reinterpret_cast<uint4 *>(plo + c0) = make_uint4(la[0] * sal, la[1] * sal, la[2] * sal, la[3] * sal);
+                    *reinterpret_cast<uint4 *>(plo + c1) = make_uint4(la[4] * sal, la[5] * sal, la[6] * sal, la[7] * sal);
+                    *reinterpret_cast<uint4 *>(plo + c2) = make_uint4(ha[0] * sbl, ha[1] * sbl, ha[2] * sbl, ha[3] * sbl);
+                    *reinterpret_cast<uint4 *>(plo + c3) = make_uint4(ha[4] * sbl, ha[5] * sbl, ha[6] * sbl, ha[7] * sbl);
+                    *reinterpret_cast<uint4 *>(phi + c0) = make_uint4(la[0] * sah, la[1] * sah, la[2] * sah, la[3] * sah);
+                    *reinterpret_cast<uint4 *>(phi + c1) = make_uint4(la[4] * sah, la[5] * sah, la[6] * sah, la[7] * sah);
+                    *reinterpret_cast<uint4 *>(phi + c2) = make_uint4(ha[0] * sbh, ha[1] * sbh, ha[2] * sbh, ha[3] * sbh);
+                    *reinterpret_cast<uint4 *>(phi + c3) = make_uint4(ha[4] * sbh, ha[5] * sbh, ha[6] * sbh, ha[7] * sbh);
+                }
+                if (!main_sweep) {
+                    uint8_t *pm = pl + (GEMM ? 0u : 2u * K4_PLANE_BYTES);
+                    const uint32_t wa = ma * 0x01010101u, wb = mb * 0x01010101u;
+                    *reinterpret_cast<uint4 *>(pm + c0) = make_uint4(wa, wa, wa, wa);
+                    *reinterpret_cast<uint4 *>(pm + c1) = make_uint4(wa, wa, wa, wa);
+                    *reinterpret_cast<uint4 *>(pm + c2) = make_uint4(wb, wb, wb, wb);
+                    *reinterpret_cast<uint4 *>(pm + c3) = make_uint4(wb, wb, wb, wb);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads these planes through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sbase + K4Smem::PL_FULL + 8 * ps);
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sbase + K4Smem::IN_EMPTY + 8 * slot);  // this warp is done with the blocks of the visit
+        }
+    } else {
+        // ---- epilogue: thread = one row x 32 tokens
+        const uint32_t quad = warp & 3u, half = warp >> 2, rl = quad * 32 + lane;
+        const uint32_t row = row0 + rl;
+        const bool row_ok = row < a.seg.w.out_dim;
+        float acc[32];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) acc[t] = 0.0f;
+        for (uint32_t u = 0; u < n_visits; ++u) {
+            const uint32_t buf = u & 1u, ring = u % K4_RING;
+            const bool min_sweep = GEMM && u < nb;
+            if (!mbar_wait(sbase + K4Smem::ACC_FULL + 8 * buf, (u / 2) & 1u, abort)) break;
+            tc_fence_after();
+            const uint32_t dw = reinterpret_cast<const uint32_t *>(smem + K4Smem::DD)[ring * TC_M + rl];
+            const float d = f16_bits_to_f32(dw & 0xffffu), dmin = f16_bits_to_f32(dw >> 16);
+            const float *xd = reinterpret_cast<const float *>(smem + K4Smem::XD) + ring * TC_N + half * 32;
+            const uint32_t tbase = tmem + ((quad * 32) << 16) + buf * ACC_STRIDE + half * 32;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {  // 16 tokens at a time
+                uint32_t p0[16], p1[16], p2[16];
+                tmem_ld16(tbase + c * 16, p0);
+                if (!GEMM || !min_sweep) tmem_ld16(tbase + TC_N + c * 16, p1);
+                if (!GEMM) tmem_ld16(tbase + 2 * TC_N + c * 16, p2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    const float ad = xd[c * 16 + t];
+                    float &o = acc[c * 16 + t];
+                    if (!GEMM) {
+                        const int isum = (int)(p1[t] << 3) + (int)p0[t], imin = (int)p2[t];
+                        o = __fadd_rn(o, __fmul_rn(ad, __fsub_rn(__fmul_rn(d, (float)isum), __fmul_rn(dmin, (float)imin))));
+                    } else if (min_sweep) {
+                        o = __fsub_rn(o, __fmul_rn(__fmul_rn(ad, dmin), (float)(int)p0[t]));
+                    } else {
+                        const int isum = (int)(p1[t] << 3) + (int)p0[t];
+                        o = __fadd_rn(o, __fmul_rn(ad, __fmul_rn(d, (float)isum)));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sbase + K4Smem::ACC_EMPTY + 8 * buf);
+        }
+        if (!*abort && row_ok) {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) {
+                const uint32_t tok = tok0 + half * 32 + t;
+                if (tok < a.n_tokens) {
+                    const uint64_t o = (uint64_t)tok * a.seg.y_stride + row;
+                    float v = acc[t];
+                    if (a.seg.epilogue == EPI_ADD_RESIDUAL) v = __fadd_rn(a.seg.residual[o], v);
+                    a.seg.y[o] = v;
+                }
+            }
+        }
+    }
+    if (*abort) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == K4_MMA_WARP) tmem_dealloc(tmem, 512);
+}
+
 // ---- host ------------------------------------------------------------------------------------------------------------
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -273,14 +520,50 @@ bool gemm_tc5_supported(const GemvArgs &a) {
     static const bool enabled = [] { const char *e = getenv("OB_TC5"); return !(e && e[0] == '0' && e[1] == 0); }();
     if (!enabled || a.n_seg < 1 || a.n_tokens < 16 || a.isum_out || !encode_fn()) return false;
     const uint32_t type = a.seg[0].w.type, in_dim = a.seg[0].w.in_dim;
-    if (type != TYPE_Q8_0 || in_dim % 128 || a.act.dim_cap % 128) return false;
+    if (type == TYPE_Q8_0) {
+        if (in_dim % 128 || a.act.dim_cap % 128) return false;
+    } else if (type == TYPE_Q4_K) {
+        if (in_dim % 256 || a.act.dim_cap % 16) return false;
+    } else {
+        return false;  // Q6_K stays on the mma.sync tiles (gemm_mma.cu)
+    }
     for (int s = 0; s < a.n_seg; ++s)
-        if (a.seg[s].w.type != type || a.seg[s].w.in_dim != in_dim || (a.seg[s].w.row_stride & 15) || (a.seg[s].w.d_off & 7)) return false;
+        if (a.seg[s].w.type != type || a.seg[s].w.in_dim != in_dim || (a.seg[s].w.row_stride & 15) || (type == TYPE_Q8_0 && (a.seg[s].w.d_off & 7))) return false;
+    return true;
+}
+
+static bool launch_q4k(const GemvArgs &a, cudaStream_t st) {
+    static PerDeviceOnce once;
+    if (once.run([] {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc5_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem::ALLOC);
+            return e != cudaSuccess ? e : cudaFuncSetAttribute(gemm_tc5_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem::ALLOC);
+        }) != cudaSuccess)
+        return false;
+    const uint32_t in_dim = a.seg[0].w.in_dim, nb = in_dim / 256;
+    CUtensorMap tm_x;
+    if (!make_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.act.q, in_dim, a.n_tokens, a.act.dim_cap, 128, TC_N, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    for (int s = 0; s < a.n_seg; ++s) {
+        const GemvSegment &g = a.seg[s];
+        CUtensorMap tm_raw, tm_hdr;
+        if (!make_map_2d(&tm_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 144, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+        if (!make_map_2d(&tm_hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 16, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+        TcK4Args k{};
+        k.seg = g;
+        k.act_d = a.act.d;
+        k.act_d_pitch = a.act.dim_cap / 256;
+        k.n_tokens = a.n_tokens;
+        k.nb = nb;
+        const dim3 grid((g.w.out_dim + TC_M - 1) / TC_M, (a.n_tokens + TC_N - 1) / TC_N);
+        if (a.gemm_order) gemm_tc5_q4k_kernel<true><<<grid, K4_THREADS, K4Smem::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
+        else gemm_tc5_q4k_kernel<false><<<grid, K4_THREADS, K4Smem::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
+        g_tc5_launched.store(true, std::memory_order_relaxed);
+    }
     return true;
 }
 
 bool launch_gemm_tc5(const GemvArgs &a, int sm_count, cudaStream_t st) {
     (void)sm_count;
+    if (a.seg[0].w.type == TYPE_Q4_K) return launch_q4k(a, st);
     static PerDeviceOnce once;
     if (once.run([] { return cudaFuncSetAttribute(gemm_tc5_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q8Smem::ALLOC); }) != cudaSuccess) return false;
     const uint32_t in_dim = a.seg[0].w.in_dim;
