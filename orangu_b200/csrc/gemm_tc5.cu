@@ -263,22 +263,30 @@ gemm_tc5_q8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 //   prefill order  first for every super-block acc -= (ad * dmin) * imin, then acc += ad * (d * isum)
 //                  (engine/vecdot.rs:2119-2143, 2213-2255): two sweeps over K in one launch, the first over the block
 //                  headers only (min plane), the accumulators staying in registers.
-constexpr int K4_IN_STAGES = 3, K4_RING = 8;
-constexpr int K4_EXP_WARPS = 8;
-constexpr int K4_TMA_WARP = 16, K4_MMA_WARP = 17;
-constexpr int K4_THREADS = 18 * 32;
-constexpr uint32_t K4_RAW_BYTES = TC_M * 144, K4_B_BYTES = 2 * TC_N * 128, K4_PLANE_BYTES = TC_M * 128;
+constexpr int K4_RING = 8;
+constexpr int K4_EXP_WARPS = 4;
+constexpr int K4_TMA_WARP = 12, K4_MMA_WARP = 13;
+constexpr int K4_THREADS = 14 * 32;
+constexpr uint32_t K4_RAW_BYTES = TC_M * 144, K4_PLANE_BYTES = TC_M * 128;
+// N: tokens per CTA tile.  The tensor core fetches its operands from shared memory at a fixed rate, so an MMA's time goes
+// with (128 + N) * 32 bytes rather than with its 128 * N * 32 multiply-adds: 128 tokens per tile amortise the three planes
+// of the weights over twice the work of 64.  Tensor memory (512 columns) holds planes * N columns per accumulator buffer:
+// two buffers for the prefill order (two planes at most), one for the decode order at N = 128 (three planes).
+template <int N>
 struct K4Smem {
-    static constexpr uint32_t RAW = 0, B = RAW + K4_IN_STAGES * K4_RAW_BYTES;       // 55,296 is a multiple of 1024
-    static constexpr uint32_t PLANES = B + K4_IN_STAGES * K4_B_BYTES;               // [2 stages][3 planes][128 x 128]
-    static constexpr uint32_t XD = PLANES + 2 * 3 * K4_PLANE_BYTES;                  // [ring][64] token scales
-    static constexpr uint32_t DD = XD + K4_RING * TC_N * 4;                          // [ring][128] d | dmin << 16
+    static constexpr uint32_t IN_STAGES = N == 64 ? 3 : 2;
+    static constexpr uint32_t B_BYTES = 2 * N * 128;
+    static constexpr uint32_t RAW = 0, B = RAW + IN_STAGES * K4_RAW_BYTES;          // a raw stage is 18 KB: B stays 1024-byte aligned
+    static constexpr uint32_t PLANES = B + IN_STAGES * B_BYTES;                     // [2 stages][3 planes][128 x 128]
+    static constexpr uint32_t XD = PLANES + 2 * 3 * K4_PLANE_BYTES;                  // [ring][N] token scales
+    static constexpr uint32_t DD = XD + K4_RING * N * 4;                             // [ring][128] d | dmin << 16
     static constexpr uint32_t BAR = DD + K4_RING * TC_M * 4;
-    static constexpr uint32_t IN_FULL = BAR, IN_EMPTY = IN_FULL + 8 * K4_IN_STAGES, PL_FULL = IN_EMPTY + 8 * K4_IN_STAGES, PL_EMPTY = PL_FULL + 16,
-                              ACC_FULL = PL_EMPTY + 16, ACC_EMPTY = ACC_FULL + 16, SLOT = ACC_EMPTY + 16, ABORT = SLOT + 8;
+    static constexpr uint32_t IN_FULL = BAR, IN_EMPTY = IN_FULL + 32, PL_FULL = IN_EMPTY + 32, PL_EMPTY = PL_FULL + 16, ACC_FULL = PL_EMPTY + 16,
+                              ACC_EMPTY = ACC_FULL + 16, SLOT = ACC_EMPTY + 16, ABORT = SLOT + 8;
     static constexpr uint32_t BYTES = ABORT + 8, ALLOC = BYTES + 1024;
 };
-static_assert((K4_IN_STAGES * K4_RAW_BYTES) % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+static_assert(K4_RAW_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+static_assert(K4Smem<128>::ALLOC <= 227 * 1024 && K4Smem<64>::ALLOC <= 227 * 1024, "shared memory plan does not fit");
 
 struct TcK4Args {
     GemvSegment seg;
@@ -287,167 +295,174 @@ struct TcK4Args {
     uint32_t n_tokens, nb;
 };
 
-template <bool GEMM>
+template <bool GEMM, int N>
 __global__ void __launch_bounds__(K4_THREADS, 1)
 gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_constant__ CUtensorMap tm_hdr, const __grid_constant__ CUtensorMap tm_x, TcK4Args a) {
+    using S = K4Smem<N>;
+    constexpr uint32_t IN_STAGES = S::IN_STAGES;
+    constexpr uint32_t MAX_PLANES = GEMM ? 2 : 3, ACC_STRIDE = MAX_PLANES * N, NBUF = 2 * ACC_STRIDE <= 512 ? 2 : 1;
+    constexpr int TPT = N / 2;  // tokens per epilogue thread
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (sbase - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * TC_N;
-    volatile uint32_t *abort = reinterpret_cast<volatile uint32_t *>(smem + K4Smem::ABORT);
+    const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * N;
+    volatile uint32_t *abort = reinterpret_cast<volatile uint32_t *>(smem + S::ABORT);
     const uint32_t nb = a.nb;
     const uint32_t n_visits = GEMM ? 2 * nb : nb;  // super-block visits; in the prefill order the first nb are the min sweep
     // planes of a visit: decode order lo, hi, min; prefill order min alone, then lo, hi
     auto n_planes = [&](uint32_t u) -> uint32_t { return GEMM ? (u < nb ? 1u : 2u) : 3u; };
-    constexpr uint32_t ACC_STRIDE = GEMM ? 128 : 192;  // tensor-memory columns per accumulator buffer
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < K4_IN_STAGES; ++s) {
-            mbar_init(sbase + K4Smem::IN_FULL + 8 * s, 1);
-            mbar_init(sbase + K4Smem::IN_EMPTY + 8 * s, 1 + K4_EXP_WARPS);  // MMA completion (activations) + the expanders (blocks)
+        for (uint32_t s = 0; s < IN_STAGES; ++s) {
+            mbar_init(sbase + S::IN_FULL + 8 * s, 1);
+            mbar_init(sbase + S::IN_EMPTY + 8 * s, 1 + K4_EXP_WARPS);  // MMA completion (activations) + the expanders (blocks)
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(sbase + K4Smem::PL_FULL + 8 * b, K4_EXP_WARPS);
-            mbar_init(sbase + K4Smem::PL_EMPTY + 8 * b, 1);
-            mbar_init(sbase + K4Smem::ACC_FULL + 8 * b, 1);
-            mbar_init(sbase + K4Smem::ACC_EMPTY + 8 * b, TC_EPI_WARPS);
+            mbar_init(sbase + S::PL_FULL + 8 * b, K4_EXP_WARPS);
+            mbar_init(sbase + S::PL_EMPTY + 8 * b, 1);
+            mbar_init(sbase + S::ACC_FULL + 8 * b, 1);
+            mbar_init(sbase + S::ACC_EMPTY + 8 * b, TC_EPI_WARPS);
         }
         *abort = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == K4_MMA_WARP) tmem_alloc(sbase + K4Smem::SLOT, 512);
+    if (warp == K4_MMA_WARP) tmem_alloc(sbase + S::SLOT, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(smem + K4Smem::SLOT);
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(smem + S::SLOT);
 
     if (warp == K4_TMA_WARP) {
         if (lane == 0) {
             for (uint32_t u = 0; u < n_visits; ++u) {
-                const uint32_t slot = u % K4_IN_STAGES, s = u % nb;
+                const uint32_t slot = u % IN_STAGES, s = u % nb;
                 const bool min_sweep = GEMM && u < nb;
-                if (u >= K4_IN_STAGES && !mbar_wait(sbase + K4Smem::IN_EMPTY + 8 * slot, ((u / K4_IN_STAGES) & 1u) ^ 1u, abort)) break;
-                const uint32_t full = sbase + K4Smem::IN_FULL + 8 * slot;
-                mbar_expect_tx(full, (min_sweep ? TC_M * 16u : K4_RAW_BYTES) + K4_B_BYTES);
-                if (min_sweep) tma_load_2d(sbase + K4Smem::RAW + slot * K4_RAW_BYTES, &tm_hdr, (int32_t)(s * 144), (int32_t)row0, full);  // the 16-byte headers
-                else tma_load_2d(sbase + K4Smem::RAW + slot * K4_RAW_BYTES, &tm_raw, (int32_t)(s * 144), (int32_t)row0, full);
-                tma_load_2d(sbase + K4Smem::B + slot * K4_B_BYTES, &tm_x, (int32_t)(s * 256), (int32_t)tok0, full);
-                tma_load_2d(sbase + K4Smem::B + slot * K4_B_BYTES + TC_N * 128, &tm_x, (int32_t)(s * 256 + 128), (int32_t)tok0, full);
+                if (u >= IN_STAGES && !mbar_wait(sbase + S::IN_EMPTY + 8 * slot, ((u / IN_STAGES) & 1u) ^ 1u, abort)) break;
+                const uint32_t full = sbase + S::IN_FULL + 8 * slot;
+                mbar_expect_tx(full, (min_sweep ? TC_M * 16u : K4_RAW_BYTES) + S::B_BYTES);
+                if (min_sweep) tma_load_2d(sbase + S::RAW + slot * K4_RAW_BYTES, &tm_hdr, (int32_t)(s * 144), (int32_t)row0, full);  // the 16-byte headers
+                else tma_load_2d(sbase + S::RAW + slot * K4_RAW_BYTES, &tm_raw, (int32_t)(s * 144), (int32_t)row0, full);
+                tma_load_2d(sbase + S::B + slot * S::B_BYTES, &tm_x, (int32_t)(s * 256), (int32_t)tok0, full);
+                tma_load_2d(sbase + S::B + slot * S::B_BYTES + N * 128, &tm_x, (int32_t)(s * 256 + 128), (int32_t)tok0, full);
             }
         }
     } else if (warp == K4_MMA_WARP) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_i8(0, 1, TC_N);  // unsigned planes x signed activations
+            constexpr uint32_t idesc = umma_idesc_i8(0, 1, N);  // unsigned planes x signed activations
             bool ok = true;
             for (uint32_t u = 0; u < n_visits && ok; ++u) {
-                const uint32_t slot = u % K4_IN_STAGES, buf = u & 1u, np = n_planes(u);
+                const uint32_t slot = u % IN_STAGES, buf = u % NBUF, np = n_planes(u);
                 for (uint32_t h = 0; h < 2; ++h) {
                     const uint32_t v = 2 * u + h, ps = v & 1u;
-                    if (!(ok = mbar_wait(sbase + K4Smem::PL_FULL + 8 * ps, (v / 2) & 1u, abort))) break;
+                    if (!(ok = mbar_wait(sbase + S::PL_FULL + 8 * ps, (v / 2) & 1u, abort))) break;
                     if (h == 0) {
-                        if (!(ok = mbar_wait(sbase + K4Smem::IN_FULL + 8 * slot, (u / K4_IN_STAGES) & 1u, abort))) break;
-                        if (u >= 2 && !(ok = mbar_wait(sbase + K4Smem::ACC_EMPTY + 8 * buf, ((u / 2) & 1u) ^ 1u, abort))) break;
+                        if (!(ok = mbar_wait(sbase + S::IN_FULL + 8 * slot, (u / IN_STAGES) & 1u, abort))) break;
+                        if (u >= NBUF && !(ok = mbar_wait(sbase + S::ACC_EMPTY + 8 * buf, ((u / NBUF) & 1u) ^ 1u, abort))) break;
                     }
                     tc_fence_after();
-                    const uint64_t db = umma_desc_sw128(sbase + K4Smem::B + slot * K4_B_BYTES + h * TC_N * 128);
+                    const uint64_t db = umma_desc_sw128(sbase + S::B + slot * S::B_BYTES + h * N * 128);
                     for (uint32_t p = 0; p < np; ++p) {
-                        const uint64_t da = umma_desc_sw128(sbase + K4Smem::PLANES + (ps * 3 + p) * K4_PLANE_BYTES);
+                        const uint64_t da = umma_desc_sw128(sbase + S::PLANES + (ps * 3 + p) * K4_PLANE_BYTES);
 #pragma unroll
-                        for (uint32_t k = 0; k < 4; ++k) umma_i8(tmem + buf * ACC_STRIDE + p * TC_N, da + 2 * k, db + 2 * k, idesc, (h | k) ? 1u : 0u);
+                        for (uint32_t k = 0; k < 4; ++k) umma_i8(tmem + buf * ACC_STRIDE + p * N, da + 2 * k, db + 2 * k, idesc, (h | k) ? 1u : 0u);
                     }
-                    umma_commit(sbase + K4Smem::PL_EMPTY + 8 * ps);
+                    umma_commit(sbase + S::PL_EMPTY + 8 * ps);
                     if (h == 1) {
-                        umma_commit(sbase + K4Smem::IN_EMPTY + 8 * slot);
-                        umma_commit(sbase + K4Smem::ACC_FULL + 8 * buf);
+                        umma_commit(sbase + S::IN_EMPTY + 8 * slot);
+                        umma_commit(sbase + S::ACC_FULL + 8 * buf);
                     }
                 }
             }
         }
     } else if (warp >= TC_EPI_WARPS) {
-        // ---- expanders: thread = (row, 64 elements) of the half super-block in flight
-        const uint32_t et = threadIdx.x - TC_EPI_WARPS * 32, r = et >> 1, gl = et & 1u;
+        // ---- expanders: thread = one row of the half super-block in flight (two runs of 64 elements)
+        const uint32_t r = threadIdx.x - TC_EPI_WARPS * 32;
         const uint32_t swz = r & 7u, row_off = (r >> 3) * 1024 + swz * 128;
         bool ok = true;
         for (uint32_t u = 0; u < n_visits && ok; ++u) {
-            const uint32_t slot = u % K4_IN_STAGES, s = u % nb;
+            const uint32_t slot = u % IN_STAGES, s = u % nb;
             const bool min_sweep = GEMM && u < nb, main_sweep = GEMM && u >= nb;
-            if (!(ok = mbar_wait(sbase + K4Smem::IN_FULL + 8 * slot, (u / K4_IN_STAGES) & 1u, abort))) break;
-            const uint8_t *raw = smem + K4Smem::RAW + slot * K4_RAW_BYTES + r * (min_sweep ? 16u : 144u);
+            if (!(ok = mbar_wait(sbase + S::IN_FULL + 8 * slot, (u / IN_STAGES) & 1u, abort))) break;
+            const uint8_t *raw = smem + S::RAW + slot * K4_RAW_BYTES + r * (min_sweep ? 16u : 144u);
             const uint4 hd = *reinterpret_cast<const uint4 *>(raw);
-            if (gl == 0) reinterpret_cast<uint32_t *>(smem + K4Smem::DD)[(u % K4_RING) * TC_M + r] = hd.x;
-            if (et < TC_N) {
-                const uint32_t tok = tok0 + et;
-                reinterpret_cast<float *>(smem + K4Smem::XD)[(u % K4_RING) * TC_N + et] = tok < a.n_tokens ? __ldg(a.act_d + (uint64_t)tok * a.act_d_pitch + s) : 0.0f;
+            reinterpret_cast<uint32_t *>(smem + S::DD)[(u % K4_RING) * TC_M + r] = hd.x;
+            if (r < (uint32_t)N) {
+                const uint32_t tok = tok0 + r;
+                reinterpret_cast<float *>(smem + S::XD)[(u % K4_RING) * N + r] = tok < a.n_tokens ? __ldg(a.act_d + (uint64_t)tok * a.act_d_pitch + s) : 0.0f;
             }
             // the eight 6-bit scales and mins (engine/quant.rs:653-662) as bytes of two words each
             const uint32_t scl = hd.y & 0x3f3f3f3fu, ml = hd.z & 0x3f3f3f3fu;
             const uint32_t sch = (hd.w & 0x0f0f0f0fu) | ((hd.y >> 2) & 0x30303030u), mh = ((hd.w >> 4) & 0x0f0f0f0fu) | ((hd.z >> 2) & 0x30303030u);
             for (uint32_t h = 0; h < 2; ++h) {
-                const uint32_t v = 2 * u + h, ps = v & 1u, g = 2 * h + gl;  // 64 elements 64 g .. of the super-block: sub-blocks 2g (low nibbles), 2g + 1 (high)
-                if (v >= 2 && !(ok = mbar_wait(sbase + K4Smem::PL_EMPTY + 8 * ps, ((v / 2) & 1u) ^ 1u, abort))) break;
-                const uint32_t scw = g < 2 ? scl : sch, mw = g < 2 ? ml : mh, sh = 16 * (g & 1u);
-                const uint32_t sa = (scw >> sh) & 0xffu, sb = (scw >> (sh + 8)) & 0xffu, ma = (mw >> sh) & 0xffu, mb = (mw >> (sh + 8)) & 0xffu;
-                uint8_t *pl = smem + K4Smem::PLANES + ps * 3 * K4_PLANE_BYTES + row_off;
-                // 16-byte chunks 4 gl .. 4 gl + 3 of the row's 128 bytes, swizzled: low-nibble sub-block in the first two, high in the last two
-                const uint32_t c0 = ((4 * gl + 0) ^ swz) * 16, c1 = ((4 * gl + 1) ^ swz) * 16, c2 = ((4 * gl + 2) ^ swz) * 16, c3 = ((4 * gl + 3) ^ swz) * 16;
-                if (!min_sweep) {
-                    const uint4 qa = *reinterpret_cast<const uint4 *>(raw + 16 + 32 * g), qb = *reinterpret_cast<const uint4 *>(raw + 32 + 32 * g);
-                    const uint32_t M = 0x0f0f0f0fu;
-                    const uint32_t la[8] = {qa.x & M, qa.y & M, qa.z & M, qa.w & M, qb.x & M, qb.y & M, qb.z & M, qb.w & M};
-                    const uint32_t ha[8] = {(qa.x >> 4) & M, (qa.y >> 4) & M, (qa.z >> 4) & M, (qa.w >> 4) & M, (qb.x >> 4) & M, (qb.y >> 4) & M, (qb.z >> 4) & M, (qb.w >> 4) & M};
-                    const uint32_t sal = sa & 7u, sah = sa >> 3, sbl = sb & 7u, sbh = sb >> 3;
-                    uint8_t *plo = pl, *phi = pl + K4_PLANE_BYTES;
-                    // four codes (each <= 15) times a digit (<= 7) in one multiply: no byte reaches 256
-                    *reinterpret_cast<uint4 *>(plo + c0) = make_uint4(la[0] * sal, la[1] * sal, la[2] * sal, la[3] * sal);
-                    *reinterpret_cast<uint4 *>(plo + c1) = make_uint4(la[4] * sal, la[5] * sal, la[6] * sal, la[7] * sal);
-                    *reinterpret_cast<uint4 *>(plo + c2) = make_uint4(ha[0] * sbl, ha[1] * sbl, ha[2] * sbl, ha[3] * sbl);
-                    *reinterpret_cast<uint4 *>(plo + c3) = make_uint4(ha[4] * sbl, ha[5] * sbl, ha[6] * sbl, ha[7] * sbl);
-                    *reinterpret_cast<uint4 *>(phi + c0) = make_uint4(la[0] * sah, la[1] * sah, la[2] * sah, la[3] * sah);
-                    *reinterpret_cast<uint4 *>(phi + c1) = make_uint4(la[4] * sah, la[5] * sah, la[6] * sah, la[7] * sah);
-                    *reinterpret_cast<uint4 *>(phi + c2) = make_uint4(ha[0] * sbh, ha[1] * sbh, ha[2] * sbh, ha[3] * sbh);
-                    *reinterpret_cast<uint4 *>(phi + c3) = make_uint4(ha[4] * sbh, ha[5] * sbh, ha[6] * sbh, ha[7] * sbh);
-                }
-                if (!main_sweep) {
-                    uint8_t *pm = pl + (GEMM ? 0u : 2u * K4_PLANE_BYTES);
-                    const uint32_t wa = ma * 0x01010101u, wb = mb * 0x01010101u;
-                    *reinterpret_cast<uint4 *>(pm + c0) = make_uint4(wa, wa, wa, wa);
-                    *reinterpret_cast<uint4 *>(pm + c1) = make_uint4(wa, wa, wa, wa);
-                    *reinterpret_cast<uint4 *>(pm + c2) = make_uint4(wb, wb, wb, wb);
-                    *reinterpret_cast<uint4 *>(pm + c3) = make_uint4(wb, wb, wb, wb);
+                const uint32_t v = 2 * u + h, ps = v & 1u;
+                if (v >= 2 && !(ok = mbar_wait(sbase + S::PL_EMPTY + 8 * ps, ((v / 2) & 1u) ^ 1u, abort))) break;
+                uint8_t *pl = smem + S::PLANES + ps * 3 * K4_PLANE_BYTES + row_off;
+#pragma unroll
+                for (uint32_t gl = 0; gl < 2; ++gl) {
+                    const uint32_t g = 2 * h + gl;  // 64 elements 64 g .. of the super-block: sub-blocks 2g (low nibbles), 2g + 1 (high)
+                    const uint32_t scw = h == 0 ? scl : sch, mw = h == 0 ? ml : mh, sh = 16 * gl;
+                    const uint32_t sa = (scw >> sh) & 0xffu, sb = (scw >> (sh + 8)) & 0xffu, ma = (mw >> sh) & 0xffu, mb = (mw >> (sh + 8)) & 0xffu;
+                    // 16-byte chunks 4 gl .. 4 gl + 3 of the row's 128 bytes, swizzled: low-nibble sub-block in the first two, high in the last two
+                    const uint32_t c0 = ((4 * gl + 0) ^ swz) * 16, c1 = ((4 * gl + 1) ^ swz) * 16, c2 = ((4 * gl + 2) ^ swz) * 16, c3 = ((4 * gl + 3) ^ swz) * 16;
+                    if (!min_sweep) {
+                        const uint4 qa = *reinterpret_cast<const uint4 *>(raw + 16 + 32 * g), qb = *reinterpret_cast<const uint4 *>(raw + 32 + 32 * g);
+                        const uint32_t M = 0x0f0f0f0fu;
+                        const uint32_t la[8] = {qa.x & M, qa.y & M, qa.z & M, qa.w & M, qb.x & M, qb.y & M, qb.z & M, qb.w & M};
+                        const uint32_t ha[8] = {(qa.x >> 4) & M, (qa.y >> 4) & M, (qa.z >> 4) & M, (qa.w >> 4) & M, (qb.x >> 4) & M, (qb.y >> 4) & M, (qb.z >> 4) & M, (qb.w >> 4) & M};
+                        const uint32_t sal = sa & 7u, sah = sa >> 3, sbl = sb & 7u, sbh = sb >> 3;
+                        uint8_t *plo = pl, *phi = pl + K4_PLANE_BYTES;
+                        // four codes (each <= 15) times a digit (<= 7) in one multiply: no byte reaches 256
+                        *reinterpret_cast<uint4 *>(plo + c0) = make_uint4(la[0] * sal, la[1] * sal, la[2] * sal, la[3] * sal);
+                        *reinterpret_cast<uint4 *>(plo + c1) = make_uint4(la[4] * sal, la[5] * sal, la[6] * sal, la[7] * sal);
+                        *reinterpret_cast<uint4 *>(plo + c2) = make_uint4(ha[0] * sbl, ha[1] * sbl, ha[2] * sbl, ha[3] * sbl);
+                        *reinterpret_cast<uint4 *>(plo + c3) = make_uint4(ha[4] * sbl, ha[5] * sbl, ha[6] * sbl, ha[7] * sbl);
+                        *reinterpret_cast<uint4 *>(phi + c0) = make_uint4(la[0] * sah, la[1] * sah, la[2] * sah, la[3] * sah);
+                        *reinterpret_cast<uint4 *>(phi + c1) = make_uint4(la[4] * sah, la[5] * sah, la[6] * sah, la[7] * sah);
+                        *reinterpret_cast<uint4 *>(phi + c2) = make_uint4(ha[0] * sbh, ha[1] * sbh, ha[2] * sbh, ha[3] * sbh);
+                        *reinterpret_cast<uint4 *>(phi + c3) = make_uint4(ha[4] * sbh, ha[5] * sbh, ha[6] * sbh, ha[7] * sbh);
+                    }
+                    if (!main_sweep) {
+                        uint8_t *pm = pl + (GEMM ? 0u : 2u * K4_PLANE_BYTES);
+                        const uint32_t wa = ma * 0x01010101u, wb = mb * 0x01010101u;
+                        *reinterpret_cast<uint4 *>(pm + c0) = make_uint4(wa, wa, wa, wa);
+                        *reinterpret_cast<uint4 *>(pm + c1) = make_uint4(wa, wa, wa, wa);
+                        *reinterpret_cast<uint4 *>(pm + c2) = make_uint4(wb, wb, wb, wb);
+                        *reinterpret_cast<uint4 *>(pm + c3) = make_uint4(wb, wb, wb, wb);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads these planes through the async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sbase + K4Smem::PL_FULL + 8 * ps);
+                if (lane == 0) mbar_arrive(sbase + S::PL_FULL + 8 * ps);
             }
             if (!ok) break;
             __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + K4Smem::IN_EMPTY + 8 * slot);  // this warp is done with the blocks of the visit
+            if (lane == 0) mbar_arrive(sbase + S::IN_EMPTY + 8 * slot);  // this warp is done with the blocks of the visit
         }
     } else {
-        // ---- epilogue: thread = one row x 32 tokens
+        // ---- epilogue: thread = one row x N / 2 tokens
         const uint32_t quad = warp & 3u, half = warp >> 2, rl = quad * 32 + lane;
         const uint32_t row = row0 + rl;
         const bool row_ok = row < a.seg.w.out_dim;
-        float acc[32];
+        float acc[TPT];
 #pragma unroll
-        for (int t = 0; t < 32; ++t) acc[t] = 0.0f;
+        for (int t = 0; t < TPT; ++t) acc[t] = 0.0f;
         for (uint32_t u = 0; u < n_visits; ++u) {
-            const uint32_t buf = u & 1u, ring = u % K4_RING;
+            const uint32_t buf = u % NBUF, ring = u % K4_RING;
             const bool min_sweep = GEMM && u < nb;
-            if (!mbar_wait(sbase + K4Smem::ACC_FULL + 8 * buf, (u / 2) & 1u, abort)) break;
+            if (!mbar_wait(sbase + S::ACC_FULL + 8 * buf, (u / NBUF) & 1u, abort)) break;
             tc_fence_after();
-            const uint32_t dw = reinterpret_cast<const uint32_t *>(smem + K4Smem::DD)[ring * TC_M + rl];
+            const uint32_t dw = reinterpret_cast<const uint32_t *>(smem + S::DD)[ring * TC_M + rl];
             const float d = f16_bits_to_f32(dw & 0xffffu), dmin = f16_bits_to_f32(dw >> 16);
-            const float *xd = reinterpret_cast<const float *>(smem + K4Smem::XD) + ring * TC_N + half * 32;
-            const uint32_t tbase = tmem + ((quad * 32) << 16) + buf * ACC_STRIDE + half * 32;
+            const float *xd = reinterpret_cast<const float *>(smem + S::XD) + ring * N + half * TPT;
+            const uint32_t tbase = tmem + ((quad * 32) << 16) + buf * ACC_STRIDE + half * TPT;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {  // 16 tokens at a time
+            for (int c = 0; c < TPT / 16; ++c) {  // 16 tokens at a time
                 uint32_t p0[16], p1[16], p2[16];
                 tmem_ld16(tbase + c * 16, p0);
-                if (!GEMM || !min_sweep) tmem_ld16(tbase + TC_N + c * 16, p1);
-                if (!GEMM) tmem_ld16(tbase + 2 * TC_N + c * 16, p2);
+                if (!GEMM || !min_sweep) tmem_ld16(tbase + N + c * 16, p1);
+                if (!GEMM) tmem_ld16(tbase + 2 * N + c * 16, p2);
                 tmem_ld_wait();
 #pragma unroll
                 for (int t = 0; t < 16; ++t) {
@@ -466,12 +481,12 @@ gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_con
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sbase + K4Smem::ACC_EMPTY + 8 * buf);
+            if (lane == 0) mbar_arrive(sbase + S::ACC_EMPTY + 8 * buf);
         }
         if (!*abort && row_ok) {
 #pragma unroll
-            for (int t = 0; t < 32; ++t) {
-                const uint32_t tok = tok0 + half * 32 + t;
+            for (int t = 0; t < TPT; ++t) {
+                const uint32_t tok = tok0 + half * TPT + t;
                 if (tok < a.n_tokens) {
                     const uint64_t o = (uint64_t)tok * a.seg.y_stride + row;
                     float v = acc[t];
@@ -524,6 +539,12 @@ bool gemm_tc5_supported(const GemvArgs &a) {
         if (in_dim % 128 || a.act.dim_cap % 128) return false;
     } else if (type == TYPE_Q4_K) {
         if (in_dim % 256 || a.act.dim_cap % 16) return false;
+        // A CTA owns 128 rows x 64 or 128 tokens and walks the whole row (the fp32 order forbids splitting K), so a small
+        // matrix at a small batch gives too few CTAs: the 64-row mma.sync tiles (gemm_mma.cu) fill the GPU better there.
+        uint32_t ctas = 0;
+        const uint32_t tok_tile = a.n_tokens > 64 ? 128 : 64;
+        for (int s = 0; s < a.n_seg; ++s) ctas += ((a.seg[s].w.out_dim + TC_M - 1) / TC_M) * ((a.n_tokens + tok_tile - 1) / tok_tile);
+        if (ctas < 96) return false;
     } else {
         return false;  // Q6_K stays on the mma.sync tiles (gemm_mma.cu)
     }
@@ -532,16 +553,13 @@ bool gemm_tc5_supported(const GemvArgs &a) {
     return true;
 }
 
-static bool launch_q4k(const GemvArgs &a, cudaStream_t st) {
+template <bool GEMM, int N>
+static bool launch_q4k_instance(const GemvArgs &a, cudaStream_t st) {
     static PerDeviceOnce once;
-    if (once.run([] {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc5_q4k_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem::ALLOC);
-            return e != cudaSuccess ? e : cudaFuncSetAttribute(gemm_tc5_q4k_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem::ALLOC);
-        }) != cudaSuccess)
-        return false;
+    if (once.run([] { return cudaFuncSetAttribute(gemm_tc5_q4k_kernel<GEMM, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem<N>::ALLOC); }) != cudaSuccess) return false;
     const uint32_t in_dim = a.seg[0].w.in_dim, nb = in_dim / 256;
     CUtensorMap tm_x;
-    if (!make_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.act.q, in_dim, a.n_tokens, a.act.dim_cap, 128, TC_N, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.act.q, in_dim, a.n_tokens, a.act.dim_cap, 128, N, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
     for (int s = 0; s < a.n_seg; ++s) {
         const GemvSegment &g = a.seg[s];
         CUtensorMap tm_raw, tm_hdr;
@@ -553,12 +571,17 @@ static bool launch_q4k(const GemvArgs &a, cudaStream_t st) {
         k.act_d_pitch = a.act.dim_cap / 256;
         k.n_tokens = a.n_tokens;
         k.nb = nb;
-        const dim3 grid((g.w.out_dim + TC_M - 1) / TC_M, (a.n_tokens + TC_N - 1) / TC_N);
-        if (a.gemm_order) gemm_tc5_q4k_kernel<true><<<grid, K4_THREADS, K4Smem::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
-        else gemm_tc5_q4k_kernel<false><<<grid, K4_THREADS, K4Smem::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
+        const dim3 grid((g.w.out_dim + TC_M - 1) / TC_M, (a.n_tokens + N - 1) / N);
+        gemm_tc5_q4k_kernel<GEMM, N><<<grid, K4_THREADS, K4Smem<N>::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
         g_tc5_launched.store(true, std::memory_order_relaxed);
     }
     return true;
+}
+
+static bool launch_q4k(const GemvArgs &a, cudaStream_t st) {
+    const bool wide = a.n_tokens > 64;  // 128-token tiles once there are tokens for them
+    if (a.gemm_order) return wide ? launch_q4k_instance<true, 128>(a, st) : launch_q4k_instance<true, 64>(a, st);
+    return wide ? launch_q4k_instance<false, 128>(a, st) : launch_q4k_instance<false, 64>(a, st);
 }
 
 bool launch_gemm_tc5(const GemvArgs &a, int sm_count, cudaStream_t st) {
