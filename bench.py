@@ -132,11 +132,11 @@ def model_config(args):
 
 
 def build_tensors(cfg, rank: int, world: int, barrier):
-    """Seeded synthetic tensors.  The generator is deterministic, so with several ranks every rank makes its own copy
-    (the library keeps only the rank's slices on the device)."""
+    """Seeded synthetic tensors.  The generator is counter-based, so with several ranks every rank makes only its own
+    tensor-parallel shards (the same bytes the whole tensors hold there) and hands them over as they are (tp_presliced)."""
     from orangu_b200 import synth
 
-    return synth.model_tensors(cfg, seed=20240)
+    return synth.model_tensors(cfg, seed=20240, tp=(rank, world) if world > 1 else None)
 
 
 def algorithmic_bytes_per_token(cfg, context: int) -> int:
@@ -151,6 +151,107 @@ def algorithmic_bytes_per_token(cfg, context: int) -> int:
     layer = q4(qd, e) + q4(kvd, e) + q6(kvd, e) + q4(e, qd) + 2 * q4(ff, e) + q4(e, ff) + 2 * e * 4
     return cfg["n_layer"] * layer + q6(V, e) + e * 4 + 2 * kvd * 2 * cfg["n_layer"] * context
 
+
+
+# ---------------------------------------------------------------------------------------- single products (configs 1 and 2)
+def operator_gemv_rooflines(be, peak):
+    """The Backend::matmul operator at one token on device-resident buffers: BASELINE.json's single Q8_0 GEMV (4096 x 4096) and
+    the Q4_K / Q6_K sweep shapes.  A single product moves 10-50 MB -- a few microseconds -- so it is timed inside a CUDA graph
+    of `reps` back-to-back launches; the launches rotate over enough copies of the matrix to exceed the 126 MB L2, so every
+    launch reads its weights from HBM.  Algorithmic bytes = GGUF bytes of the matrix + the fp32 input and output vectors."""
+    import torch
+
+    from orangu_b200 import QuantMatrix, capi, synth
+    from orangu_b200.backend import tensor_byte_size
+
+    L = capi.load()
+    out = {}
+    cases = [("config 1: Q8_0 4096x4096", 8, 4096, 4096)] + [
+        (f"config 2: {'Q4_K' if t == 12 else 'Q6_K'} {o}x{i}", t, o, i) for t in (12, 14) for (o, i) in ((4096, 4096), (14336, 4096), (4096, 14336))]
+    stream = torch.cuda.Stream()
+    for name, t, out_dim, in_dim in cases:
+        wbytes = out_dim * tensor_byte_size(t, in_dim)
+        copies = max(2, -(-160_000_000 // wbytes))
+        mats = [synth.matrix(t, out_dim, in_dim, 900 + c) for c in range(copies)]
+        handles = [be._weight(QuantMatrix(m["data"], t, in_dim, out_dim)) for m in mats]
+        x = torch.randn(in_dim, device="cuda", dtype=torch.float32)
+        y = torch.empty(out_dim, device="cuda", dtype=torch.float32)
+        reps = 4 * copies
+        with torch.cuda.stream(stream):
+            for h in handles:  # warm-up outside capture: scratch allocation, one-time kernel attributes
+                capi.check(be._h, L.ob_matmul_device(be._h, x.data_ptr(), 1, h, y.data_ptr(), 0, stream.cuda_stream))
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for r in range(reps):
+                    capi.check(be._h, L.ob_matmul_device(be._h, x.data_ptr(), 1, handles[r % copies], y.data_ptr(), 0, stream.cuda_stream))
+            g.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (5 * reps)
+        nbytes = wbytes + 4 * (in_dim + out_dim)
+        out[name] = {"avg_launch_us": us, "algorithmic_bytes": nbytes, "GB/s": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
+                     "timed": f"CUDA graph of {reps} products rotating over {copies} copies of the matrix ({copies * wbytes / 1e6:.0f} MB > L2), 5 replays",
+                     "kernels_per_product": 1 if t != 8 else 2}
+        for h in handles:
+            L.ob_weight_release(be._h, h)
+            be._weights.remove(h)
+    return out
+
+
+# ---------------------------------------------------------------------------------------- 70B shape under tensor parallel
+def run_70b(be, rank, world, uid, barrier, max_over_ranks, peak):
+    """BASELINE.json's last configuration: 70B-shape Q4_K_M decoder (80 layers, d_model 8192, 64 query / 8 KV heads, FFN 28672),
+    tensor parallel over this run's GPUs, batch-1 and batch-32 greedy decode at an 8192-token context.  Every rank generates
+    only its own shards.  Reports tokens/s (device time, max over ranks) and the per-GPU fraction of the HBM roofline."""
+    import orangu_b200
+    from orangu_b200 import synth
+
+    cfg = dict(synth.CONFIGS["70b"])
+    ctx_len, steps1, steps32, n_seq = 8192, 8, 4, 32
+    t0 = time.time()
+    tensors = synth.model_tensors(cfg, seed=20270, tp=(rank, world))
+    t_gen = time.time() - t0
+    per_seq = ctx_len + 64
+    model = orangu_b200.LlamaModel(be, cfg, tensors, max_seq_len=per_seq, max_batch_tokens=512, kv_pool_tokens=n_seq * per_seq + 64,
+                                   tp_rank=rank, tp_size=world, tp_unique_id=uid, tp_presliced=True)
+    del tensors
+    kv = model.new_kv_cache(per_seq)
+    prompt = np.random.default_rng(13).integers(0, cfg["n_vocab"], ctx_len).astype(np.uint32)
+    t0 = time.time()
+    first = model.forward_maybe_sampling(kv, prompt, 0)
+    t_prefill = time.time() - t0
+    model.decode_loop([kv], [first], 3)
+    barrier()
+    model.decode_loop([kv], [int(first)], steps1)
+    ms1 = max_over_ranks(be.last_device_ms()) / steps1
+    kv.truncate(ctx_len)
+    caches = [kv]
+    for _ in range(n_seq - 1):
+        c = model.new_kv_cache(per_seq)
+        c.copy_prefix_from(kv, ctx_len)
+        caches.append(c)
+    firsts = [int(first)] * n_seq
+    model.decode_loop(caches, firsts, 2)
+    barrier()
+    model.decode_loop(caches, firsts, steps32)
+    ms32 = max_over_ranks(be.last_device_ms()) / steps32
+    w_bytes = algorithmic_bytes_per_token(cfg, 0)
+    kv_bytes = algorithmic_bytes_per_token(cfg, ctx_len) - w_bytes
+    out = {"workload": "70B-shape Llama decoder, Q4_K_M (Q6_K output and attn_v), 80 layers, context 8192 prefilled through the library",
+           "parallelism": f"tp{world}", "setup_s": {"synthetic_shards": round(t_gen, 1), "prefill_8192": round(t_prefill, 1)},
+           "batch1": {"value": 1e3 / ms1, "unit": UNIT, "ms_per_step": ms1, "steps": steps1,
+                      "hbm_frac_per_gpu": (w_bytes + kv_bytes) / world / (ms1 * 1e-3) / 1e9 / peak},
+           "batch32": {"value": n_seq * 1e3 / ms32, "unit": UNIT, "ms_per_step": ms32, "steps": steps32, "sequences": n_seq,
+                       "kv": "31 sequences share the first one's prefilled pages by device copy (KvCache::copy_prefix_from)",
+                       "hbm_frac_per_gpu": (w_bytes + n_seq * kv_bytes) / world / (ms32 * 1e-3) / 1e9 / peak}}
+    model.close()
+    return out
 
 # ---------------------------------------------------------------------------------------- CPU arm
 def cpu_decode_tokens_per_s(cfg, tensors, budget_s: float, max_tokens: int):
@@ -205,7 +306,7 @@ def run_reference(args, rank: int, world: int):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": f"{args.model}-shape Q4_K_M decode, batch 1, CPU path of the reference restated in C++ (oracle/); no Rust toolchain here",
-                   "n_layer": cfg["n_layer"], "host_cores": cores},
+                   "n_layer": cfg["n_layer"], "host_cores": cores, "context": f"{4 + args.warmup}..{4 + args.warmup + args.steps} positions (a 4-token prompt; the GPU arm decodes at {args.context})"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -254,8 +355,11 @@ def main():
     t_build = time.time() - t_build
 
     be = orangu_b200.CudaBackend.init(local_rank)
-    uid = None
-    if world > 1:
+
+    def make_uid():
+        """A fresh communicator id from rank 0, the same 128 bytes on every rank."""
+        if world == 1:
+            return None
         buf = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             import ctypes as C
@@ -264,7 +368,9 @@ def main():
             capi.check(None, capi.load().ob_tp_unique_id(cbuf))
             buf.copy_(torch.tensor(list(cbuf), dtype=torch.uint8))
         dist.broadcast(buf, 0)
-        uid = bytes(buf.cpu().tolist())
+        return bytes(buf.cpu().tolist())
+
+    uid = make_uid()
 
     ctx_len, K, W = args.context, args.steps, args.warmup
     b64 = args.batch64_steps
@@ -272,7 +378,7 @@ def main():
     per_seq = ctx_len + margin
     model = orangu_b200.LlamaModel(be, cfg, tensors, max_seq_len=per_seq, max_batch_tokens=512,
                                    kv_pool_tokens=per_seq + (63 * (ctx_len + b64 + 64 + 16) if b64 else 0) + 64,
-                                   tp_rank=rank, tp_size=world, tp_unique_id=uid)
+                                   tp_rank=rank, tp_size=world, tp_unique_id=uid, tp_presliced=world > 1)
     kv = model.new_kv_cache(per_seq)
     prompt = np.random.default_rng(11).integers(0, cfg["n_vocab"], ctx_len).astype(np.uint32)
     t_prefill = time.time()
@@ -311,35 +417,31 @@ def main():
     peak, peak_kind = measured_peak_gbs()
     iters = 20
     step_bytes = algorithmic_bytes_per_token(cfg, len(kv)) // world
-    kernels = None
-    if world == 1:
-        # the fused decode kernels, each timed back to back over all layers (every launch streams its own layer's weights);
-        # the gate/up kernel carries 43% of a token's bytes and is the one reported
-        names = {1: "attn_q/k/v + RoPE + KV append", 2: "attn_output + residual", 3: "ffn_gate + ffn_up + SwiGLU + int8 output",
-                 4: "ffn_down + residual", 5: "output projection"}
-        kernels = {}
-        for v in (1, 2, 3, 4, 5):
-            ms, nbytes, nl = model.profile_gemv(12, iters, v)
-            us = ms * 1e3 / (iters * nl)
-            kernels[names[v]] = {"avg_launch_us": us, "algorithmic_bytes_per_launch": nbytes // nl, "GB/s": nbytes / nl / us / 1e3,
-                                 "launches_per_token": nl}
-        dom = kernels[names[3]]
-        kname, per_launch_s, bytes_per_launch, timed = "stream_gemv_kernel<16, Q4_K> (" + names[3] + ")", dom["avg_launch_us"] * 1e-6, dom["algorithmic_bytes_per_launch"], iters * cfg["n_layer"]
-    else:
-        ms, nbytes, nl = model.profile_gemv(12, iters)
-        kname, per_launch_s, bytes_per_launch, timed = "gemv_kernel<Q4_K, 1 token>", ms * 1e-3 / (iters * nl), nbytes // nl, iters * nl
+    # the fused decode kernels, each timed back to back over all layers (every launch streams its own layer's weights; on
+    # several GPUs: this rank's slices); the gate/up kernel carries 43% of a token's bytes and is the one reported
+    names = {1: "attn_q/k/v + RoPE + KV append", 2: "attn_output + residual", 3: "ffn_gate + ffn_up + SwiGLU + int8 output",
+             4: "ffn_down + residual", 5: "output projection"}
+    kernels = {}
+    for v in (1, 2, 3, 4, 5):
+        ms, nbytes, nl = model.profile_gemv(12, iters, v)
+        us = max_over_ranks(ms * 1e3 / (iters * nl))
+        kernels[names[v]] = {"avg_launch_us": us, "algorithmic_bytes_per_launch": nbytes // nl, "GB/s": nbytes / nl / us / 1e3,
+                             "frac": nbytes / nl / us / 1e3 / peak, "launches_per_token": nl}
+    dom = kernels[names[3]]
+    kname = "stream_gemv_kernel<lanes per row pair 32, Q4_K> (" + names[3] + ")"
+    per_launch_s, bytes_per_launch, timed = dom["avg_launch_us"] * 1e-6, dom["algorithmic_bytes_per_launch"], iters * cfg["n_layer"]
     achieved = bytes_per_launch / per_launch_s / 1e9
-    # DRAM read + write bytes of one launch of the gate/up kernel of the 8B shape, taken from an ncu capture of this kernel
-    # on a two-layer model of the same shape (dram__bytes_read.sum + dram__bytes_write.sum; a capture cannot run inside a
-    # timed bench)
+    # DRAM read + write bytes of one launch of the gate/up kernel of the 8B shape on one GPU, from the ncu capture of this kernel on
+    # a two-layer model of the same shape (a capture cannot run inside a timed bench): dram__bytes_read.sum + dram__bytes_write.sum
     traffic = 66128896 + 896000 if world == 1 and (cfg["n_embd"], cfg["n_ff"]) == (4096, 14336) else None
     roofline = {"bound": "hbm", "kernel": kname, "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": traffic, "launches_timed": timed, "avg_launch_us": per_launch_s * 1e6,
-                "algorithmic_bytes_per_launch": bytes_per_launch,
+                "frac": achieved / peak, "traffic": traffic, "traffic_source": "profiles/decode_step_kernels_8b_ncu_full.md" if traffic else None,
+                "launches_timed": timed, "avg_launch_us": per_launch_s * 1e6, "algorithmic_bytes_per_launch": bytes_per_launch,
                 "step": {"algorithmic_bytes_per_token_per_gpu": step_bytes, "achieved": step_bytes / (dev_ms * 1e-3 / K) / 1e9,
-                         "frac": step_bytes / (dev_ms * 1e-3 / K) / 1e9 / peak}}
-    if kernels:
-        roofline["kernels"] = kernels
+                         "frac": step_bytes / (dev_ms * 1e-3 / K) / 1e9 / peak},
+                "kernels": kernels}
+    if world == 1:
+        roofline["operator_gemv"] = operator_gemv_rooflines(be, peak)
 
     # ---- batch 64 extra ---------------------------------------------------------------------------------
     batch64 = None
@@ -367,6 +469,16 @@ def main():
         v, cores, sample = cpu_decode_tokens_per_s(cfg, tensors, budget_s=15.0, max_tokens=400)
         cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
 
+    # ---- 70B shape, tensor parallel (2, 4, 8 GPUs): batch 1 and batch 32 at context 8192 --------------------------------
+    model70b = None
+    if world > 1 and args.model == "8b" and not args.layers and os.environ.get("OB_BENCH_70B", "1") != "0":
+        model.close()
+        model = None
+        try:
+            model70b = run_70b(be, rank, world, make_uid(), barrier, max_over_ranks, peak)
+        except Exception as e:  # the headline line must not depend on the extra
+            model70b = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(W, 3), "ms_per_step": dev_ms / K,
@@ -382,8 +494,11 @@ def main():
         }
         if batch64:
             line["batch64"] = batch64
+        if model70b:
+            line["model70b"] = model70b
         print(json.dumps(line), flush=True)
-    model.close()
+    if model is not None:
+        model.close()
     be.close()
     if world > 1:
         dist.destroy_process_group()

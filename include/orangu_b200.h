@@ -29,8 +29,9 @@ extern "C" {
 #pragma GCC visibility push(default) /* the library is built with hidden visibility; these are its exports */
 #endif
 
-/* 2: ob_model_desc gained rope_freqs (layout change); the GGUF, static-attention and KV-copy entry points were added. */
-#define OB_ABI_VERSION 2u
+/* 2: ob_model_desc gained rope_freqs (layout change); the GGUF, static-attention and KV-copy entry points were added.
+ * 3: ob_model_desc gained tp_presliced. */
+#define OB_ABI_VERSION 3u
 
 typedef enum ob_status {
     OB_OK = 0,
@@ -230,6 +231,12 @@ typedef struct ob_model_desc {
     const void *tp_unique_id;   /* tp_size > 1: the 128-byte id from ob_tp_unique_id, identical on every rank */
     const float *rope_freqs;    /* optional rope_freqs.weight: rope_dim / 2 factors that divide the rotation frequencies
                                  * (E/arch/llama.rs:186-200, E/tensor.rs:1143-1145); NULL: none */
+    uint32_t tp_presliced;      /* tp_size > 1 only.  0: the matrix descriptors are the FULL tensors (the model keeps its shard).
+                                 * 1: they already hold this rank's shard and nothing else -- rows [rank * out/tp, +out/tp) of
+                                 * attn_q/k/v, ffn_gate/up and output, input columns [rank * in/tp, +in/tp) of attn_output and
+                                 * ffn_down (QuantMatrix::rows, E/loader.rs:627-646, and its column counterpart); token_embd
+                                 * and the norm vectors are whole.  For hosts that never hold the full tensors (a 70B model
+                                 * on eight ranks). */
 } ob_model_desc;
 
 /* ------------------------------------------------- GGUF files
@@ -337,6 +344,12 @@ int ob_profile_gemv(ob_model *model, uint32_t ggml_type, uint32_t variant, uint3
 /* No counterpart in the reference: its only multi-GPU mode is a host-bounced layer split
  * (B/multi.rs:16-35).  Rank 0 makes an id, every rank passes the same bytes in ob_model_desc. */
 int ob_tp_unique_id(void *out128);
+/* Diagnostic, on one GPU (no counterpart in the reference): the single-token step's peer exchange waits for every rank's
+ * tagged words with a time limit and, when it runs out, reports OB_ERR_COMM instead of hanging.  This runs n_rounds exchanges
+ * of n values (a multiple of 256) through the real consumer kernel with both "ranks" in local memory: rank 0 always delivers
+ * (1.0), rank 1 (2.0) only in the rounds whose byte in peer_delivers is non-zero.  sums_out[k] is the summed value of round k
+ * (3.0), or -1 when that round's wait ran out after timeout_ms (0 = 50 ms).  Returns OB_ERR_COMM if any round ran out. */
+int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *sums_out);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

@@ -33,7 +33,7 @@ class ModelDesc(C.Structure):
         ("max_seq_len", C.c_uint32), ("max_batch_tokens", C.c_uint32), ("kv_pool_tokens", C.c_uint64), ("exact_attention_max_pos", C.c_uint32),
         ("token_embd", MatrixDesc), ("output_norm", C.c_void_p), ("output", MatrixDesc),
         ("layers", C.POINTER(LayerDesc)), ("tp_rank", C.c_uint32), ("tp_size", C.c_uint32), ("tp_unique_id", C.c_void_p),
-        ("rope_freqs", C.c_void_p)]
+        ("rope_freqs", C.c_void_p), ("tp_presliced", C.c_uint32)]
 
 
 class MatmulOpC(C.Structure):
@@ -104,6 +104,7 @@ SIGNATURES = {
     "ob_launch_count": (_u64, [_vp]),
     "ob_last_device_ms": (_f32, [_vp]),
     "ob_tp_unique_id": (_i32, [_vp]),
+    "ob_tp_exchange_selftest": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
 }
 
 _lib = None

@@ -259,6 +259,20 @@ int quantize_for(ob_ctx *ctx, const float *x_dev, uint32_t n_tokens, uint32_t in
 
 int matmul_device(ob_ctx *ctx, const float *x_dev, uint32_t n_tokens, const ob_weight *w, float *y_dev, bool decode, cudaStream_t st,
                   int32_t *isum_out, int32_t *imin_out, uint32_t first_row, uint32_t n_rows) {
+    if (n_tokens == 1 && !isum_out && (w->w.type == TYPE_Q4_K || w->w.type == TYPE_Q6_K)) {
+        // one token, K-type weights: the streaming kernel of the decode step, quantizing the row in its prologue (one launch)
+        StreamArgs sa{};
+        sa.n_seg = 1;
+        sa.in_dim = w->w.in_dim;
+        sa.prologue = SG_PRO_PLAIN;
+        sa.x = x_dev;
+        sa.seg[0] = StreamSeg{w->w, DevWeight{}, y_dev, SG_EP_STORE};
+        if (stream_gemv_supported(sa)) {
+            launch_stream_gemv(sa, ctx->sm_count, false, st);
+            ctx->launches++;
+            return OB_OK;
+        }
+    }
     ActBuf act;
     int rc = quantize_for(ctx, x_dev, n_tokens, w->w.in_dim, w->w.type, &act, st);
     if (rc) return rc;

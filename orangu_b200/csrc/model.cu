@@ -55,6 +55,15 @@ __global__ void advance_kernel(uint32_t *tokens, uint32_t *positions, uint32_t *
     if (i == 0) *step_counter = step + 1;
 }
 
+// Pages [0, n_pages) of every layer's K and V pools from one sequence's page table to another's: one CTA per (page, layer, K | V).
+__global__ void __launch_bounds__(256) copy_pages_kernel(__half *k_pool, __half *v_pool, size_t layer_stride, const int32_t *__restrict__ src_table,
+                                                          const int32_t *__restrict__ dst_table, uint32_t page_elems) {
+    __half *pool = (blockIdx.z ? v_pool : k_pool) + (size_t)blockIdx.y * layer_stride;
+    const uint4 *src = reinterpret_cast<const uint4 *>(pool + (size_t)src_table[blockIdx.x] * page_elems);
+    uint4 *dst = reinterpret_cast<uint4 *>(pool + (size_t)dst_table[blockIdx.x] * page_elems);
+    for (uint32_t i = threadIdx.x; i < page_elems / 8; i += blockDim.x) dst[i] = src[i];
+}
+
 }  // namespace
 
 struct ob_model {
@@ -685,10 +694,13 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     if (tp > 1 && !c.tp_unique_id) return fail(ctx, OB_ERR_INVALID, "model_create: tp_size > 1 needs tp_unique_id");
 
     int rc;
-    {  // validate every matrix before touching the device
-        const uint32_t qd = c.n_head * c.head_dim, kvd = c.n_head_kv * c.head_dim;
+    const bool presliced = tp > 1 && c.tp_presliced != 0;
+    {  // validate every matrix before touching the device (a presliced description carries the rank's shard shapes)
+        const uint32_t ps = presliced ? tp : 1u;
+        const uint32_t qd = c.n_head * c.head_dim / ps, kvd = c.n_head_kv * c.head_dim / ps, ffd = c.n_ff / ps;
         if ((rc = check_matrix(ctx, c.token_embd, c.n_embd, c.n_vocab, "token_embd.weight"))) return rc;
-        if (c.output.data && (rc = check_matrix(ctx, c.output, c.n_embd, c.n_vocab, "output.weight"))) return rc;
+        if (c.output.data && (rc = check_matrix(ctx, c.output, c.n_embd, c.n_vocab / ps, "output.weight"))) return rc;
+        if (presliced && !c.output.data) return fail(ctx, OB_ERR_INVALID, "model_create: a presliced model needs its output.weight shard (a tied output cannot be cut from the whole token_embd on the device)");
         for (uint32_t i = 0; i < c.n_layer; ++i) {
             const ob_layer_desc &L = c.layers[i];
             if (!L.attn_norm || !L.ffn_norm) return fail(ctx, OB_ERR_INVALID, "model_create: layer norm weights missing");
@@ -696,9 +708,9 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
             if ((rc = check_matrix(ctx, L.wk, c.n_embd, kvd, "attn_k.weight"))) return rc;
             if ((rc = check_matrix(ctx, L.wv, c.n_embd, kvd, "attn_v.weight"))) return rc;
             if ((rc = check_matrix(ctx, L.wo, qd, c.n_embd, "attn_output.weight"))) return rc;
-            if ((rc = check_matrix(ctx, L.w_gate, c.n_embd, c.n_ff, "ffn_gate.weight"))) return rc;
-            if ((rc = check_matrix(ctx, L.w_up, c.n_embd, c.n_ff, "ffn_up.weight"))) return rc;
-            if ((rc = check_matrix(ctx, L.w_down, c.n_ff, c.n_embd, "ffn_down.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_gate, c.n_embd, ffd, "ffn_gate.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_up, c.n_embd, ffd, "ffn_up.weight"))) return rc;
+            if ((rc = check_matrix(ctx, L.w_down, ffd, c.n_embd, "ffn_down.weight"))) return rc;
         }
     }
 
@@ -740,17 +752,18 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         LayerDev &D = m->layers[i];
         if ((rc = upload_f32(m, L.attn_norm, c.n_embd, &D.attn_norm))) return bail(rc);
         if ((rc = upload_f32(m, L.ffn_norm, c.n_embd, &D.ffn_norm))) return bail(rc);
-        if ((rc = slice_weight(m, L.wq, rank * q_dim, q_dim, 0, c.n_embd, &D.wq))) return bail(rc);
-        if ((rc = slice_weight(m, L.wk, rank * kv_dim, kv_dim, 0, c.n_embd, &D.wk))) return bail(rc);
-        if ((rc = slice_weight(m, L.wv, rank * kv_dim, kv_dim, 0, c.n_embd, &D.wv))) return bail(rc);
-        if ((rc = slice_weight(m, L.wo, 0, c.n_embd, rank * q_dim, q_dim, &D.wo))) return bail(rc);
-        if ((rc = slice_weight(m, L.w_gate, rank * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.gate))) return bail(rc);
-        if ((rc = slice_weight(m, L.w_up, rank * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.up))) return bail(rc);
-        if ((rc = slice_weight(m, L.w_down, 0, c.n_embd, rank * m->n_ff_l, m->n_ff_l, &D.down))) return bail(rc);
+        const uint32_t sr = presliced ? 0u : rank;  // a presliced tensor starts at the shard
+        if ((rc = slice_weight(m, L.wq, sr * q_dim, q_dim, 0, c.n_embd, &D.wq))) return bail(rc);
+        if ((rc = slice_weight(m, L.wk, sr * kv_dim, kv_dim, 0, c.n_embd, &D.wk))) return bail(rc);
+        if ((rc = slice_weight(m, L.wv, sr * kv_dim, kv_dim, 0, c.n_embd, &D.wv))) return bail(rc);
+        if ((rc = slice_weight(m, L.wo, 0, c.n_embd, sr * q_dim, q_dim, &D.wo))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_gate, sr * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.gate))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_up, sr * m->n_ff_l, m->n_ff_l, 0, c.n_embd, &D.up))) return bail(rc);
+        if ((rc = slice_weight(m, L.w_down, 0, c.n_embd, sr * m->n_ff_l, m->n_ff_l, &D.down))) return bail(rc);
     }
     if ((rc = slice_weight(m, c.token_embd, 0, c.n_vocab, 0, c.n_embd, &m->token_embd))) return bail(rc);
     if (c.output.data) {
-        if ((rc = slice_weight(m, c.output, m->vocab0, m->vocab_l, 0, c.n_embd, &m->output))) return bail(rc);
+        if ((rc = slice_weight(m, c.output, presliced ? 0u : m->vocab0, m->vocab_l, 0, c.n_embd, &m->output))) return bail(rc);
     } else if (tp == 1) {
         m->output = m->token_embd;  // tied (llama.rs:133-139)
     } else {
@@ -950,15 +963,12 @@ int ob_kv_copy_prefix(ob_kv *dst, const ob_kv *src, uint32_t n) {
     if (dst->len != 0) return fail(ctx, OB_ERR_INVALID, "kv_copy_prefix: the destination is not empty");
     if (n > src->len || n > dst->capacity) return fail(ctx, OB_ERR_CAPACITY, "kv_copy_prefix: n exceeds the source length or the destination capacity");
     Bind b(ctx);
-    const size_t page_elems = (size_t)m->n_head_kv_l * KV_PAGE * m->cfg.head_dim;
+    const size_t page_elems = (size_t)m->n_head_kv_l * KV_PAGE * m->cfg.head_dim;  // a multiple of 8 halves: head_dim is even and a page holds 16 tokens
     const uint32_t n_pages = (n + KV_PAGE - 1) / KV_PAGE;
-    for (uint32_t li = 0; li < m->cfg.n_layer; ++li)
-        for (uint32_t p = 0; p < n_pages; ++p)
-            for (__half *pool : {m->k_pool, m->v_pool}) {
-                __half *base = pool + (size_t)li * m->layer_stride;
-                OB_CUDA(ctx, cudaMemcpyAsync(base + (size_t)dst->pages[p] * page_elems, base + (size_t)src->pages[p] * page_elems, page_elems * 2,
-                                             cudaMemcpyDeviceToDevice, ctx->stream));
-            }
+    if (n_pages) {
+        copy_pages_kernel<<<dim3(n_pages, m->cfg.n_layer, 2), 256, 0, ctx->stream>>>(m->k_pool, m->v_pool, m->layer_stride, src->d_table, dst->d_table, (uint32_t)page_elems);
+        ctx->launches++;
+    }
     OB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     dst->len = n;
     return OB_OK;
@@ -973,7 +983,6 @@ int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t variant, uint32_t 
     cudaStream_t st = ctx->stream;
     if (variant) {
         if (m->last_T == 0) return fail(ctx, OB_ERR_INVALID, "profile_gemv: run a decode step first (the fused kernels read its position and page table)");
-        if (m->tp_size > 1) return fail(ctx, OB_ERR_UNSUPPORTED, "profile_gemv: the fused kernels are single-GPU");
         uint64_t bytes = 0;
         uint32_t launches = 0;
         auto seg_bytes = [](const StreamSeg &sg) {
@@ -988,7 +997,12 @@ int ob_profile_gemv(ob_model *m, uint32_t ggml_type, uint32_t variant, uint32_t 
             if (it == 1) OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
             const uint32_t n = variant == 5 ? 1u : m->cfg.n_layer;
             for (uint32_t li = 0; li < n; ++li) {
-                const StreamArgs a = stream_args(m, li, (int)variant);
+                StreamArgs a = stream_args(m, li, (int)variant);
+                if (a.seg[0].epilogue == SG_EP_XCHG) {  // tensor parallel: time the product on this rank's slice; a store into the
+                    a.seg[0].epilogue = SG_EP_STORE;     // peers' exchange slots would carry the tag of the next real exchange
+                    a.seg[0].y = m->proj;
+                    a.px = obtp::PeerXchg{};
+                }
                 if (!stream_gemv_supported(a)) return fail(ctx, OB_ERR_UNSUPPORTED, "profile_gemv: this model's tensors do not take the fused kernels");
                 launch_stream_gemv(a, ctx->sm_count, true, st);
                 if (it == 1) {
@@ -1227,7 +1241,7 @@ int check_peer(ob_model *m) {
     if (cudaMemcpy(&e, m->px.err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(m->ctx, OB_ERR_CUDA, "reading the exchange status failed");
     if (!e) return OB_OK;
     cudaMemset(m->px.err, 0, 4);
-    return fail(m->ctx, OB_ERR_COMM, "tensor-parallel exchange: a rank did not deliver its partial within 4 s");
+    return fail(m->ctx, OB_ERR_COMM, "tensor-parallel exchange: a rank did not deliver its partial within " + std::to_string(m->px.timeout_ms ? m->px.timeout_ms : 4000u) + " ms");
 }
 
 // kind 0: H2D metadata + step + D2H token (one host round trip per step)
@@ -1369,6 +1383,66 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
     ctx->launches += m->graph_launches[key] * n_steps;
     for (uint32_t s = 0; s < n_seq; ++s) kvs[s]->len += n_steps;
     return check_peer(m);
+}
+
+namespace {
+__global__ void selftest_deliver_kernel(uint2 *slot, uint32_t n, float value, uint32_t tag) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) slot[i] = make_uint2(__float_as_uint(value), tag);
+}
+}  // namespace
+
+int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *sums_out) {
+    if (!ctx || !peer_delivers || n == 0 || n % 256 || n_rounds == 0 || n_rounds > 64) return fail(ctx, OB_ERR_INVALID, "tp_exchange_selftest: bad argument");
+    std::lock_guard<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    cudaStream_t st = ctx->stream;
+    // a two-rank exchange whose slots are all local memory: this "rank 0" delivers every round, "rank 1" only when told to
+    uint8_t *region = nullptr;
+    float *x = nullptr;
+    const size_t slot_bytes = (size_t)2 * 2 * n * sizeof(uint2);
+    OB_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&region), 512 + slot_bytes));
+    if (cudaMalloc(reinterpret_cast<void **>(&x), (size_t)n * 4) != cudaSuccess) {
+        cudaFree(region);
+        return fail(ctx, OB_ERR_OOM, "tp_exchange_selftest: allocation failed");
+    }
+    cudaMemsetAsync(region, 0, 512 + slot_bytes, st);
+    obtp::PeerXchg px{};
+    px.rank = 0;
+    px.size = 2;
+    px.n = n;
+    px.timeout_ms = timeout_ms ? timeout_ms : 50;
+    px.seq = reinterpret_cast<uint32_t *>(region);
+    px.err = reinterpret_cast<uint32_t *>(region) + 32;
+    px.slots[0] = px.slots[1] = reinterpret_cast<uint2 *>(region + 512);
+    int rc = OB_OK;
+    for (uint32_t k = 0; k < n_rounds; ++k) {  // exchange number k: tag k + 1, slot parity k & 1 (tp.h)
+        cudaMemsetAsync(x, 0, (size_t)n * 4, st);
+        uint2 *base = px.slots[0] + (size_t)(k & 1u) * 2 * n;
+        selftest_deliver_kernel<<<(n + 255) / 256, 256, 0, st>>>(base, n, 1.0f, k + 1);
+        if (peer_delivers[k]) selftest_deliver_kernel<<<(n + 255) / 256, 256, 0, st>>>(base + n, n, 2.0f, k + 1);
+        launch_norm_quant_consume(x, nullptr, n, 1e-5f, nullptr, nullptr, px, false, st);
+        ctx->launches += 2 + (peer_delivers[k] ? 1 : 0);
+        uint32_t err = 0;
+        float first = 0.0f;
+        cudaError_t e = cudaMemcpyAsync(&err, px.err, 4, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(&first, x + (n - 1), 4, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) {
+            rc = fail(ctx, OB_ERR_CUDA, std::string("tp_exchange_selftest: ") + cudaGetErrorString(e));
+            break;
+        }
+        if (sums_out) sums_out[k] = first;
+        if (err) {  // the wait ran out: report as the model's step does, clear, go on with the next round
+            cudaMemsetAsync(px.err, 0, 4, st);
+            rc = fail(ctx, OB_ERR_COMM, "tensor-parallel exchange: a rank did not deliver its partial within " + std::to_string(px.timeout_ms) + " ms (round " + std::to_string(k) + ")");
+            if (sums_out) sums_out[k] = -1.0f;
+        }
+    }
+    cudaStreamSynchronize(st);
+    cudaFree(region);
+    cudaFree(x);
+    return rc;
 }
 
 int ob_tp_unique_id(void *out128) {

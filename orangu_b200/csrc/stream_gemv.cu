@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(NS_THREADS) norm_scale_kernel(float *__restric
                         if ((spin & 1023u) == 1023u) {
                             unsigned long long t1;
                             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-                            if (t1 - t0 > 4000000000ull) {  // four seconds: a rank is gone; report and go on with what is there
+                            if (t1 - t0 > (unsigned long long)(px.timeout_ms ? px.timeout_ms : 4000u) * 1000000ull) {  // a rank is gone: report and go on with what is there
                                 *px.err = 1u;
                                 gave_up = true;
                             }

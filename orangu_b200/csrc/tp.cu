@@ -4,7 +4,10 @@
 #include "tp.h"
 
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <algorithm>
 
 #include <vector>
 
@@ -205,6 +208,8 @@ static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std:
     uint32_t *local = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(c->peer_region) + kFlagBytes);
     px.seq = local;
     px.err = local + 32;
+    px.timeout_ms = 4000;
+    if (const char *e = getenv("OB_TP_TIMEOUT_MS")) px.timeout_ms = (uint32_t)std::max(1, atoi(e));
     *out = px;
     return true;
 }

@@ -36,6 +36,7 @@ struct PeerXchg {
     uint32_t *seq;       // this rank: exchanges completed
     uint32_t *err;       // this rank: set to 1 when a wait ran out of time
     uint32_t rank, size, n;
+    uint32_t timeout_ms;  // how long the consumer waits for a rank's words before it reports and goes on (0 = 4000)
 };
 // Allocates this rank's region, exchanges CUDA IPC handles over the communicator and maps the peers' regions.
 // False (with *err) when peer access is not available; the caller then keeps to NCCL.

@@ -63,7 +63,8 @@ class LlamaModel:
     ``{"data": np.ndarray, "type": ggml_type, "in_dim": .., "out_dim": ..}``; norm vectors are f32."""
 
     def __init__(self, backend: CudaBackend, cfg: dict, tensors: dict, max_seq_len: int = 4096, max_batch_tokens: int = 512,
-                 kv_pool_tokens: int = 0, exact_attention_max_pos: int = 0, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: bytes | None = None):
+                 kv_pool_tokens: int = 0, exact_attention_max_pos: int = 0, tp_rank: int = 0, tp_size: int = 1, tp_unique_id: bytes | None = None,
+                 tp_presliced: bool = False):
         self.backend = backend
         self._lib = backend._lib
         self.cfg = dict(cfg)
@@ -90,6 +91,7 @@ class LlamaModel:
             d.output = _matrix(tensors["output.weight"])
         d.layers = layers
         d.tp_rank, d.tp_size = tp_rank, tp_size
+        d.tp_presliced = 1 if (tp_presliced and tp_size > 1) else 0  # the tensors are this rank's shards already (synth.model_tensors(..., tp=(rank, size)))
         self._id = C.create_string_buffer(tp_unique_id, 128) if tp_unique_id else None
         d.tp_unique_id = C.addressof(self._id) if self._id else None
         if "rope_freqs.weight" in tensors:  # llama.rs:186-200

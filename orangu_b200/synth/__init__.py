@@ -28,6 +28,7 @@ def _load():
         L.obs_fill_normal.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64, C.c_float]
         L.obs_quantize_rows.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
         L.obs_synth_matrix.argtypes = [C.c_uint32, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t, C.c_void_p]
+        L.obs_synth_matrix_slice.argtypes = [C.c_uint32, C.c_uint64, C.c_float, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]
         _lib = L
     return _lib
 
@@ -71,6 +72,21 @@ def matrix(ggml_type: int, out_dim: int, in_dim: int, seed: int, std: float = 0.
     return {"data": out, "type": ggml_type, "in_dim": in_dim, "out_dim": out_dim}
 
 
+def matrix_slice(ggml_type: int, out_dim: int, in_dim: int, seed: int, rows: tuple[int, int], cols: tuple[int, int], std: float = 0.02) -> dict:
+    """Rows [rows[0], rows[0] + rows[1]) x columns [cols[0], cols[0] + cols[1]) of matrix(ggml_type, out_dim, in_dim, seed), made
+    directly (bit-identical to cutting them out of the whole matrix); column bounds are whole blocks."""
+    bb, be = BLOCK[ggml_type]
+    if ggml_type in _CODE_STD:
+        raise ValueError("slices are made for the generator-backed types only")
+    (r0, nr), (c0, nc) = rows, cols
+    if r0 + nr > out_dim or c0 % be or nc % be or c0 + nc > in_dim:
+        raise ValueError("slice outside the matrix or not on block boundaries")
+    out = np.empty(nr * (nc // be) * bb, np.uint8)
+    if _load().obs_synth_matrix_slice(ggml_type, seed, std, in_dim, r0, nr, c0, nc, out.ctypes.data):
+        raise ValueError("bad slice")
+    return {"data": out, "type": ggml_type, "in_dim": nc, "out_dim": nr}
+
+
 CONFIGS = {
     # Llama-style shapes; weights N(0, 0.02^2), norm weights all ones
     "tiny": dict(n_vocab=512, n_embd=256, n_layer=2, n_head=4, n_head_kv=2, head_dim=64, n_ff=512, rope_freq_base=10000.0, rms_eps=1e-5),
@@ -81,10 +97,44 @@ CONFIGS = {
 }
 
 
-def model_tensors(cfg: dict, seed: int = 0, n_layer: int | None = None, types: dict | None = None) -> dict:
+def _model_tensor_shards(cfg, seed, n_layer, types, rank, size):
+    e, hd = cfg["n_embd"], cfg["head_dim"]
+    qd, kvd, ff, V = cfg["n_head"] * hd, cfg["n_head_kv"] * hd, cfg["n_ff"], cfg["n_vocab"]
+    t = {}
+
+    def rows(name, key, default, out_dim, in_dim):  # split by output rows
+        n = out_dim // size
+        t[name] = matrix_slice(types.get(key, default), out_dim, in_dim, seed_of(seed, name), (rank * n, n), (0, in_dim))
+
+    def cols(name, key, default, out_dim, in_dim):  # split by the contraction dimension
+        n = in_dim // size
+        t[name] = matrix_slice(types.get(key, default), out_dim, in_dim, seed_of(seed, name), (0, out_dim), (rank * n, n))
+
+    t["token_embd.weight"] = matrix(types.get("token_embd", Q4_K), V, e, seed_of(seed, "token_embd.weight"))
+    rows("output.weight", "output", Q6_K, V, e)
+    t["output_norm.weight"] = {"data": np.ones(e, np.float32), "type": F32}
+    for i in range(n_layer):
+        p = f"blk.{i}."
+        t[p + "attn_norm.weight"] = {"data": np.ones(e, np.float32), "type": F32}
+        t[p + "ffn_norm.weight"] = {"data": np.ones(e, np.float32), "type": F32}
+        rows(p + "attn_q.weight", "attn_q", Q4_K, qd, e)
+        rows(p + "attn_k.weight", "attn_k", Q4_K, kvd, e)
+        rows(p + "attn_v.weight", "attn_v", Q6_K, kvd, e)
+        cols(p + "attn_output.weight", "attn_output", Q4_K, e, qd)
+        rows(p + "ffn_gate.weight", "ffn_gate", Q4_K, ff, e)
+        rows(p + "ffn_up.weight", "ffn_up", Q4_K, ff, e)
+        cols(p + "ffn_down.weight", "ffn_down", Q4_K, e, ff)
+    return t
+
+
+def model_tensors(cfg: dict, seed: int = 0, n_layer: int | None = None, types: dict | None = None, tp: tuple[int, int] | None = None) -> dict:
     """Q4_K_M-style model: Q4_K everywhere except attn_v and output in Q6_K; token_embd Q4_K; norms f32 ones.
-    `types` overrides per tensor suffix, e.g. {"attn_q": Q8_0}."""
+    `types` overrides per tensor suffix, e.g. {"attn_q": Q8_0}.  tp = (rank, size): only that rank's tensor-parallel shards
+    are made (rows of Q/K/V/gate/up/output, input columns of attn_output/ffn_down; token_embd whole) -- the same bytes the
+    whole tensors hold there -- for LlamaModel(..., tp_presliced=True)."""
     types = types or {}
+    if tp is not None and tp[1] > 1:
+        return _model_tensor_shards(cfg, seed, cfg["n_layer"] if n_layer is None else n_layer, types, tp[0], tp[1])
     n_layer = cfg["n_layer"] if n_layer is None else n_layer
     e, hd = cfg["n_embd"], cfg["head_dim"]
     qd, kvd, ff, V = cfg["n_head"] * hd, cfg["n_head_kv"] * hd, cfg["n_ff"], cfg["n_vocab"]

@@ -265,4 +265,23 @@ int obs_synth_matrix(uint32_t type, uint64_t seed, float std, size_t out_dim, si
     return 0;
 }
 
+/* Rows [row0, row0 + n_rows) x columns [col0, col0 + n_cols) of the matrix obs_synth_matrix(type, seed, std, *, in_dim)
+ * makes, quantized: the values come from a counter-based generator and the block quantizers work block by block, so a
+ * shard is produced directly, bit-identical to the same region cut out of the whole matrix (col0 and n_cols are whole
+ * blocks).  This is what lets every rank of a tensor-parallel run build only its own slices of a large model. */
+int obs_synth_matrix_slice(uint32_t type, uint64_t seed, float std, size_t in_dim, size_t row0, size_t n_rows, size_t col0, size_t n_cols, uint8_t *out) {
+    size_t rb = row_bytes(type, n_cols);
+    if (!rb || !row_bytes(type, in_dim) || col0 + n_cols > in_dim || !row_bytes(type, col0 ? col0 : n_cols)) return -1;
+#pragma omp parallel
+    {
+        std::vector<float> row(n_cols);
+#pragma omp for schedule(static)
+        for (size_t r = 0; r < n_rows; ++r) {
+            fill_normal(row.data(), (row0 + r) * in_dim + col0, n_cols, seed, std);
+            quantize_row(type, row.data(), n_cols, out + r * rb);
+        }
+    }
+    return 0;
+}
+
 } /* extern "C" */

@@ -26,6 +26,7 @@ def main():
     from orangu_b200 import capi, synth
 
     name, n_layer, n_prompt, n_decode = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
+    presliced = len(sys.argv) > 5 and sys.argv[5] == "presliced"  # every rank builds only its own shards
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
     dist.init_process_group("gloo")
     torch.cuda.set_device(local)
@@ -40,10 +41,10 @@ def main():
 
     cfg = dict(synth.CONFIGS[name])
     cfg["n_layer"] = n_layer
-    tensors = synth.model_tensors(cfg, seed=11)
+    tensors = synth.model_tensors(cfg, seed=11, tp=(rank, world) if presliced else None)
     be = orangu_b200.CudaBackend.init(local)
     model = orangu_b200.LlamaModel(be, cfg, tensors, max_seq_len=n_prompt + n_decode + 16, max_batch_tokens=32,
-                                   kv_pool_tokens=n_prompt + n_decode + 64, tp_rank=rank, tp_size=world, tp_unique_id=box[0])
+                                   kv_pool_tokens=n_prompt + n_decode + 64, tp_rank=rank, tp_size=world, tp_unique_id=box[0], tp_presliced=presliced)
     toks = np.random.default_rng(5).integers(0, cfg["n_vocab"], n_prompt).astype(np.uint32)
     kv = model.new_kv_cache(n_prompt + n_decode + 8)
     logits = [model.forward(kv, toks, 0)]
@@ -58,7 +59,7 @@ def main():
     dist.all_gather_object(all_digests, digest)
 
     if rank == 0:
-        ref = O.Model(cfg, tensors)
+        ref = O.Model(cfg, synth.model_tensors(cfg, seed=11) if presliced else tensors)
         rkv = ref.new_kv(n_prompt + n_decode + 8, f16=True)
         want = [ref.forward(rkv, toks, 0)]
         want_tok = [O.argmax(want[0])]
@@ -71,7 +72,8 @@ def main():
                 first_diverged = i + 1
         err = [float(np.abs(a - b).max()) for a, b in zip(logits, want)]
         scale = float(np.abs(np.stack(want)).max())
-        print(json.dumps({"world": world, "max_abs_err": max(err), "prefill_err": err[0], "logit_scale": scale,
+        digest_all = float(np.sum(np.stack(logits).astype(np.float64)))
+        print(json.dumps({"world": world, "digest": digest_all, "max_abs_err": max(err), "prefill_err": err[0], "logit_scale": scale,
                           "tokens_equal": first_diverged is None and got[0] == want_tok[0], "first_diverged": first_diverged,
                           "ranks_agree": all(d == all_digests[0] for d in all_digests), "launches": be.launch_count()}), flush=True)
     dist.barrier()
