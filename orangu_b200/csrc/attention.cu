@@ -769,6 +769,222 @@ bool launch_attn_decode_fused(const AttnDecodeArgs &a, bool programmatic, cudaSt
 }  // namespace ob
 
 // ====================================================================================================
+// Prefill attention: the rows are consecutive tokens of ONE sequence (a prefill chunk), so all of them attend to the same
+// pages.  A CTA takes 16 tokens x the G query heads of one kv head -- warp g holds the 16 x head_dim queries of head g as
+// A fragments -- and walks the causal window in tiles of 64 positions (four pages, staged once per CTA in a two-stage
+// cp.async ring): S = Q K^T and O += P V through mma.sync.m16n8k16 (f16 x f16 -> f32) with Q and P entered as a rounded
+// fp16 part plus its fp16 remainder (two instructions per product), which keeps their error near 2^-22 as in the
+// decode kernel; K and V are exactly what the cache holds.  Online softmax in registers; token t sees positions
+// 0 .. n_pos[t] - 1.  Every K/V byte of the window is read once per 16 tokens instead of once per token.
+// (engine/attention.rs:426-549 is the arithmetic; its CPU loop is also parallel over query tokens, :444.)
+// ====================================================================================================
+namespace ob {
+
+namespace {
+
+constexpr int PF_TOK = 16, PF_TILE = 64;
+
+template <int HD>
+struct PrefillSmem {
+    static constexpr int ROW = HD * 2 + 16;  // bytes per position: the pad spreads eight rows over all banks
+    uint8_t k[2][PF_TILE * ROW];
+    uint8_t v[2][PF_TILE * ROW];
+};
+
+template <int HD, int G>
+__global__ void __launch_bounds__(G * 32) attn_prefill_kernel(AttnDecodeArgs a) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    using Smem = PrefillSmem<HD>;
+    Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
+    constexpr int ROW = Smem::ROW, THREADS = G * 32, KS = HD / 16, NT = HD / 8;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
+    const uint32_t tok0 = blockIdx.x * PF_TOK, kvh = blockIdx.y, head = kvh * G + warp;
+    const uint32_t n_rows = a.n_seq;
+    const uint32_t last_row = min(tok0 + PF_TOK, n_rows) - 1;
+    const uint32_t pos_end = a.n_pos[last_row];            // the longest window of this CTA's tokens
+    const int32_t *table = a.page_tables[tok0];             // one sequence: every row carries the same table
+    const uint32_t n_tiles = (pos_end + PF_TILE - 1) / PF_TILE;
+    const uint32_t kb_base = (uint32_t)__cvta_generic_to_shared(&sm.k[0][0]), vb_base = (uint32_t)__cvta_generic_to_shared(&sm.v[0][0]);
+
+    auto stage_tile = [&](uint32_t tile, int st) {
+        constexpr int CPR = HD / 8;                       // 16-byte chunks per position
+        constexpr int CHUNKS = PF_TILE * CPR;
+        for (int ch = tid; ch < CHUNKS; ch += THREADS) {
+            const uint32_t p = ch / CPR, j = ch % CPR, pos = tile * PF_TILE + p;
+            const uint32_t off = st * PF_TILE * ROW + p * ROW + j * 16;
+            if (pos >= pos_end) {  // masked for every token of this CTA: zeros, so that probability 0 times V stays 0
+                *reinterpret_cast<uint4 *>(&sm.k[0][0] + off) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(&sm.v[0][0] + off) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            const uint64_t base = (((uint64_t)table[pos / KV_PAGE] * a.n_head_kv + kvh) * KV_PAGE + pos % KV_PAGE) * HD;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kb_base + off), "l"(reinterpret_cast<const uint8_t *>(a.k_pool + base) + j * 16) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vb_base + off), "l"(reinterpret_cast<const uint8_t *>(a.v_pool + base) + j * 16) : "memory");
+        }
+    };
+    stage_tile(0, 0);
+    __pipeline_commit();
+
+    // this thread's query rows: tokens tok0 + gid and tok0 + gid + 8 of head `head`; rounded part and remainder
+    const uint32_t r0 = tok0 + gid, r1 = tok0 + gid + 8;
+    const uint32_t np0 = r0 < n_rows ? a.n_pos[r0] : 0u, np1 = r1 < n_rows ? a.n_pos[r1] : 0u;
+    uint32_t qh[KS][4], ql[KS][4];
+    {
+        const float *q0 = a.q + (uint64_t)min(r0, n_rows - 1) * a.n_head * HD + (uint64_t)head * HD;
+        const float *q1 = a.q + (uint64_t)min(r1, n_rows - 1) * a.n_head * HD + (uint64_t)head * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const float2 x0 = *reinterpret_cast<const float2 *>(q0 + 16 * ks + 2 * tig), x2 = *reinterpret_cast<const float2 *>(q0 + 16 * ks + 8 + 2 * tig);
+            const float2 y0 = *reinterpret_cast<const float2 *>(q1 + 16 * ks + 2 * tig), y2 = *reinterpret_cast<const float2 *>(q1 + 16 * ks + 8 + 2 * tig);
+            qh[ks][0] = pack_half2(x0.x, x0.y);
+            qh[ks][1] = pack_half2(y0.x, y0.y);
+            qh[ks][2] = pack_half2(x2.x, x2.y);
+            qh[ks][3] = pack_half2(y2.x, y2.y);
+            ql[ks][0] = pack_half2_rest(x0.x, x0.y);
+            ql[ks][1] = pack_half2_rest(y0.x, y0.y);
+            ql[ks][2] = pack_half2_rest(x2.x, x2.y);
+            ql[ks][3] = pack_half2_rest(y2.x, y2.y);
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+
+    for (uint32_t tile = 0; tile < n_tiles; ++tile) {
+        const int st = (int)(tile & 1);
+        if (tile + 1 < n_tiles) stage_tile(tile + 1, st ^ 1);
+        __pipeline_commit();
+        __pipeline_wait_prior(1);
+        __syncthreads();  // tile `tile` has landed for everybody
+        const uint32_t kb = kb_base + st * PF_TILE * ROW, vb = vb_base + st * PF_TILE * ROW;
+        const uint32_t pos0 = tile * PF_TILE;
+        // ---- scores of the 64 positions: eight n-tiles of 8 positions
+        float sc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int kk = 0; kk < KS / 2; ++kk) {
+                uint32_t b0, b1, b2, b3;  // positions 8 nt .., dims 32 kk + 8 * (lane / 8) ..
+                ldmatrix_x4(kb + (8 * nt + (lane & 7)) * ROW + (32 * kk + 8 * (lane >> 3)) * 2, b0, b1, b2, b3);
+                mma_16816(c, qh[2 * kk][0], qh[2 * kk][1], qh[2 * kk][2], qh[2 * kk][3], b0, b1);
+                mma_16816(c, ql[2 * kk][0], ql[2 * kk][1], ql[2 * kk][2], ql[2 * kk][3], b0, b1);
+                mma_16816(c, qh[2 * kk + 1][0], qh[2 * kk + 1][1], qh[2 * kk + 1][2], qh[2 * kk + 1][3], b2, b3);
+                mma_16816(c, ql[2 * kk + 1][0], ql[2 * kk + 1][1], ql[2 * kk + 1][2], ql[2 * kk + 1][3], b2, b3);
+            }
+            const uint32_t p = pos0 + 8 * nt + 2 * tig;  // c[0], c[1]: row gid, positions p, p + 1; c[2], c[3]: row gid + 8
+            sc[nt][0] = p < np0 ? __fmul_rn(c[0], a.scale) : -INFINITY;
+            sc[nt][1] = p + 1 < np0 ? __fmul_rn(c[1], a.scale) : -INFINITY;
+            sc[nt][2] = p < np1 ? __fmul_rn(c[2], a.scale) : -INFINITY;
+            sc[nt][3] = p + 1 < np1 ? __fmul_rn(c[3], a.scale) : -INFINITY;
+        }
+        // ---- online softmax: the four lanes of a quad hold a row's 64 scores
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float al0 = m0 == -INFINITY ? 0.0f : expf(m0 - mn0), al1 = m1 == -INFINITY ? 0.0f : expf(m1 - mn1);
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            sc[nt][0] = sc[nt][0] == -INFINITY ? 0.0f : expf(sc[nt][0] - mn0);
+            sc[nt][1] = sc[nt][1] == -INFINITY ? 0.0f : expf(sc[nt][1] - mn0);
+            sc[nt][2] = sc[nt][2] == -INFINITY ? 0.0f : expf(sc[nt][2] - mn1);
+            sc[nt][3] = sc[nt][3] == -INFINITY ? 0.0f : expf(sc[nt][3] - mn1);
+            s0 += sc[nt][0] + sc[nt][1];
+            s1 += sc[nt][2] + sc[nt][3];
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        l0 = __fmaf_rn(l0, al0, s0);
+        l1 = __fmaf_rn(l1, al1, s1);
+        m0 = mn0;
+        m1 = mn1;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            o[j][0] *= al0;
+            o[j][1] *= al0;
+            o[j][2] *= al1;
+            o[j][3] *= al1;
+        }
+        // ---- output: k-steps of 16 positions; the score fragments of n-tiles 2 j2, 2 j2 + 1 are the A fragment
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+            const uint32_t ph0 = pack_half2(sc[2 * j2][0], sc[2 * j2][1]), ph1 = pack_half2(sc[2 * j2][2], sc[2 * j2][3]);
+            const uint32_t ph2 = pack_half2(sc[2 * j2 + 1][0], sc[2 * j2 + 1][1]), ph3 = pack_half2(sc[2 * j2 + 1][2], sc[2 * j2 + 1][3]);
+            const uint32_t pl0 = pack_half2_rest(sc[2 * j2][0], sc[2 * j2][1]), pl1 = pack_half2_rest(sc[2 * j2][2], sc[2 * j2][3]);
+            const uint32_t pl2 = pack_half2_rest(sc[2 * j2 + 1][0], sc[2 * j2 + 1][1]), pl3 = pack_half2_rest(sc[2 * j2 + 1][2], sc[2 * j2 + 1][3]);
+#pragma unroll
+            for (int j = 0; j < NT / 2; ++j) {
+                uint32_t b0, b1, b2, b3;  // positions 16 j2 + (lane & 7) + 8 * ((lane >> 3) & 1), dims 16 j + 8 * (lane >> 4) ..
+                ldmatrix_x4_trans(vb + (16 * j2 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + (16 * j + 8 * (lane >> 4)) * 2, b0, b1, b2, b3);
+                mma_16816(o[2 * j], ph0, ph1, ph2, ph3, b0, b1);
+                mma_16816(o[2 * j], pl0, pl1, pl2, pl3, b0, b1);
+                mma_16816(o[2 * j + 1], ph0, ph1, ph2, ph3, b2, b3);
+                mma_16816(o[2 * j + 1], pl0, pl1, pl2, pl3, b2, b3);
+            }
+        }
+        __syncthreads();  // everybody is done with this stage before it is refilled
+    }
+    __pipeline_wait_prior(0);
+
+    const float i0 = l0 > 0.0f ? __fdiv_rn(1.0f, l0) : 0.0f, i1 = l1 > 0.0f ? __fdiv_rn(1.0f, l1) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        if (r0 < n_rows) *reinterpret_cast<float2 *>(a.out + (uint64_t)r0 * a.n_head * HD + (uint64_t)head * HD + 8 * j + 2 * tig) = make_float2(o[j][0] * i0, o[j][1] * i0);
+        if (r1 < n_rows) *reinterpret_cast<float2 *>(a.out + (uint64_t)r1 * a.n_head * HD + (uint64_t)head * HD + 8 * j + 2 * tig) = make_float2(o[j][2] * i1, o[j][3] * i1);
+    }
+}
+
+template <int HD, int G>
+bool launch_prefill_instance(const AttnDecodeArgs &a, cudaStream_t st) {
+    static PerDeviceOnce once;  // one per instantiation
+    if (once.run([] { return cudaFuncSetAttribute(attn_prefill_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PrefillSmem<HD>)); }) != cudaSuccess) return false;
+    attn_prefill_kernel<HD, G><<<dim3((a.n_seq + PF_TOK - 1) / PF_TOK, a.n_head_kv), G * 32, sizeof(PrefillSmem<HD>), st>>>(a);
+    return true;
+}
+
+}  // namespace
+
+// n_seq rows = consecutive tokens of one sequence (every row's page table is the same); n_pos non-decreasing.
+bool launch_attn_prefill(const AttnDecodeArgs &a, cudaStream_t st) {
+    if (a.n_seq == 0) return true;
+    if (a.n_head % a.n_head_kv) return false;
+    const uint32_t group = a.n_head / a.n_head_kv;
+    if (a.head_dim == 128) {
+        switch (group) {
+        case 1: return launch_prefill_instance<128, 1>(a, st);
+        case 2: return launch_prefill_instance<128, 2>(a, st);
+        case 4: return launch_prefill_instance<128, 4>(a, st);
+        case 8: return launch_prefill_instance<128, 8>(a, st);
+        default: return false;
+        }
+    }
+    if (a.head_dim == 64) {
+        switch (group) {
+        case 1: return launch_prefill_instance<64, 1>(a, st);
+        case 2: return launch_prefill_instance<64, 2>(a, st);
+        case 4: return launch_prefill_instance<64, 4>(a, st);
+        case 8: return launch_prefill_instance<64, 8>(a, st);
+        default: return false;
+        }
+    }
+    return false;
+}
+
+}  // namespace ob
+
+// ====================================================================================================
 // Exact-order attention: the reference's CPU loop reproduced operation for operation, so that the
 // output equals the CPU's bit for bit (given the same f16 K/V and the same exp).  Three kernels:
 //

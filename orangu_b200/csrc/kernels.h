@@ -188,6 +188,10 @@ void launch_attn_decode(const AttnDecodeArgs &a, cudaStream_t st);
 // finish merges them (and quantizes the result when `image` is set).  False when the shape is not covered.
 bool launch_attn_decode_fused(const AttnDecodeArgs &a, bool programmatic, cudaStream_t st);
 
+// The rows (n_seq of them) are consecutive tokens of ONE sequence: tiled tensor-core attention, 16 tokens x the query heads of a kv
+// head per CTA, K/V of the window read once per 16 tokens.  Needs no partial buffers.  False when the shape is not covered.
+bool launch_attn_prefill(const AttnDecodeArgs &a, cudaStream_t st);
+
 // Exact-order attention (three kernels: scores, softmax, output); see attention.cu.
 struct AttnExactArgs {
     const float *q;            // [n_rows][n_head*head_dim]

@@ -109,6 +109,7 @@ struct ob_model {
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
     bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
+    bool use_prefill_attn = true;  // OB_PREFILL_ATTN=0: prefill chunks take the decode kernel row by row
     bool comm_failed = false;    // a collective could not be enqueued during the last step (reported by check_peer)
     // Persistent layer kernel (layer_stream.cu): the single-token products between two attention kernels as one launch.
     // Phase list: [q/k/v of layer 0] then per layer [attention-output, gate/up, down, q/k/v of the next layer | output projection].
@@ -374,8 +375,9 @@ int build_persistent_phases(ob_model *m) {
 }
 
 // Returns true when `image` (the quantized output, for the single-token product kernels) has been written.
+// one_sequence: the rows are consecutive tokens of one sequence (a prefill chunk)
 bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32_t pos_bound, uint8_t *image, const int32_t *const *d_tables,
-                   const uint32_t *d_npos, cudaStream_t st) {
+                   const uint32_t *d_npos, cudaStream_t st, bool one_sequence = false) {
     const uint32_t hd = m->cfg.head_dim;
     const __half *k_pool = m->k_pool + (size_t)li * m->layer_stride, *v_pool = m->v_pool + (size_t)li * m->layer_stride;
     if (exact_attn) {
@@ -416,6 +418,10 @@ bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
         at.max_pos = m->cfg.max_seq_len;
         at.counters = m->attn_counters;
         at.image = image;
+        if (one_sequence && T > 1 && m->use_prefill_attn && launch_attn_prefill(at, st)) {  // a prefill chunk: the tiled kernel
+            m->ctx->launches += 1;
+            return false;
+        }
         AttnDecodeArgs fused = at;
         {   // one 8-warp CTA per SM; with at least two (row, kv head) pairs per SM, 4-warp CTAs, two per SM, and the split
             // count that wastes least of the last wave
@@ -574,7 +580,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         launch_rope_kv(rk, st);
         m->ctx->launches++;
 
-        run_attention(m, li, T, exact_attn, pos_bound, nullptr, d_tables, d_npos, st);
+        run_attention(m, li, T, exact_attn, pos_bound, nullptr, d_tables, d_npos, st, gemm_order);
 
         quantize_into(m, ACT_PLAIN, m->attn, nullptr, T, q_dim, m->act_attn, needs_k({L.wo}), needs_flat({L.wo}), st);
         if (!tp) {
@@ -728,6 +734,7 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
     if (m->cfg.max_batch_tokens == 0) m->cfg.max_batch_tokens = 1;
     if (const char *e = getenv("OB_STREAM_GEMV")) m->use_stream = !(e[0] == '0' && e[1] == 0);
     if (const char *e = getenv("OB_FUSED_ATTN")) m->use_fused_attn = !(e[0] == '0' && e[1] == 0);
+    if (const char *e = getenv("OB_PREFILL_ATTN")) m->use_prefill_attn = !(e[0] == '0' && e[1] == 0);
     m->tp_rank = rank;
     m->tp_size = tp;
     m->n_head_l = c.n_head / tp;
