@@ -31,7 +31,7 @@ extern "C" {
 
 /* 2: ob_model_desc gained rope_freqs (layout change); the GGUF, static-attention and KV-copy entry points were added.
  * 3: ob_model_desc gained tp_presliced. */
-#define OB_ABI_VERSION 3u
+#define OB_ABI_VERSION 4u
 
 typedef enum ob_status {
     OB_OK = 0,
@@ -281,8 +281,18 @@ void ob_model_destroy(ob_model *model);
 /* ModelForward::new_kv_cache (E/arch/llama.rs:1002-1005): an empty per-sequence cache of fp16
  * pages (16 tokens per page) with room for capacity_tokens. */
 int ob_kv_create(ob_model *model, uint32_t capacity_tokens, ob_kv **out);
+/* The same cache with its pages taken on demand: none at creation, one more from the model's pool each time the sequence
+ * crosses a 16-token boundary (a call that finds the pool empty returns OB_ERR_CAPACITY and changes nothing), and whole pages
+ * past new_len go back on ob_kv_truncate.  The reference sizes each KvCache up front (E/kv_cache.rs:496-511 only moves the
+ * length); this is what lets many slots share one pool.  Results are identical to ob_kv_create's. */
+int ob_kv_create_paged(ob_model *model, uint32_t capacity_tokens, ob_kv **out);
 void ob_kv_destroy(ob_kv *kv);
 uint32_t ob_kv_len(const ob_kv *kv);
+uint32_t ob_kv_pages(const ob_kv *kv);              /* pages this cache holds now */
+uint32_t ob_model_pool_pages(const ob_model *model); /* pages in the model's KV pool */
+uint32_t ob_model_free_pages(const ob_model *model); /* of which no cache holds */
+uint32_t ob_model_n_vocab(const ob_model *model);
+ob_ctx *ob_model_ctx(const ob_model *model);
 /* KvCache::truncate (E/kv_cache.rs:496-511): roll back to new_len positions. */
 int ob_kv_truncate(ob_kv *kv, uint32_t new_len);
 /* Test hook: reads positions [pos0, pos0+n) of one layer back as f32 [n][n_head_kv*head_dim]. */
@@ -350,6 +360,56 @@ int ob_tp_unique_id(void *out128);
  * (1.0), rank 1 (2.0) only in the rounds whose byte in peer_delivers is non-zero.  sums_out[k] is the summed value of round k
  * (3.0), or -1 when that round's wait ran out after timeout_ms (0 = 50 ms).  Returns OB_ERR_COMM if any round ran out. */
 int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *sums_out);
+
+/* ------------------------------------------------- slot pool and decode window */
+/* SlotPool (E/scheduler.rs:36-317) + BatchCoordinator (E/batch.rs:184-324) + chunked prefill (E/generate.rs:1299-1338) over
+ * ob_forward.  One thread per generating request, as in generate::run: acquire a slot, prefill, call ob_slot_decode per token,
+ * release.  Every slot owns an on-demand paged KV cache of the model (ob_kv_create_paged). */
+typedef struct ob_slot_pool ob_slot_pool;
+typedef struct ob_slot_pool_desc {
+    uint32_t n_slots;              /* concurrent generations (`slots`) */
+    uint32_t slot_capacity_tokens; /* longest sequence one slot may hold */
+    uint32_t max_queue;            /* SlotPool::with_queue_limit: waiters beyond this are refused; 0 = unbounded */
+    uint32_t batch_wait_ms;        /* collection window, ORANGU_BATCH_WAIT_MS; 0 = 4 (E/batch.rs:63) */
+    uint32_t prefill_batch;        /* prefill chunk width, ORANGU_PREFILL_BATCH; 0 = 512 (E/generate.rs:1265) */
+    uint32_t batch_decode;         /* ORANGU_BATCH_DECODE: 0 = each step runs alone, 1 = steps inside one window run as one batch */
+} ob_slot_pool_desc;
+typedef struct ob_slot_state { /* SlotState, E/scheduler.rs:29-34 */
+    uint32_t id, busy, prompt_tokens, generated_tokens;
+} ob_slot_state;
+typedef struct ob_slot_pool_stats { /* batch_stats (E/batch.rs:117-122) and the pool's gauges */
+    uint64_t batches, batched_seqs, refused;
+    uint32_t total, busy, queued, free_pages;
+} ob_slot_pool_stats;
+
+int ob_slot_pool_create(ob_model *model, const ob_slot_pool_desc *desc, ob_slot_pool **out);
+void ob_slot_pool_destroy(ob_slot_pool *pool);
+/* SlotPool::try_acquire: whichever slot frees first, waiters served in arrival order.  timeout_ms < 0 waits without limit,
+ * 0 does not wait.  OB_ERR_CAPACITY when the queue limit is reached or the time runs out (the caller answers "overloaded"). */
+int ob_slot_acquire(ob_slot_pool *pool, int32_t timeout_ms, uint32_t *slot_id);
+/* SlotPool::acquire_slot: that slot and no other (a request pinned to the slot that holds its prompt prefix). */
+int ob_slot_acquire_id(ob_slot_pool *pool, uint32_t slot_id, int32_t timeout_ms);
+/* Drop of SlotGuard: empties the slot's cache (its pages go back to the pool) and wakes the next waiter. */
+int ob_slot_release(ob_slot_pool *pool, uint32_t slot_id);
+/* prefill: the prompt in chunks of prefill_batch tokens, each continuing the cache; the last chunk's greedy token and/or
+ * logits [n_vocab] come back (either may be NULL).  Other slots' decode batches run between the chunks. */
+int ob_slot_prefill(ob_slot_pool *pool, uint32_t slot_id, const uint32_t *tokens, uint32_t n_tokens, uint32_t *out_token, float *out_logits);
+/* BatchCoordinator::submit: one decode step of this slot's sequence.  Blocks until the batch it joined has run.  greedy may
+ * be NULL (plain argmax); its n_recent[0] ids of `recent` are this sequence's penalty window.  A failed batch fails every
+ * member with the same status. */
+int ob_slot_decode(ob_slot_pool *pool, uint32_t slot_id, uint32_t token, const ob_greedy *greedy, uint32_t *out_token, float *out_logits);
+int ob_slot_truncate(ob_slot_pool *pool, uint32_t slot_id, uint32_t new_len);
+uint32_t ob_slot_len(const ob_slot_pool *pool, uint32_t slot_id);
+ob_kv *ob_slot_kv(ob_slot_pool *pool, uint32_t slot_id);
+/* SlotPool::snapshot: fills at most cap entries, returns the slot count. */
+uint32_t ob_slot_pool_snapshot(ob_slot_pool *pool, ob_slot_state *out, uint32_t cap);
+int ob_slot_pool_get_stats(ob_slot_pool *pool, ob_slot_pool_stats *out);
+/* Text of the last failure on slot_id, or (slot_id < 0) of the calling thread's last failed pool call. */
+const char *ob_slot_last_error(ob_slot_pool *pool, int64_t slot_id);
+/* Host-only check of the pool and the window with a stand-in forward pass (no device, no model): n_threads generating
+ * threads contend for n_slots slots and run n_steps decode steps each through the window.  OB_OK when every submitter got
+ * its own answer, no slot had two holders and nothing leaked; `out` gets the totals. */
+int ob_slot_pool_selftest(uint32_t n_slots, uint32_t n_threads, uint32_t n_steps, uint32_t batch_wait_ms, uint32_t max_queue, ob_slot_pool_stats *out);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

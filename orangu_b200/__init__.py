@@ -8,5 +8,6 @@ There is no CPU fallback: every operator raises if the library or an sm_100 devi
 from .capi import OranguError, lib_path, load  # noqa: F401
 from .backend import CudaBackend, QuantMatrix, MatmulOp  # noqa: F401
 from .model import LlamaModel, KvCache  # noqa: F401
+from .scheduler import SlotPool, SlotGuard  # noqa: F401
 
 GGML_TYPE_F32, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_Q6_K = 0, 8, 12, 14

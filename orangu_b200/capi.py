@@ -91,7 +91,13 @@ SIGNATURES = {
     "ob_model_create": (_i32, [_vp, C.POINTER(ModelDesc), _PP]),
     "ob_model_destroy": (None, [_vp]),
     "ob_kv_create": (_i32, [_vp, _u32, _PP]),
+    "ob_kv_create_paged": (_i32, [_vp, _u32, _PP]),
     "ob_kv_destroy": (None, [_vp]),
+    "ob_kv_pages": (_u32, [_vp]),
+    "ob_model_pool_pages": (_u32, [_vp]),
+    "ob_model_free_pages": (_u32, [_vp]),
+    "ob_model_n_vocab": (_u32, [_vp]),
+    "ob_model_ctx": (_vp, [_vp]),
     "ob_kv_len": (_u32, [_vp]),
     "ob_kv_truncate": (_i32, [_vp, _u32]),
     "ob_kv_read": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
@@ -105,6 +111,20 @@ SIGNATURES = {
     "ob_last_device_ms": (_f32, [_vp]),
     "ob_tp_unique_id": (_i32, [_vp]),
     "ob_tp_exchange_selftest": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
+    "ob_slot_pool_create": (_i32, [_vp, _vp, _PP]),
+    "ob_slot_pool_destroy": (None, [_vp]),
+    "ob_slot_acquire": (_i32, [_vp, _i32, _vp]),
+    "ob_slot_acquire_id": (_i32, [_vp, _u32, _i32]),
+    "ob_slot_release": (_i32, [_vp, _u32]),
+    "ob_slot_prefill": (_i32, [_vp, _u32, _vp, _u32, _vp, _vp]),
+    "ob_slot_decode": (_i32, [_vp, _u32, _u32, _vp, _vp, _vp]),
+    "ob_slot_truncate": (_i32, [_vp, _u32, _u32]),
+    "ob_slot_len": (_u32, [_vp, _u32]),
+    "ob_slot_kv": (_vp, [_vp, _u32]),
+    "ob_slot_pool_snapshot": (_u32, [_vp, _vp, _u32]),
+    "ob_slot_pool_get_stats": (_i32, [_vp, _vp]),
+    "ob_slot_last_error": (C.c_char_p, [_vp, C.c_int64]),
+    "ob_slot_pool_selftest": (_i32, [_u32, _u32, _u32, _u32, _u32, _vp]),
 }
 
 _lib = None

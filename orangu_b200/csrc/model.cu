@@ -129,8 +129,9 @@ struct ob_model {
 struct ob_kv {
     ob_model *m = nullptr;
     uint32_t capacity = 0, len = 0;
-    std::vector<int32_t> pages;
-    int32_t *d_table = nullptr;
+    std::vector<int32_t> pages;   // pages held, in position order
+    int32_t *d_table = nullptr;   // device copy, room for ceil(capacity / 16) entries
+    bool on_demand = false;       // pages are taken from the pool as the sequence grows (ob_kv_create_paged) and go back on truncate
 };
 
 namespace {
@@ -238,6 +239,8 @@ void quantize_into(ob_model *m, int source, const float *x, const float *aux, ui
 }
 
 int check_peer(ob_model *m);
+uint32_t pages_missing(const ob_kv *kv, uint32_t new_len);
+int grow_pages(ob_kv *kv, uint32_t new_len);
 // Before the synchronisation that ends a step: the persistent kernel's status word comes down with the results.
 inline void fetch_status(ob_model *m, cudaStream_t st) {
     if (m->persist_ok) cudaMemcpyAsync(m->h_ls_status, m->ls_status, 4, cudaMemcpyDeviceToHost, st);
@@ -371,6 +374,28 @@ int build_persistent_phases(ob_model *m) {
     m->h_phases = std::move(ph);
     m->ls_layout = L;
     m->persist_ok = true;
+    return OB_OK;
+}
+
+// Pages an on-demand cache needs before it can hold `new_len` positions (0 for a cache that reserved its pages at creation).
+uint32_t pages_missing(const ob_kv *kv, uint32_t new_len) {
+    if (!kv->on_demand) return 0;
+    const uint32_t need = (new_len + KV_PAGE - 1) / KV_PAGE;
+    return need > kv->pages.size() ? need - (uint32_t)kv->pages.size() : 0u;
+}
+
+// Takes the missing pages from the pool and appends them to the device table.  The caller has checked that the pool has them.
+int grow_pages(ob_kv *kv, uint32_t new_len) {
+    const uint32_t n = pages_missing(kv, new_len);
+    if (!n) return OB_OK;
+    ob_model *m = kv->m;
+    const size_t first = kv->pages.size();
+    for (uint32_t i = 0; i < n; ++i) {
+        kv->pages.push_back(m->free_pages.back());
+        m->free_pages.pop_back();
+    }
+    OB_CUDA(m->ctx, cudaMemcpyAsync(kv->d_table + first, kv->pages.data() + first, (size_t)n * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+    OB_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));  // the host vector may reallocate before the copy would otherwise run
     return OB_OK;
 }
 
@@ -884,24 +909,27 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
 
 // ------------------------------------------------------------------------------------ KV cache
 
-int ob_kv_create(ob_model *m, uint32_t capacity_tokens, ob_kv **out) {
+static int kv_create(ob_model *m, uint32_t capacity_tokens, bool on_demand, ob_kv **out) {
     if (!m || !out || capacity_tokens == 0) return fail(m ? m->ctx : nullptr, OB_ERR_INVALID, "kv_create: bad argument");
     ob_ctx *ctx = m->ctx;
     std::lock_guard<std::mutex> g(ctx->mu);
     *out = nullptr;
     if (capacity_tokens > m->cfg.max_seq_len) return fail(ctx, OB_ERR_CAPACITY, "kv_create: capacity exceeds the model's max_seq_len");
     const uint32_t n_pages = (capacity_tokens + KV_PAGE - 1) / KV_PAGE;
-    if (n_pages > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "kv_create: KV pool exhausted");
+    if (!on_demand && n_pages > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "kv_create: KV pool exhausted");
     Bind b(ctx);
     ob_kv *kv = new ob_kv;
     kv->m = m;
     kv->capacity = capacity_tokens;
-    for (uint32_t i = 0; i < n_pages; ++i) {
-        kv->pages.push_back(m->free_pages.back());
-        m->free_pages.pop_back();
-    }
+    kv->on_demand = on_demand;
+    if (!on_demand)
+        for (uint32_t i = 0; i < n_pages; ++i) {
+            kv->pages.push_back(m->free_pages.back());
+            m->free_pages.pop_back();
+        }
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&kv->d_table), (size_t)n_pages * 4);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(kv->d_table, kv->pages.data(), (size_t)n_pages * 4, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(kv->d_table, 0, (size_t)n_pages * 4, ctx->stream);
+    if (e == cudaSuccess && !kv->pages.empty()) e = cudaMemcpyAsync(kv->d_table, kv->pages.data(), kv->pages.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         for (int32_t p : kv->pages) m->free_pages.push_back(p);
@@ -912,6 +940,9 @@ int ob_kv_create(ob_model *m, uint32_t capacity_tokens, ob_kv **out) {
     *out = kv;
     return OB_OK;
 }
+
+int ob_kv_create(ob_model *m, uint32_t capacity_tokens, ob_kv **out) { return kv_create(m, capacity_tokens, false, out); }
+int ob_kv_create_paged(ob_model *m, uint32_t capacity_tokens, ob_kv **out) { return kv_create(m, capacity_tokens, true, out); }
 
 void ob_kv_destroy(ob_kv *kv) {
     if (!kv) return;
@@ -926,11 +957,34 @@ void ob_kv_destroy(ob_kv *kv) {
 
 uint32_t ob_kv_len(const ob_kv *kv) { return kv ? kv->len : 0; }
 
+uint32_t ob_kv_pages(const ob_kv *kv) {
+    if (!kv) return 0;
+    std::lock_guard<std::mutex> g(kv->m->ctx->mu);
+    return (uint32_t)kv->pages.size();
+}
+
+uint32_t ob_model_free_pages(const ob_model *m) {
+    if (!m) return 0;
+    std::lock_guard<std::mutex> g(m->ctx->mu);
+    return (uint32_t)m->free_pages.size();
+}
+
+uint32_t ob_model_pool_pages(const ob_model *m) { return m ? (uint32_t)m->pool_pages : 0u; }
+uint32_t ob_model_n_vocab(const ob_model *m) { return m ? m->cfg.n_vocab : 0u; }
+ob_ctx *ob_model_ctx(const ob_model *m) { return m ? m->ctx : nullptr; }
+
 int ob_kv_truncate(ob_kv *kv, uint32_t new_len) {
     if (!kv) return OB_ERR_INVALID;
     std::lock_guard<std::mutex> g(kv->m->ctx->mu);
     if (new_len > kv->len) return fail(kv->m->ctx, OB_ERR_INVALID, "kv_truncate: new_len exceeds the current length");
     kv->len = new_len;
+    if (kv->on_demand) {  // whole pages past the new length go back to the pool (the device table keeps stale ids nobody reads)
+        const size_t keep = (new_len + KV_PAGE - 1) / KV_PAGE;
+        while (kv->pages.size() > keep) {
+            kv->m->free_pages.push_back(kv->pages.back());
+            kv->pages.pop_back();
+        }
+    }
     return OB_OK;
 }
 
@@ -969,7 +1023,9 @@ int ob_kv_copy_prefix(ob_kv *dst, const ob_kv *src, uint32_t n) {
     std::lock_guard<std::mutex> g(ctx->mu);
     if (dst->len != 0) return fail(ctx, OB_ERR_INVALID, "kv_copy_prefix: the destination is not empty");
     if (n > src->len || n > dst->capacity) return fail(ctx, OB_ERR_CAPACITY, "kv_copy_prefix: n exceeds the source length or the destination capacity");
+    if (pages_missing(dst, n) > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "kv_copy_prefix: KV pool exhausted");
     Bind b(ctx);
+    if (int rc = grow_pages(dst, n)) return rc;
     const size_t page_elems = (size_t)m->n_head_kv_l * KV_PAGE * m->cfg.head_dim;  // a multiple of 8 halves: head_dim is even and a page holds 16 tokens
     const uint32_t n_pages = (n + KV_PAGE - 1) / KV_PAGE;
     if (n_pages) {
@@ -1172,6 +1228,15 @@ int ob_forward(ob_model *m, ob_kv *const *kvs, const uint32_t *tokens, const uin
     }
     for (uint64_t i = 0; i < total; ++i)
         if (tokens[i] >= m->cfg.n_vocab) return fail(ctx, OB_ERR_INVALID, "forward: token id out of vocabulary range");
+    {   // on-demand caches: all the pages this call needs, or none of them
+        uint64_t need = 0;
+        for (uint32_t s = 0; s < n_seq; ++s) need += pages_missing(kvs[s], kvs[s]->len + n_tokens[s]);
+        if (need > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "forward: KV pool exhausted");
+        for (uint32_t s = 0; s < n_seq; ++s) {
+            int rc = grow_pages(kvs[s], kvs[s]->len + n_tokens[s]);
+            if (rc) return rc;
+        }
+    }
     ctx->last_ms = 0.0f;
 
     if (all_single) {
@@ -1311,7 +1376,9 @@ int ob_decode_greedy(ob_model *m, ob_kv *kv, uint32_t token, uint32_t *out_token
     std::lock_guard<std::mutex> g(ctx->mu);
     if (token >= m->cfg.n_vocab) return fail(ctx, OB_ERR_INVALID, "decode_greedy: token id out of vocabulary range");
     if (kv->len >= kv->capacity) return fail(ctx, OB_ERR_CAPACITY, "decode_greedy: KV cache is full");
+    if (pages_missing(kv, kv->len + 1) > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "decode_greedy: KV pool exhausted");
     Bind b(ctx);
+    if (int rc = grow_pages(kv, kv->len + 1)) return rc;
     const MetaLayout ml(m->T);
     reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens)[0] = token;
     reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions)[0] = kv->len;
@@ -1348,6 +1415,13 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
             if (kvs[s2] == kvs[s]) return fail(ctx, OB_ERR_INVALID, "decode_loop: the same KV cache appears twice");
     }
     Bind b(ctx);
+    {
+        uint64_t need = 0;
+        for (uint32_t s = 0; s < n_seq; ++s) need += pages_missing(kvs[s], kvs[s]->len + n_steps);
+        if (need > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "decode_loop: KV pool exhausted");
+        for (uint32_t s = 0; s < n_seq; ++s)
+            if (int rc = grow_pages(kvs[s], kvs[s]->len + n_steps)) return rc;
+    }
     if ((uint64_t)n_steps * n_seq > m->history_cap) {
         int rc = dev_alloc(m, &m->d_history, (size_t)n_steps * n_seq);
         if (rc) return rc;

@@ -20,12 +20,17 @@ def _matrix(t) -> capi.MatrixDesc:
 class KvCache:
     """Per-sequence paged fp16 KV cache (ModelForward::new_kv_cache, arch/llama.rs:1002-1005)."""
 
-    def __init__(self, model: "LlamaModel", capacity: int):
+    def __init__(self, model: "LlamaModel", capacity: int, paged: bool = False):
         self.model = model
         self._lib = model._lib
         self._h = C.c_void_p()
-        capi.check(model.backend._h, self._lib.ob_kv_create(model._h, capacity, C.byref(self._h)))
+        create = self._lib.ob_kv_create_paged if paged else self._lib.ob_kv_create  # paged: pages on demand, back on truncate
+        capi.check(model.backend._h, create(model._h, capacity, C.byref(self._h)))
         self.capacity = capacity
+
+    @property
+    def pages(self) -> int:
+        return int(self._lib.ob_kv_pages(self._h))
 
     def __len__(self):
         return int(self._lib.ob_kv_len(self._h))
@@ -130,8 +135,16 @@ class LlamaModel:
         self.max_batch_tokens = max_batch_tokens
         return self
 
-    def new_kv_cache(self, capacity: int) -> KvCache:
-        return KvCache(self, capacity)
+    def new_kv_cache(self, capacity: int, paged: bool = False) -> KvCache:
+        return KvCache(self, capacity, paged)
+
+    @property
+    def free_pages(self) -> int:
+        return int(self._lib.ob_model_free_pages(self._h))
+
+    @property
+    def pool_pages(self) -> int:
+        return int(self._lib.ob_model_pool_pages(self._h))
 
     # ModelForward::forward (arch/llama.rs:1007-1032): logits of the last token
     def forward(self, cache: KvCache, tokens, start_pos: int) -> np.ndarray:

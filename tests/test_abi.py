@@ -33,7 +33,7 @@ def test_header_and_binding_agree(lib):
 
 
 def test_constants_without_a_device(lib):
-    assert lib.ob_abi_version() == 3
+    assert lib.ob_abi_version() == 4
     assert [lib.ob_supports_type(t) for t in (0, 8, 12, 14, 2, 6, 20)] == [1, 1, 1, 1, 1, 1, 1]
     assert [lib.ob_supports_type(t) for t in (1, 3, 7, 10, 13, 30)] == [0, 0, 0, 0, 0, 0]
     assert lib.ob_reduced_surface() is None
