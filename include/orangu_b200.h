@@ -48,6 +48,7 @@ typedef enum ob_status {
 #define OB_TYPE_F32 0u
 #define OB_TYPE_Q8_0 8u
 #define OB_TYPE_Q4_K 12u
+#define OB_TYPE_Q5_K 13u
 #define OB_TYPE_Q6_K 14u
 /* Per-32 symmetric types (one f16 scale, 32 signed codes).  The CPU kernels for them are the Q8_0 loops over the unpacked
  * codes (E/vecdot.rs:2842-2881 decode, :1277-1340 + :2598-2629 batched), so the library unpacks them once, at registration,
@@ -74,7 +75,7 @@ const char *ob_last_error(const ob_ctx *ctx);
 
 unsigned ob_abi_version(void);
 
-/* Replaces Backend::supports_type (B/mod.rs:479-495): 1 for Q8_0, Q4_K, Q6_K, Q4_0, Q5_0, IQ4_NL (and F32
+/* Replaces Backend::supports_type (B/mod.rs:479-495): 1 for Q8_0, Q4_K, Q5_K, Q6_K, Q4_0, Q5_0, IQ4_NL (and F32
  * for norm vectors), 0 otherwise, so a missing kernel is a named start-up error. */
 int ob_supports_type(uint32_t ggml_type);
 
@@ -207,6 +208,13 @@ typedef struct ob_layer_desc {
     ob_matrix_desc w_gate;  /* blk.N.ffn_gate.weight    [n_embd -> n_ff] */
     ob_matrix_desc w_up;    /* blk.N.ffn_up.weight */
     ob_matrix_desc w_down;  /* blk.N.ffn_down.weight    [n_ff -> n_embd] */
+    /* Qwen2 / Qwen3-style extras (E/arch/llama.rs:45-60, 171-175, 750-780); each NULL when the file has no such tensor.
+     * Always the FULL vectors, also with tp_presliced (they are small; the model takes its part). */
+    const float *q_bias;    /* blk.N.attn_q.bias        [n_head*head_dim]     added to every projected row */
+    const float *k_bias;    /* blk.N.attn_k.bias        [n_head_kv*head_dim] */
+    const float *v_bias;    /* blk.N.attn_v.bias        [n_head_kv*head_dim] */
+    const float *q_norm;    /* blk.N.attn_q_norm.weight [head_dim]            per-head RMSNorm of q after the bias, before RoPE */
+    const float *k_norm;    /* blk.N.attn_k_norm.weight [head_dim] */
 } ob_layer_desc;
 
 /* ModelConfig (E/loader.rs:34-58) plus run-time sizing. */
@@ -237,6 +245,8 @@ typedef struct ob_model_desc {
                                  * ffn_down (QuantMatrix::rows, E/loader.rs:627-646, and its column counterpart); token_embd
                                  * and the norm vectors are whole.  For hosts that never hold the full tensors (a 70B model
                                  * on eight ranks). */
+    uint32_t rope_neox;         /* RopeLayout (E/tensor.rs:873-889): 0 = Norm, pairs (2i, 2i+1) -- llama, mistral; 1 = Neox, pairs
+                                 * (i, i + rope_dim/2) -- qwen2, qwen3, qwen3vl (rope_layout_for, E/arch/llama.rs:114-119) */
 } ob_model_desc;
 
 /* ------------------------------------------------- GGUF files

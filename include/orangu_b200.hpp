@@ -34,6 +34,7 @@ struct QuantMatrix {
         case OB_TYPE_Q4_0: case OB_TYPE_IQ4_NL: be = 32; bb = 18; break;
         case OB_TYPE_Q5_0: be = 32; bb = 22; break;
         case OB_TYPE_Q4_K: be = 256; bb = 144; break;
+        case OB_TYPE_Q5_K: be = 256; bb = 176; break;
         default: break;
         }
         return (uint64_t)(in_dim / be) * bb;

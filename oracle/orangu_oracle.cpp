@@ -939,14 +939,19 @@ void oref_rope_table(float *sin_cos, size_t n_pos, size_t rope_dim, float freq_b
 }
 
 /* E/tensor.rs:1162-1176, RopeLayout::Norm */
-static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors);
+static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors,
+                         int neox = 0);
+
+void oref_rope_layout(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors, int neox) {
+    rope_norm_ff(x, n_head, head_dim, pos, rope_dim, freq_base, freq_factors, neox);
+}
 
 void oref_rope_norm(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base) {
     rope_norm_ff(x, n_head, head_dim, pos, rope_dim, freq_base, nullptr);
 }
 
-/* E/tensor.rs:1140-1176 with optional frequency factors (freq /= ff[i], :1143-1145) */
-static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors) {
+/* E/tensor.rs:1140-1176 with optional frequency factors (freq /= ff[i], :1143-1145); the pairing is :1167-1170 */
+static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base, const float *freq_factors, int neox) {
     size_t half = rope_dim / 2;
     std::vector<float> rot(half * 2);
     for (size_t i = 0; i < half; ++i) {
@@ -960,9 +965,10 @@ static void rope_norm_ff(float *x, size_t n_head, size_t head_dim, size_t pos, s
         float *head = x + h * head_dim;
         for (size_t i = 0; i < half; ++i) {
             float sn = rot[2 * i], cs = rot[2 * i + 1];
-            float a = head[2 * i], b = head[2 * i + 1];
-            head[2 * i] = a * cs - b * sn;
-            head[2 * i + 1] = a * sn + b * cs;
+            size_t lo = neox ? i : 2 * i, hi = neox ? i + half : 2 * i + 1;
+            float a = head[lo], b = head[hi];
+            head[lo] = a * cs - b * sn;
+            head[hi] = a * sn + b * cs;
         }
     }
 }
@@ -1127,11 +1133,19 @@ int oref_forward(const oref_model *m, oref_kv *kv, const uint32_t *tokens, size_
         if (mm(normed.data(), n_tokens, L.wq, q.data(), n_threads)) return -3;
         if (mm(normed.data(), n_tokens, L.wk, k.data(), n_threads)) return -3;
         if (mm(normed.data(), n_tokens, L.wv, v.data(), n_threads)) return -3;
+        /* E/arch/llama.rs:750-780: biases (add_bias_per_row, E/tensor.rs:1233-1239), then the per-head RMSNorm of q and k */
+        for (size_t t = 0; t < n_tokens; ++t) {
+            if (L.q_bias) oref_add(&q[t * q_dim], L.q_bias, q_dim);
+            if (L.k_bias) oref_add(&k[t * kv_dim], L.k_bias, kv_dim);
+            if (L.v_bias) oref_add(&v[t * kv_dim], L.v_bias, kv_dim);
+        }
+        if (L.q_norm) oref_rmsnorm(q.data(), q.data(), L.q_norm, n_tokens * n_head, head_dim, c.rms_eps);
+        if (L.k_norm) oref_rmsnorm(k.data(), k.data(), L.k_norm, n_tokens * n_head_kv, head_dim, c.rms_eps);
         std::vector<float> &ck = kv->k[li], &cv = kv->v[li];
         for (size_t t = 0; t < n_tokens; ++t) { /* E/arch/llama.rs:787-809 */
             size_t pos = start_pos + t;
-            rope_norm_ff(&q[t * q_dim], n_head, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs);
-            rope_norm_ff(&k[t * kv_dim], n_head_kv, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs);
+            rope_norm_ff(&q[t * q_dim], n_head, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs, (int)c.rope_neox);
+            rope_norm_ff(&k[t * kv_dim], n_head_kv, head_dim, pos, c.rope_dim, c.rope_freq_base, c.rope_freqs, (int)c.rope_neox);
             for (size_t i = 0; i < kv_dim; ++i) {
                 float kk = k[t * kv_dim + i], vv = v[t * kv_dim + i];
                 if (kv->f16) {

@@ -86,6 +86,8 @@ void oref_rmsnorm(float *dst, const float *src, const float *weight, size_t n_to
                   size_t dim, float eps);                                                 /* E/tensor.rs:732-757 */
 void oref_rope_norm(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim,
                     float freq_base);                                                     /* E/tensor.rs:1115-1177, NORM layout, no YaRN */
+void oref_rope_layout(float *x, size_t n_head, size_t head_dim, size_t pos, size_t rope_dim, float freq_base,
+                      const float *freq_factors, int neox);                                /* E/tensor.rs:1115-1177, either pairing */
 void oref_rope_table(float *sin_cos, size_t n_pos, size_t rope_dim, float freq_base);     /* the (sin,cos) pairs the loop above applies */
 void oref_softmax(float *x, size_t n);                                                    /* E/tensor.rs:809-821 */
 float oref_silu(float x);                                                                 /* E/tensor.rs:825-827 */
@@ -112,12 +114,17 @@ typedef struct {
     const float *attn_norm;
     const float *ffn_norm;
     oref_matrix wq, wk, wv, wo, w_gate, w_up, w_down;
+    /* Qwen2/Qwen3-style extras, each NULL when the file has no such tensor (E/arch/llama.rs:45-60, 171-175):
+     * attn_{q,k,v}.bias added to every projected row, attn_{q,k}_norm.weight [head_dim] as a per-head RMSNorm before RoPE */
+    const float *q_bias, *k_bias, *v_bias, *q_norm, *k_norm;
 } oref_layer;
 
 typedef struct {
     uint32_t n_vocab, n_embd, n_layer, n_head, n_head_kv, head_dim, rope_dim, n_ff;
     float rope_freq_base, rms_eps;
     const float *rope_freqs; /* optional rope_freqs.weight, rope_dim / 2 factors dividing the frequencies (E/arch/llama.rs:186-200); NULL: none */
+    uint32_t rope_neox;      /* 0: RopeLayout::Norm, pairs (2i, 2i+1) -- llama, mistral; 1: RopeLayout::Neox, pairs (i, i + rope_dim/2) --
+                              * qwen2, qwen3, qwen3vl and unknown architectures (rope_layout_for, E/arch/llama.rs:114-119) */
 } oref_config;
 
 typedef struct oref_model oref_model;

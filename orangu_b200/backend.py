@@ -13,7 +13,7 @@ import numpy as np
 
 from . import capi
 
-BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 2: (18, 32), 6: (22, 32), 20: (18, 32)}
+BLOCK = {8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256), 2: (18, 32), 6: (22, 32), 20: (18, 32)}
 
 
 def tensor_byte_size(ggml_type: int, n_elems: int) -> int:

@@ -20,7 +20,7 @@ OBJDIR = os.path.join(LIBDIR, "obj")
 LIB = os.path.join(LIBDIR, "liborangu_b200.so")
 SYNTH_LIB = os.path.join(LIBDIR, "libob_synth.so")
 
-CU_SOURCES = ["formats.cu", "act_quant.cu", "gemv.cu", "glue.cu", "attention.cu", "api.cu", "model.cu", "tp.cu", "noalloc.cu", "stream_gemv.cu", "layer_stream.cu", "gemm_mma.cu", "gemm_tc5.cu", "gguf.cu", "sched.cu"]
+CU_SOURCES = ["formats.cu", "act_quant.cu", "gemv.cu", "glue.cu", "attention.cu", "api.cu", "model.cu", "tp.cu", "noalloc.cu", "stream_gemv.cu", "layer_stream.cu", "gemm_mma.cu", "gemm_tc5.cu", "gguf.cu", "sched.cu", "q5k.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     # The reproduced arithmetic never fuses a*b+c; FMAs are written out where wanted.

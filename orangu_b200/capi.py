@@ -24,7 +24,8 @@ class MatrixDesc(C.Structure):
 
 class LayerDesc(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + [
-        (n, MatrixDesc) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")]
+        (n, MatrixDesc) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")] + [
+        (n, C.c_void_p) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
 
 
 class ModelDesc(C.Structure):
@@ -33,7 +34,7 @@ class ModelDesc(C.Structure):
         ("max_seq_len", C.c_uint32), ("max_batch_tokens", C.c_uint32), ("kv_pool_tokens", C.c_uint64), ("exact_attention_max_pos", C.c_uint32),
         ("token_embd", MatrixDesc), ("output_norm", C.c_void_p), ("output", MatrixDesc),
         ("layers", C.POINTER(LayerDesc)), ("tp_rank", C.c_uint32), ("tp_size", C.c_uint32), ("tp_unique_id", C.c_void_p),
-        ("rope_freqs", C.c_void_p), ("tp_presliced", C.c_uint32)]
+        ("rope_freqs", C.c_void_p), ("tp_presliced", C.c_uint32), ("rope_neox", C.c_uint32)]
 
 
 class MatmulOpC(C.Structure):

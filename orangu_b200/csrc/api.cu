@@ -44,7 +44,7 @@ int ensure(ob_ctx *ctx, Scratch &s, size_t bytes) {
     return OB_OK;
 }
 
-bool type_supported(uint32_t t) { return t == TYPE_Q8_0 || t == TYPE_Q4_K || t == TYPE_Q6_K || is_sym32_source(t); }
+bool type_supported(uint32_t t) { return t == TYPE_Q8_0 || t == TYPE_Q4_K || t == TYPE_Q5_K || t == TYPE_Q6_K || is_sym32_source(t); }
 
 }  // namespace obrt
 
@@ -143,7 +143,7 @@ int make_weight(ob_ctx *ctx, const uint8_t *raw, uint64_t row_bytes, uint32_t ty
     d.in_dim = n_cols;
     d.out_dim = n_rows;
     d.nb = n_cols / be;
-    const uint32_t main_bytes = d.type == TYPE_Q4_K ? 144u : (d.type == TYPE_Q6_K ? 208u : 32u);
+    const uint32_t main_bytes = d.type == TYPE_Q4_K ? 144u : d.type == TYPE_Q5_K ? 176u : (d.type == TYPE_Q6_K ? 208u : 32u);
     d.d_off = d.nb * main_bytes;
     const uint64_t row_size = (uint64_t)d.nb * block_bytes_gguf(d.type);
     d.row_stride = (row_size + 15) & ~(uint64_t)15;

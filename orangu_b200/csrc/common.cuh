@@ -15,7 +15,7 @@
 
 namespace ob {
 
-constexpr uint32_t TYPE_F32 = 0, TYPE_Q8_0 = 8, TYPE_Q4_K = 12, TYPE_Q6_K = 14;
+constexpr uint32_t TYPE_F32 = 0, TYPE_Q8_0 = 8, TYPE_Q4_K = 12, TYPE_Q5_K = 13, TYPE_Q6_K = 14;
 // Source-only types: per-32 symmetric formats (one f16 scale, 32 signed codes, no min term) whose CPU kernels are the
 // Q8_0 loops over the unpacked codes (engine/vecdot.rs:2842-2881, :1277-1340).  They are unpacked to the device's Q8_0
 // layout at registration, so every kernel sees TYPE_Q8_0 and gives the CPU's bits; the price is 34 instead of 18 or 22
@@ -104,6 +104,7 @@ __device__ __forceinline__ int warp_sum_i(int v) {
 //
 // Rows keep the GGUF block contents but are re-laid so that every 16-byte load is aligned:
 //   Q4_K  unchanged: nb blocks of 144 B  [d f16 | dmin f16 | scales 12 | qs 128]
+//   Q5_K  unchanged: nb blocks of 176 B  [d f16 | dmin f16 | scales 12 | qh 32 | qs 128]
 //   Q6_K  nb blocks of 208 B [ql 128 | qh 64 | scales 16], then the nb f16 d values
 //   Q8_0  nb runs of 32 int8 codes, then the nb f16 d values
 // row_stride is the row size rounded up to 16 bytes.  The byte count per row is the GGUF one.
@@ -119,7 +120,7 @@ struct DevWeight {
 
 __host__ __device__ inline uint32_t block_elems(uint32_t type) { return type == TYPE_Q8_0 || is_sym32_source(type) ? 32u : 256u; }
 __host__ __device__ inline uint32_t block_bytes_gguf(uint32_t type) {
-    return type == TYPE_Q8_0 ? 34u : type == TYPE_Q4_K ? 144u : type == TYPE_Q5_0 ? 22u : is_sym32_source(type) ? 18u : 210u;
+    return type == TYPE_Q8_0 ? 34u : type == TYPE_Q4_K ? 144u : type == TYPE_Q5_K ? 176u : type == TYPE_Q5_0 ? 22u : is_sym32_source(type) ? 18u : 210u;
 }
 
 // Quantized activations of one token row, natural element order.

@@ -1,7 +1,7 @@
 // GGUF block formats on the device: re-layout at registration and exact dequantisation.
 //
 // Dequantisation follows the reference's decode rules operation for operation
-// (src/bin/orangu-server/engine/quant.rs:639-649 Q8_0, :666-697 Q4_K, :746-787 Q6_K),
+// (src/bin/orangu-server/engine/quant.rs:639-649 Q8_0, :666-697 Q4_K, :703-742 Q5_K, :746-787 Q6_K),
 // so a row read back from the device equals QuantMatrix::row bit for bit.
 #include "common.cuh"
 #include "kernels.h"
@@ -43,6 +43,9 @@ __global__ void repack_kernel(const uint8_t *__restrict__ src, uint64_t src_row_
     } else if (w.type == TYPE_Q4_K) {
         uint8_t *d = drow + (uint64_t)b * 144;
         for (int i = 0; i < 144; ++i) d[i] = s[i];
+    } else if (w.type == TYPE_Q5_K) {
+        uint8_t *d = drow + (uint64_t)b * 176;
+        for (int i = 0; i < 176; ++i) d[i] = s[i];
     } else if (w.type == TYPE_Q6_K) {
         uint8_t *d = drow + (uint64_t)b * 208;
         for (int i = 0; i < 208; ++i) d[i] = s[i];
@@ -82,6 +85,16 @@ __device__ float dequant_element(const DevWeight &w, uint32_t r, uint32_t e) {
         scale_min_k4(j, blk + 4, sc, m);
         uint8_t byte = blk[16 + (j >> 1) * 32 + (i & 31)];
         int q = (j & 1) ? (byte >> 4) : (byte & 0x0F);
+        float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)m);
+        return __fsub_rn(__fmul_rn(dl, (float)q), ml);
+    }
+    if (w.type == TYPE_Q5_K) {  // quant.rs:703-742
+        const uint8_t *blk = row + (uint64_t)b * 176;
+        float d = f16_bits_to_f32(blk[0] | (blk[1] << 8)), dmin = f16_bits_to_f32(blk[2] | (blk[3] << 8));
+        int j = i >> 5, sc, m;
+        scale_min_k4(j, blk + 4, sc, m);
+        uint8_t byte = blk[48 + (j >> 1) * 32 + (i & 31)];
+        int q = ((j & 1) ? (byte >> 4) : (byte & 0x0F)) + (((blk[16 + (i & 31)] >> j) & 1) ? 16 : 0);
         float dl = __fmul_rn(d, (float)sc), ml = __fmul_rn(dmin, (float)m);
         return __fsub_rn(__fmul_rn(dl, (float)q), ml);
     }

@@ -383,6 +383,7 @@ size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, boo
 }
 
 uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order) {
+    if (type == TYPE_Q5_K) return 1;
     if ((type == TYPE_Q4_K || type == TYPE_Q6_K) && n_tokens >= 9) return 1;  // the tensor-core kernel covers all tokens in one launch
     uint32_t T = 8;
     while (T > 1 && (T / 2 >= n_tokens || gemv_smem_bytes(type, in_dim, T, gemm_order) > 200 * 1024)) T /= 2;
@@ -391,6 +392,10 @@ uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool g
 
 void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st) {
     if (a.n_tokens == 0 || a.n_seg == 0) return;
+    if (a.seg[0].w.type == TYPE_Q5_K) {  // its own kernel, both orders (q5k.cu)
+        launch_q5k(a, sm_count, st);
+        return;
+    }
     static const bool use_mma = [] { const char *e = getenv("OB_MMA"); return !(e && e[0] == '0' && e[1] == 0); }();
     if (gemm_tc5_supported(a) && launch_gemm_tc5(a, sm_count, st)) return;  // many tokens: tcgen05 tiles (gemm_tc5.cu)
     if (use_mma && gemm_mma_supported(a)) {  // many tokens: tensor-core tiles (gemm_mma.cu)

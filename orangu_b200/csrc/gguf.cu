@@ -289,7 +289,9 @@ int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *d) {
     const Value *av = find(g, "general.architecture");
     if (!av || av->type != 8) return gfail(OB_ERR_INVALID, "gguf_model_desc: general.architecture is missing");
     const std::string arch = av->s;
-    if (arch != "llama") return gfail(OB_ERR_UNSUPPORTED, "gguf_model_desc: architecture '" + arch + "' is outside this build (llama only)");
+    // LLAMA_STYLE_ARCHITECTURES, loader.rs:190
+    if (arch != "llama" && arch != "qwen2" && arch != "qwen3" && arch != "mistral" && arch != "qwen3vl")
+        return gfail(OB_ERR_UNSUPPORTED, "gguf_model_desc: architecture '" + arch + "' is outside this build (llama, mistral, qwen2, qwen3, qwen3vl)");
     auto req = [&](const char *suffix, uint64_t *out) { return as_u64(find(g, arch + "." + suffix), out); };
     uint64_t n_embd = 0, n_layer = 0, n_head = 0, n_head_kv = 0, n_vocab = 0, head_dim = 0, rope_dim = 0, n_ff = 0;
     if (!req("embedding_length", &n_embd) || !req("block_count", &n_layer) || !req("attention.head_count", &n_head))
@@ -354,6 +356,12 @@ int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *d) {
         if (n_ff == 0) n_ff = L.w_gate.out_dim;  // <arch>.feed_forward_length is optional here: the tensor says it
         if ((rc = matrix(p + "ffn_up.weight", n_embd, n_ff, &L.w_up, false))) return rc;
         if ((rc = matrix(p + "ffn_down.weight", n_ff, n_embd, &L.w_down, false))) return rc;
+        // present on Qwen2 / Qwen3-shaped files only (llama.rs:171-175)
+        if ((rc = vector_f32(p + "attn_q.bias", q_dim, &L.q_bias, true))) return rc;
+        if ((rc = vector_f32(p + "attn_k.bias", kv_dim, &L.k_bias, true))) return rc;
+        if ((rc = vector_f32(p + "attn_v.bias", kv_dim, &L.v_bias, true))) return rc;
+        if ((rc = vector_f32(p + "attn_q_norm.weight", head_dim, &L.q_norm, true))) return rc;
+        if ((rc = vector_f32(p + "attn_k_norm.weight", head_dim, &L.k_norm, true))) return rc;
     }
     uint64_t ff_meta = 0;
     if (req("feed_forward_length", &ff_meta) && n_layer && ff_meta != n_ff)
@@ -368,6 +376,7 @@ int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *d) {
     d->n_ff = (uint32_t)n_ff;
     d->rope_freq_base = freq_base;
     d->rms_eps = eps;
+    d->rope_neox = (arch == "llama" || arch == "mistral") ? 0u : 1u;  // rope_layout_for, llama.rs:114-119
     d->layers = g->layers.data();
     uint64_t ctx_train = 0;
     d->max_seq_len = req("context_length", &ctx_train) ? (uint32_t)std::min<uint64_t>(ctx_train, 1u << 20) : 4096u;  // the caller may lower it

@@ -81,6 +81,63 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(RopeKvArgs a) {
     }
 }
 
+// The same step for the Qwen-style variants: bias, per-head RMSNorm, either pairing.  One CTA per token; the rows live in
+// shared memory between the steps.  The per-head sum of squares is added left to right by one thread per head, as
+// rmsnorm_inplace does it (engine/tensor.rs:691-700) -- head_dim is 64..256, so the sequential loop is short.
+__global__ void __launch_bounds__(256) qkv_post_kernel(RopeKvArgs a) {
+    extern __shared__ float sm[];
+    const uint32_t t = blockIdx.x, hd = a.head_dim, half = a.rope_dim / 2;
+    const uint32_t q_dim = a.n_head * hd, kv_dim = a.n_head_kv * hd, n_heads = a.n_head + 2 * a.n_head_kv;
+    float *sq = sm, *sk = sm + q_dim, *sv = sk + kv_dim, *scale = sv + kv_dim;  // scale[n_head + n_head_kv]
+    float *q = a.q + (uint64_t)t * q_dim;
+    const float *k = a.k + (uint64_t)t * kv_dim, *v = a.v + (uint64_t)t * kv_dim;
+    for (uint32_t i = threadIdx.x; i < q_dim; i += blockDim.x) sq[i] = a.q_bias ? __fadd_rn(q[i], a.q_bias[i]) : q[i];
+    for (uint32_t i = threadIdx.x; i < kv_dim; i += blockDim.x) {
+        sk[i] = a.k_bias ? __fadd_rn(k[i], a.k_bias[i]) : k[i];
+        sv[i] = a.v_bias ? __fadd_rn(v[i], a.v_bias[i]) : v[i];
+    }
+    __syncthreads();
+    if (a.q_norm || a.k_norm) {
+        for (uint32_t h = threadIdx.x; h < a.n_head + a.n_head_kv; h += blockDim.x) {
+            const bool is_q = h < a.n_head;
+            if (is_q ? a.q_norm != nullptr : a.k_norm != nullptr) {
+                const float *row = is_q ? sq + h * hd : sk + (h - a.n_head) * hd;
+                float sum = 0.0f;
+                for (uint32_t i = 0; i < hd; ++i) sum = __fadd_rn(sum, __fmul_rn(row[i], row[i]));
+                scale[h] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(sum, (float)hd), a.rms_eps)));
+            }
+        }
+        __syncthreads();
+        if (a.q_norm)
+            for (uint32_t i = threadIdx.x; i < q_dim; i += blockDim.x) sq[i] = __fmul_rn(__fmul_rn(sq[i], scale[i / hd]), a.q_norm[i % hd]);
+        if (a.k_norm)
+            for (uint32_t i = threadIdx.x; i < kv_dim; i += blockDim.x) sk[i] = __fmul_rn(__fmul_rn(sk[i], scale[a.n_head + i / hd]), a.k_norm[i % hd]);
+        __syncthreads();
+    }
+    const uint32_t pos = a.positions[t];
+    const float2 *rot = reinterpret_cast<const float2 *>(a.rope_table) + (uint64_t)pos * half;
+    for (uint32_t i = threadIdx.x; i < (a.n_head + a.n_head_kv) * half; i += blockDim.x) {  // every pair is touched by one thread only
+        const uint32_t h = i / half, p = i % half;
+        float *head = h < a.n_head ? sq + h * hd : sk + (h - a.n_head) * hd;
+        const uint32_t lo = a.neox ? p : 2 * p, hi = a.neox ? p + half : 2 * p + 1;
+        const float2 sc = rot[p];  // (sin, cos)
+        const float va = head[lo], vb = head[hi];
+        head[lo] = __fsub_rn(__fmul_rn(va, sc.y), __fmul_rn(vb, sc.x));
+        head[hi] = __fadd_rn(__fmul_rn(va, sc.x), __fmul_rn(vb, sc.y));
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < q_dim; i += blockDim.x) q[i] = sq[i];
+    const int32_t page = a.page_tables[t][pos / KV_PAGE];
+    const uint32_t slot = pos % KV_PAGE;
+    for (uint32_t i = threadIdx.x; i < kv_dim / 2; i += blockDim.x) {
+        const uint32_t h = (2 * i) / hd, e = (2 * i) % hd;
+        const uint64_t o = (((uint64_t)page * a.n_head_kv + h) * KV_PAGE + slot) * hd + e;
+        *reinterpret_cast<__half2 *>(a.k_pool + o) = __floats2half2_rn(sk[2 * i], sk[2 * i + 1]);
+        *reinterpret_cast<__half2 *>(a.v_pool + o) = __floats2half2_rn(sv[2 * i], sv[2 * i + 1]);
+    }
+    (void)n_heads;
+}
+
 __global__ void rope_plain_kernel(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *__restrict__ sin_cos) {
     const uint32_t half = rope_dim / 2, pairs = head_dim / 2;
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -161,7 +218,15 @@ void launch_add(float *a, const float *b, uint64_t n, cudaStream_t st) {
     if (n) add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a, b, n);
 }
 void launch_rope_kv(const RopeKvArgs &a, cudaStream_t st) {
-    if (a.n_tokens) rope_kv_kernel<<<a.n_tokens, 256, 0, st>>>(a);
+    if (!a.n_tokens) return;
+    if (!a.q_bias && !a.k_bias && !a.v_bias && !a.q_norm && !a.k_norm && !a.neox) {
+        rope_kv_kernel<<<a.n_tokens, 256, 0, st>>>(a);
+        return;
+    }
+    const size_t smem = ((size_t)(a.n_head + 2 * a.n_head_kv) * a.head_dim + a.n_head + a.n_head_kv) * 4;
+    static PerDeviceOnce once;
+    if (once.run([] { return cudaFuncSetAttribute(qkv_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); }) != cudaSuccess) return;
+    qkv_post_kernel<<<a.n_tokens, 256, smem, st>>>(a);
 }
 void launch_rope_plain(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *sin_cos_row, cudaStream_t st) {
     uint32_t n = n_head * head_dim / 2;

@@ -57,6 +57,9 @@ void launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t st);
 size_t gemv_smem_bytes(uint32_t type, uint32_t in_dim, uint32_t tile_tokens, bool gemm_order);
 uint32_t gemv_launches(uint32_t type, uint32_t in_dim, uint32_t n_tokens, bool gemm_order);  // kernels launch_gemv issues
 
+// ---- q5k.cu: Q5_K weights, one kernel for any token count and both fp32 orders
+void launch_q5k(const GemvArgs &a, int sm_count, cudaStream_t st);
+
 // ---- gemm_mma.cu: many-token products on the tensor cores (Q4_K and Q6_K; 9 tokens or more)
 bool gemm_mma_supported(const GemvArgs &a);
 void launch_gemm_mma(const GemvArgs &a, int sm_count, cudaStream_t st);
@@ -152,6 +155,11 @@ struct RopeKvArgs {
     __half *k_pool;           // this layer's pages [page][n_head_kv][16][head_dim]
     __half *v_pool;
     uint32_t n_tokens, n_head, n_head_kv, head_dim, rope_dim;
+    // Qwen2 / Qwen3-style extras (engine/arch/llama.rs:750-780), all optional: biases added to the projected rows, then a
+    // per-head RMSNorm of q and k (weights [head_dim]), then the rotation with either pairing.
+    const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    float rms_eps = 0.0f;
+    bool neox = false;  // pairs (i, i + rope_dim/2) instead of (2i, 2i+1)
 };
 void launch_rope_kv(const RopeKvArgs &a, cudaStream_t st);
 void launch_rope_plain(float *x, uint32_t n_head, uint32_t head_dim, uint32_t rope_dim, const float *sin_cos_row, cudaStream_t st);

@@ -20,6 +20,8 @@ namespace {
 
 struct LayerDev {
     float *attn_norm = nullptr, *ffn_norm = nullptr;
+    float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr, *q_norm = nullptr, *k_norm = nullptr;  // this rank's part; null: absent
+    bool variant = false;  // any of the above, or the NEOX pairing: the layer takes the operator-by-operator path
     ob_weight *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
 };
 
@@ -546,7 +548,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
     for (uint32_t li = 0; li < c.n_layer; ++li) {
         const LayerDev &L = m->layers[li];
         const bool stream_layer = stream && m->stream_ok && k_type(L.wq) && k_type(L.wk) && k_type(L.wv) && k_type(L.wo) && k_type(L.gate) && k_type(L.up) &&
-                                  k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0);
+                                  k_type(L.down) && L.gate->w.type == L.up->w.type && (hd % 2 == 0) && !L.variant;
         if (stream_layer) {
             const bool peer = tp && m->px.size > 1;
             if (pending_exchange) launch_norm_quant_consume(m->x, L.attn_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
@@ -602,6 +604,13 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         rk.n_head_kv = m->n_head_kv_l;
         rk.head_dim = hd;
         rk.rope_dim = c.rope_dim;
+        rk.q_bias = L.q_bias;
+        rk.k_bias = L.k_bias;
+        rk.v_bias = L.v_bias;
+        rk.q_norm = L.q_norm;
+        rk.k_norm = L.k_norm;
+        rk.rms_eps = c.rms_eps;
+        rk.neox = c.rope_neox != 0;
         launch_rope_kv(rk, st);
         m->ctx->launches++;
 
@@ -784,6 +793,13 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         LayerDev &D = m->layers[i];
         if ((rc = upload_f32(m, L.attn_norm, c.n_embd, &D.attn_norm))) return bail(rc);
         if ((rc = upload_f32(m, L.ffn_norm, c.n_embd, &D.ffn_norm))) return bail(rc);
+        // the optional vectors are always whole; this rank keeps the entries of its own heads
+        if (L.q_bias && (rc = upload_f32(m, L.q_bias + (size_t)rank * q_dim, q_dim, &D.q_bias))) return bail(rc);
+        if (L.k_bias && (rc = upload_f32(m, L.k_bias + (size_t)rank * kv_dim, kv_dim, &D.k_bias))) return bail(rc);
+        if (L.v_bias && (rc = upload_f32(m, L.v_bias + (size_t)rank * kv_dim, kv_dim, &D.v_bias))) return bail(rc);
+        if (L.q_norm && (rc = upload_f32(m, L.q_norm, hd, &D.q_norm))) return bail(rc);
+        if (L.k_norm && (rc = upload_f32(m, L.k_norm, hd, &D.k_norm))) return bail(rc);
+        D.variant = D.q_bias || D.k_bias || D.v_bias || D.q_norm || D.k_norm || c.rope_neox != 0;
         const uint32_t sr = presliced ? 0u : rank;  // a presliced tensor starts at the shard
         if ((rc = slice_weight(m, L.wq, sr * q_dim, q_dim, 0, c.n_embd, &D.wq))) return bail(rc);
         if ((rc = slice_weight(m, L.wk, sr * kv_dim, kv_dim, 0, c.n_embd, &D.wk))) return bail(rc);
@@ -900,7 +916,9 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         }
     }
     if (const char *e = getenv("OB_PERSIST")) m->use_persist = e[0] == '1' && e[1] == 0;
-    if (m->stream_ok && m->use_persist && tp == 1) {
+    bool any_variant = false;
+    for (const LayerDev &D : m->layers) any_variant |= D.variant;
+    if (m->stream_ok && m->use_persist && tp == 1 && !any_variant) {
         if ((rc = build_persistent_phases(m))) return bail(rc);
     }
     *out = m;

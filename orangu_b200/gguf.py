@@ -35,13 +35,14 @@ def _value(kind: str, v) -> bytes:
 
 def write_gguf(path: str, cfg: dict, tensors: dict, alignment: int = 32, extra_metadata: list | None = None, version: int = 3) -> None:
     """cfg: a synth.CONFIGS-style dict; tensors: name -> {"data", "type", ["in_dim", "out_dim"]} (orangu_b200.synth)."""
-    meta = [("general.architecture", "str", "llama"), ("general.alignment", "u32", alignment),
-            ("llama.embedding_length", "u32", cfg["n_embd"]), ("llama.block_count", "u32", cfg["n_layer"]),
-            ("llama.attention.head_count", "u32", cfg["n_head"]), ("llama.attention.head_count_kv", "u32", cfg["n_head_kv"]),
-            ("llama.attention.key_length", "u32", cfg["head_dim"]), ("llama.rope.dimension_count", "u32", cfg.get("rope_dim", cfg["head_dim"])),
-            ("llama.feed_forward_length", "u32", cfg["n_ff"]), ("llama.context_length", "u32", cfg.get("n_ctx_train", 4096)),
-            ("llama.vocab_size", "u32", cfg["n_vocab"]), ("llama.rope.freq_base", "f32", cfg["rope_freq_base"]),
-            ("llama.attention.layer_norm_rms_epsilon", "f32", cfg["rms_eps"])] + list(extra_metadata or [])
+    a = cfg.get("architecture", "llama")  # metadata keys carry the architecture's name (loader.rs:1652-1712)
+    meta = [("general.architecture", "str", a), ("general.alignment", "u32", alignment),
+            (f"{a}.embedding_length", "u32", cfg["n_embd"]), (f"{a}.block_count", "u32", cfg["n_layer"]),
+            (f"{a}.attention.head_count", "u32", cfg["n_head"]), (f"{a}.attention.head_count_kv", "u32", cfg["n_head_kv"]),
+            (f"{a}.attention.key_length", "u32", cfg["head_dim"]), (f"{a}.rope.dimension_count", "u32", cfg.get("rope_dim", cfg["head_dim"])),
+            (f"{a}.feed_forward_length", "u32", cfg["n_ff"]), (f"{a}.context_length", "u32", cfg.get("n_ctx_train", 4096)),
+            (f"{a}.vocab_size", "u32", cfg["n_vocab"]), (f"{a}.rope.freq_base", "f32", cfg["rope_freq_base"]),
+            (f"{a}.attention.layer_norm_rms_epsilon", "f32", cfg["rms_eps"])] + list(extra_metadata or [])
     head = b"GGUF" + struct.pack("<IQQ", version, len(tensors), len(meta))
     for k, kind, v in meta:
         head += _string(k) + _value(kind, v)

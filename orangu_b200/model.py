@@ -9,6 +9,8 @@ import numpy as np
 from . import capi
 from .backend import CudaBackend
 
+LAYER_VECTORS = (("q_bias", "attn_q.bias"), ("k_bias", "attn_k.bias"), ("v_bias", "attn_v.bias"),
+                 ("q_norm", "attn_q_norm.weight"), ("k_norm", "attn_k_norm.weight"))  # Qwen2 / Qwen3 extras, arch/llama.rs:45-60
 LAYER_FIELDS = (("wq", "attn_q"), ("wk", "attn_k"), ("wv", "attn_v"), ("wo", "attn_output"),
                 ("w_gate", "ffn_gate"), ("w_up", "ffn_up"), ("w_down", "ffn_down"))
 
@@ -80,12 +82,16 @@ class LlamaModel:
             layers[i].ffn_norm = tensors[f"blk.{i}.ffn_norm.weight"]["data"].ctypes.data
             for field, name in LAYER_FIELDS:
                 setattr(layers[i], field, _matrix(tensors[f"blk.{i}.{name}.weight"]))
+            for field, name in LAYER_VECTORS:
+                if f"blk.{i}.{name}" in tensors:
+                    setattr(layers[i], field, tensors[f"blk.{i}.{name}"]["data"].ctypes.data)  # f32, contiguous, kept alive by the caller's dict
         d = capi.ModelDesc()
         for k in ("n_vocab", "n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "n_ff"):
             setattr(d, k, cfg[k])
         d.rope_dim = cfg.get("rope_dim", cfg["head_dim"])
         d.rope_freq_base = cfg["rope_freq_base"]
         d.rms_eps = cfg["rms_eps"]
+        d.rope_neox = 1 if cfg.get("rope_neox") else 0  # rope_layout_for, arch/llama.rs:114-119
         d.max_seq_len = max_seq_len
         d.max_batch_tokens = max_batch_tokens
         d.kv_pool_tokens = kv_pool_tokens

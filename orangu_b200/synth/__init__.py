@@ -11,7 +11,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(os.path.dirname(HERE), "_lib", "libob_synth.so")
 F32, Q8_0, Q4_K, Q6_K = 0, 8, 12, 14
 Q4_0, Q5_0, IQ4_NL = 2, 6, 20
-BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32)}
+Q5_K = 13
+BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q5_K: (176, 256), Q6_K: (210, 256), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32)}
 # standard deviation of a uniformly random code of the per-32 symmetric types (sets the block scale for a wanted std)
 _CODE_STD = {Q4_0: 4.61, Q5_0: 9.23, IQ4_NL: 70.2}
 
@@ -57,6 +58,17 @@ def quantize(w: np.ndarray, ggml_type: int) -> np.ndarray:
 def matrix(ggml_type: int, out_dim: int, in_dim: int, seed: int, std: float = 0.02) -> dict:
     """[out_dim, in_dim] ~ N(0, std^2), quantized; the fp32 matrix is never materialised."""
     bb, be = BLOCK[ggml_type]
+    if ggml_type == Q5_K:
+        # uniformly random scale, min and code bits; d spread over [0.5, 1.5] x the value that gives the wanted std, and
+        # dmin = 15.5 d so that the values centre on zero (value = d * sc * code - dmin * m, code 0..31)
+        if in_dim % be:
+            raise ValueError("in_dim is not a whole number of blocks")
+        rng = np.random.default_rng(seed & 0xFFFFFFFFFFFF)
+        blocks = rng.integers(0, 256, (out_dim * (in_dim // be), bb), dtype=np.uint8)
+        d = (std / (36.0 * 9.23) * rng.uniform(0.5, 1.5, blocks.shape[0])).astype(np.float16)
+        blocks[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+        blocks[:, 2:4] = (d.astype(np.float32) * np.float32(15.5)).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return {"data": blocks.reshape(-1), "type": ggml_type, "in_dim": in_dim, "out_dim": out_dim}
     if ggml_type in _CODE_STD:
         # uniformly random codes; block scales spread over [0.5, 1.5] x the value that gives the wanted std
         if in_dim % be:
@@ -158,3 +170,20 @@ def model_tensors(cfg: dict, seed: int = 0, n_layer: int | None = None, types: d
         mat(p + "ffn_up.weight", "ffn_up", Q4_K, ff, e)
         mat(p + "ffn_down.weight", "ffn_down", Q4_K, e, ff)
     return t
+
+
+def add_qwen_extras(cfg: dict, tensors: dict, seed: int = 0, bias: bool = True, qk_norm: bool = True) -> dict:
+    """Adds the per-layer tensors Qwen2 (q/k/v bias) and Qwen3 (per-head q/k RMSNorm weights) files carry
+    (engine/arch/llama.rs:45-60).  Biases N(0, 0.1^2); norm weights 1 + N(0, 0.1^2).  Always the whole vectors."""
+    hd = cfg["head_dim"]
+    qd, kvd = cfg["n_head"] * hd, cfg["n_head_kv"] * hd
+    n_layer = 1 + max(int(k.split(".")[1]) for k in tensors if k.startswith("blk."))
+    for i in range(n_layer):
+        p = f"blk.{i}."
+        if bias:
+            for name, n in (("attn_q.bias", qd), ("attn_k.bias", kvd), ("attn_v.bias", kvd)):
+                tensors[p + name] = {"data": (normal(n, seed_of(seed, p + name)) * np.float32(0.1)).astype(np.float32), "type": F32}
+        if qk_norm:
+            for name in ("attn_q_norm.weight", "attn_k_norm.weight"):
+                tensors[p + name] = {"data": (np.float32(1.0) + normal(hd, seed_of(seed, p + name)) * np.float32(0.1)).astype(np.float32), "type": F32}
+    return tensors

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(ROOT, "oracle", "_build", "liborangu_oracle.so")
 
 F32, Q8_0, Q4_K, Q6_K = 0, 8, 12, 14
-Q5_K = 13  # oracle only: no device kernel yet
+Q5_K = 13
 Q4_0, Q5_0, IQ4_NL = 2, 6, 20   # per-32 symmetric types: one f16 scale and 32 signed codes per block, like Q8_0
 PER_32 = (Q8_0, Q4_0, Q5_0, IQ4_NL)
 BLOCK = {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256), F32: (4, 1), Q4_0: (18, 32), Q5_0: (22, 32), IQ4_NL: (18, 32), Q5_K: (176, 256)}
@@ -39,7 +39,7 @@ class Matrix(C.Structure):
 class Layer(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p)] + [
         (n, Matrix) for n in ("wq", "wk", "wv", "wo", "w_gate", "w_up", "w_down")
-    ]
+    ] + [(n, C.c_void_p) for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")]
 
 
 class Config(C.Structure):
@@ -47,6 +47,7 @@ class Config(C.Structure):
         ("rope_freq_base", C.c_float),
         ("rms_eps", C.c_float),
         ("rope_freqs", C.c_void_p),
+        ("rope_neox", C.c_uint32),
     ]
 
 
@@ -83,6 +84,8 @@ def lib():
         L.oref_rmsnorm.argtypes = [vp, vp, vp, u64, u64, f32]
         L.oref_rope_norm.argtypes = [vp, u64, u64, u64, u64, f32]
         L.oref_rope_table.argtypes = [vp, u64, u64, f32]
+        L.oref_rope_layout.argtypes = [vp, u64, u64, u64, u64, f32, vp, C.c_int]
+        L.oref_rope_layout.restype = None
         L.oref_softmax.argtypes = [vp, u64]
         L.oref_silu.restype = f32
         L.oref_silu.argtypes = [f32]
@@ -195,6 +198,14 @@ def rmsnorm(x, w, eps):
     return out.reshape(x.shape)
 
 
+def rope_layout(x, n_head, head_dim, pos, rope_dim, base, neox, freq_factors=None):
+    """tensor.rs:1115-1177 with either pairing; returns a rotated copy."""
+    x = np.array(x, dtype=np.float32, copy=True)
+    ff = np.ascontiguousarray(freq_factors, np.float32) if freq_factors is not None else None
+    lib().oref_rope_layout(_p(x), n_head, head_dim, pos, rope_dim, base, _p(ff) if ff is not None else None, 1 if neox else 0)
+    return x
+
+
 def rope_norm(x, n_head, head_dim, pos, rope_dim, base):
     x = _f32(x).copy()
     lib().oref_rope_norm(_p(x), n_head, head_dim, pos, rope_dim, base)
@@ -256,7 +267,8 @@ class Model:
         self.cfg = cfg
         c = Config(cfg["n_vocab"], cfg["n_embd"], cfg["n_layer"], cfg["n_head"], cfg["n_head_kv"], cfg["head_dim"],
                    cfg.get("rope_dim", cfg["head_dim"]), cfg["n_ff"], cfg["rope_freq_base"], cfg["rms_eps"],
-                   tensors["rope_freqs.weight"]["data"].ctypes.data if "rope_freqs.weight" in tensors else None)
+                   tensors["rope_freqs.weight"]["data"].ctypes.data if "rope_freqs.weight" in tensors else None,
+                   1 if cfg.get("rope_neox") else 0)
 
         def mat(name):
             t = tensors[name]
@@ -270,6 +282,10 @@ class Model:
             for field, suffix in (("wq", "attn_q"), ("wk", "attn_k"), ("wv", "attn_v"), ("wo", "attn_output"),
                                   ("w_gate", "ffn_gate"), ("w_up", "ffn_up"), ("w_down", "ffn_down")):
                 setattr(l, field, mat(f"blk.{i}.{suffix}.weight"))
+            for field, name in (("q_bias", "attn_q.bias"), ("k_bias", "attn_k.bias"), ("v_bias", "attn_v.bias"),
+                                ("q_norm", "attn_q_norm.weight"), ("k_norm", "attn_k_norm.weight")):
+                if f"blk.{i}.{name}" in tensors:
+                    setattr(l, field, tensors[f"blk.{i}.{name}"]["data"].ctypes.data)
         emb = mat("token_embd.weight")
         out = mat("output.weight") if "output.weight" in tensors else None
         self._h = L.oref_model_create(C.byref(c), C.byref(emb), tensors["output_norm.weight"]["data"].ctypes.data,

@@ -34,8 +34,8 @@ def test_header_and_binding_agree(lib):
 
 def test_constants_without_a_device(lib):
     assert lib.ob_abi_version() == 4
-    assert [lib.ob_supports_type(t) for t in (0, 8, 12, 14, 2, 6, 20)] == [1, 1, 1, 1, 1, 1, 1]
-    assert [lib.ob_supports_type(t) for t in (1, 3, 7, 10, 13, 30)] == [0, 0, 0, 0, 0, 0]
+    assert [lib.ob_supports_type(t) for t in (0, 8, 12, 13, 14, 2, 6, 20)] == [1, 1, 1, 1, 1, 1, 1, 1]
+    assert [lib.ob_supports_type(t) for t in (1, 3, 7, 10, 11, 30)] == [0, 0, 0, 0, 0, 0]
     assert lib.ob_reduced_surface() is None
 
 
@@ -115,6 +115,10 @@ def test_struct_layouts_agree_between_header_binding_and_integration_notes(lib):
     rust = rust[:rust.index("}")]
     for name, _ in capi.ModelDesc._fields_:
         assert f"pub {name}:" in rust, f"INTEGRATION.md's ob_model_desc lacks {name}"
+    rust_layer = notes[notes.index("pub struct ob_layer_desc"):]
+    rust_layer = rust_layer[:rust_layer.index("}")]
+    for name, _ in capi.LayerDesc._fields_:
+        assert f"pub {name}:" in rust_layer, f"INTEGRATION.md's ob_layer_desc lacks {name}"
     header = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "orangu_b200.h")).read(), flags=re.S)
     for name in declared_symbols():
         assert f"pub fn {name}(" in notes, f"INTEGRATION.md does not declare {name}"
@@ -124,9 +128,9 @@ def test_struct_layouts_agree_between_header_binding_and_integration_notes(lib):
 def test_row_bytes_of_the_cpp_wrapper_for_every_type():
     out = _compile_and_run(
         '#include <cstdio>\n#include "orangu_b200.hpp"\n'
-        'int main(){ for (unsigned t : {8u, 12u, 14u, 2u, 6u, 20u}) { orangu::QuantMatrix m{nullptr, t, 4096, 3}; std::printf("%llu ", (unsigned long long)m.row_bytes()); } }\n',
+        'int main(){ for (unsigned t : {8u, 12u, 13u, 14u, 2u, 6u, 20u}) { orangu::QuantMatrix m{nullptr, t, 4096, 3}; std::printf("%llu ", (unsigned long long)m.row_bytes()); } }\n',
         extra=["-L", os.path.dirname(__import__("orangu_b200").capi.lib_path()), "-lorangu_b200"])
-    assert [int(v) for v in out.split()] == [4096 // 32 * 34, 4096 // 256 * 144, 4096 // 256 * 210, 4096 // 32 * 18, 4096 // 32 * 22, 4096 // 32 * 18]
+    assert [int(v) for v in out.split()] == [4096 // 32 * 34, 4096 // 256 * 144, 4096 // 256 * 176, 4096 // 256 * 210, 4096 // 32 * 18, 4096 // 32 * 22, 4096 // 32 * 18]
 
 
 @pytest.mark.gpu

@@ -124,18 +124,57 @@ def test_malformed_files_are_refused_with_a_message(tmp_path):
     # a model whose architecture or tensor types are outside the build is named, not crashed on
     p = str(tmp_path / "arch.gguf")
     write_gguf(p, cfg, tensors)
-    data = open(p, "rb").read().replace(b"\x05\x00\x00\x00\x00\x00\x00\x00llama", b"\x05\x00\x00\x00\x00\x00\x00\x00qwen2", 1)
+    data = open(p, "rb").read().replace(b"\x05\x00\x00\x00\x00\x00\x00\x00llama", b"\x05\x00\x00\x00\x00\x00\x00\x00gemma", 1)
     open(p, "wb").write(data)
     with GgufFile(p) as g, pytest.raises(capi.OranguError) as e:
         g.model_desc()
-    assert "qwen2" in str(e.value)
+    assert "gemma" in str(e.value)
     bad = dict(tensors)
-    bad["blk.0.attn_q.weight"] = dict(tensors["blk.0.attn_q.weight"], type=13)  # Q5_K: sized, but no kernel
-    bad["blk.0.attn_q.weight"]["data"] = np.zeros(cfg["n_head"] * cfg["head_dim"] * cfg["n_embd"] // 256 * 176, np.uint8)
+    bad["blk.0.attn_q.weight"] = dict(tensors["blk.0.attn_q.weight"], type=10)  # Q2_K: sized, but no kernel
+    bad["blk.0.attn_q.weight"]["data"] = np.zeros(cfg["n_head"] * cfg["head_dim"] * cfg["n_embd"] // 256 * 84, np.uint8)
     write_gguf(p, cfg, bad)
     with GgufFile(p) as g, pytest.raises(capi.OranguError) as e:
         g.model_desc()
-    assert "blk.0.attn_q.weight" in str(e.value) and "13" in str(e.value)
+    assert "blk.0.attn_q.weight" in str(e.value) and "10" in str(e.value)
+
+
+@pytest.mark.parametrize("arch,bias,qk_norm,neox", [("qwen2", True, False, 1), ("qwen3", False, True, 1), ("mistral", False, False, 0), ("qwen3vl", True, True, 1)])
+def test_llama_style_architectures_and_their_extra_tensors(tmp_path, arch, bias, qk_norm, neox):
+    """LLAMA_STYLE_ARCHITECTURES (loader.rs:190); attn_{q,k,v}.bias and attn_{q,k}_norm.weight are optional per file
+    (arch/llama.rs:171-175); the pairing follows the architecture (rope_layout_for, arch/llama.rs:114-119)."""
+    cfg, tensors = tiny()
+    cfg["architecture"] = arch
+    synth.add_qwen_extras(cfg, tensors, seed=3, bias=bias, qk_norm=qk_norm)
+    path = str(tmp_path / "q.gguf")
+    write_gguf(path, cfg, tensors)
+    with GgufFile(path) as g:
+        assert g.get_string("general.architecture") == arch
+        d = g.model_desc()
+        assert d.rope_neox == neox and d.n_head == cfg["n_head"]
+        for i in range(cfg["n_layer"]):
+            L = d.layers[i]
+            assert bool(L.q_bias) == bool(L.k_bias) == bool(L.v_bias) == bias and bool(L.q_norm) == bool(L.k_norm) == qk_norm
+            if bias:
+                got = np.ctypeslib.as_array((capi.C.c_float * (cfg["n_head_kv"] * cfg["head_dim"])).from_address(L.k_bias))
+                assert (got == tensors[f"blk.{i}.attn_k.bias"]["data"]).all()
+
+
+@pytest.mark.gpu
+def test_qwen3_style_file_runs_and_equals_the_oracle(backend, tmp_path):
+    import oracle as O
+    import orangu_b200
+    from gpu_common import assert_bit_equal
+
+    cfg, tensors = tiny(seed=13)
+    cfg.update(architecture="qwen3", rope_neox=True)
+    synth.add_qwen_extras(cfg, tensors, seed=4)
+    path = str(tmp_path / "q3.gguf")
+    write_gguf(path, cfg, tensors)
+    model, ref = orangu_b200.LlamaModel.from_gguf(backend, path, max_seq_len=64, max_batch_tokens=16), O.Model(cfg, tensors)
+    toks = np.random.default_rng(2).integers(0, cfg["n_vocab"], 19).astype(np.uint32)
+    kv, rkv = model.new_kv_cache(40), ref.new_kv(40, f16=True)
+    assert_bit_equal(model.forward(kv, toks, 0), ref.forward(rkv, toks, 0), "prefill logits")
+    assert_bit_equal(model.forward(kv, [5], 19), ref.forward(rkv, [5], 19), "decode step")
 
 
 @pytest.mark.gpu

@@ -13,8 +13,8 @@ from refdata import activations, fixture_bytes, fixture_row, k_fixture
 from test_oracle_golden import adversarial_blocks
 
 pytestmark = pytest.mark.gpu
-Q8_0, Q4_K, Q6_K = 8, 12, 14
-TYPES = [Q8_0, Q4_K, Q6_K]
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+TYPES = [Q8_0, Q4_K, Q5_K, Q6_K]
 
 
 def gauss_matrix(t, out_dim, in_dim, seed):
@@ -279,13 +279,13 @@ def test_unsupported_and_invalid_inputs_are_statuses(backend):
     L = capi.load()
     h = C.c_void_p()
     raw = np.zeros(144, np.uint8)
-    assert L.ob_weight_register(backend._h, raw.ctypes.data, 144, 13, 256, 1, C.byref(h)) == -2  # Q5_K: no kernel
-    assert b"ggml type 13" in L.ob_last_error(backend._h)
+    assert L.ob_weight_register(backend._h, raw.ctypes.data, 84, 10, 256, 1, C.byref(h)) == -2  # Q2_K: no kernel
+    assert b"ggml type 10" in L.ob_last_error(backend._h)
     assert L.ob_weight_register(backend._h, raw.ctypes.data, 100, 12, 256, 1, C.byref(h)) == -1  # wrong row_bytes
     assert L.ob_weight_register(backend._h, raw.ctypes.data, 144, 12, 200, 1, C.byref(h)) == -2  # not a block multiple
     w = gauss_matrix(Q4_K, 4, 256, 1)
     with pytest.raises(ValueError):
         backend.matmul(np.zeros(255, np.float32), 1, w)
     assert backend.matmul(np.zeros(0, np.float32), 0, w).shape == (0, 4)
-    assert backend.supports_type(12) and not backend.supports_type(13)
+    assert backend.supports_type(12) and backend.supports_type(13) and not backend.supports_type(10)
     assert backend.reduced_surface() is None

@@ -33,7 +33,11 @@ def prompt(cfg, n, seed):
                                          ("small", {"attn_k": 14, "ffn_gate": 14, "token_embd": 14}),
                                          # Q4_0 / Q5_0 / IQ4_NL everywhere
                                          ("tiny", {"token_embd": 2, "output": 6, "attn_q": 2, "attn_k": 20, "attn_v": 6, "attn_output": 2,
-                                                   "ffn_gate": 20, "ffn_up": 2, "ffn_down": 6})])
+                                                   "ffn_gate": 20, "ffn_up": 2, "ffn_down": 6}),
+                                         # Q5_K everywhere (a Q5_K_M / Q5_K_S file), and mixed into a Q4_K_M-style model
+                                         ("tiny", {k: 13 for k in ("token_embd", "output", "attn_q", "attn_k", "attn_v", "attn_output",
+                                                                  "ffn_gate", "ffn_up", "ffn_down")}),
+                                         ("small", {"attn_v": 13, "ffn_down": 13, "output": 13})])
 def test_prefill_then_greedy_decode_matches_the_oracle(backend, name, types):
     cfg, tensors, model, ref = build(backend, name, seed=3, types=types, max_seq_len=256, max_batch_tokens=32, kv_pool_tokens=512)
     toks = prompt(cfg, 45, 1)
@@ -372,3 +376,53 @@ def test_large_decode_batch_takes_the_small_cta_attention_and_agrees_with_single
         # few 1e-2 now and then (the kernel itself is held to 2e-5 in test_gpu_glue.py)
         assert np.abs(logits[i] - got_alone).max() < 3 * LOGIT_TOL, i
         assert np.abs(logits[i] - want).max() < 3 * LOGIT_TOL, i
+
+
+# ---------------------------------------------------------------- Qwen2 / Qwen3-style variants (arch/llama.rs:45-60, 107-120, 750-780)
+@pytest.mark.parametrize("bias,qk_norm,neox", [(True, False, True), (False, True, True), (True, True, True), (False, False, True), (True, True, False)])
+def test_qwen_style_variants_are_bit_exact(backend, bias, qk_norm, neox):
+    """q/k/v bias, per-head q/k RMSNorm and the NEOX pairing, in every combination a real file has (qwen2: bias + NEOX;
+    qwen3: q/k norm + NEOX) plus the remaining ones: prefill in chunks, single-token steps, a decode batch and the device loop."""
+    cfg = dict(synth.CONFIGS["small"])
+    cfg["rope_neox"] = neox
+    tensors = synth.add_qwen_extras(cfg, synth.model_tensors(cfg, seed=21), seed=22, bias=bias, qk_norm=qk_norm)
+    model, ref = LlamaModel(backend, cfg, tensors, max_seq_len=128, max_batch_tokens=16, kv_pool_tokens=512), O.Model(cfg, tensors)
+    toks = prompt(cfg, 37, 4)
+    kv, rkv = model.new_kv_cache(96), ref.new_kv(96, f16=True)
+    logits = model.forward(kv, toks, 0)
+    want, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
+    assert_bit_equal(logits, want, "prefill logits")
+    assert_bit_equal(model.last_hidden(37)[-5:], hidden[-5:], "residual stream")
+    nxt = O.argmax(want)
+    for step in range(10):
+        got, want = model.forward(kv, [nxt], 37 + step), ref.forward(rkv, [nxt], 37 + step)
+        assert_bit_equal(got, want, f"decode step {step}")
+        nxt = O.argmax(want)
+    # the same sequence through the captured graph and the device loop, and as one row of a decode batch
+    kv2, kv3 = model.new_kv_cache(96), model.new_kv_cache(96)
+    first = model.forward_maybe_sampling(kv2, toks, 0)
+    assert first == model.forward_maybe_sampling(kv3, toks, 0) == O.argmax(ref.forward(ref.new_kv(96, f16=True), toks, 0))
+    a = [model.decode_greedy(kv2, first)]
+    for _ in range(5):
+        a.append(model.decode_greedy(kv2, a[-1]))
+    b = model.decode_loop([kv3], [first], 6)[:, 0]
+    assert a == list(b)
+    model.close()
+
+
+def test_qwen_style_variants_differ_from_the_plain_graph(backend):
+    """The extras are not silently ignored: each one changes the logits."""
+    cfg = dict(synth.CONFIGS["tiny"])
+    base = synth.model_tensors(cfg, seed=3)
+    toks = prompt(cfg, 9, 1)
+
+    def run(c, t):
+        m = LlamaModel(backend, c, t, max_seq_len=64, max_batch_tokens=16)
+        out = m.forward(m.new_kv_cache(32), toks, 0)
+        m.close()
+        return out
+
+    plain = run(cfg, base)
+    for kw in (dict(bias=True, qk_norm=False), dict(bias=False, qk_norm=True)):
+        assert (run(cfg, synth.add_qwen_extras(cfg, dict(base), seed=5, **kw)) != plain).any()
+    assert (run({**cfg, "rope_neox": True}, base) != plain).any()

@@ -404,6 +404,38 @@ def test_rope_identity_at_position_zero_and_norm_preservation():
     assert (want.view(np.uint32) == y.view(np.uint32)).all()
 
 
+def test_rope_layouts_as_the_reference_tests_state_them():
+    """tensor.rs:1731-1783 (rope_neox_layout_rotates_pairs_offset_by_half, rope_norm_layout_rotates_consecutive_pairs),
+    :1785-1823 (rope_freq_factors_divide_the_rotation_frequency), :1825-1842 (rope_layouts_preserve_total_energy)."""
+    x = np.arange(1, 9, dtype=np.float32)
+    theta = [np.float32(3.0) * np.float32(np.float32(10000.0) ** np.float32(-2.0 * p / 8.0)) for p in range(4)]
+    neox, norm = O.rope_layout(x, 1, 8, 3, 8, 10000.0, True), O.rope_layout(x, 1, 8, 3, 8, 10000.0, False)
+    want_neox, want_norm = x.copy(), x.copy()
+    for p in range(4):
+        sn, cs = np.float32(np.sin(theta[p])), np.float32(np.cos(theta[p]))
+        a, b = want_neox[p], want_neox[p + 4]
+        want_neox[p], want_neox[p + 4] = a * cs - b * sn, a * sn + b * cs
+        a, b = want_norm[2 * p], want_norm[2 * p + 1]
+        want_norm[2 * p], want_norm[2 * p + 1] = a * cs - b * sn, a * sn + b * cs
+    assert np.abs(neox - want_neox).max() < 1e-6 and np.abs(norm - want_norm).max() < 1e-6
+    assert (neox != norm).any(), "NORM and NEOX must not coincide"
+    assert (norm.view(np.uint32) == O.rope_norm(x, 1, 8, 3, 8, 10000.0).view(np.uint32)).all()
+    # a factor of 32 on pair 0 rotates it 32 times slower: the angle of (1, 0) after rotation is theta / 32
+    e = np.zeros(8, np.float32)
+    e[0] = 1
+    ff = np.array([32.0, 1.0, 1.0, 1.0], np.float32)
+    for is_neox, hi in ((True, 4), (False, 1)):
+        plain, slowed = O.rope_layout(e, 1, 8, 5, 8, 10000.0, is_neox), O.rope_layout(e, 1, 8, 5, 8, 10000.0, is_neox, ff)
+        ang_plain, ang_slow = np.arctan2(plain[hi], plain[0]), np.arctan2(slowed[hi], slowed[0])
+        assert abs(ang_slow * 32 - (ang_plain % (2 * np.pi))) < 1e-4 or abs(ang_slow * 32 - 5.0) < 1e-4
+    rng = np.random.default_rng(6)
+    y = rng.standard_normal(3 * 16).astype(np.float32)
+    for is_neox in (True, False):
+        r = O.rope_layout(y, 3, 16, 11, 8, 10000.0, is_neox)  # rope_dim < head_dim: the tail of every head is left alone
+        assert abs(float((r.astype(np.float64) ** 2).sum()) - float((y.astype(np.float64) ** 2).sum())) < 1e-4
+        assert (r.reshape(3, 16)[:, 8:] == y.reshape(3, 16)[:, 8:]).all()
+
+
 def test_rmsnorm_written_out():
     rng = np.random.default_rng(4)
     x = rng.standard_normal((3, 96)).astype(np.float32)
@@ -461,3 +493,40 @@ def test_repeat_penalty_compounds_and_respects_last_n():
     got = O.repeat_penalty(l, [0, 1, 2], 1, 2.0)
     assert list(got) == [2.0, -2.0, 2.0, 1.0]      # only the last one
     assert list(O.repeat_penalty(l, [0, 1], 64, 1.0)) == list(l)
+
+
+def test_oracle_graph_applies_bias_then_head_norm_then_rope_in_the_reference_order():
+    """arch/llama.rs:750-809: q = Wq x; q += bias; per-head RMSNorm; RoPE (pairing by architecture).  One layer, one token,
+    checked against the same steps written out with the oracle's own operators."""
+    from orangu_b200 import synth
+
+    cfg = dict(synth.CONFIGS["tiny"], n_layer=1, rope_neox=True)
+    t = synth.add_qwen_extras(cfg, synth.model_tensors(cfg, seed=9), seed=10)
+    m = O.Model(cfg, t)
+    toks = np.array([7, 300, 12], np.uint32)
+    logits, hidden = m.forward(m.new_kv(8), toks, 0, want_hidden=True)
+    e, hd, nh, nkv, ff = cfg["n_embd"], cfg["head_dim"], cfg["n_head"], cfg["n_head_kv"], cfg["n_ff"]
+
+    def mm(x, n, name):
+        w = t[name]
+        return O.matmul(x, n, w["data"], w["type"], w["in_dim"], w["out_dim"]).reshape(n, -1)
+
+    emb = t["token_embd.weight"]
+    rb = O.row_bytes(emb["type"], e)
+    rows = np.ascontiguousarray(emb["data"]).view(np.uint8).reshape(-1, rb)
+    x = np.stack([O.dequantize(emb["type"], rows[int(tok)], e) for tok in toks])
+    normed = O.rmsnorm(x, t["blk.0.attn_norm.weight"]["data"], cfg["rms_eps"])
+    q, k, v = mm(normed, 3, "blk.0.attn_q.weight"), mm(normed, 3, "blk.0.attn_k.weight"), mm(normed, 3, "blk.0.attn_v.weight")
+    q, k, v = q + t["blk.0.attn_q.bias"]["data"], k + t["blk.0.attn_k.bias"]["data"], v + t["blk.0.attn_v.bias"]["data"]
+    q = O.rmsnorm(q.reshape(3 * nh, hd), t["blk.0.attn_q_norm.weight"]["data"], cfg["rms_eps"]).reshape(3, -1)
+    k = O.rmsnorm(k.reshape(3 * nkv, hd), t["blk.0.attn_k_norm.weight"]["data"], cfg["rms_eps"]).reshape(3, -1)
+    for pos in range(3):
+        q[pos] = O.rope_layout(q[pos], nh, hd, pos, hd, cfg["rope_freq_base"], True)
+        k[pos] = O.rope_layout(k[pos], nkv, hd, pos, hd, cfg["rope_freq_base"], True)
+    att = O.attention(q, k, v, nh, nkv, hd, np.float32(1.0) / np.sqrt(np.float32(hd)), 3, 0)
+    proj = mm(att.reshape(3, -1), 3, "blk.0.attn_output.weight")
+    x = x + proj
+    n2 = O.rmsnorm(x, t["blk.0.ffn_norm.weight"]["data"], cfg["rms_eps"])
+    g, u = mm(n2, 3, "blk.0.ffn_gate.weight"), mm(n2, 3, "blk.0.ffn_up.weight")
+    x = x + mm(O.swiglu(g, u), 3, "blk.0.ffn_down.weight")
+    assert (x.view(np.uint32) == hidden.view(np.uint32)).all()
