@@ -166,7 +166,7 @@ __global__ void argmax_reset_kernel(unsigned long long *scratch, uint32_t n) {
 // grid (chunks, n_seq).  (key << 32 | index) under max: of equal keys the largest index wins.
 __global__ void __launch_bounds__(256) argmax_kernel(ArgmaxArgs a) {
     const uint32_t seq = blockIdx.y;
-    const float *l = a.logits + (uint64_t)seq * a.n_vocab;
+    const float *l = a.logits + (uint64_t)seq * (a.row_stride ? a.row_stride : a.n_vocab);
     unsigned long long best = 0ull;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < a.n_vocab; i += gridDim.x * blockDim.x) {
         unsigned long long cand = ((unsigned long long)total_order_key(l[i]) << 32) | i;
@@ -189,6 +189,51 @@ __global__ void __launch_bounds__(256) argmax_kernel(ArgmaxArgs a) {
 __global__ void argmax_finish_kernel(const unsigned long long *scratch, uint32_t *out, uint32_t n) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = (uint32_t)(scratch[i] & 0xffffffffull);
+}
+
+// Tensor parallel: this rank's (key, id) of every row goes, tagged, into every rank's exchange slot; the largest wins.
+__global__ void __launch_bounds__(256) argmax_finish_xchg_kernel(const unsigned long long *scratch, uint32_t *out, uint32_t n, uint32_t index_base,
+                                                                 obtp::PeerXchg px) {
+    const uint32_t k = *reinterpret_cast<const volatile uint32_t *>(px.seq), tag = k + 1u;
+    const uint64_t base = (uint64_t)((k & 1u) * px.size) * px.n;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const unsigned long long best = scratch[i];
+        const uint32_t key = (uint32_t)(best >> 32), id = (uint32_t)best + index_base;
+        for (uint32_t r = 0; r < px.size; ++r)
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(px.slots[r] + base + (uint64_t)px.rank * px.n + 2 * i), "r"(key), "r"(tag), "r"(id),
+                         "r"(tag)
+                         : "memory");
+    }
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const uint2 *mine = px.slots[px.rank] + base;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        unsigned long long best = 0ull;
+        bool gave_up = false;
+        for (uint32_t r = 0; r < px.size; ++r) {
+            const uint2 *src = mine + (uint64_t)r * px.n + 2 * i;
+            uint4 w;
+            for (uint32_t spin = 0;; ++spin) {
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(src) : "memory");
+                if ((w.y == tag && w.w == tag) || gave_up) break;
+                if ((spin & 1023u) == 1023u) {
+                    unsigned long long t1;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                    if (t1 - t0 > (unsigned long long)(px.timeout_ms ? px.timeout_ms : 4000u) * 1000000ull) {  // a rank is gone: report, go on with what is there
+                        *px.err = 1u;
+                        gave_up = true;
+                    }
+                }
+            }
+            if (w.y == tag && w.w == tag) {
+                const unsigned long long cand = ((unsigned long long)w.x << 32) | w.z;
+                best = cand > best ? cand : best;
+            }
+        }
+        out[i] = (uint32_t)best;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *px.seq = k + 1u;
 }
 
 // Sequential on purpose: a token that repeats is penalised once per occurrence, compounding.
@@ -237,7 +282,8 @@ void launch_argmax(const ArgmaxArgs &a, cudaStream_t st) {
     argmax_reset_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.n_seq);
     dim3 grid(min(64u, (a.n_vocab + 255) / 256), a.n_seq);
     argmax_kernel<<<grid, 256, 0, st>>>(a);
-    argmax_finish_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.out, a.n_seq);
+    if (a.px.size > 1) argmax_finish_xchg_kernel<<<1, 256, 0, st>>>(a.scratch, a.out, a.n_seq, a.index_base, a.px);
+    else argmax_finish_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.out, a.n_seq);
 }
 void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st) {
     if (n_recent && penalty != 1.0f) repeat_penalty_kernel<<<1, 32, 0, st>>>(logits, n_vocab, recent, n_recent, penalty);

@@ -168,6 +168,13 @@ struct ArgmaxArgs {
     uint32_t n_seq, n_vocab;
     uint32_t *out;         // [n_seq]
     unsigned long long *scratch; // [n_seq] packed (key, index)
+    // Tensor parallel with a peer exchange (px.size > 1): `logits` points at this rank's columns of every row, n_vocab is
+    // their count, row_stride the distance between rows (0: n_vocab) and index_base the vocabulary id of the first column.
+    // Each rank finds the maximum of its columns; the finish kernel stores (key, id) tagged into every rank's exchange slot,
+    // waits for the others' and keeps the largest (key, id): the last of equal maxima wins across ranks as it does within one
+    // (engine/sampling.rs:336-343).  2 * n_seq words of the slot are used, so n_seq <= px.n / 2.
+    uint32_t row_stride = 0, index_base = 0;
+    obtp::PeerXchg px{};
 };
 void launch_argmax(const ArgmaxArgs &a, cudaStream_t st);
 void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st);

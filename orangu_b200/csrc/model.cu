@@ -484,7 +484,7 @@ bool run_attention(ob_model *m, uint32_t li, uint32_t T, bool exact_attn, uint32
 //   gemm_order: the rows are consecutive tokens of one sequence (prefill chunk)
 //   logit_row0 / n_logit_rows: which rows get the output projection
 //   exact_attn: take the exact-order attention kernels (every row's window <= pos_bound <= exact_attn_max_pos)
-void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0, uint32_t n_logit_rows, bool want_argmax, bool exact_attn,
+void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0, uint32_t n_logit_rows, bool want_argmax, bool full_logits, bool exact_attn,
                   uint32_t pos_bound, cudaStream_t st) {
     const ob_model_desc &c = m->cfg;
     const MetaLayout ml(m->T);
@@ -639,6 +639,32 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         }
     }
 
+    // Every rank holds its own columns of the logits.  When only the greedy token is wanted and the ranks share peer memory,
+    // each takes the maximum of its columns and the ranks exchange one (key, id) pair per row; otherwise the columns are
+    // gathered (the caller wants the logits, or a repeat penalty has to touch them first) and the argmax runs over all of them.
+    auto finish_logits = [&](uint32_t rows) {
+        const bool pairs_only = tp && want_argmax && !full_logits && m->px.size > 1 && 2 * rows <= m->px.n;
+        if (tp && !pairs_only) {
+            if (!obtp::all_gather_logits(m->comm, m->logits, rows, c.n_vocab, m->vocab0, m->vocab_l, st)) m->comm_failed = true;
+            m->ctx->launches++;
+        }
+        if (!want_argmax) return;
+        ArgmaxArgs am{};
+        am.logits = m->logits;
+        am.n_seq = rows;
+        am.n_vocab = c.n_vocab;
+        am.out = m->d_out_tokens;
+        am.scratch = m->argmax_scratch;
+        if (pairs_only) {
+            am.logits = m->logits + m->vocab0;
+            am.n_vocab = m->vocab_l;
+            am.row_stride = c.n_vocab;
+            am.index_base = m->vocab0;
+            am.px = m->px;
+        }
+        launch_argmax(am, st);
+        m->ctx->launches += 3;
+    };
     if (n_logit_rows == 1 && stream && m->stream_ok && k_type(m->output)) {
         StreamArgs la = stream_args(m, 0, 5);
         if (pending_exchange) launch_norm_quant_consume(m->x, m->output_norm, n_embd, c.rms_eps, nullptr, m->ready_embd, m->px, true, st);
@@ -646,20 +672,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         pending_exchange = false;
         launch_stream_gemv(la, m->ctx->sm_count, true, st);
         m->ctx->launches += 2;
-        if (tp) {
-            if (!obtp::all_gather_logits(m->comm, m->logits, 1, c.n_vocab, m->vocab0, m->vocab_l, st)) m->comm_failed = true;
-            m->ctx->launches++;
-        }
-        if (want_argmax) {
-            ArgmaxArgs am{};
-            am.logits = m->logits;
-            am.n_seq = 1;
-            am.n_vocab = c.n_vocab;
-            am.out = m->d_out_tokens;
-            am.scratch = m->argmax_scratch;
-            launch_argmax(am, st);
-            m->ctx->launches += 3;
-        }
+        finish_logits(1);
     } else if (pending_exchange) {
         launch_norm_quant_consume(m->x, nullptr, n_embd, c.rms_eps, m->norm_scale, nullptr, m->px, true, st);
         m->ctx->launches++;
@@ -670,20 +683,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         quantize_into(m, ACT_RMSNORM, xl, m->output_norm, n_logit_rows, n_embd, m->act_embd, needs_k({m->output}), needs_flat({m->output}), st);
         // Always the single-token kernel: forward() projects one row (llama.rs:1026-1030).
         run_products(m, m->act_embd, {{m->output, m->logits + m->vocab0, c.n_vocab, nullptr}}, n_logit_rows, false, st);
-        if (tp) {
-            if (!obtp::all_gather_logits(m->comm, m->logits, n_logit_rows, c.n_vocab, m->vocab0, m->vocab_l, st)) m->comm_failed = true;
-            m->ctx->launches++;
-        }
-        if (want_argmax) {
-            ArgmaxArgs am{};
-            am.logits = m->logits;
-            am.n_seq = n_logit_rows;
-            am.n_vocab = c.n_vocab;
-            am.out = m->d_out_tokens;
-            am.scratch = m->argmax_scratch;
-            launch_argmax(am, st);
-            m->ctx->launches += 3;
-        }
+        finish_logits(n_logit_rows);
     }
     m->last_T = T;
 }
@@ -1179,7 +1179,7 @@ int run_rows(ob_model *m, const std::vector<ob_kv *> &row_kv, const uint32_t *to
     OB_CUDA(ctx, cudaEventRecord(ctx->ev0, st));
     OB_CUDA(ctx, cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st));
     const bool penalise = greedy && greedy->repeat_penalty != 1.0f && greedy->recent && greedy->n_recent;
-    enqueue_step(m, T, gemm_order, logit_row0, n_logit_rows, out_token != nullptr && !penalise, exact_attn, pos_bound, st);
+    enqueue_step(m, T, gemm_order, logit_row0, n_logit_rows, out_token != nullptr && !penalise, out_logits != nullptr || penalise, exact_attn, pos_bound, st);
     if (out_token && penalise) {
         // repeat penalty, then argmax (sampling.rs:345-359); the history comes from the caller per call
         for (uint32_t r = 0; r < n_logit_rows; ++r) {
@@ -1353,7 +1353,7 @@ int get_graph(ob_model *m, uint32_t n_seq, int kind, bool exact, cudaGraphExec_t
     // function attributes outside capture and counts what a step launches.  It rewrites the KV slot of
     // the current position with the values the replay will write again.
     const uint64_t launches_before = ctx->launches;
-    enqueue_step(m, n_seq, false, 0, n_seq, true, exact, pos_bound, st);
+    enqueue_step(m, n_seq, false, 0, n_seq, true, false, exact, pos_bound, st);
     OB_CUDA(ctx, cudaStreamSynchronize(st));
     OB_CUDA(ctx, cudaGetLastError());
     m->graph_launches[key] = ctx->launches - launches_before + (kind == 1 ? 1 : 0);
@@ -1361,7 +1361,7 @@ int get_graph(ob_model *m, uint32_t n_seq, int kind, bool exact, cudaGraphExec_t
     cudaGraph_t graph = nullptr;
     OB_CUDA(ctx, cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     if (kind == 0) cudaMemcpyAsync(m->d_meta, m->h_meta, ml.bytes, cudaMemcpyHostToDevice, st);
-    enqueue_step(m, n_seq, false, 0, n_seq, true, exact, pos_bound, st);
+    enqueue_step(m, n_seq, false, 0, n_seq, true, false, exact, pos_bound, st);
     if (kind == 0) {
         cudaMemcpyAsync(m->h_out_tokens, m->d_out_tokens, (size_t)n_seq * 4, cudaMemcpyDeviceToHost, st);
         fetch_status(m, st);

@@ -169,7 +169,7 @@ def test_errors_are_statuses(backend):
         model.new_kv_cache(32)  # pool of 64 (+1 page) tokens is spent
     assert e.value.status == -6 and "exhausted" in e.value.message
     bad = dict(tensors)
-    bad["blk.0.attn_q.weight"] = dict(bad["blk.0.attn_q.weight"], type=13)
+    bad["blk.0.attn_q.weight"] = dict(bad["blk.0.attn_q.weight"], type=10)  # Q2_K: no kernel
     with pytest.raises(OranguError) as e:
         LlamaModel(backend, cfg, bad)
     assert e.value.status == -2 and "attn_q" in e.value.message
@@ -392,7 +392,7 @@ def test_qwen_style_variants_are_bit_exact(backend, bias, qk_norm, neox):
     logits = model.forward(kv, toks, 0)
     want, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
     assert_bit_equal(logits, want, "prefill logits")
-    assert_bit_equal(model.last_hidden(37)[-5:], hidden[-5:], "residual stream")
+    assert_bit_equal(model.last_hidden(5), hidden[-5:], "residual stream of the last chunk (37 = 16 + 16 + 5)")
     nxt = O.argmax(want)
     for step in range(10):
         got, want = model.forward(kv, [nxt], 37 + step), ref.forward(rkv, [nxt], 37 + step)
