@@ -273,10 +273,15 @@ int matmul_device(ob_ctx *ctx, const float *x_dev, uint32_t n_tokens, const ob_w
             return OB_OK;
         }
     }
-    ActBuf act;
-    int rc = quantize_for(ctx, x_dev, n_tokens, w->w.in_dim, w->w.type, &act, st);
-    if (rc) return rc;
+    // one token, Q8_0: the product kernel quantizes the row in its prologue (one launch instead of two)
+    const bool fused_q8 = n_tokens == 1 && w->w.type == TYPE_Q8_0;
+    ActBuf act{};
+    if (!fused_q8) {
+        int rc = quantize_for(ctx, x_dev, n_tokens, w->w.in_dim, w->w.type, &act, st);
+        if (rc) return rc;
+    }
     GemvArgs a{};
+    a.x_f32 = fused_q8 ? x_dev : nullptr;
     a.n_seg = 1;
     a.seg[0].w = w->w;
     if (isum_out) {  // row window for the partial-sum capture

@@ -100,7 +100,43 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(GemvArgs a, uint3
     if (threadIdx.x == 0) *next_group = (int)g_begin;
 
     // ---- stage activations -----------------------------------------------------------
-    {
+    if (TYPE == TYPE_Q8_0 && T == 1 && a.x_f32) {
+        // the row arrives as fp32: quantize it per 32 here (quantize_act, engine/vecdot.rs:95-126) -- four lanes x eight values
+        // are one block -- straight into the layout the loop below reads
+        const uint32_t n_chunks = in_dim / 8;
+        for (uint32_t c = threadIdx.x; c < ((n_chunks + 31) & ~31u); c += GEMV_THREADS) {
+            const bool live = c < n_chunks;
+            float v[8];
+            if (live) {
+                const float4 a0 = *reinterpret_cast<const float4 *>(a.x_f32 + c * 8), a1 = *reinterpret_cast<const float4 *>(a.x_f32 + c * 8 + 4);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
+                v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+            }
+            float amax = 0.0f;  // fmaxf drops a NaN operand, as f32::max does
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const float scale = __fdiv_rn(amax, 127.0f), inv = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+            int qv[8], s8 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                qv[i] = quantize_value(v[i], inv);
+                s8 += qv[i];
+            }
+            const int s16 = s8 + __shfl_xor_sync(0xffffffffu, s8, 1);
+            if (live) {
+                const uint32_t lo = (qv[0] & 0xff) | ((qv[1] & 0xff) << 8) | ((qv[2] & 0xff) << 16) | ((uint32_t)(qv[3] & 0xff) << 24);
+                const uint32_t hi = (qv[4] & 0xff) | ((qv[5] & 0xff) << 8) | ((qv[6] & 0xff) << 16) | ((uint32_t)(qv[7] & 0xff) << 24);
+                *reinterpret_cast<uint2 *>(sq + permuted_chunk(type, c >> 1) + (c & 1) * 8) = make_uint2(lo, hi);
+                if ((c & 3) == 0) sd[c >> 2] = scale;
+                if ((c & 1) == 0 && (c >> 1) < sp.n_sums) ssum[c >> 1] = (int16_t)s16;
+            }
+        }
+    } else {
         const uint32_t chunks = in_dim / 16;
         for (uint32_t i = threadIdx.x; i < nt * chunks; i += GEMV_THREADS) {
             uint32_t t = i / chunks, c = i % chunks;

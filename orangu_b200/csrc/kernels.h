@@ -48,6 +48,7 @@ struct GemvArgs {
     GemvSegment seg[3];    // all of one ggml type and one in_dim
     int n_seg;
     ActBuf act;            // activations of the matching granularity
+    const float *x_f32 = nullptr;  // Q8_0, one token: the fp32 row instead of `act`; the kernel quantizes it per 32 itself (one launch per product)
     uint32_t n_tokens;
     bool gemm_order;       // false: every (row, token) is the single-token GEMV; true: the prefill GEMM's fp32 order
     int32_t *isum_out;     // optional debug capture (single segment, token 0): [out_dim][nb]
