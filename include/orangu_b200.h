@@ -369,6 +369,13 @@ int ob_tp_unique_id(void *out128);
  * of n values (a multiple of 256) through the real consumer kernel with both "ranks" in local memory: rank 0 always delivers
  * (1.0), rank 1 (2.0) only in the rounds whose byte in peer_delivers is non-zero.  sums_out[k] is the summed value of round k
  * (3.0), or -1 when that round's wait ran out after timeout_ms (0 = 50 ms).  Returns OB_ERR_COMM if any round ran out. */
+/* Host-only check of the ranks' meeting point (no counterpart in the reference, no device): under tensor parallel every
+ * ob_forward / ob_decode_* call first meets the other ranks of the node in a small shared-memory segment named after the
+ * communicator id, so that a rank that is gone, or that refused the call on its own arguments, costs the others
+ * OB_TP_RENDEZVOUS_MS (30000; 0 = off) on the host and an OB_ERR_COMM with nothing launched, not a wait inside a collective.
+ * This opens the segment for (id128, rank, size), arrives n_steps times with the given limit and closes; OB_ERR_COMM and
+ * *missing = the first absent rank when a step's limit runs out. */
+int ob_tp_rendezvous_selftest(const void *id128, uint32_t rank, uint32_t size, uint32_t n_steps, uint32_t timeout_ms, int32_t *missing);
 int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *sums_out);
 
 /* ------------------------------------------------- slot pool and decode window */

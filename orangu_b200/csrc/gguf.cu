@@ -47,6 +47,16 @@ struct Tensor {
     uint64_t offset = 0, n_bytes = 0;
 };
 
+// elements per block of a type (1 for the unquantized ones, 0 = a type this build does not size)
+uint32_t type_block(uint32_t type) {
+    switch (type) {
+    case 0: case 1: return 1;
+    case 8: case 2: case 3: case 6: case 7: case 20: return 32;
+    case 12: case 14: case 10: case 11: case 13: case 15: return 256;
+    default: return 0;
+    }
+}
+
 // bytes of a tensor of `n` elements whose rows have dims[0] elements; 0 = a type this build does not size
 uint64_t tensor_bytes(uint32_t type, uint64_t n) {
     switch (type) {
@@ -228,13 +238,17 @@ int ob_gguf_open(const char *path, ob_gguf **out) {
         t.offset = r.get<uint64_t>();
         if (!r.ok) return bail(OB_ERR_INVALID, "truncated tensor table");
         t.n_bytes = tensor_bytes(t.ggml_type, n);
+        // a row (dims[0] elements) must be a whole number of blocks, or the byte count above undercounts the tensor
+        if (const uint32_t blk = type_block(t.ggml_type); blk > 1 && t.dims[0] % blk)
+            return bail(OB_ERR_INVALID, "tensor " + t.name + ": its rows are not a whole number of " + std::to_string(blk) + "-element blocks");
         g->by_name[t.name] = g->tensors.size();
         g->tensors.push_back(std::move(t));
     }
     g->data_offset = (r.pos + g->alignment - 1) / g->alignment * g->alignment;  // gguf.rs:258-266
     for (const Tensor &t : g->tensors) {
         if (t.offset % g->alignment) return bail(OB_ERR_INVALID, "tensor " + t.name + " is not aligned to general.alignment");
-        if (g->data_offset + t.offset > g->size || t.n_bytes > g->size - g->data_offset - t.offset)
+        // no sum that could wrap: the offset is compared with what is left after the data section starts
+        if (g->data_offset > g->size || t.offset > g->size - g->data_offset || t.n_bytes > g->size - g->data_offset - t.offset)
             return bail(OB_ERR_INVALID, "tensor " + t.name + " reaches past the end of the file");
     }
     *out = g;
@@ -298,6 +312,11 @@ int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *d) {
         return gfail(OB_ERR_INVALID, "gguf_model_desc: " + arch + ".embedding_length, .block_count and .attention.head_count are required");
     if (!req("attention.head_count_kv", &n_head_kv)) n_head_kv = n_head;  // loader.rs:1656-1658
     if (n_head == 0 || n_head_kv == 0) return gfail(OB_ERR_INVALID, "gguf_model_desc: head counts must be nonzero");
+    // every layer owns at least nine tensors, and every size is later held in 32 bits
+    if (n_layer == 0 || n_layer > g->tensors.size() / 9 || n_layer > 4096)
+        return gfail(OB_ERR_INVALID, "gguf_model_desc: " + arch + ".block_count = " + std::to_string(n_layer) + " does not fit the file's " + std::to_string(g->tensors.size()) + " tensors");
+    if (n_embd == 0 || n_embd > (1u << 24) || n_head > (1u << 16) || n_head_kv > n_head)
+        return gfail(OB_ERR_INVALID, "gguf_model_desc: implausible embedding_length or head counts");
     if (!req("attention.key_length", &head_dim)) head_dim = n_embd / n_head;  // loader.rs:1676-1678
     if (!req("rope.dimension_count", &rope_dim)) rope_dim = head_dim;         // loader.rs:1682-1684
     if (!req("vocab_size", &n_vocab)) {                                       // loader.rs:1660-1671
@@ -366,6 +385,8 @@ int ob_gguf_model_desc(ob_gguf *g, ob_model_desc *d) {
     uint64_t ff_meta = 0;
     if (req("feed_forward_length", &ff_meta) && n_layer && ff_meta != n_ff)
         return gfail(OB_ERR_INVALID, "gguf_model_desc: " + arch + ".feed_forward_length disagrees with the ffn tensors");
+    if (n_vocab > (1ull << 31) || head_dim == 0 || head_dim > (1u << 16) || rope_dim > head_dim || n_ff > (1ull << 31))
+        return gfail(OB_ERR_INVALID, "gguf_model_desc: vocabulary, head or feed-forward sizes out of range");
     d->n_vocab = (uint32_t)n_vocab;
     d->n_embd = (uint32_t)n_embd;
     d->n_layer = (uint32_t)n_layer;

@@ -113,6 +113,9 @@ struct ob_model {
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
     bool use_prefill_attn = true;  // OB_PREFILL_ATTN=0: prefill chunks take the decode kernel row by row
     bool comm_failed = false;    // a collective could not be enqueued during the last step (reported by check_peer)
+    obtp::Rendezvous *rdv = nullptr;  // host-side meeting of the ranks before a step is enqueued (tensor parallel only)
+    uint32_t rdv_timeout_ms = 30000;  // OB_TP_RENDEZVOUS_MS; 0 = off
+    bool out_of_step = false;         // a rendezvous failed: the ranks no longer run the same sequence of steps
     // Persistent layer kernel (layer_stream.cu): the single-token products between two attention kernels as one launch.
     // Phase list: [q/k/v of layer 0] then per layer [attention-output, gate/up, down, q/k/v of the next layer | output projection].
     bool use_persist = false;    // OB_PERSIST=1; measured slower than one launch per product (barrier waits and the synchronous norm outweigh the launches saved)
@@ -241,6 +244,7 @@ void quantize_into(ob_model *m, int source, const float *x, const float *aux, ui
 }
 
 int check_peer(ob_model *m);
+int pre_step(ob_model *m);
 uint32_t pages_missing(const ob_kv *kv, uint32_t new_len);
 int grow_pages(ob_kv *kv, uint32_t new_len);
 // Before the synchronisation that ends a step: the persistent kernel's status word comes down with the results.
@@ -699,6 +703,7 @@ void ob_model_destroy(ob_model *m) {
     Bind b(ctx);
     cudaStreamSynchronize(ctx->stream);
     for (auto &kvp : m->graphs) cudaGraphExecDestroy(kvp.second);
+    if (m->rdv) obtp::rendezvous_close(m->rdv);
     if (m->comm) obtp::destroy(m->comm);
     auto rel = [&](ob_weight *w) {
         if (w) {
@@ -897,6 +902,11 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         std::string err;
         m->comm = obtp::create(c.tp_unique_id, (int)rank, (int)tp, ctx->device, &err);
         if (!m->comm) return bail(fail(ctx, OB_ERR_COMM, "model_create: " + err));
+        if (const char *re = getenv("OB_TP_RENDEZVOUS_MS")) m->rdv_timeout_ms = (uint32_t)std::max(0, atoi(re));
+        if (m->rdv_timeout_ms) {
+            m->rdv = obtp::rendezvous_open(c.tp_unique_id, (int)rank, (int)tp, &err);
+            if (!m->rdv) return bail(fail(ctx, OB_ERR_COMM, "model_create: " + err));
+        }
         const char *pe = getenv("OB_TP_PEER");
         if (!(pe && pe[0] == '0' && pe[1] == 0) && tp <= 8) {
             std::string perr;
@@ -1255,6 +1265,7 @@ int ob_forward(ob_model *m, ob_kv *const *kvs, const uint32_t *tokens, const uin
             if (rc) return rc;
         }
     }
+    if (int rc = pre_step(m)) return rc;
     ctx->last_ms = 0.0f;
 
     if (all_single) {
@@ -1309,6 +1320,18 @@ int ob_last_hidden(ob_model *m, uint32_t n_tokens, float *out) {
 namespace {
 
 // After a synchronisation: did a peer exchange of the tensor-parallel step run out of time?
+// Tensor parallel: every rank is about to enqueue the same step.  Meet on the host first, so that a rank that is gone (or has
+// refused the call on its own arguments) costs the others a time limit here and not a wait inside a collective on the GPU.
+int pre_step(ob_model *m) {
+    if (!m->rdv) return OB_OK;
+    if (m->out_of_step) return fail(m->ctx, OB_ERR_COMM, "tensor parallel: an earlier step lost a rank; the model has to be created again on every rank");
+    int missing = -1;
+    if (obtp::rendezvous_arrive(m->rdv, m->rdv_timeout_ms, &missing)) return OB_OK;
+    m->out_of_step = true;
+    return fail(m->ctx, OB_ERR_COMM, "tensor parallel: rank " + std::to_string(missing) + " did not arrive for this step within " + std::to_string(m->rdv_timeout_ms) +
+                                         " ms; nothing was launched");
+}
+
 int check_peer(ob_model *m) {
     if (gemm_tc5_take_status()) return fail(m->ctx, OB_ERR_CUDA, "a tensor-core product gave up a bounded wait (pipeline barrier); the step's output is not valid");
     if (m->launch_failed) {
@@ -1397,6 +1420,7 @@ int ob_decode_greedy(ob_model *m, ob_kv *kv, uint32_t token, uint32_t *out_token
     if (pages_missing(kv, kv->len + 1) > m->free_pages.size()) return fail(ctx, OB_ERR_CAPACITY, "decode_greedy: KV pool exhausted");
     Bind b(ctx);
     if (int rc = grow_pages(kv, kv->len + 1)) return rc;
+    if (int rc = pre_step(m)) return rc;
     const MetaLayout ml(m->T);
     reinterpret_cast<uint32_t *>(m->h_meta + ml.off_tokens)[0] = token;
     reinterpret_cast<uint32_t *>(m->h_meta + ml.off_positions)[0] = kv->len;
@@ -1440,6 +1464,7 @@ int ob_decode_loop(ob_model *m, ob_kv *const *kvs, const uint32_t *first_tokens,
         for (uint32_t s = 0; s < n_seq; ++s)
             if (int rc = grow_pages(kvs[s], kvs[s]->len + n_steps)) return rc;
     }
+    if (int rc = pre_step(m)) return rc;
     if ((uint64_t)n_steps * n_seq > m->history_cap) {
         int rc = dev_alloc(m, &m->d_history, (size_t)n_steps * n_seq);
         if (rc) return rc;
@@ -1541,6 +1566,18 @@ int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32
     cudaStreamSynchronize(st);
     cudaFree(region);
     cudaFree(x);
+    return rc;
+}
+
+int ob_tp_rendezvous_selftest(const void *id128, uint32_t rank, uint32_t size, uint32_t n_steps, uint32_t timeout_ms, int32_t *missing) {
+    std::string err;
+    obtp::Rendezvous *r = obtp::rendezvous_open(id128, (int)rank, (int)size, &err);
+    if (!r) return fail(nullptr, OB_ERR_COMM, err);
+    int who = -1, rc = OB_OK;
+    for (uint32_t i = 0; i < n_steps && rc == OB_OK; ++i)
+        if (!obtp::rendezvous_arrive(r, timeout_ms ? timeout_ms : 1000u, &who)) rc = fail(nullptr, OB_ERR_COMM, "rendezvous: rank " + std::to_string(who) + " did not arrive");
+    if (missing) *missing = who;
+    obtp::rendezvous_close(r);
     return rc;
 }
 

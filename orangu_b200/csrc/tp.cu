@@ -1,11 +1,18 @@
-// NCCL binding for the tensor-parallel all-reduce after the row-split products (attention output
-// and FFN down).  The reference engine has no collective of any kind; its multi-GPU mode moves
-// activations through host memory between layer ranges (engine/backend/multi.rs:16-35).
+// Tensor-parallel plumbing: the NCCL binding (all-reduce after the contraction-split products, logits gather), resolved with
+// dlopen at run time, and the set-up of the peer-memory exchange the single-token step uses instead (a region per rank, CUDA
+// IPC handles all-gathered over the communicator, the peers' regions mapped).  The reference engine has no collective of any
+// kind; its multi-GPU mode moves activations through host memory between layer ranges (engine/backend/multi.rs:16-35).
 #include "tp.h"
 
 #include <dlfcn.h>
+#include <fcntl.h>
+#include <sched.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
+#include <time.h>
+#include <unistd.h>
 
 #include <algorithm>
 
@@ -82,7 +89,10 @@ struct Comm {
     std::string err;
     void *peer_region = nullptr;    // this rank's exchange region
     void *peer_mapped[8] = {};      // the peers' regions as mapped here
+    unsigned char *scratch = nullptr;  // small device buffer for the set-up collectives, made with the communicator so that
+                                       // no rank can fail to have it when the others already wait inside NCCL
 };
+constexpr size_t kScratchBytes = 8 * sizeof(cudaIpcMemHandle_t) + 64;
 
 bool unique_id(void *out128, std::string *err) {
     Api *a = api();
@@ -118,6 +128,12 @@ Comm *create(const void *id128, int rank, int size, int device, std::string *err
         delete c;
         return nullptr;
     }
+    if (cudaMalloc(reinterpret_cast<void **>(&c->scratch), kScratchBytes) != cudaSuccess) {  // 576 bytes, right after NCCL took its megabytes
+        if (err) *err = "cudaMalloc of the communicator's scratch buffer failed";
+        a->CommDestroy(c->comm);
+        delete c;
+        return nullptr;
+    }
     return c;
 }
 
@@ -126,6 +142,7 @@ void destroy(Comm *c) {
     for (void *p : c->peer_mapped)
         if (p) cudaIpcCloseMemHandle(p);
     if (c->peer_region) cudaFree(c->peer_region);
+    if (c->scratch) cudaFree(c->scratch);
     Api *a = api();
     if (a && c->comm) a->CommDestroy(c->comm);
     delete c;
@@ -182,14 +199,12 @@ static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std:
         if (cudaIpcGetMemHandle(&mine, c->peer_region) != cudaSuccess) early = std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(cudaGetLastError());
     }
     // all-gather the 64-byte handles through the communicator
-    unsigned char *stage = nullptr;
-    if (cudaMalloc(reinterpret_cast<void **>(&stage), (size_t)c->size * sizeof(mine)) != cudaSuccess) return bail("cudaMalloc failed");
+    unsigned char *stage = c->scratch;  // preallocated: nothing between here and the collective can fail on one rank only
     cudaMemcpy(stage + (size_t)c->rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice);
     NcclResult r = a->AllGather(stage + (size_t)c->rank * sizeof(mine), stage, sizeof(mine), /* ncclChar */ 0, c->comm, nullptr);
     cudaError_t e = cudaStreamSynchronize(nullptr);
     std::vector<cudaIpcMemHandle_t> all((size_t)c->size);
     if (r == 0 && e == cudaSuccess) e = cudaMemcpy(all.data(), stage, all.size() * sizeof(mine), cudaMemcpyDeviceToHost);
-    cudaFree(stage);
     if (!early.empty()) return bail(early);
     if (r != 0 || e != cudaSuccess) return bail("exchange of the IPC handles failed");
     PeerXchg px{};
@@ -218,19 +233,95 @@ bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err)
     Api *a = api();
     if (!a || !c) return false;
     // Every rank must take the same path afterwards: the exchange is used only if it could be set up everywhere.
-    // (The handle all-gather inside peer_init_local is reached by every rank or by none: its preconditions are the same
-    // on all ranks, and allocation failures this early are not expected; the agreement below covers the mapping step.)
+    // Both collectives -- the handle all-gather inside peer_init_local and the agreement below -- run out of the scratch
+    // buffer made with the communicator, so a rank whose own allocations fail still reaches them (with a zero handle and
+    // a 0 vote) instead of leaving the others waiting inside NCCL.
     const bool mine = peer_init_local(c, n, device, out, err);
-    int *flag = nullptr;
-    if (cudaMalloc(reinterpret_cast<void **>(&flag), sizeof(int)) != cudaSuccess) return false;
+    int *flag = reinterpret_cast<int *>(c->scratch + 8 * sizeof(cudaIpcMemHandle_t));
     const int v = mine ? 1 : 0;
     cudaMemcpy(flag, &v, sizeof(int), cudaMemcpyHostToDevice);
     const NcclResult r = a->AllReduce(flag, flag, 1, /* ncclInt32 */ 2, /* ncclMin */ 2, c->comm, nullptr);
     int all = 0;
     if (r == 0 && cudaStreamSynchronize(nullptr) == cudaSuccess) cudaMemcpy(&all, flag, sizeof(int), cudaMemcpyDeviceToHost);
-    cudaFree(flag);
     if (!all && err && err->empty()) *err = "another rank could not set up the peer exchange";
     return all == 1;
+}
+
+// ---- host-side rendezvous ----------------------------------------------------------------------------------------------
+struct Rendezvous {
+    volatile uint64_t *slots = nullptr;  // one counter per rank, 64 bytes apart
+    std::string name;
+    int rank = 0, size = 1;
+    uint64_t step = 0;
+    bool unlinked = false;
+};
+
+Rendezvous *rendezvous_open(const void *id128, int rank, int size, std::string *err) {
+    if (!id128 || rank < 0 || size < 1 || size > 64 || rank >= size) {
+        if (err) *err = "rendezvous: bad rank or size";
+        return nullptr;
+    }
+    uint64_t h = 1469598103934665603ull;  // FNV-1a over the id: the name only has to differ between jobs
+    for (int i = 0; i < 128; ++i) h = (h ^ static_cast<const unsigned char *>(id128)[i]) * 1099511628211ull;
+    char name[64];
+    snprintf(name, sizeof(name), "/ob_tp_%016llx", (unsigned long long)h);
+    const int fd = shm_open(name, O_CREAT | O_RDWR, 0600);
+    if (fd < 0 || ftruncate(fd, 4096) != 0) {
+        if (fd >= 0) close(fd);
+        if (err) *err = std::string("rendezvous: shm_open/ftruncate of ") + name + " failed";
+        return nullptr;
+    }
+    void *p = mmap(nullptr, 4096, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);  // a fresh segment reads as zeros
+    close(fd);
+    if (p == MAP_FAILED) {
+        if (err) *err = "rendezvous: mmap failed";
+        return nullptr;
+    }
+    Rendezvous *r = new Rendezvous;
+    r->slots = static_cast<volatile uint64_t *>(p);
+    r->name = name;
+    r->rank = rank;
+    r->size = size;
+    return r;
+}
+
+bool rendezvous_arrive(Rendezvous *r, uint32_t timeout_ms, int *missing) {
+    if (!r || timeout_ms == 0) return true;
+    const uint64_t step = ++r->step;
+    __atomic_store_n(const_cast<uint64_t *>(&r->slots[(size_t)r->rank * 8]), step, __ATOMIC_RELEASE);
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (int p = 0; p < r->size; ++p) {
+        for (uint32_t spin = 0; __atomic_load_n(const_cast<uint64_t *>(&r->slots[(size_t)p * 8]), __ATOMIC_ACQUIRE) < step; ++spin) {
+            if ((spin & 255u) != 255u) continue;
+            timespec t1;
+            clock_gettime(CLOCK_MONOTONIC, &t1);
+            const int64_t ms = (int64_t)(t1.tv_sec - t0.tv_sec) * 1000 + (t1.tv_nsec - t0.tv_nsec) / 1000000;
+            if (ms > (int64_t)timeout_ms) {
+                if (missing) *missing = p;
+                return false;
+            }
+            if (spin > 4096u) {  // the others are not about to arrive: stop burning the core
+                timespec nap{0, 50000};
+                nanosleep(&nap, nullptr);
+            } else {
+                sched_yield();
+            }
+        }
+    }
+    // everybody has the segment mapped by now: its name can go, so that nothing is left behind whichever way the job ends
+    if (step == 1 && r->rank == 0 && !r->unlinked) {
+        shm_unlink(r->name.c_str());
+        r->unlinked = true;
+    }
+    return true;
+}
+
+void rendezvous_close(Rendezvous *r) {
+    if (!r) return;
+    if (r->rank == 0 && !r->unlinked) shm_unlink(r->name.c_str());
+    munmap(const_cast<uint64_t *>(r->slots), 4096);
+    delete r;
 }
 
 }  // namespace obtp

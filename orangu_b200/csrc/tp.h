@@ -23,6 +23,17 @@ bool all_reduce_sum(Comm *, float *buf, size_t count, cudaStream_t st);
 bool all_gather_logits(Comm *, float *logits, uint32_t rows, uint32_t n_vocab, uint32_t vocab0, uint32_t vocab_l, cudaStream_t st);
 const char *last_error(Comm *);
 
+// Host-side rendezvous of the ranks of one node, for use BEFORE a step that contains collectives or exchanges is enqueued:
+// a rank that has died, or has failed its own argument checks and returned, is then found on the host after a time limit,
+// with nothing launched, instead of the others waiting for it inside a collective on their GPUs.  A small POSIX
+// shared-memory segment named after the communicator's id holds one arrival counter per rank.
+struct Rendezvous;
+Rendezvous *rendezvous_open(const void *id128, int rank, int size, std::string *err);
+// Publishes this rank's next step number and waits until every rank has published it.  False when the time runs out;
+// *missing is then the first rank that had not arrived.  timeout_ms == 0 returns true at once (the guard is off).
+bool rendezvous_arrive(Rendezvous *, uint32_t timeout_ms, int *missing);
+void rendezvous_close(Rendezvous *);
+
 // One-shot exchange of the ranks' partial vectors through peer memory (NVLink stores between the GPUs of one node), for
 // the single-token decode step where an NCCL all-reduce of 16 KB costs more than the product it follows.
 // Every rank owns 2 x size slots of n (value, tag) pairs.  In exchange number k (counted per rank in *seq, the same on

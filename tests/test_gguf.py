@@ -121,6 +121,28 @@ def test_malformed_files_are_refused_with_a_message(tmp_path):
     refused(blob[:8] + struct.pack("<Q", 1 << 40) + blob[16:], "implausible")
     with pytest.raises(capi.OranguError):
         GgufFile(str(tmp_path / "missing.gguf"))
+    # a tensor offset chosen so that data_offset + offset wraps around 2^64 must not pass the bounds check
+    with GgufFile(good) as g:
+        data_offset = g.data_offset
+    first_off = blob.index(struct.pack("<IQ", tensors["token_embd.weight"]["type"], 0), 24) + 4  # the first tensor's offset field
+    wrap = (1 << 64) - data_offset + 64
+    wrap -= wrap % 32
+    refused(blob[:first_off] + struct.pack("<Q", wrap) + blob[first_off + 8:], "past the end")
+    # rows that are not a whole number of blocks (a Q4_K tensor 100 elements wide)
+    odd = dict(tensors)
+    odd["blk.0.attn_q.weight"] = dict(tensors["blk.0.attn_q.weight"], in_dim=100)
+    p_odd = str(tmp_path / "odd.gguf")
+    write_gguf(p_odd, cfg, odd)
+    with pytest.raises(capi.OranguError) as e:
+        GgufFile(p_odd)
+    assert "whole number of 256-element blocks" in str(e.value)
+    # a block count far beyond what the file's tensors could make up is an error, not an allocation
+    p_big = str(tmp_path / "big.gguf")
+    huge = dict(cfg, n_layer=(1 << 32) - 1)
+    write_gguf(p_big, huge, tensors)
+    with GgufFile(p_big) as g, pytest.raises(capi.OranguError) as e:
+        g.model_desc()
+    assert "block_count" in str(e.value)
     # a model whose architecture or tensor types are outside the build is named, not crashed on
     p = str(tmp_path / "arch.gguf")
     write_gguf(p, cfg, tensors)

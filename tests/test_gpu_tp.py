@@ -73,6 +73,20 @@ def test_presliced_shards_give_the_same_model():
     assert shards["digest"] == whole["digest"], (whole, shards)
 
 
+def test_a_rank_that_stays_away_from_a_step_is_found_on_the_host_before_anything_is_launched():
+    """Failure made on the host, between steps: the last of two ranks skips one step.  The other meets nobody at the host-side
+    rendezvous, gives up after OB_TP_RENDEZVOUS_MS, reports OB_ERR_COMM naming the rank, leaves its KV cache where it was and
+    refuses further steps -- no kernel or collective was enqueued, so no GPU waits for anybody."""
+    if gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    r = run_ranks(2, ["small", 1, 20, 2, "absent"], OB_TP_RENDEZVOUS_MS="1500")
+    present, away = r["absent"]
+    assert away is None
+    assert present["status"] == -7 and "rank 1 did not arrive" in present["message"] and "nothing was launched" in present["message"]
+    assert 1.4 < present["seconds"] < 20 and present["kv_len"] == 22
+    assert present["second"] == -7
+
+
 def test_exchange_wait_runs_out_and_reports_instead_of_hanging():
     """One GPU, no fault, no hang: a two-rank exchange whose second rank's slot is local memory nobody writes in some rounds.
     The consumer kernel's wait ends after the limit (50 ms here), the round is reported as OB_ERR_COMM (-7), and the rounds

@@ -113,3 +113,45 @@ def test_plan_rejects_shapes_that_do_not_split():
         tp_shard.plan(dict(synth.CONFIGS["tiny"]), 2, 0)  # 2 heads x 64 per rank is not a multiple of 256
     p = tp_shard.plan(dict(synth.CONFIGS["8b"]), 8, 3)
     assert p["attn_k"] == ("rows", 3 * 128, 128) and p["ffn_down"] == ("cols", 3 * 1792, 1792)
+
+
+# ---------------------------------------------------------------- the ranks' host-side meeting point (no device, no NCCL)
+def _rendezvous_rank(rank, world, ident, n_steps, timeout_ms, out):
+    import ctypes as C
+
+    from orangu_b200 import capi
+
+    missing = C.c_int32(-1)
+    rc = capi.load().ob_tp_rendezvous_selftest(ident, rank, world, n_steps, timeout_ms, C.byref(missing))
+    out.put((rank, rc, missing.value))
+
+
+def _run_ranks(steps_of_rank, timeout_ms):
+    import multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ident = os.urandom(128)
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_rendezvous_rank, args=(r, len(steps_of_rank), ident, n, timeout_ms, out)) for r, n in enumerate(steps_of_rank)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=60) for _ in procs)
+    for p in procs:
+        p.join(30)
+    return got
+
+
+def test_ranks_that_all_arrive_pass_every_step():
+    assert _run_ranks([50, 50, 50], 5000) == [(0, 0, -1), (1, 0, -1), (2, 0, -1)]
+
+
+def test_a_rank_that_stays_away_costs_a_time_limit_on_the_host_and_is_named():
+    """Rank 1 leaves after two steps (between steps, nothing in flight); rank 0 finds out at its third arrival, on the host, after
+    the limit, and learns which rank is missing: the status ob_forward returns as OB_ERR_COMM with nothing launched."""
+    import time
+
+    t0 = time.time()
+    got = _run_ranks([3, 2], 300)
+    assert got[1] == (1, 0, -1)
+    assert got[0] == (0, -7, 1)
+    assert time.time() - t0 < 30

@@ -27,6 +27,7 @@ def main():
 
     name, n_layer, n_prompt, n_decode = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4])
     presliced = len(sys.argv) > 5 and sys.argv[5] == "presliced"  # every rank builds only its own shards
+    absent = len(sys.argv) > 5 and sys.argv[5] == "absent"        # the last rank stays away from one step (made on the host, between steps)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
     dist.init_process_group("gloo")
     torch.cuda.set_device(local)
@@ -52,6 +53,34 @@ def main():
     for i in range(n_decode):
         logits.append(model.forward(kv, [got[-1]], n_prompt + i))
         got.append(be.argmax(logits[-1]))
+
+    if absent:
+        # One more step, which the last rank does not take part in (as if it had refused the call on its own arguments, or
+        # died between steps).  The others meet on the host first, find it missing after OB_TP_RENDEZVOUS_MS, and return
+        # OB_ERR_COMM without having launched anything; afterwards the model refuses further steps.
+        import time
+
+        outcome = None
+        if rank != world - 1:
+            t0 = time.time()
+            try:
+                model.forward(kv, [got[-1]], n_prompt + n_decode)
+                outcome = {"status": 0}
+            except orangu_b200.OranguError as e:
+                outcome = {"status": e.status, "message": e.message, "seconds": time.time() - t0, "kv_len": len(kv)}
+            try:
+                model.forward(kv, [got[-1]], n_prompt + n_decode)
+                outcome["second"] = 0
+            except orangu_b200.OranguError as e:
+                outcome["second"] = e.status
+        outcomes = [None] * world
+        dist.all_gather_object(outcomes, outcome)
+        if rank == 0:
+            print(json.dumps({"world": world, "absent": outcomes}), flush=True)
+        dist.barrier()
+        model.close()
+        dist.destroy_process_group()
+        return
 
     # every rank must hold the same logits (the gather completed) -- compare a digest through the store
     digest = [float(np.sum(np.stack(logits).astype(np.float64)))]
