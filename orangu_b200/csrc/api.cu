@@ -268,7 +268,9 @@ int matmul_device(ob_ctx *ctx, const float *x_dev, uint32_t n_tokens, const ob_w
         sa.x = x_dev;
         sa.seg[0] = StreamSeg{w->w, DevWeight{}, y_dev, SG_EP_STORE};
         if (stream_gemv_supported(sa)) {
-            launch_stream_gemv(sa, ctx->sm_count, false, st);
+            // programmatic serialisation: the kernel requests its first weights while the previous work on the stream is
+            // finishing and waits for it before it reads x or writes y, so stream order is kept
+            launch_stream_gemv(sa, ctx->sm_count, true, st);
             ctx->launches++;
             return OB_OK;
         }

@@ -101,6 +101,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(GemvArgs a, uint3
 
     // ---- stage activations -----------------------------------------------------------
     if (TYPE == TYPE_Q8_0 && T == 1 && a.x_f32) {
+        // launched with programmatic stream serialisation: this grid may have started while its predecessor was finishing;
+        // let the successor do the same, then wait for the predecessor's output (x) to be complete.  Nothing above this point
+        // reads or writes memory another kernel touches.
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         // the row arrives as fp32: quantize it per 32 here (quantize_act, engine/vecdot.rs:95-126) -- four lanes x eight values
         // are one block -- straight into the layout the loop below reads
         const uint32_t n_chunks = in_dim / 8;
@@ -399,6 +404,20 @@ template <uint32_t TYPE, int T, bool GEMM>
 void launch_tile(const GemvArgs &a, int grid, size_t smem, cudaStream_t st) {
     static PerDeviceOnce once;  // one per instantiation
     if (once.run([] { return cudaFuncSetAttribute(gemv_kernel<TYPE, T, GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); }) != cudaSuccess) return;
+    if (TYPE == TYPE_Q8_0 && T == 1 && a.x_f32) {  // the fused single-token form overlaps its launch with its predecessor's tail
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3(GEMV_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaLaunchKernelEx(&cfg, gemv_kernel<TYPE, T, GEMM>, a, 0u);
+        return;
+    }
     for (uint32_t tok0 = 0; tok0 < a.n_tokens; tok0 += T) gemv_kernel<TYPE, T, GEMM><<<grid, GEMV_THREADS, smem, st>>>(a, tok0);
 }
 
