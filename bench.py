@@ -197,7 +197,7 @@ def operator_gemv_rooflines(be, peak):
         nbytes = wbytes + 4 * (in_dim + out_dim)
         out[name] = {"avg_launch_us": us, "algorithmic_bytes": nbytes, "GB/s": nbytes / us / 1e3, "frac": nbytes / us / 1e3 / peak,
                      "timed": f"CUDA graph of {reps} products rotating over {copies} copies of the matrix ({copies * wbytes / 1e6:.0f} MB > L2), 5 replays",
-                     "kernels_per_product": 1 if t != 8 else 2}
+                     "kernels_per_product": 1}
         for h in handles:
             L.ob_weight_release(be._h, h)
             be._weights.remove(h)

@@ -290,6 +290,8 @@ static_assert(K4Smem<128>::ALLOC <= 227 * 1024 && K4Smem<64>::ALLOC <= 227 * 102
 
 struct TcK4Args {
     GemvSegment seg;
+    GemvSegment seg2;      // a second matrix of the same type and width served by the same launch (tiles0 < gridDim.x), e.g. ffn_up next to ffn_gate
+    uint32_t tiles0;       // row tiles of `seg`; CTAs with blockIdx.x >= tiles0 work on seg2
     const float *act_d;    // [token][pitch] per-256 activation scales
     uint32_t act_d_pitch;
     uint32_t n_tokens, nb;
@@ -297,7 +299,8 @@ struct TcK4Args {
 
 template <bool GEMM, int N>
 __global__ void __launch_bounds__(K4_THREADS, 1)
-gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_constant__ CUtensorMap tm_hdr, const __grid_constant__ CUtensorMap tm_x, TcK4Args a) {
+gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw0, const __grid_constant__ CUtensorMap tm_hdr0, const __grid_constant__ CUtensorMap tm_raw1,
+                    const __grid_constant__ CUtensorMap tm_hdr1, const __grid_constant__ CUtensorMap tm_x, TcK4Args a) {
     using S = K4Smem<N>;
     constexpr uint32_t IN_STAGES = S::IN_STAGES;
     constexpr uint32_t MAX_PLANES = GEMM ? 2 : 3, ACC_STRIDE = MAX_PLANES * N, NBUF = 2 * ACC_STRIDE <= 512 ? 2 : 1;
@@ -306,7 +309,11 @@ gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_con
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (sbase - smem_u32(smem_raw));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t row0 = blockIdx.x * TC_M, tok0 = blockIdx.y * N;
+    // two matrices in one launch fill the last wave better than two launches: 2 x 448 CTAs are 6.05 waves of 148, not 2 x 4
+    const bool second = blockIdx.x >= a.tiles0;
+    const CUtensorMap &tm_raw = second ? tm_raw1 : tm_raw0, &tm_hdr = second ? tm_hdr1 : tm_hdr0;
+    const GemvSegment &seg = second ? a.seg2 : a.seg;
+    const uint32_t row0 = (blockIdx.x - (second ? a.tiles0 : 0u)) * TC_M, tok0 = blockIdx.y * N;
     volatile uint32_t *abort = reinterpret_cast<volatile uint32_t *>(smem + S::ABORT);
     const uint32_t nb = a.nb;
     const uint32_t n_visits = GEMM ? 2 * nb : nb;  // super-block visits; in the prefill order the first nb are the min sweep
@@ -444,7 +451,7 @@ gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_con
         // ---- epilogue: thread = one row x N / 2 tokens
         const uint32_t quad = warp & 3u, half = warp >> 2, rl = quad * 32 + lane;
         const uint32_t row = row0 + rl;
-        const bool row_ok = row < a.seg.w.out_dim;
+        const bool row_ok = row < seg.w.out_dim;
         float acc[TPT];
 #pragma unroll
         for (int t = 0; t < TPT; ++t) acc[t] = 0.0f;
@@ -488,10 +495,10 @@ gemm_tc5_q4k_kernel(const __grid_constant__ CUtensorMap tm_raw, const __grid_con
             for (int t = 0; t < TPT; ++t) {
                 const uint32_t tok = tok0 + half * TPT + t;
                 if (tok < a.n_tokens) {
-                    const uint64_t o = (uint64_t)tok * a.seg.y_stride + row;
+                    const uint64_t o = (uint64_t)tok * seg.y_stride + row;
                     float v = acc[t];
-                    if (a.seg.epilogue == EPI_ADD_RESIDUAL) v = __fadd_rn(a.seg.residual[o], v);
-                    a.seg.y[o] = v;
+                    if (seg.epilogue == EPI_ADD_RESIDUAL) v = __fadd_rn(seg.residual[o], v);
+                    seg.y[o] = v;
                 }
             }
         }
@@ -554,39 +561,48 @@ bool gemm_tc5_supported(const GemvArgs &a) {
 }
 
 template <bool GEMM, int N>
-static bool launch_q4k_instance(const GemvArgs &a, cudaStream_t st) {
+static bool launch_q4k_instance(const GemvArgs &a, int sm_count, cudaStream_t st) {
     static PerDeviceOnce once;
     if (once.run([] { return cudaFuncSetAttribute(gemm_tc5_q4k_kernel<GEMM, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, K4Smem<N>::ALLOC); }) != cudaSuccess) return false;
     const uint32_t in_dim = a.seg[0].w.in_dim, nb = in_dim / 256;
     CUtensorMap tm_x;
     if (!make_map_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.act.q, in_dim, a.n_tokens, a.act.dim_cap, 128, N, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    auto maps = [&](const GemvSegment &g, CUtensorMap *raw, CUtensorMap *hdr) {
+        return make_map_2d(raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 144, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+               make_map_2d(hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 16, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE);
+    };
+    const uint32_t tok_tiles = (a.n_tokens + N - 1) / N, sms = (uint32_t)std::max(1, sm_count);
+    auto tiles = [&](int s) { return (a.seg[s].w.out_dim + TC_M - 1) / TC_M; };
+    auto waves = [&](uint32_t ctas) { return (ctas + sms - 1) / sms; };
     for (int s = 0; s < a.n_seg; ++s) {
-        const GemvSegment &g = a.seg[s];
-        CUtensorMap tm_raw, tm_hdr;
-        if (!make_map_2d(&tm_raw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 144, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
-        if (!make_map_2d(&tm_hdr, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.w.data, (uint64_t)nb * 144, g.w.out_dim, g.w.row_stride, 16, TC_M, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+        // pair this matrix with the next one when one launch takes fewer waves than two
+        const bool pair = s + 1 < a.n_seg && waves((tiles(s) + tiles(s + 1)) * tok_tiles) < waves(tiles(s) * tok_tiles) + waves(tiles(s + 1) * tok_tiles);
+        CUtensorMap raw0, hdr0, raw1, hdr1;
+        if (!maps(a.seg[s], &raw0, &hdr0) || !maps(a.seg[pair ? s + 1 : s], &raw1, &hdr1)) return false;
         TcK4Args k{};
-        k.seg = g;
+        k.seg = a.seg[s];
+        k.seg2 = a.seg[pair ? s + 1 : s];
+        k.tiles0 = tiles(s);
         k.act_d = a.act.d;
         k.act_d_pitch = a.act.dim_cap / 256;
         k.n_tokens = a.n_tokens;
         k.nb = nb;
-        const dim3 grid((g.w.out_dim + TC_M - 1) / TC_M, (a.n_tokens + N - 1) / N);
-        gemm_tc5_q4k_kernel<GEMM, N><<<grid, K4_THREADS, K4Smem<N>::ALLOC, st>>>(tm_raw, tm_hdr, tm_x, k);
+        const dim3 grid(tiles(s) + (pair ? tiles(s + 1) : 0u), tok_tiles);
+        gemm_tc5_q4k_kernel<GEMM, N><<<grid, K4_THREADS, K4Smem<N>::ALLOC, st>>>(raw0, hdr0, raw1, hdr1, tm_x, k);
         g_tc5_launched.store(true, std::memory_order_relaxed);
+        if (pair) ++s;
     }
     return true;
 }
 
-static bool launch_q4k(const GemvArgs &a, cudaStream_t st) {
+static bool launch_q4k(const GemvArgs &a, int sm_count, cudaStream_t st) {
     const bool wide = a.n_tokens > 64;  // 128-token tiles once there are tokens for them
-    if (a.gemm_order) return wide ? launch_q4k_instance<true, 128>(a, st) : launch_q4k_instance<true, 64>(a, st);
-    return wide ? launch_q4k_instance<false, 128>(a, st) : launch_q4k_instance<false, 64>(a, st);
+    if (a.gemm_order) return wide ? launch_q4k_instance<true, 128>(a, sm_count, st) : launch_q4k_instance<true, 64>(a, sm_count, st);
+    return wide ? launch_q4k_instance<false, 128>(a, sm_count, st) : launch_q4k_instance<false, 64>(a, sm_count, st);
 }
 
 bool launch_gemm_tc5(const GemvArgs &a, int sm_count, cudaStream_t st) {
-    (void)sm_count;
-    if (a.seg[0].w.type == TYPE_Q4_K) return launch_q4k(a, st);
+    if (a.seg[0].w.type == TYPE_Q4_K) return launch_q4k(a, sm_count, st);
     static PerDeviceOnce once;
     if (once.run([] { return cudaFuncSetAttribute(gemm_tc5_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q8Smem::ALLOC); }) != cudaSuccess) return false;
     const uint32_t in_dim = a.seg[0].w.in_dim;

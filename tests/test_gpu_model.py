@@ -286,6 +286,22 @@ def test_8b_shape_two_layers_bit_exact(backend):
     assert model.decode_loop([kv2], [first], 6)[:, 0].tolist() == ref_tokens
 
 
+def test_8b_shape_prefill_chunk_of_300_tokens_is_bit_exact(backend):
+    """One 300-token chunk at the 8B widths: three 128-token tiles, where the tcgen05 kernel serves ffn_gate and ffn_up from one
+    launch (2 x 336 CTAs are five waves of 148 together, six apart) and attn_q / attn_output / ffn_down from their own."""
+    cfg = dict(synth.CONFIGS["8b"])
+    cfg["n_layer"] = 1
+    cfg["n_vocab"] = 4096
+    tensors = synth.model_tensors(cfg, seed=43)
+    model, ref = LlamaModel(backend, cfg, tensors, max_seq_len=512, max_batch_tokens=512, kv_pool_tokens=1024), O.Model(cfg, tensors)
+    toks = prompt(cfg, 300, 15)
+    kv, rkv = model.new_kv_cache(320), ref.new_kv(320, f16=True)
+    want, hidden = ref.forward(rkv, toks, 0, want_hidden=True)
+    assert_bit_equal(model.forward(kv, toks, 0), want, "prefill logits")
+    assert_bit_equal(model.last_hidden(300), hidden, "residual stream of all 300 rows")
+    model.close()
+
+
 @pytest.mark.parametrize("n_layer", [2, 4])
 def test_8b_shape_at_context_4096_fused_flash_decode_error_is_measured(backend, n_layer, capsys):
     """The configuration the decode throughput is quoted on: 8B shape, context past 4096, the one-kernel flash-decode
