@@ -463,6 +463,45 @@ def main():
         batch64["hbm_frac_per_gpu"] = batch64["algorithmic_bytes_per_step"] / world / (ms64 / b64 * 1e-3) / 1e9 / peak
         batch64["parallelism"] = f"tp{world}"
 
+    # ---- serving extra: eight request threads through the slot pool and the decode window (one GPU) ------------------------
+    serving = None
+    if b64 and world == 1:
+        import threading
+
+        from orangu_b200 import SlotPool
+
+        for c in caches[1:]:
+            c.close()  # their pages go back to the pool the slots draw from
+        n_req, n_prompt, n_new = 8, 256, 33
+        pool = SlotPool(model, n_slots=n_req, slot_capacity_tokens=n_prompt + n_new + 16, batch_wait_ms=2, prefill_batch=512, batch_decode=True)
+        prompts = [np.random.default_rng(100 + i).integers(0, cfg["n_vocab"], n_prompt).astype(np.uint32) for i in range(n_req)]
+        done_tokens, failures = [0] * n_req, []
+
+        def request(i):
+            try:
+                with pool.try_acquire() as slot:
+                    tok = slot.prefill(prompts[i])
+                    for _ in range(n_new - 1):
+                        tok = slot.decode(tok)
+                        done_tokens[i] += 1
+            except Exception as e:  # noqa: BLE001
+                failures.append(repr(e)[:200])
+
+        threads = [threading.Thread(target=request, args=(i,)) for i in range(n_req)]
+        t0 = time.perf_counter()
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        wall = time.perf_counter() - t0
+        st = pool.stats()
+        pool.close()
+        serving = {"requests": n_req, "prompt_tokens": n_prompt, "new_tokens": n_new, "wall_s": wall,
+                   "tok_s_generated": sum(done_tokens) / wall, "tok_s_prefill_and_decode": (n_req * n_prompt + sum(done_tokens)) / wall,
+                   "decode_batches": st["batches"], "mean_decode_batch": st["batched_seqs"] / max(1, st["batches"]), "refused": st["refused"],
+                   "failures": failures, "how": "one thread per request: ob_slot_acquire, ob_slot_prefill, ob_slot_decode per token through a 2 ms "
+                   "collection window, ob_slot_release; on-demand KV pages; host round trip per token"}
+
     # ---- CPU baseline (rank 0, single GPU runs only) --------------------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -496,6 +535,8 @@ def main():
         }
         if batch64:
             line["batch64"] = batch64
+        if serving:
+            line["serving"] = serving
         if model70b:
             line["model70b"] = model70b
         print(json.dumps(line), flush=True)
