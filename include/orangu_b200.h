@@ -369,6 +369,12 @@ int ob_tp_unique_id(void *out128);
  * of n values (a multiple of 256) through the real consumer kernel with both "ranks" in local memory: rank 0 always delivers
  * (1.0), rank 1 (2.0) only in the rounds whose byte in peer_delivers is non-zero.  sums_out[k] is the summed value of round k
  * (3.0), or -1 when that round's wait ran out after timeout_ms (0 = 50 ms).  Returns OB_ERR_COMM if any round ran out. */
+/* The exchange the tensor-parallel steps of a few rows use (one kernel: push the partial to every peer, wait for theirs, add in
+ * rank order, add to the residual), run as rank 0 of 2 on one GPU with the peer's part written beforehand by a copy in the
+ * rounds whose byte in peer_delivers is non-zero.  x starts at 0.5, the partials are i % 1000 and 2 (i % 1000) + 1:
+ * x_out[round][count] receives the result.  Rounds without delivery must end by the time limit (timeout_ms, 0 = 50) and report;
+ * OB_OK when every round behaved as it should.  No counterpart in the reference. */
+int ob_tp_bulk_selftest(ob_ctx *ctx, uint32_t count, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *x_out);
 /* Host-only check of the ranks' meeting point (no counterpart in the reference, no device): under tensor parallel every
  * ob_forward / ob_decode_* call first meets the other ranks of the node in a small shared-memory segment named after the
  * communicator id, so that a rank that is gone, or that refused the call on its own arguments, costs the others

@@ -113,6 +113,7 @@ SIGNATURES = {
     "ob_tp_unique_id": (_i32, [_vp]),
     "ob_tp_exchange_selftest": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "ob_tp_rendezvous_selftest": (_i32, [_vp, _u32, _u32, _u32, _u32, _vp]),
+    "ob_tp_bulk_selftest": (_i32, [_vp, _u32, _u32, _u32, _vp, _vp]),
     "ob_slot_pool_create": (_i32, [_vp, _vp, _PP]),
     "ob_slot_pool_destroy": (None, [_vp]),
     "ob_slot_acquire": (_i32, [_vp, _i32, _vp]),

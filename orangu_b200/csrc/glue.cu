@@ -236,6 +236,79 @@ __global__ void __launch_bounds__(256) argmax_finish_xchg_kernel(const unsigned 
     if (threadIdx.x == 0) *px.seq = k + 1u;
 }
 
+// One CTA per 8 KB chunk: push this rank's chunk to every peer, announce it, wait for the peers' chunks, add in rank order.
+// A CTA pushes before it waits and waits only for words that the peers' CTAs of the same chunk write after their own push, so
+// no CTA depends on another CTA of its own grid.  Every wait is bounded (the exchange's time limit -> error word).
+__global__ void __launch_bounds__(256) bulk_allreduce_add_kernel(float *__restrict__ x, const float *__restrict__ proj, uint32_t count, obtp::PeerXchg px,
+                                                                 obtp::PeerBulk bulk) {
+    const uint32_t k = *reinterpret_cast<const volatile uint32_t *>(px.seq), tag = k + 1u, par = k & 1u;
+    const uint32_t c = blockIdx.x, o = c * obtp::kBulkChunk, n = min(obtp::kBulkChunk, count - o);  // n is a multiple of 4
+    const uint64_t area = (uint64_t)(par * px.size + px.rank) * bulk.cap + o;                        // where this rank's chunk lands, in every region
+    // push: 16-byte stores into the peers' landing areas
+    float4 mine[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t i = (threadIdx.x + u * 256) * 4;
+        mine[u] = i < n ? *reinterpret_cast<const float4 *>(proj + o + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < n)
+            for (uint32_t r = 0; r < px.size; ++r)
+                if (r != px.rank) *reinterpret_cast<float4 *>(bulk.data[r] + area + i) = mine[u];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();  // the CTA's stores (ordered before this thread by the barrier) become visible before the arrival words
+        for (uint32_t r = 0; r < px.size; ++r)
+            if (r != px.rank)
+                asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(bulk.flags[r] + (uint64_t)(par * px.size + px.rank) * bulk.max_chunks + c), "r"(tag) : "memory");
+    }
+    // wait for the other ranks' arrival words of this chunk
+    if (threadIdx.x < px.size && threadIdx.x != px.rank) {
+        const uint32_t *f = bulk.flags[px.rank] + (uint64_t)(par * px.size + threadIdx.x) * bulk.max_chunks + c;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (uint32_t spin = 0;; ++spin) {
+            uint32_t v;
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v == tag) break;
+            if ((spin & 1023u) == 1023u) {
+                unsigned long long t1;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+                if (t1 - t0 > (unsigned long long)(px.timeout_ms ? px.timeout_ms : 4000u) * 1000000ull) {  // a rank is gone: report, go on with what is there
+                    *px.err = 1u;
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+    // add in rank order; the landing area is read past L1 (the peers wrote it)
+    const float *land = bulk.data[px.rank] + (uint64_t)(par * px.size) * bulk.cap + o;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t i = (threadIdx.x + u * 256) * 4;
+        if (i >= n) continue;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t r = 0; r < px.size; ++r) {
+            const float4 v = r == px.rank ? mine[u] : __ldcg(reinterpret_cast<const float4 *>(land + (uint64_t)r * bulk.cap + i));
+            if (r == 0) sum = v;
+            else sum = make_float4(__fadd_rn(sum.x, v.x), __fadd_rn(sum.y, v.y), __fadd_rn(sum.z, v.z), __fadd_rn(sum.w, v.w));
+        }
+        float4 xv = *reinterpret_cast<float4 *>(x + o + i);
+        xv = make_float4(__fadd_rn(xv.x, sum.x), __fadd_rn(xv.y, sum.y), __fadd_rn(xv.z, sum.z), __fadd_rn(xv.w, sum.w));
+        *reinterpret_cast<float4 *>(x + o + i) = xv;
+    }
+    // the last CTA to finish closes the exchange
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(bulk.done, 1u) == gridDim.x - 1) {
+            *bulk.done = 0u;
+            *px.seq = k + 1u;
+        }
+    }
+}
+
 // Sequential on purpose: a token that repeats is penalised once per occurrence, compounding.
 __global__ void repeat_penalty_kernel(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -284,6 +357,10 @@ void launch_argmax(const ArgmaxArgs &a, cudaStream_t st) {
     argmax_kernel<<<grid, 256, 0, st>>>(a);
     if (a.px.size > 1) argmax_finish_xchg_kernel<<<1, 256, 0, st>>>(a.scratch, a.out, a.n_seq, a.index_base, a.px);
     else argmax_finish_kernel<<<(a.n_seq + 255) / 256, 256, 0, st>>>(a.scratch, a.out, a.n_seq);
+}
+void launch_bulk_allreduce_add(float *x, const float *proj, uint32_t count, const obtp::PeerXchg &px, const obtp::PeerBulk &bulk, cudaStream_t st) {
+    if (!count) return;
+    bulk_allreduce_add_kernel<<<(count + obtp::kBulkChunk - 1) / obtp::kBulkChunk, 256, 0, st>>>(x, proj, count, px, bulk);
 }
 void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st) {
     if (n_recent && penalty != 1.0f) repeat_penalty_kernel<<<1, 32, 0, st>>>(logits, n_vocab, recent, n_recent, penalty);

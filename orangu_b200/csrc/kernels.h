@@ -178,6 +178,9 @@ struct ArgmaxArgs {
     obtp::PeerXchg px{};
 };
 void launch_argmax(const ArgmaxArgs &a, cudaStream_t st);
+// Tensor parallel, a few rows: x[0..count) += sum over ranks of proj (this rank's partial), through peer memory (tp.h, PeerBulk).
+// count <= bulk.cap.  `programmatic` is not used: the kernel is an ordinary stream-ordered launch.
+void launch_bulk_allreduce_add(float *x, const float *proj, uint32_t count, const obtp::PeerXchg &px, const obtp::PeerBulk &bulk, cudaStream_t st);
 void launch_repeat_penalty(float *logits, uint32_t n_vocab, const uint32_t *recent, uint32_t n_recent, float penalty, cudaStream_t st);
 
 // ---- attention.cu

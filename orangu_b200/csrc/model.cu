@@ -108,6 +108,7 @@ struct ob_model {
     std::map<uint64_t, uint64_t> graph_launches;  // kernels one replay stands for
     obtp::Comm *comm = nullptr;
     obtp::PeerXchg px{};         // size > 1: the single-token step exchanges partials through peer memory instead of NCCL
+    obtp::PeerBulk bulk{};       // cap > 0: so do steps of a few rows (decode batches, short prefill chunks)
     bool use_stream = true;  // OB_STREAM_GEMV=0 keeps batch-1 decode on the unfused kernels
     bool stream_ok = false;      // every fused decode kernel of this model's shapes fits (shared memory)
     bool use_fused_attn = true;  // OB_FUSED_ATTN=0 keeps the two-kernel flash-decode
@@ -548,6 +549,18 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
         return;
     }
 
+    // x += sum over ranks of proj for T rows: one kernel through peer memory when the rows fit its landing area, else NCCL + add
+    auto reduce_rows = [&](uint32_t rows) {
+        const uint64_t count = (uint64_t)rows * n_embd;
+        if (m->px.size > 1 && m->bulk.cap && count <= m->bulk.cap && (count & 3) == 0) {
+            launch_bulk_allreduce_add(m->x, m->proj, (uint32_t)count, m->px, m->bulk, st);
+            m->ctx->launches += 1;
+            return;
+        }
+        if (!obtp::all_reduce_sum(m->comm, m->proj, count, st)) m->comm_failed = true;
+        launch_add(m->x, m->proj, count, st);
+        m->ctx->launches += 2;
+    };
     bool pending_exchange = false;  // a peer exchange has been started and the residual stream does not hold its sum yet
     for (uint32_t li = 0; li < c.n_layer; ++li) {
         const LayerDev &L = m->layers[li];
@@ -625,9 +638,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             run_products(m, m->act_attn, {{L.wo, m->x, n_embd, m->x}}, T, gemm_order, st);
         } else {
             run_products(m, m->act_attn, {{L.wo, m->proj, n_embd, nullptr}}, T, gemm_order, st);
-            if (!obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st)) m->comm_failed = true;
-            launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
-            m->ctx->launches += 2;
+            reduce_rows(T);
         }
 
         quantize_into(m, ACT_RMSNORM, m->x, L.ffn_norm, T, n_embd, m->act_embd, needs_k({L.gate, L.up}), needs_flat({L.gate, L.up}), st);
@@ -637,9 +648,7 @@ void enqueue_step(ob_model *m, uint32_t T, bool gemm_order, uint32_t logit_row0,
             run_products(m, m->act_ff, {{L.down, m->x, n_embd, m->x}}, T, gemm_order, st);
         } else {
             run_products(m, m->act_ff, {{L.down, m->proj, n_embd, nullptr}}, T, gemm_order, st);
-            if (!obtp::all_reduce_sum(m->comm, m->proj, (size_t)T * n_embd, st)) m->comm_failed = true;
-            launch_add(m->x, m->proj, (uint64_t)T * n_embd, st);
-            m->ctx->launches += 2;
+            reduce_rows(T);
         }
     }
 
@@ -910,7 +919,11 @@ int ob_model_create(ob_ctx *ctx, const ob_model_desc *desc, ob_model **out) {
         const char *pe = getenv("OB_TP_PEER");
         if (!(pe && pe[0] == '0' && pe[1] == 0) && tp <= 8) {
             std::string perr;
-            if (!obtp::peer_init(m->comm, c.n_embd, ctx->device, &m->px, &perr)) m->px = obtp::PeerXchg{};  // no peer access: NCCL all-reduce
+            const uint32_t bulk_rows = std::min<uint32_t>(128u, m->cfg.max_batch_tokens);  // decode batches; longer prefill chunks stay with NCCL
+            if (!obtp::peer_init(m->comm, c.n_embd, bulk_rows * c.n_embd, ctx->device, &m->px, &m->bulk, &perr)) {  // no peer access: NCCL all-reduce
+                m->px = obtp::PeerXchg{};
+                m->bulk = obtp::PeerBulk{};
+            }
         }
     }
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
@@ -1566,6 +1579,86 @@ int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32
     cudaStreamSynchronize(st);
     cudaFree(region);
     cudaFree(x);
+    return rc;
+}
+
+// The few-rows exchange on one GPU: this "rank 0" runs the real kernel; what "rank 1" would have pushed (2 i + 1 at element i,
+// and its arrival words) is written beforehand by a copy when peer_delivers is set, and is absent otherwise.  x starts at 0.5,
+// rank 0's partial is i, so a delivered exchange leaves 0.5 + 3 i + 1; an undelivered one runs into the time limit.
+int ob_tp_bulk_selftest(ob_ctx *ctx, uint32_t count, uint32_t timeout_ms, uint32_t n_rounds, const uint8_t *peer_delivers, float *x_out) {
+    if (!ctx || !peer_delivers || !x_out || count == 0 || (count & 3) || count > (1u << 22) || n_rounds == 0 || n_rounds > 16)
+        return fail(ctx, OB_ERR_INVALID, "tp_bulk_selftest: bad argument");
+    std::lock_guard<std::mutex> g(ctx->mu);
+    Bind b(ctx);
+    cudaStream_t st = ctx->stream;
+    const uint32_t cap = (count + obtp::kBulkChunk - 1) / obtp::kBulkChunk * obtp::kBulkChunk, chunks = cap / obtp::kBulkChunk;
+    const size_t flag_bytes = ((size_t)2 * 2 * chunks * 4 + 255) & ~(size_t)255, data_bytes = (size_t)2 * 2 * cap * 4;
+    uint8_t *mine = nullptr, *peer = nullptr;  // the two ranks' regions, both local
+    float *x = nullptr, *proj = nullptr;
+    std::vector<float> h_proj(count), h_peer(count), h_x(count, 0.5f);
+    for (uint32_t i = 0; i < count; ++i) {
+        h_proj[i] = (float)(i % 1000);
+        h_peer[i] = (float)(2 * (i % 1000) + 1);
+    }
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&mine), 512 + flag_bytes + data_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&peer), 512 + flag_bytes + data_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&x), (size_t)count * 4);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&proj), (size_t)count * 4);
+    int rc = OB_OK;
+    if (e != cudaSuccess) rc = fail(ctx, OB_ERR_OOM, "tp_bulk_selftest: allocation failed");
+    if (rc == OB_OK) {
+        cudaMemsetAsync(mine, 0, 512 + flag_bytes + data_bytes, st);
+        cudaMemsetAsync(peer, 0, 512 + flag_bytes + data_bytes, st);
+        cudaMemcpyAsync(proj, h_proj.data(), (size_t)count * 4, cudaMemcpyHostToDevice, st);
+        obtp::PeerXchg px{};
+        px.rank = 0;
+        px.size = 2;
+        px.n = 0;
+        px.timeout_ms = timeout_ms ? timeout_ms : 50;
+        px.seq = reinterpret_cast<uint32_t *>(mine);
+        px.err = reinterpret_cast<uint32_t *>(mine) + 32;
+        obtp::PeerBulk bk{};
+        bk.done = reinterpret_cast<uint32_t *>(mine) + 40;
+        bk.cap = cap;
+        bk.max_chunks = chunks;
+        bk.flags[0] = reinterpret_cast<uint32_t *>(mine + 512);
+        bk.flags[1] = reinterpret_cast<uint32_t *>(peer + 512);
+        bk.data[0] = reinterpret_cast<float *>(mine + 512 + flag_bytes);
+        bk.data[1] = reinterpret_cast<float *>(peer + 512 + flag_bytes);
+        std::vector<uint32_t> tags(chunks);
+        for (uint32_t k = 0; k < n_rounds && rc == OB_OK; ++k) {
+            const uint32_t par = k & 1u;
+            cudaMemcpyAsync(x, h_x.data(), (size_t)count * 4, cudaMemcpyHostToDevice, st);
+            if (peer_delivers[k]) {  // rank 1's chunks and arrival words of exchange k, in rank 0's region
+                std::fill(tags.begin(), tags.end(), k + 1u);
+                cudaMemcpyAsync(bk.data[0] + (size_t)(par * 2 + 1) * cap, h_peer.data(), (size_t)count * 4, cudaMemcpyHostToDevice, st);
+                cudaMemcpyAsync(bk.flags[0] + (size_t)(par * 2 + 1) * chunks, tags.data(), (size_t)chunks * 4, cudaMemcpyHostToDevice, st);
+                cudaStreamSynchronize(st);  // `tags` is reused by the next round
+            }
+            launch_bulk_allreduce_add(x, proj, count, px, bk, st);
+            ctx->launches++;
+            uint32_t err = 0, seq = 0;
+            e = cudaMemcpyAsync(&err, px.err, 4, cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(&seq, px.seq, 4, cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(x_out + (size_t)k * count, x, (size_t)count * 4, cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) {
+                rc = fail(ctx, OB_ERR_CUDA, std::string("tp_bulk_selftest: ") + cudaGetErrorString(e));
+            } else if (seq != k + 1) {
+                rc = fail(ctx, OB_ERR_CUDA, "tp_bulk_selftest: the exchange counter did not advance");
+            } else if (err) {
+                cudaMemsetAsync(px.err, 0, 4, st);
+                if (peer_delivers[k]) rc = fail(ctx, OB_ERR_COMM, "tp_bulk_selftest: a delivered exchange ran into the time limit");
+            } else if (!peer_delivers[k]) {
+                rc = fail(ctx, OB_ERR_CUDA, "tp_bulk_selftest: an undelivered exchange did not report");
+            }
+        }
+        cudaStreamSynchronize(st);
+    }
+    cudaFree(mine);
+    cudaFree(peer);
+    cudaFree(x);
+    cudaFree(proj);
     return rc;
 }
 

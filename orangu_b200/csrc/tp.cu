@@ -176,7 +176,7 @@ bool all_gather_logits(Comm *c, float *logits, uint32_t rows, uint32_t n_vocab, 
 
 const char *last_error(Comm *c) { return c ? c->err.c_str() : ""; }
 
-static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
+static bool peer_init_local(Comm *c, uint32_t n, uint32_t bulk_floats, int device, PeerXchg *out, PeerBulk *bulk_out, std::string *err) {
     auto bail = [&](const std::string &m) {
         if (err) *err = m;
         return false;
@@ -185,7 +185,10 @@ static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std:
     if (!a || !c || c->size < 2 || c->size > 8) return bail("peer exchange needs 2 to 8 ranks");
     cudaSetDevice(device);
     constexpr size_t kFlagBytes = 256, kLocalBytes = 256;
-    const size_t slot_bytes = (size_t)2 * c->size * n * sizeof(uint2), total = kFlagBytes + kLocalBytes + slot_bytes;
+    const uint32_t bulk_cap = (bulk_floats + kBulkChunk - 1) / kBulkChunk * kBulkChunk, max_chunks = bulk_cap / kBulkChunk;
+    const size_t slot_bytes = (size_t)2 * c->size * n * sizeof(uint2);
+    const size_t bulk_flag_bytes = ((size_t)2 * c->size * max_chunks * 4 + 255) & ~(size_t)255, bulk_bytes = (size_t)2 * c->size * bulk_cap * 4;
+    const size_t total = kFlagBytes + kLocalBytes + slot_bytes + bulk_flag_bytes + bulk_bytes;
     // Every rank reaches the all-gather below, whatever happened before it (a rank that skipped it would leave the others
     // waiting in NCCL); a rank without a region sends a zero handle and fails afterwards.
     cudaIpcMemHandle_t mine;
@@ -219,24 +222,33 @@ static bool peer_init_local(Comm *c, uint32_t n, int device, PeerXchg *out, std:
             c->peer_mapped[p] = base;
         }
         px.slots[p] = reinterpret_cast<uint2 *>(static_cast<unsigned char *>(base) + kFlagBytes + kLocalBytes);
+        if (bulk_out) {
+            bulk_out->flags[p] = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(base) + kFlagBytes + kLocalBytes + slot_bytes);
+            bulk_out->data[p] = reinterpret_cast<float *>(static_cast<unsigned char *>(base) + kFlagBytes + kLocalBytes + slot_bytes + bulk_flag_bytes);
+        }
     }
     uint32_t *local = reinterpret_cast<uint32_t *>(static_cast<unsigned char *>(c->peer_region) + kFlagBytes);
     px.seq = local;
     px.err = local + 32;
+    if (bulk_out) {
+        bulk_out->done = local + 40;
+        bulk_out->cap = bulk_cap;
+        bulk_out->max_chunks = max_chunks;
+    }
     px.timeout_ms = 4000;
     if (const char *e = getenv("OB_TP_TIMEOUT_MS")) px.timeout_ms = (uint32_t)std::max(1, atoi(e));
     *out = px;
     return true;
 }
 
-bool peer_init(Comm *c, uint32_t n, int device, PeerXchg *out, std::string *err) {
+bool peer_init(Comm *c, uint32_t n, uint32_t bulk_floats, int device, PeerXchg *out, PeerBulk *bulk_out, std::string *err) {
     Api *a = api();
     if (!a || !c) return false;
     // Every rank must take the same path afterwards: the exchange is used only if it could be set up everywhere.
     // Both collectives -- the handle all-gather inside peer_init_local and the agreement below -- run out of the scratch
     // buffer made with the communicator, so a rank whose own allocations fail still reaches them (with a zero handle and
     // a 0 vote) instead of leaving the others waiting inside NCCL.
-    const bool mine = peer_init_local(c, n, device, out, err);
+    const bool mine = peer_init_local(c, n, bulk_floats, device, out, bulk_out, err);
     int *flag = reinterpret_cast<int *>(c->scratch + 8 * sizeof(cudaIpcMemHandle_t));
     const int v = mine ? 1 : 0;
     cudaMemcpy(flag, &v, sizeof(int), cudaMemcpyHostToDevice);

@@ -49,8 +49,23 @@ struct PeerXchg {
     uint32_t rank, size, n;
     uint32_t timeout_ms;  // how long the consumer waits for a rank's words before it reports and goes on (0 = 4000)
 };
+// The same idea for a few rows at a time (decode batches, short prefill chunks): every rank copies its partial [rows][n]
+// into a landing area in EVERY rank's memory, chunk by chunk, each chunk followed by a system-scope fence and a tagged
+// arrival word; the CTA that owns a chunk waits for the other ranks' arrival words of that chunk only, adds the partials in
+// rank order (every rank gets the same bits) and adds the result to the residual stream.  One kernel instead of an NCCL
+// all-reduce plus an add; it shares the exchange numbering (*seq), the error word and the time limit of PeerXchg.
+struct PeerBulk {
+    float *data[8];       // data[r]: rank r's landing area [2][size][cap] as mapped here
+    uint32_t *flags[8];   // flags[r]: rank r's arrival words [2][size][max_chunks]
+    uint32_t *done;       // this rank: CTAs of the running exchange that have finished
+    uint32_t cap;         // floats per (parity, source rank); 0: not set up
+    uint32_t max_chunks;
+};
+constexpr uint32_t kBulkChunk = 2048;  // floats per chunk (8 KB)
+
 // Allocates this rank's region, exchanges CUDA IPC handles over the communicator and maps the peers' regions.
-// False (with *err) when peer access is not available; the caller then keeps to NCCL.
-bool peer_init(Comm *, uint32_t n, int device, PeerXchg *out, std::string *err);
+// False (with *err) when peer access is not available; the caller then keeps to NCCL.  bulk_floats: capacity of the
+// many-row exchange per source rank (0: none).
+bool peer_init(Comm *, uint32_t n, uint32_t bulk_floats, int device, PeerXchg *out, PeerBulk *bulk_out, std::string *err);
 
 }  // namespace obtp

@@ -119,3 +119,38 @@ def test_exchange_wait_runs_out_and_reports_instead_of_hanging():
         assert be.argmax(np.arange(100, dtype=np.float32)) == 99
     finally:
         be.close()
+
+
+def test_few_rows_exchange_kernel_on_one_gpu():
+    """The one-kernel all-reduce + residual add of decode batches, as rank 0 of 2 with the peer's chunks and arrival words
+    written beforehand (delivered rounds) or missing (the bounded wait runs out and reports; nothing hangs).  Counts that end
+    inside a chunk, several chunks, both parities."""
+    import ctypes as C
+    import time
+
+    import numpy as np
+
+    import orangu_b200
+    from orangu_b200 import capi
+
+    be = orangu_b200.CudaBackend.init(0)
+    L = capi.load()
+    try:
+        for count in (2048, 4 * 4096, 64 * 4096, 3 * 4096 + 1028):
+            delivers = np.array([1, 1, 0, 1, 1], np.uint8)
+            out = np.zeros((len(delivers), count), np.float32)
+            t0 = time.time()
+            rc = L.ob_tp_bulk_selftest(be._h, count, 50, len(delivers), delivers.ctypes.data, out.ctypes.data)
+            assert rc == 0, (count, L.ob_last_error(be._h))
+            assert time.time() - t0 < 5.0
+            i = (np.arange(count) % 1000).astype(np.float32)
+            full, alone = np.float32(0.5) + (i + (2 * i + 1)), np.float32(0.5) + (i + np.float32(0.0))
+            for k, d in enumerate(delivers):
+                want = full if d else None
+                if d:
+                    assert (out[k] == want).all(), (count, k)
+                else:  # the peer's landing area of this parity holds whatever an earlier round left: only this rank's part is certain
+                    assert np.isfinite(out[k]).all() and (out[k] >= alone).all()
+        assert be.argmax(np.arange(100, dtype=np.float32)) == 99
+    finally:
+        be.close()
