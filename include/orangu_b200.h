@@ -302,6 +302,7 @@ uint32_t ob_kv_pages(const ob_kv *kv);              /* pages this cache holds no
 uint32_t ob_model_pool_pages(const ob_model *model); /* pages in the model's KV pool */
 uint32_t ob_model_free_pages(const ob_model *model); /* of which no cache holds */
 uint32_t ob_model_n_vocab(const ob_model *model);
+uint32_t ob_model_tp_size(const ob_model *model);    /* 1 for a single-GPU model */
 ob_ctx *ob_model_ctx(const ob_model *model);
 /* KvCache::truncate (E/kv_cache.rs:496-511): roll back to new_len positions. */
 int ob_kv_truncate(ob_kv *kv, uint32_t new_len);
@@ -387,7 +388,9 @@ int ob_tp_exchange_selftest(ob_ctx *ctx, uint32_t n, uint32_t timeout_ms, uint32
 /* ------------------------------------------------- slot pool and decode window */
 /* SlotPool (E/scheduler.rs:36-317) + BatchCoordinator (E/batch.rs:184-324) + chunked prefill (E/generate.rs:1299-1338) over
  * ob_forward.  One thread per generating request, as in generate::run: acquire a slot, prefill, call ob_slot_decode per token,
- * release.  Every slot owns an on-demand paged KV cache of the model (ob_kv_create_paged). */
+ * release.  Every slot owns an on-demand paged KV cache of the model (ob_kv_create_paged).  Single-GPU models only: the
+ * window forms its batches by arrival time, which the ranks of a tensor-parallel model would each see differently, while they
+ * must all make the same calls (OB_ERR_UNSUPPORTED for tp_size > 1). */
 typedef struct ob_slot_pool ob_slot_pool;
 typedef struct ob_slot_pool_desc {
     uint32_t n_slots;              /* concurrent generations (`slots`) */

@@ -98,6 +98,7 @@ SIGNATURES = {
     "ob_model_pool_pages": (_u32, [_vp]),
     "ob_model_free_pages": (_u32, [_vp]),
     "ob_model_n_vocab": (_u32, [_vp]),
+    "ob_model_tp_size": (_u32, [_vp]),
     "ob_model_ctx": (_vp, [_vp]),
     "ob_kv_len": (_u32, [_vp]),
     "ob_kv_truncate": (_i32, [_vp, _u32]),

@@ -1012,6 +1012,7 @@ uint32_t ob_model_free_pages(const ob_model *m) {
 
 uint32_t ob_model_pool_pages(const ob_model *m) { return m ? (uint32_t)m->pool_pages : 0u; }
 uint32_t ob_model_n_vocab(const ob_model *m) { return m ? m->cfg.n_vocab : 0u; }
+uint32_t ob_model_tp_size(const ob_model *m) { return m ? std::max(1u, m->tp_size) : 0u; }
 ob_ctx *ob_model_ctx(const ob_model *m) { return m ? m->ctx : nullptr; }
 
 int ob_kv_truncate(ob_kv *kv, uint32_t new_len) {

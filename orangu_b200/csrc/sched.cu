@@ -262,6 +262,8 @@ extern "C" {
 int ob_slot_pool_create(ob_model *model, const ob_slot_pool_desc *desc, ob_slot_pool **out) {
     if (!model || !desc || !out || desc->n_slots == 0 || desc->slot_capacity_tokens == 0) return pool_fail(nullptr, -1, OB_ERR_INVALID, "slot_pool_create: bad argument");
     *out = nullptr;
+    if (ob_model_tp_size(model) > 1)  // every rank of a tensor-parallel model has to make the same calls; batches formed by arrival time would differ
+        return pool_fail(nullptr, -1, OB_ERR_UNSUPPORTED, "slot_pool_create: the decode window serves single-GPU models only");
     ob_slot_pool *p = new ob_slot_pool;
     p->model = model;
     p->desc = *desc;
