@@ -74,6 +74,7 @@ struct ob_slot_pool {
     std::vector<Step *> pending;
     bool window_open = false;
     Clock::time_point deadline;
+    uint32_t in_flight = 0;  // batches being executed right now
     uint64_t batches = 0, batched_seqs = 0, refused = 0;
 
     uint32_t busy_count() {
@@ -192,15 +193,22 @@ void submit(ob_slot_pool *p, Step *st) {
         const uint32_t target = std::max(1u, p->busy_count());
         lk.lock();
         if (st->done) return;
-        if (p->window_open && (p->pending.size() >= target || Clock::now() >= p->deadline)) {
+        // The reference closes a window when it is full or its deadline has passed (E/batch.rs:241-246).  One more condition
+        // here: a window whose deadline has passed stays open while another batch is executing -- the model runs one batch at
+        // a time, so leading now would only queue behind it, and whoever finishes meanwhile can still join.  Without it, eight
+        // streams whose step takes longer than the window never meet: every completion releases one stream into a window of
+        // its own (the mean batch of 1.6-2.2 the reference measured, E/batch.rs:66-75).
+        if (p->window_open && (p->pending.size() >= target || (Clock::now() >= p->deadline && p->in_flight == 0))) {
             std::vector<Step *> batch;
             batch.swap(p->pending);
             p->window_open = false;
             ++p->batches;
             p->batched_seqs += batch.size();
+            ++p->in_flight;
             lk.unlock();
             p->forward(batch);
             lk.lock();
+            --p->in_flight;
             for (Step *s : batch) s->done = true;
             p->cv.notify_all();
             return;
