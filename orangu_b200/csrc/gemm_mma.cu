@@ -76,7 +76,11 @@ __device__ __forceinline__ int dp2a_hi_su(uint32_t a, uint32_t b, int c) {  // c
 
 // GEMM: the prefill association (Q4_K: two passes); otherwise every (row, token) is the single-token product.
 // NT: n-tiles of 8 tokens per CTA.
-template <uint32_t TYPE, bool GEMM, int NT>
+// STAGES: depth of the cp.async ring, one super-block per stage: four for the 16-token tile, three for 32 tokens, two for the
+// 64-token tile whose stages are 30 KB.  (Measured: the depth does not change the time of any shape -- 4096 x 14336 at 16 tokens
+// takes 60 us with two stages and with four; the kernel is bound by its instruction count per super-block, about 600 per warp at
+// the 16-token tile, not by the arrival of the stages.)
+template <uint32_t TYPE, bool GEMM, int NT, int STAGES>
 __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
     using S = MmStage<TYPE, NT>;
     constexpr uint32_t TOK = S::TOK, BLK = S::BLK;
@@ -96,8 +100,21 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
     const uint32_t row0 = tile * MM_ROWS, tok0 = blockIdx.y * TOK;
     const uint32_t n_tok = min(TOK, a.n_tokens - tok0);
 
-    // activation rows of tokens past the end stay zero in both stages
-    for (uint32_t i = tid; i < 2 * S::BYTES / 16; i += MM_WARPS * 32) *reinterpret_cast<uint4 *>(smem + i * 16) = make_uint4(0, 0, 0, 0);
+    // activation rows of tokens past the end stay zero in every stage
+    for (uint32_t i = tid; i < STAGES * S::BYTES / 16; i += MM_WARPS * 32) *reinterpret_cast<uint4 *>(smem + i * 16) = make_uint4(0, 0, 0, 0);
+    // the per-block scales of the tile's tokens (and, Q6_K, of its rows) for the whole row, once: loaded inside the loop they
+    // would be a synchronous trip to memory per super-block
+    float *ad_all = reinterpret_cast<float *>(smem + STAGES * S::BYTES);  // [TOK][nb]
+    float *dw_all = ad_all + TOK * nb;                                    // Q6_K: [MM_ROWS][nb]
+    for (uint32_t i = tid; i < TOK * nb; i += MM_WARPS * 32) {
+        const uint32_t t = i / nb, b = i % nb;
+        ad_all[i] = t < n_tok ? a.act.d[(uint64_t)(tok0 + t) * (a.act.dim_cap / 256) + b] : 0.0f;
+    }
+    if (TYPE == TYPE_Q6_K)
+        for (uint32_t i = tid; i < MM_ROWS * nb; i += MM_WARPS * 32) {
+            const uint32_t r = i / nb, b = i % nb, row = min(row0 + r, out_dim - 1);
+            dw_all[i] = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(seg.w.data + (uint64_t)row * seg.w.row_stride + seg.w.d_off + 2 * b));
+        }
     __syncthreads();
 
     auto stage_block = [&](uint32_t b, int st, bool codes) {
@@ -112,11 +129,6 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
                 const uint32_t t = c >> 4, j = c & 15;
                 cp16(base + S::B + t * MM_B_ROW + j * 16, a.act.q + (uint64_t)(tok0 + t) * a.act.dim_cap + (uint64_t)b * 256 + j * 16);
             }
-            if (TYPE == TYPE_Q6_K && tid < MM_ROWS) {  // the rows' f16 d of this block, from the plane behind the blocks
-                const uint32_t row = min(row0 + tid, out_dim - 1);
-                const uint16_t bits = *reinterpret_cast<const uint16_t *>(seg.w.data + (uint64_t)row * seg.w.row_stride + seg.w.d_off + 2 * b);
-                *reinterpret_cast<float *>(smem + st * S::BYTES + S::DW + tid * 4) = f16_bits_to_f32(bits);
-            }
         } else {
             for (uint32_t r = tid; r < MM_ROWS; r += MM_WARPS * 32) {  // only the 16-byte headers: d, dmin, scales and mins
                 const uint32_t row = min(row0 + r, out_dim - 1);
@@ -129,8 +141,6 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
                 cp16(base + S::S16 + t * 32 + j * 16, a.act.sums + (uint64_t)(tok0 + t) * (a.act.dim_cap / 16) + (uint64_t)b * 16 + j * 8);
             }
         }
-        if (tid < (int)n_tok)
-            *reinterpret_cast<float *>(smem + st * S::BYTES + S::AD + tid * 4) = a.act.d[(uint64_t)(tok0 + tid) * (a.act.dim_cap / 256) + b];
     };
 
     float acc[NT][4];
@@ -140,13 +150,15 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
     constexpr int N_PASS = GEMM && TYPE == TYPE_Q4_K ? 2 : 1;
     for (int pass = 0; pass < N_PASS; ++pass) {
         const bool min_pass = N_PASS == 2 && pass == 0;  // pass 1 of the Q4_K prefill order: the min terms of all super-blocks
-        stage_block(0, 0, !min_pass);
-        __pipeline_commit();
-        for (uint32_t b = 0; b < nb; ++b) {
-            const int st = (int)(b & 1);
-            if (b + 1 < nb) stage_block(b + 1, st ^ 1, !min_pass);
+        for (int p = 0; p < STAGES - 1; ++p) {
+            if ((uint32_t)p < nb) stage_block((uint32_t)p, p, !min_pass);
             __pipeline_commit();
-            __pipeline_wait_prior(1);
+        }
+        for (uint32_t b = 0; b < nb; ++b) {
+            const int st = (int)(b % STAGES);
+            if (b + STAGES - 1 < nb) stage_block(b + STAGES - 1, (int)((b + STAGES - 1) % STAGES), !min_pass);  // the stage block b - 1 left
+            __pipeline_commit();
+            __pipeline_wait_prior(STAGES - 1);
             __syncthreads();  // block b has landed
             const uint32_t base = sbase + st * S::BYTES;
             if (TYPE == TYPE_Q4_K) {  // per-32 sums from the per-16 sums: token t, pair j
@@ -215,7 +227,7 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const uint32_t t = 8 * nt + 2 * tig + k;
-                        const float ad = __uint_as_float(lds_u32(base + S::AD + t * 4));
+                        const float ad = ad_all[t * nb + b];
                         int imin[2] = {0, 0};
                         if (!GEMM || min_pass) {
                             const uint4 bsv = lds_u128(base + S::BS + t * 16);
@@ -281,12 +293,12 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
                         }
                     }
                 }
-                const float dw[2] = {__uint_as_float(lds_u32(base + S::DW + (warp * 16 + gid) * 4)), __uint_as_float(lds_u32(base + S::DW + (warp * 16 + gid + 8) * 4))};
+                const float dw[2] = {dw_all[(warp * 16 + gid) * nb + b], dw_all[(warp * 16 + gid + 8) * nb + b]};
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
-                        const float ad = __uint_as_float(lds_u32(base + S::AD + (8 * nt + 2 * tig + k) * 4));
+                        const float ad = ad_all[(8 * nt + 2 * tig + k) * nb + b];
 #pragma unroll
                         for (int r = 0; r < 2; ++r) {
                             const float fi = (float)isum[nt][2 * r + k];
@@ -317,11 +329,13 @@ __global__ void __launch_bounds__(MM_WARPS * 32) gemm_mma_kernel(GemvArgs a) {
 
 template <uint32_t TYPE, bool GEMM, int NT>
 void launch_mma_instance(const GemvArgs &a, uint32_t tiles, cudaStream_t st) {
+    constexpr int STAGES = NT == 8 ? 2 : NT == 4 ? 3 : 4;
     static PerDeviceOnce once;  // one per instantiation
-    constexpr uint32_t smem = 2 * MmStage<TYPE, NT>::BYTES;
-    if (once.run([] { return cudaFuncSetAttribute(gemm_mma_kernel<TYPE, GEMM, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); }) != cudaSuccess) return;
+    if (once.run([] { return cudaFuncSetAttribute(gemm_mma_kernel<TYPE, GEMM, NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); }) != cudaSuccess) return;
+    const uint32_t nb = a.seg[0].w.nb;
+    const size_t smem = (size_t)STAGES * MmStage<TYPE, NT>::BYTES + (size_t)8 * NT * nb * 4 + (TYPE == TYPE_Q6_K ? (size_t)MM_ROWS * nb * 4 : 0);
     const dim3 grid(tiles, (a.n_tokens + 8 * NT - 1) / (8 * NT));
-    gemm_mma_kernel<TYPE, GEMM, NT><<<grid, MM_WARPS * 32, smem, st>>>(a);
+    gemm_mma_kernel<TYPE, GEMM, NT, STAGES><<<grid, MM_WARPS * 32, smem, st>>>(a);
 }
 
 template <uint32_t TYPE, bool GEMM>
