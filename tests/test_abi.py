@@ -125,6 +125,57 @@ def test_struct_layouts_agree_between_header_binding_and_integration_notes(lib):
     assert header
 
 
+def test_cpp_model_and_slot_pool_wrappers_compile():
+    """The ModelForward / KvCache / SlotPool part of the C++ mirror, compiled with warnings on and linked against the library
+    (run without a device: try_init_index gives an empty optional and main returns)."""
+    src = ('#include "orangu_b200.hpp"\n'
+           'int main(){ auto be = orangu::CudaBackend::try_init_index(0); if (!be) return 0; ob_model_desc d{};\n'
+           ' try { orangu::LlamaModel m(*be, d); auto kv = m.new_kv_cache(16, true); auto t = m.forward_maybe_sampling(kv, {1, 2, 3}, 0);\n'
+           '  (void)m.decode_greedy(kv, t); (void)m.forward(kv, {t}, kv.len()); ob_slot_pool_desc pd{2, 64, 0, 0, 0, 1}; orangu::SlotPool pool(m, pd);\n'
+           '  if (auto g = pool.try_acquire(0)) { auto x = g->prefill({1, 2}); (void)g->decode(x); g->truncate(1); }\n'
+           '  (void)pool.snapshot(); (void)pool.stats(); std::vector<orangu::KvCache *> c{&kv}; (void)m.forward_batch_decode(c, {1}); }\n'
+           ' catch (const std::exception &) { return 0; } return 0; }\n')
+    from orangu_b200 import capi
+
+    _compile_and_run(src, extra=["-Wall", "-Wextra", "-Werror", "-L", os.path.dirname(capi.lib_path()), "-lorangu_b200"], run=False)
+
+
+@pytest.mark.gpu
+def test_cpp_model_and_slot_pool_run_a_gguf_model_on_the_gpu(tmp_path):
+    """A tiny model written to a .gguf file, opened by the library, run through the C++ classes: prefill + greedy decode through
+    LlamaModel (reserved and paged caches) and through a SlotPool guard give the oracle's tokens."""
+    import numpy as np
+
+    import oracle as O
+    from orangu_b200 import capi, synth
+    from orangu_b200.gguf import write_gguf
+
+    cfg = dict(synth.CONFIGS["tiny"])
+    tensors = synth.model_tensors(cfg, seed=31)
+    path = str(tmp_path / "tiny.gguf")
+    write_gguf(path, cfg, tensors)
+    toks = np.random.default_rng(3).integers(0, cfg["n_vocab"], 21).astype(np.uint32)
+    ref = O.Model(cfg, tensors)
+    rkv = ref.new_kv(64, f16=True)
+    want = [O.argmax(ref.forward(rkv, toks, 0))]
+    for i in range(5):
+        want.append(O.argmax(ref.forward(rkv, [want[-1]], 21 + i)))
+    src = (
+        '#include <cstdio>\n#include "orangu_b200.hpp"\n'
+        'int main(){ auto be = orangu::CudaBackend::try_init_index(0); if (!be) return 3;\n'
+        ' ob_gguf *g = nullptr; if (ob_gguf_open("%s", &g) != OB_OK) return 4; ob_model_desc d{}; if (ob_gguf_model_desc(g, &d) != OB_OK) return 5;\n'
+        ' d.max_seq_len = 64; d.max_batch_tokens = 16; orangu::LlamaModel m(*be, d); ob_gguf_close(g);\n'
+        ' std::vector<uint32_t> toks{%s};\n'
+        ' for (int paged = 0; paged < 2; ++paged) { auto kv = m.new_kv_cache(48, paged != 0); uint32_t t = m.forward_maybe_sampling(kv, toks, 0); std::printf("%%u", t);\n'
+        '  for (int i = 0; i < 5; ++i) { t = i %% 2 ? m.decode_greedy(kv, t) : m.forward_maybe_sampling(kv, {t}, kv.len()); std::printf(" %%u", t); } std::printf("\\n"); }\n'
+        ' ob_slot_pool_desc pd{2, 48, 0, 1, 8, 1}; orangu::SlotPool pool(m, pd); auto s = pool.try_acquire(0); if (!s) return 6;\n'
+        ' uint32_t t = s->prefill(toks); std::printf("%%u", t); for (int i = 0; i < 5; ++i) { t = s->decode(t); std::printf(" %%u", t); } std::printf("\\n");\n'
+        ' return pool.stats().busy == 1 ? 0 : 7; }\n' % (path, ", ".join(str(int(t)) for t in toks)))
+    out = _compile_and_run(src, extra=["-L", os.path.dirname(capi.lib_path()), "-lorangu_b200"])
+    lines = [[int(v) for v in ln.split()] for ln in out.strip().splitlines()]
+    assert lines == [want, want, want], (lines, want)
+
+
 def test_row_bytes_of_the_cpp_wrapper_for_every_type():
     out = _compile_and_run(
         '#include <cstdio>\n#include "orangu_b200.hpp"\n'
