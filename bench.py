@@ -41,7 +41,9 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))  # tests/oracle.py: the ctypes b
 # torch.distributed.run exports OMP_NUM_THREADS=1; the synthetic-weight generator and the CPU oracle are OpenMP code and
 # would take minutes on one thread.  Give every rank its share of the host cores (before any OpenMP runtime starts).
 if int(os.environ.get("WORLD_SIZE", "1")) > 1 and os.environ.get("OMP_NUM_THREADS", "1") == "1":
-    os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // int(os.environ.get("LOCAL_WORLD_SIZE", os.environ["WORLD_SIZE"]))))
+    # the reference arm works on rank 0 alone (the other ranks return at once): it gets all the cores
+    _ranks_at_work = 1 if "reference" in sys.argv else int(os.environ.get("LOCAL_WORLD_SIZE", os.environ["WORLD_SIZE"]))
+    os.environ["OMP_NUM_THREADS"] = str(max(1, (os.cpu_count() or 1) // _ranks_at_work))
 
 import numpy as np  # noqa: E402
 
