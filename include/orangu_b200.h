@@ -408,6 +408,8 @@ typedef struct ob_slot_pool_stats { /* batch_stats (E/batch.rs:117-122) and the 
     uint32_t total, busy, queued, free_pages;
 } ob_slot_pool_stats;
 
+/* model == NULL makes a pool that schedules only (no caches, ob_slot_prefill refuses, ob_slot_decode answers
+ * token * 31 + slot * 7 + 1 from a host-side stand-in): the form the host-only tests use. */
 int ob_slot_pool_create(ob_model *model, const ob_slot_pool_desc *desc, ob_slot_pool **out);
 void ob_slot_pool_destroy(ob_slot_pool *pool);
 /* SlotPool::try_acquire: whichever slot frees first, waiters served in arrival order.  timeout_ms < 0 waits without limit,

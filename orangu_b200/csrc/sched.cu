@@ -14,6 +14,7 @@
 // can drive it with a host-side stand-in, the way the reference's own tests use a ModelForward that touches no weights
 // (E/batch.rs:326-451).
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <condition_variable>
 #include <cstring>
@@ -267,18 +268,33 @@ bool slot_held(ob_slot_pool *p, uint32_t slot) {
 
 extern "C" {
 
+// The stand-in for the forward pass of a pool that has no model: the next token of a step is a fixed function of (slot, token),
+// so every submitter can tell its own answer from another's (the reference's tests use a ModelForward of that kind,
+// E/batch.rs:326-369).
+static void forward_stand_in(std::vector<Step *> &b) {
+    for (Step *s : b) {
+        if (s->out_token) *s->out_token = s->token * 31u + s->slot * 7u + 1u;
+        s->rc = OB_OK;
+    }
+}
+
 int ob_slot_pool_create(ob_model *model, const ob_slot_pool_desc *desc, ob_slot_pool **out) {
-    if (!model || !desc || !out || desc->n_slots == 0 || desc->slot_capacity_tokens == 0) return pool_fail(nullptr, -1, OB_ERR_INVALID, "slot_pool_create: bad argument");
+    if (!desc || !out || desc->n_slots == 0 || (model && desc->slot_capacity_tokens == 0)) return pool_fail(nullptr, -1, OB_ERR_INVALID, "slot_pool_create: bad argument");
     *out = nullptr;
-    if (ob_model_tp_size(model) > 1)  // every rank of a tensor-parallel model has to make the same calls; batches formed by arrival time would differ
+    if (model && ob_model_tp_size(model) > 1)  // every rank of a tensor-parallel model has to make the same calls; batches formed by arrival time would differ
         return pool_fail(nullptr, -1, OB_ERR_UNSUPPORTED, "slot_pool_create: the decode window serves single-GPU models only");
     ob_slot_pool *p = new ob_slot_pool;
     p->model = model;
     p->desc = *desc;
     if (p->desc.batch_wait_ms == 0) p->desc.batch_wait_ms = 4;    // MAX_BATCH_WAIT_DEFAULT_MS, E/batch.rs:63
     if (p->desc.prefill_batch == 0) p->desc.prefill_batch = 512;  // PREFILL_BATCH_DEFAULT, E/generate.rs:1265
-    p->n_vocab = ob_model_n_vocab(model);
     p->slots.resize(desc->n_slots);
+    if (!model) {  // scheduling only (host-side tests, or a host that wants the pool without the library's caches)
+        p->forward = forward_stand_in;
+        *out = p;
+        return OB_OK;
+    }
+    p->n_vocab = ob_model_n_vocab(model);
     for (auto &s : p->slots) {
         const int rc = ob_kv_create_paged(model, desc->slot_capacity_tokens, &s.kv);
         if (rc != OB_OK) {
@@ -434,13 +450,11 @@ int ob_slot_pool_selftest(uint32_t n_slots, uint32_t n_threads, uint32_t n_steps
     pool.slots.resize(n_slots);
     std::vector<int> holders(n_slots, 0);
     std::mutex hmu;
-    pool.forward = [](std::vector<Step *> &b) {
-        for (Step *s : b) {
-            *s->out_token = s->token * 31u + s->slot * 7u + 1u;
-            s->rc = OB_OK;
-        }
-    };
+    pool.forward = forward_stand_in;
     std::vector<int> bad(n_threads, 0), refused(n_threads, 0);
+    // the first holders of the slots start stepping together, so that the window has company from its first step on
+    std::atomic<uint32_t> holders_so_far{0};
+    const uint32_t first_wave = std::min(n_threads, n_slots);
     std::vector<std::thread> th;
     for (uint32_t t = 0; t < n_threads; ++t)
         th.emplace_back([&, t] {
@@ -453,6 +467,8 @@ int ob_slot_pool_selftest(uint32_t n_slots, uint32_t n_threads, uint32_t n_steps
                 std::lock_guard<std::mutex> g(hmu);
                 if (++holders[slot] != 1) bad[t] = 1;  // every_concurrent_acquire_gets_a_distinct_slot
             }
+            if (holders_so_far.fetch_add(1) < first_wave)
+                while (holders_so_far.load() < first_wave) std::this_thread::yield();
             uint32_t tok = 1000u * t;
             for (uint32_t i = 0; i < n_steps; ++i) {
                 uint32_t next = 0;

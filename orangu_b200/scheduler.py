@@ -87,10 +87,11 @@ class SlotGuard:
 class SlotPool:
     def __init__(self, model, n_slots: int, slot_capacity_tokens: int, max_queue: int = 0, batch_wait_ms: int = 0, prefill_batch: int = 0,
                  batch_decode: bool = True):
-        self.model, self._lib = model, model._lib
+        self.model, self._lib = model, (model._lib if model is not None else capi.load())
         d = SlotPoolDesc(n_slots, slot_capacity_tokens, max_queue, batch_wait_ms, prefill_batch, 1 if batch_decode else 0)
         self._h = C.c_void_p()
-        rc = self._lib.ob_slot_pool_create(model._h, C.byref(d), C.byref(self._h))
+        # model None: a pool that schedules only, its decode answered by the library's host-side stand-in (tests without a device)
+        rc = self._lib.ob_slot_pool_create(model._h if model is not None else None, C.byref(d), C.byref(self._h))
         if rc:
             raise capi.OranguError(rc, (self._lib.ob_slot_last_error(None, -1) or b"").decode())
 

@@ -4,6 +4,7 @@ The host-only cases follow the reference's own tests of SlotPool (src/bin/orangu
 BatchCoordinator (engine/batch.rs:371-451), which use a ModelForward that touches no weights; here the library's self-test
 plays that part.  The GPU cases run real sequences through the pool and compare every token with the CPU oracle."""
 import threading
+import time
 
 import numpy as np
 import pytest
@@ -44,6 +45,148 @@ def test_pool_rejects_bad_arguments_without_a_device():
     assert L.ob_slot_acquire(None, 0, None) == -1
     assert L.ob_slot_len(None, 0) == 0 and L.ob_kv_pages(None) == 0 and L.ob_model_free_pages(None) == 0
     assert L.ob_slot_pool_selftest(0, 1, 1, 1, 0, None) == -1
+
+
+# ---- the pool itself, without a model: the cases of the reference's own SlotPool tests (scheduler.rs:355-639) ---------------
+def bare_pool(n, **kw):
+    return scheduler.SlotPool(None, n_slots=n, slot_capacity_tokens=0, **kw)
+
+
+def test_acquire_marks_a_slot_busy_and_release_frees_it():
+    pool = bare_pool(2)
+    assert pool.busy_count() == 0
+    g = pool.try_acquire()
+    assert pool.busy_count() == 1 and pool.snapshot()[g.id()]["busy"] == 1
+    g.release()
+    assert pool.busy_count() == 0
+    pool.close()
+
+
+def test_acquire_slot_gives_back_the_slot_that_was_asked_for_and_waits_for_it_even_when_others_are_free():
+    pool = bare_pool(3)
+    g = pool.acquire_slot(2)
+    assert g.id() == 2
+    assert pool.acquire_slot(2, timeout_ms=30) is None  # slot 2 is busy; slots 0 and 1 being free does not matter
+    got = []
+    t = threading.Thread(target=lambda: got.append(pool.acquire_slot(2, timeout_ms=5000)))
+    t.start()
+    time.sleep(0.05)
+    assert not got  # still waiting for that slot
+    g.release()
+    t.join(5)
+    assert got and got[0].id() == 2
+    got[0].release()
+    pool.close()
+
+
+def test_every_concurrent_acquire_gets_a_distinct_slot_and_a_third_request_waits_when_both_are_busy():
+    pool = bare_pool(2)
+    a, b = pool.try_acquire(), pool.try_acquire()
+    assert {a.id(), b.id()} == {0, 1}
+    got = []
+    t = threading.Thread(target=lambda: got.append(pool.try_acquire(5000)))
+    t.start()
+    time.sleep(0.05)
+    assert not got and pool.stats()["queued"] == 1
+    freed = b.id()
+    b.release()
+    t.join(5)
+    assert got and got[0].id() == freed and pool.stats()["queued"] == 0
+    a.release()
+    got[0].release()
+    pool.close()
+
+
+def test_waiters_are_served_in_arrival_order_and_an_abandoned_waiter_does_not_stall_the_queue():
+    pool = bare_pool(1)
+    held = pool.try_acquire()
+    order, lock = [], threading.Lock()
+
+    def waiter(name, timeout_ms):
+        g = pool.try_acquire(timeout_ms)
+        with lock:
+            order.append((name, g is not None))
+        if g is not None:
+            time.sleep(0.02)
+            g.release()
+
+    threads = []
+    for name, timeout_ms in (("first", 5000), ("gives up", 60), ("third", 5000), ("fourth", 5000)):
+        th = threading.Thread(target=waiter, args=(name, timeout_ms))
+        th.start()
+        threads.append(th)
+        time.sleep(0.03)  # arrival order is the start order
+    time.sleep(0.15)      # "gives up" has left the queue by now, from the middle of it
+    assert order == [("gives up", False)]
+    held.release()
+    for th in threads:
+        th.join(5)
+    assert order == [("gives up", False), ("first", True), ("third", True), ("fourth", True)]
+    assert pool.stats()["queued"] == 0 and pool.busy_count() == 0
+    pool.close()
+
+
+def test_a_pinned_waiter_does_not_starve_or_deadlock_unpinned_requests():
+    """A request waiting for a named slot holds no place in the queue: the others keep cycling through the free slot."""
+    pool = bare_pool(2)
+    pinned_holder = pool.acquire_slot(0)
+    got = []
+    t = threading.Thread(target=lambda: got.append(pool.acquire_slot(0, timeout_ms=5000)))
+    t.start()
+    time.sleep(0.03)
+    for _ in range(5):  # slot 1 keeps serving unpinned requests while the pinned one waits
+        g = pool.try_acquire(1000)
+        assert g is not None and g.id() == 1
+        g.release()
+    assert not got
+    pinned_holder.release()
+    t.join(5)
+    assert got and got[0].id() == 0
+    got[0].release()
+    pool.close()
+
+
+def test_a_full_queue_refuses_through_the_public_calls_and_counts_it():
+    pool = bare_pool(1, max_queue=1)
+    held = pool.try_acquire()
+    t = threading.Thread(target=lambda: pool.try_acquire(300))  # fills the queue
+    t.start()
+    time.sleep(0.05)
+    assert pool.try_acquire(1000) is None  # refused at once: the queue is full
+    assert pool.stats()["refused"] >= 1
+    t.join(5)
+    held.release()
+    pool.close()
+
+
+def test_decode_steps_through_the_window_of_a_bare_pool_get_their_own_answers():
+    pool = bare_pool(4, batch_wait_ms=5)
+    results = {}
+    all_hold_a_slot = threading.Barrier(4)  # the window's target is the number of busy slots: let every stream hold one first
+
+    def run(i):
+        with pool.try_acquire() as slot:
+            all_hold_a_slot.wait(10)
+            tok, out = 100 * i, []
+            for _ in range(50):
+                nxt = slot.decode(tok)
+                assert nxt == (tok * 31 + slot.id() * 7 + 1) % (1 << 32)
+                out.append(nxt)
+                tok = nxt % 50021
+            results[i] = out
+
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join(30)
+    assert len(results) == 4
+    st = pool.stats()
+    assert st["batched_seqs"] == 200 and st["batches"] < 200
+    with pytest.raises(Exception):
+        with pool.try_acquire() as slot:
+            slot.prefill([1, 2, 3])  # a pool without a model schedules only
+    pool.close()
 
 
 # ------------------------------------------------------------------------------------------ on a GPU
