@@ -60,6 +60,30 @@ def main():
         logits.append(ref.forward(kv, [steps[-1]], 9 + i))
         steps.append(O.argmax(logits[-1]))
     out["model_tokens"], out["model_logits"], out["model_greedy"] = toks, np.stack(logits), np.array(steps, np.uint32)
+    # (new vectors are appended below so that the random stream of the ones above never changes)
+    # Q5_K products, as the K types above
+    m = synth.matrix(13, 6, 512, seed=1013)
+    x = rng.standard_normal((3, 512)).astype(np.float32)
+    out["mm13_w"], out["mm13_x"] = m["data"], x
+    out["mm13_decode"] = O.matmul_decode(x, 3, m["data"], 13, 512, 6)
+    out["mm13_prefill"] = O.matmul(x, 3, m["data"], 13, 512, 6)
+    out["mm13_dequant"] = O.dequantize(13, m["data"], 6 * 512)
+    # rotation with the NEOX pairing and frequency factors
+    xr2 = rng.standard_normal(4 * 64).astype(np.float32)
+    ff = np.linspace(1.0, 8.0, 16).astype(np.float32)
+    out["rope2_x"], out["rope2_ff"], out["rope2_y"] = xr2, ff, O.rope_layout(xr2, 4, 64, 23, 32, 10000.0, True, ff)
+    # the tiny model as a Qwen3-style file would have it: q/k/v bias, per-head q/k norm, NEOX pairing
+    qcfg = dict(synth.CONFIGS["tiny"], rope_neox=True)
+    qt = synth.add_qwen_extras(qcfg, synth.model_tensors(qcfg, seed=78), seed=79)
+    qref = O.Model(qcfg, qt)
+    qkv = qref.new_kv(32, f16=True)
+    qtoks = rng.integers(0, qcfg["n_vocab"], 11).astype(np.uint32)
+    qlogits = [qref.forward(qkv, qtoks, 0)]
+    qsteps = [O.argmax(qlogits[0])]
+    for i in range(3):
+        qlogits.append(qref.forward(qkv, [qsteps[-1]], 11 + i))
+        qsteps.append(O.argmax(qlogits[-1]))
+    out["qmodel_tokens"], out["qmodel_logits"], out["qmodel_greedy"] = qtoks, np.stack(qlogits), np.array(qsteps, np.uint32)
     np.savez_compressed(os.path.join(HERE, "hotpath.npz"), **out)
     print("wrote", os.path.join(HERE, "hotpath.npz"), os.path.getsize(os.path.join(HERE, "hotpath.npz")), "bytes")
 
